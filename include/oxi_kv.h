@@ -1,0 +1,184 @@
+/*
+ * liboxi_kv — B200 (sm_100a) kernels for the pointer-table KV-cache path of
+ * oxide-infer's batched engine, behind a C ABI.
+ *
+ * The reference has no C ABI of its own on this path: its Rust engine calls
+ * cuda_core::launch_kernel_on_stream() on PTX entry points looked up by name
+ * (crates/oxide-infer-kernels/src/ptx.rs:13-26,
+ *  crates/oxide-infer-server/src/batch_engine.rs:387-404).  Every function
+ * below therefore cites the PTX entry point(s) and the engine launch site it
+ * replaces; a Rust `extern "C"` block binding these symbols is the only change
+ * the engine needs.
+ *
+ * Conventions (same as the reference's launch sites):
+ *   - every tensor argument is a DEVICE pointer owned by the caller; fp16
+ *     storage, fp32 arithmetic; geometry is LFM's: 16 query heads, 4 KV heads,
+ *     head_dim 128, conv hidden 2048 with 7 taps (6 live state slots);
+ *   - k_ptrs / v_ptrs / conv_ptrs are device arrays of per-sequence device
+ *     pointers, already offset to the layer (batch_engine.rs:709-740);
+ *     each K or V cache is row-major [token][kv_head 4][128] f16 (1024 B per
+ *     token) and must be 16-byte aligned;
+ *   - seq_lens[b] counts the token appended in this step
+ *     (batch_engine.rs:689-691), pos_ids[b] = seq_lens[b] - 1;
+ *   - `stream` is the caller's CUstream / cudaStream_t; calls only enqueue
+ *     work, never synchronise and never allocate after oxi_create();
+ *   - return value: 0 = ok, negative = OXI_ERR_* argument error detected on the
+ *     host before anything was enqueued, positive = cudaError_t passed through.
+ *     No exceptions cross the ABI and nothing aborts.
+ *   - a handle may be used by one thread at a time (the reference drives the
+ *     path from one worker thread owning one stream, server.rs:319-321).
+ */
+#ifndef OXI_KV_H
+#define OXI_KV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OXI_VERSION 100 /* major*10000 + minor*100 + patch */
+
+enum {
+    OXI_OK = 0,
+    OXI_ERR_NULL = -1,      /* a required pointer (or the handle) is null   */
+    OXI_ERR_BATCH = -2,     /* batch/rows is 0 or exceeds the handle limit  */
+    OXI_ERR_ARG = -3,       /* a scalar argument is out of range            */
+    OXI_ERR_WORKSPACE = -4, /* the handle's workspace cannot hold the call  */
+    OXI_ERR_NO_DEVICE = -5  /* no usable CUDA device / wrong architecture   */
+};
+
+/* Bits of the device-side status word (oxi_device_status). */
+enum {
+    OXI_DEV_MISALIGNED_PTR = 1u, /* a K/V/state pointer was not 16-byte aligned; row skipped */
+    OXI_DEV_BAD_SEQ_LEN = 2u,    /* seq_len 0 or beyond the handle's max_seq_len; row skipped */
+    OXI_DEV_WAIT_TIMEOUT = 4u    /* an in-kernel pipeline wait gave up (internal error)       */
+};
+
+typedef struct oxi_handle oxi_handle;
+
+int32_t oxi_version(void);
+const char* oxi_status_string(int32_t status);
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* oxi_last_error_string(void);
+
+/* Creates the per-device workspace (split-KV partials, arrival counters, conv
+ * staging, host-entry staging).  Replaces the scratch half of
+ * BatchEngine::new (batch_engine.rs:320-364).  max_batch <= 4096. */
+int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_t max_seq_len,
+                   uint32_t max_prefill_rows);
+int32_t oxi_destroy(oxi_handle* h);
+/* Bytes of device memory the handle owns. */
+size_t oxi_workspace_bytes(const oxi_handle* h);
+/* Synchronises `stream`, returns and clears the OR of OXI_DEV_* bits raised by
+ * kernels since the last call.  For tests and debugging; not on the hot path. */
+int32_t oxi_device_status(oxi_handle* h, void* stream, uint32_t* bits_out);
+
+/* ---- fused operators (the product path) -------------------------------- */
+
+/* Per-head Q/K RMSNorm + RoPE + KV append in ONE launch.
+ * Replaces batched_qk_rmsnorm_fp16 x2, batched_rope_fp16 x2 and
+ * batched_kv_copy_fp16 x2 (batched_attn.rs:13-118, 128-219, 233-287; launched
+ * at batch_engine.rs:941-1014).
+ *   q_io  [B][16][128]  in: projected q; out: normed + rotated q
+ *   k_in  [B][4][128], v_in [B][4][128]  projected k, v (not modified)
+ *   q_norm_w, k_norm_w [128]; cos, sin [max_pos][128] f16 tables (rope.rs:158-201)
+ *   pos_ids [B] u32; row pos_ids[b] of k_ptrs[b] / v_ptrs[b] receives the
+ *   normed + rotated k and the copied v.
+ * K/V/q bytes are bit-identical to the reference kernels' on the same GPU. */
+int32_t oxi_append(oxi_handle* h, void* stream, void* q_io, const void* k_in, const void* v_in,
+                   const void* q_norm_w, const void* k_norm_w, const void* cos_table,
+                   const void* sin_table, const uint32_t* pos_ids, const uint64_t* k_ptrs,
+                   const uint64_t* v_ptrs, uint32_t batch, float eps);
+
+/* Batched GQA decode attention with the per-head sigmoid output gate in ONE
+ * launch (split-KV flash-decode; the CTA finishing a row's last key range
+ * merges the partials and applies the gate).
+ * Replaces batched_gqa_attention_split4_fp16 + batched_gqa_attn_combine_fp16
+ * (or batched_gqa_attention_online_fp16) + batched_sigmoid_gate_fp16
+ * (batched_attn.rs:2665-3035, 1597-1717, 1194-1370, 583-655; launched at
+ * batch_engine.rs:1154-1239).
+ *   ctx_out [B][16][128]; q [B][16][128]; gate [B][16] or NULL (no gating);
+ *   window: 0 = full attention, else key t is masked iff (seq_len-1) - t >= window. */
+int32_t oxi_decode_attn(oxi_handle* h, void* stream, void* ctx_out, const void* q,
+                        const void* gate, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
+                        const uint32_t* seq_lens, uint32_t batch, uint32_t window);
+
+/* oxi_append followed by oxi_decode_attn on the same stream (the whole
+ * attention-layer hot path of one decode step, batch_engine.rs:941-1239). */
+int32_t oxi_append_decode(oxi_handle* h, void* stream, void* ctx_out, void* q_io, const void* k_in,
+                          const void* v_in, const void* gate, const void* q_norm_w,
+                          const void* k_norm_w, const void* cos_table, const void* sin_table,
+                          const uint32_t* pos_ids, const uint32_t* seq_lens,
+                          const uint64_t* k_ptrs, const uint64_t* v_ptrs, uint32_t batch,
+                          uint32_t window, float eps);
+
+/* Chunked-prefill causal GQA attention with the gate, over per-row tables:
+ * row r attends keys [window start, seq_lens[r]) of its own cache.  All rows'
+ * K/V must already be appended (batch_engine.rs:1011-1014).  One fused kernel;
+ * scores and weights never touch HBM.
+ * Replaces BatchEngine::gemm_attention_chunk (batch_engine.rs:439-592:
+ * batched_attn_pack_q_fp16, cuBLASLt QK^T, batched_attn_softmax_mask_fp16,
+ * cuBLASLt PV, batched_attn_gate_scatter_fp16) and the online-kernel fallback
+ * (batch_engine.rs:1214-1239). */
+int32_t oxi_prefill_attn(oxi_handle* h, void* stream, void* ctx_out, const void* q,
+                         const void* gate, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
+                         const uint32_t* seq_lens, uint32_t rows, uint32_t window);
+
+/* One-token causal conv1d + gating with the 6-slot carry state, one launch.
+ * Replaces batched_fused_causal_conv1d_gating_ptr_fp16 (batched_attn.rs:727-881,
+ * launched at batch_engine.rs:840-899).
+ *   y_out [B][2048]; conv_ptrs [B] -> state [2048][6] f16, updated in place;
+ *   bcx [B][6144] = [B | C | x]; conv_w [2048][7].  y and state bit-exact. */
+int32_t oxi_conv_decode(oxi_handle* h, void* stream, void* y_out, const uint64_t* conv_ptrs,
+                        const void* bcx, const void* conv_w, uint32_t batch);
+
+/* Prefill conv for one wave: every row's 7-tap window is read from the wave's
+ * own B*x history or the request's carry state, y is written for every row and
+ * each chunk's final 6-slot state replaces the request's persistent state.
+ * Replaces conv_state_prefill_fp16 + the conv kernel on pool rows + the
+ * per-chunk device copies (batched_attn.rs:1049-1176, batch_engine.rs:847-899,
+ * server.rs:1192-1224).
+ *   carry_ptrs [rows] u64 (row's request state for this layer, [2048][6]);
+ *   origin [rows] u32 wave row where the row's chunk starts; local_pos [rows]
+ *   u32 position inside the chunk (as PrefillMeta, batch_engine.rs:156-160). */
+int32_t oxi_conv_prefill(oxi_handle* h, void* stream, void* y_out, const uint64_t* carry_ptrs,
+                         const uint32_t* origin, const uint32_t* local_pos, const void* bcx,
+                         const void* conv_w, uint32_t rows);
+
+/* ---- unfused operators with the reference's exact semantics ------------ */
+/* Same contract as the PTX entry of the same name, so a harness can swap the
+ * reference kernels for these one by one and localise a mismatch. */
+int32_t oxi_qk_rmsnorm(oxi_handle* h, void* stream, void* x_io, const void* weight, float eps,
+                       uint32_t num_heads, uint32_t batch); /* batched_attn.rs:13-118   */
+int32_t oxi_rope(oxi_handle* h, void* stream, void* x_io, const void* cos_table,
+                 const void* sin_table, const uint32_t* pos_ids, uint32_t num_heads,
+                 uint32_t batch);                           /* batched_attn.rs:128-219  */
+int32_t oxi_kv_copy(oxi_handle* h, void* stream, const uint64_t* dst_ptrs, const void* src,
+                    const uint32_t* pos_ids, uint32_t batch); /* batched_attn.rs:233-287 */
+int32_t oxi_sigmoid_gate(oxi_handle* h, void* stream, void* ctx_io, const void* gate,
+                         uint32_t batch);                   /* batched_attn.rs:583-655  */
+
+/* ---- host-buffer entry (what an engine without device staging calls) --- */
+
+/* One decode step of `layers` attention layers driven from HOST memory: per
+ * layer l the call uploads q/k/v/gate [l][B][...], the layer's pointer tables
+ * and the step's pos_ids (seq_lens = pos_ids + 1), runs oxi_append +
+ * oxi_decode_attn, and downloads ctx [l][B][16][128].  Mirrors the metadata
+ * uploads of forward_step_with_embeds (batch_engine.rs:681-740).  All host
+ * buffers should be pinned; the call returns after enqueueing (the caller
+ * synchronises the stream before reading ctx_host).  K/V caches stay on the
+ * device.  norm weights: [layers][128]; tables: [layers*B]. */
+int32_t oxi_decode_step_host(oxi_handle* h, void* stream, void* ctx_host, const void* q_host,
+                             const void* k_host, const void* v_host, const void* gate_host,
+                             const void* q_norm_w_dev, const void* k_norm_w_dev,
+                             const void* cos_table_dev, const void* sin_table_dev,
+                             const uint32_t* pos_ids_host, const uint64_t* k_ptrs_host,
+                             const uint64_t* v_ptrs_host, uint32_t batch, uint32_t layers,
+                             uint32_t window, float eps);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OXI_KV_H */

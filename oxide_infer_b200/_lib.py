@@ -1,0 +1,55 @@
+"""ctypes binding of liboxi_kv.so.  There is no fallback: if the library is
+missing or fails to load, importing the operators raises."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+SO_PATH = os.path.join(HERE, "liboxi_kv.so")
+
+_vp, _u32, _i32, _f32 = C.c_void_p, C.c_uint32, C.c_int32, C.c_float
+
+# name -> argument ctypes (all functions return int32 unless listed in _RESTYPE)
+SIGNATURES = {
+    "oxi_version": [],
+    "oxi_status_string": [_i32],
+    "oxi_last_error_string": [],
+    "oxi_create": [C.POINTER(_vp), _i32, _u32, _u32, _u32],
+    "oxi_destroy": [_vp],
+    "oxi_workspace_bytes": [_vp],
+    "oxi_device_status": [_vp, _vp, C.POINTER(_u32)],
+    "oxi_append": [_vp] * 12 + [_u32, _f32],
+    "oxi_decode_attn": [_vp] * 8 + [_u32, _u32],
+    "oxi_append_decode": [_vp] * 15 + [_u32, _u32, _f32],
+    "oxi_prefill_attn": [_vp] * 8 + [_u32, _u32],
+    "oxi_conv_decode": [_vp] * 6 + [_u32],
+    "oxi_conv_prefill": [_vp] * 8 + [_u32],
+    "oxi_qk_rmsnorm": [_vp, _vp, _vp, _vp, _f32, _u32, _u32],
+    "oxi_rope": [_vp] * 6 + [_u32, _u32],
+    "oxi_kv_copy": [_vp] * 5 + [_u32],
+    "oxi_sigmoid_gate": [_vp] * 4 + [_u32],
+    "oxi_decode_step_host": [_vp] * 14 + [_u32, _u32, _u32, _f32],
+}
+_RESTYPE = {"oxi_status_string": C.c_char_p, "oxi_last_error_string": C.c_char_p,
+            "oxi_workspace_bytes": C.c_size_t}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the shared library and bind every declared symbol (raises if any is missing)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(SO_PATH):
+        raise ImportError(
+            f"{SO_PATH} is missing: build it with `python -m oxide_infer_b200.build` "
+            "(nvcc, sm_100a). This package has no CPU or PyTorch fallback.")
+    lib = C.CDLL(SO_PATH)
+    for name, args in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.argtypes = args
+        fn.restype = _RESTYPE.get(name, _i32)
+    _lib = lib
+    return lib

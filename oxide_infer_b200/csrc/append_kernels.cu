@@ -1,0 +1,196 @@
+// Fused per-head Q/K RMSNorm + RoPE + KV append, and the unfused operators
+// with the reference's semantics (batched_attn.rs:13-118, 128-219, 233-287,
+// 583-655).  Arithmetic order follows the reference instruction for
+// instruction so q, K and V bytes match its kernels exactly on the same GPU:
+// lane l sums dims l, l+32, l+64, l+96 with fma, the warp reduces with a
+// shfl.down tree, mean = div.approx(sum, 128), r = rsqrt.approx(mean + eps),
+// y = f16((x*r)*w); then on the f16-rounded y: f16(fma(+-y[d^64], sin, y*cos)).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace oxi {
+
+// One warp normalises (and optionally rotates) one head held in registers.
+// x[i] is dim lane + 32*i.  Returns the f16 bit patterns in out[i].
+template <bool kNorm, bool kRope>
+__device__ __forceinline__ void head_norm_rope(const uint16_t* __restrict__ x_head,
+                                               const uint16_t* __restrict__ w, float eps,
+                                               const uint16_t* __restrict__ cos_row,
+                                               const uint16_t* __restrict__ sin_row, int lane,
+                                               uint16_t (&out)[4]) {
+    float x[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) x[i] = h2f(x_head[lane + 32 * i]);
+    uint16_t y16[4];
+    if (kNorm) {
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) sum = __fmaf_rn(x[i], x[i], sum);
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1)
+            sum = __fadd_rn(sum, __shfl_down_sync(0xffffffffu, sum, off));
+        float mean = div_approx_ftz(sum, 128.0f);
+        mean = __fadd_rn(mean, eps);
+        float r = rsqrt_approx_ftz(mean);
+        r = __shfl_sync(0xffffffffu, r, 0);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float fw = h2f(w[lane + 32 * i]);
+            y16[i] = f2h(__fmul_rn(__fmul_rn(x[i], r), fw));
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) y16[i] = x_head[lane + 32 * i];
+    }
+    if (kRope) {
+        float y[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) y[i] = h2f(y16[i]);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            // dim d = lane + 32 i pairs with d + 64 (i < 2) or d - 64 (i >= 2)
+            float other = (i < 2) ? -y[i + 2] : y[i - 2];
+            float c = h2f(cos_row[lane + 32 * i]);
+            float s = h2f(sin_row[lane + 32 * i]);
+            float res = __fmul_rn(y[i], c);
+            res = __fmaf_rn(other, s, res);
+            out[i] = f2h(res);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 4; i++) out[i] = y16[i];
+    }
+}
+
+// grid = B, block = 20 warps: warps 0..15 own the query heads, 16..19 the K
+// heads; threads 0..63 also copy the 1 KB V row with 16-byte vectors.
+__global__ void __launch_bounds__(640)
+append_kernel(uint16_t* __restrict__ q_io, const uint16_t* __restrict__ k_in,
+              const uint16_t* __restrict__ v_in, const uint16_t* __restrict__ q_norm_w,
+              const uint16_t* __restrict__ k_norm_w, const uint16_t* __restrict__ cos_t,
+              const uint16_t* __restrict__ sin_t, const uint32_t* __restrict__ pos_ids,
+              const uint64_t* __restrict__ k_ptrs, const uint64_t* __restrict__ v_ptrs, float eps,
+              uint32_t* __restrict__ status) {
+    const uint32_t b = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t pos = pos_ids[b];
+    const uint64_t kp = k_ptrs[b], vp = v_ptrs[b];
+    const bool aligned = ((kp | vp) & 15ull) == 0ull;
+    if (!aligned && threadIdx.x == 0) atomicOr(status, DEV_MISALIGNED_PTR);
+    const uint16_t* cos_row = cos_t + (size_t)pos * HD;
+    const uint16_t* sin_row = sin_t + (size_t)pos * HD;
+    uint16_t out[4];
+    if (warp < NQ) {
+        uint16_t* xh = q_io + ((size_t)b * NQ + warp) * HD;
+        head_norm_rope<true, true>(xh, q_norm_w, eps, cos_row, sin_row, lane, out);
+#pragma unroll
+        for (int i = 0; i < 4; i++) xh[lane + 32 * i] = out[i];
+    } else {
+        const int kh = warp - NQ;
+        const uint16_t* xh = k_in + ((size_t)b * NKV + kh) * HD;
+        head_norm_rope<true, true>(xh, k_norm_w, eps, cos_row, sin_row, lane, out);
+        if (aligned) {
+            uint16_t* dst = reinterpret_cast<uint16_t*>(kp) + (size_t)pos * (NKV * HD) + kh * HD;
+#pragma unroll
+            for (int i = 0; i < 4; i++) dst[lane + 32 * i] = out[i];
+        }
+    }
+    if (threadIdx.x < 64 && aligned) {
+        const uint4* src = reinterpret_cast<const uint4*>(v_in + (size_t)b * (NKV * HD));
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(vp) + (size_t)pos * KV_ROW_BYTES);
+        dst[threadIdx.x] = src[threadIdx.x];
+    }
+}
+
+__global__ void __launch_bounds__(128)
+qk_rmsnorm_kernel(uint16_t* __restrict__ x_io, const uint16_t* __restrict__ w, float eps,
+                  uint32_t total_heads) {
+    const uint32_t head = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (head >= total_heads) return;
+    uint16_t out[4];
+    uint16_t* xh = x_io + (size_t)head * HD;
+    const int lane = threadIdx.x & 31;
+    head_norm_rope<true, false>(xh, w, eps, nullptr, nullptr, lane, out);
+#pragma unroll
+    for (int i = 0; i < 4; i++) xh[lane + 32 * i] = out[i];
+}
+
+__global__ void __launch_bounds__(128)
+rope_kernel(uint16_t* __restrict__ x_io, const uint16_t* __restrict__ cos_t,
+            const uint16_t* __restrict__ sin_t, const uint32_t* __restrict__ pos_ids,
+            uint32_t heads, uint32_t total_heads) {
+    const uint32_t head = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (head >= total_heads) return;
+    const uint32_t pos = pos_ids[head / heads];
+    uint16_t out[4];
+    uint16_t* xh = x_io + (size_t)head * HD;
+    const int lane = threadIdx.x & 31;
+    head_norm_rope<false, true>(xh, nullptr, 0.0f, cos_t + (size_t)pos * HD,
+                                sin_t + (size_t)pos * HD, lane, out);
+#pragma unroll
+    for (int i = 0; i < 4; i++) xh[lane + 32 * i] = out[i];
+}
+
+__global__ void __launch_bounds__(64)
+kv_copy_kernel(const uint64_t* __restrict__ dst_ptrs, const uint16_t* __restrict__ src,
+               const uint32_t* __restrict__ pos_ids, uint32_t* __restrict__ status) {
+    const uint32_t b = blockIdx.x;
+    const uint64_t dp = dst_ptrs[b];
+    if (dp & 15ull) {
+        if (threadIdx.x == 0) atomicOr(status, DEV_MISALIGNED_PTR);
+        return;
+    }
+    const uint4* s = reinterpret_cast<const uint4*>(src + (size_t)b * (NKV * HD));
+    uint4* d = reinterpret_cast<uint4*>(reinterpret_cast<char*>(dp) + (size_t)pos_ids[b] * KV_ROW_BYTES);
+    d[threadIdx.x] = s[threadIdx.x];
+}
+
+__global__ void __launch_bounds__(128)
+sigmoid_gate_kernel(uint16_t* __restrict__ ctx_io, const uint16_t* __restrict__ gate) {
+    const uint32_t bh = blockIdx.x;  // b*16 + head
+    const float sig = sigmoid_ref(h2f(gate[bh]));
+    uint16_t* p = ctx_io + (size_t)bh * HD + threadIdx.x;
+    *p = f2h(__fmul_rn(h2f(*p), sig));
+}
+
+cudaError_t launch_append(cudaStream_t stream, void* q_io, const void* k_in, const void* v_in,
+                          const void* q_norm_w, const void* k_norm_w, const void* cos_t,
+                          const void* sin_t, const uint32_t* pos_ids, const uint64_t* k_ptrs,
+                          const uint64_t* v_ptrs, uint32_t batch, float eps, uint32_t* status) {
+    append_kernel<<<batch, 640, 0, stream>>>(
+        (uint16_t*)q_io, (const uint16_t*)k_in, (const uint16_t*)v_in, (const uint16_t*)q_norm_w,
+        (const uint16_t*)k_norm_w, (const uint16_t*)cos_t, (const uint16_t*)sin_t, pos_ids, k_ptrs,
+        v_ptrs, eps, status);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_qk_rmsnorm(cudaStream_t stream, void* x_io, const void* w, float eps,
+                              uint32_t heads, uint32_t batch) {
+    const uint32_t total = heads * batch;
+    qk_rmsnorm_kernel<<<(total + 3) / 4, 128, 0, stream>>>((uint16_t*)x_io, (const uint16_t*)w,
+                                                           eps, total);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rope(cudaStream_t stream, void* x_io, const void* cos_t, const void* sin_t,
+                        const uint32_t* pos_ids, uint32_t heads, uint32_t batch) {
+    const uint32_t total = heads * batch;
+    rope_kernel<<<(total + 3) / 4, 128, 0, stream>>>((uint16_t*)x_io, (const uint16_t*)cos_t,
+                                                     (const uint16_t*)sin_t, pos_ids, heads,
+                                                     total);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_kv_copy(cudaStream_t stream, const uint64_t* dst_ptrs, const void* src,
+                           const uint32_t* pos_ids, uint32_t batch, uint32_t* status) {
+    kv_copy_kernel<<<batch, 64, 0, stream>>>(dst_ptrs, (const uint16_t*)src, pos_ids, status);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_sigmoid_gate(cudaStream_t stream, void* ctx_io, const void* gate,
+                                uint32_t batch) {
+    sigmoid_gate_kernel<<<batch * NQ, 128, 0, stream>>>((uint16_t*)ctx_io, (const uint16_t*)gate);
+    return cudaGetLastError();
+}
+
+}  // namespace oxi

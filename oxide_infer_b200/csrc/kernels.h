@@ -1,0 +1,53 @@
+// Internal launch functions of liboxi_kv (one per kernel file).  Every function
+// only enqueues work on `stream` and returns the launch's cudaError_t.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace oxi {
+
+struct DecodeWorkspace {
+    float* partial_acc;     // [max_batch][max_chunks][16][128]
+    float* partial_stats;   // [max_batch][max_chunks][16][2]  (running max in log2 units, sum)
+    uint32_t* counters;     // [max_batch][4] arrivals per (row, kv head); all zero between launches
+    uint32_t* status;       // device status word (OR of DEV_* bits)
+    uint32_t max_chunks;    // partial slots per row
+    uint32_t max_seq_len;
+    int num_sms;
+};
+
+cudaError_t launch_append(cudaStream_t stream, void* q_io, const void* k_in, const void* v_in,
+                          const void* q_norm_w, const void* k_norm_w, const void* cos_t,
+                          const void* sin_t, const uint32_t* pos_ids, const uint64_t* k_ptrs,
+                          const uint64_t* v_ptrs, uint32_t batch, float eps, uint32_t* status);
+cudaError_t launch_qk_rmsnorm(cudaStream_t stream, void* x_io, const void* w, float eps,
+                              uint32_t heads, uint32_t batch);
+cudaError_t launch_rope(cudaStream_t stream, void* x_io, const void* cos_t, const void* sin_t,
+                        const uint32_t* pos_ids, uint32_t heads, uint32_t batch);
+cudaError_t launch_kv_copy(cudaStream_t stream, const uint64_t* dst_ptrs, const void* src,
+                           const uint32_t* pos_ids, uint32_t batch, uint32_t* status);
+cudaError_t launch_sigmoid_gate(cudaStream_t stream, void* ctx_io, const void* gate,
+                                uint32_t batch);
+
+cudaError_t decode_attn_init();  // one-time function attributes (dynamic shared memory)
+cudaError_t launch_decode_attn(cudaStream_t stream, const DecodeWorkspace& ws, void* ctx_out,
+                               const void* q, const void* gate, const uint64_t* k_ptrs,
+                               const uint64_t* v_ptrs, const uint32_t* seq_lens, uint32_t batch,
+                               uint32_t window);
+uint32_t decode_chunk_keys();    // keys per split-KV work item
+
+cudaError_t prefill_attn_init();
+cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* q,
+                                const void* gate, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
+                                const uint32_t* seq_lens, uint32_t rows, uint32_t window,
+                                uint32_t* status, int num_sms);
+
+cudaError_t launch_conv_decode(cudaStream_t stream, void* y_out, const uint64_t* conv_ptrs,
+                               const void* bcx, const void* conv_w, uint32_t batch,
+                               uint32_t* status);
+cudaError_t launch_conv_prefill(cudaStream_t stream, void* y_out, const uint64_t* carry_ptrs,
+                                const uint32_t* origin, const uint32_t* local_pos,
+                                const void* bcx, const void* conv_w, uint32_t rows,
+                                void* stage /* [rows][2048][6] f16 */, uint32_t* status);
+
+}  // namespace oxi

@@ -1,0 +1,352 @@
+// C ABI of liboxi_kv: handle/workspace management, host-side argument
+// validation, and the launch sequences behind each exported operator.
+#include "../../include/oxi_kv.h"
+
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+#include "kernels.h"
+
+using namespace oxi;
+
+struct oxi_handle {
+    int device;
+    int num_sms;
+    uint32_t max_batch, max_seq_len, max_prefill_rows;
+    DecodeWorkspace dws;
+    void* conv_stage;     // [max_prefill_rows][2048][6] f16
+    // staging for the host-buffer entry, one layer at a time, double buffered
+    void* stg_q[2];       // [max_batch][16][128]
+    void* stg_k[2];       // [max_batch][4][128]
+    void* stg_v[2];
+    void* stg_gate[2];    // [max_batch][16]
+    void* stg_ctx[2];     // [max_batch][16][128]
+    uint64_t* stg_kp[2];  // [max_batch]
+    uint64_t* stg_vp[2];
+    uint32_t* stg_pos;    // [max_batch]
+    uint32_t* stg_len;    // [max_batch]
+    uint32_t* host_len;   // pinned [max_batch]
+    cudaEvent_t stg_free[2];
+    size_t bytes;
+};
+
+static thread_local char g_err[256] = "";
+
+static int32_t fail(int32_t code, const char* msg) {
+    snprintf(g_err, sizeof(g_err), "%s", msg);
+    return code;
+}
+static int32_t cuda_fail(cudaError_t e, const char* where) {
+    snprintf(g_err, sizeof(g_err), "%s: %s", where, cudaGetErrorString(e));
+    return (int32_t)e;
+}
+#define OXI_CUDA(call, where)                          \
+    do {                                               \
+        cudaError_t e__ = (call);                      \
+        if (e__ != cudaSuccess) return cuda_fail(e__, where); \
+    } while (0)
+
+extern "C" {
+
+int32_t oxi_version(void) { return OXI_VERSION; }
+
+const char* oxi_status_string(int32_t s) {
+    switch (s) {
+        case OXI_OK: return "ok";
+        case OXI_ERR_NULL: return "null pointer or handle";
+        case OXI_ERR_BATCH: return "batch/rows is zero or exceeds the handle limit";
+        case OXI_ERR_ARG: return "scalar argument out of range";
+        case OXI_ERR_WORKSPACE: return "workspace too small for this call";
+        case OXI_ERR_NO_DEVICE: return "no usable CUDA device";
+        default: return s > 0 ? cudaGetErrorString((cudaError_t)s) : "unknown status";
+    }
+}
+
+const char* oxi_last_error_string(void) { return g_err; }
+
+static int32_t dev_alloc(oxi_handle* h, void** p, size_t bytes) {
+    cudaError_t e = cudaMalloc(p, bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc");
+    h->bytes += bytes;
+    return OXI_OK;
+}
+
+int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_t max_seq_len,
+                   uint32_t max_prefill_rows) {
+    if (!out) return fail(OXI_ERR_NULL, "oxi_create: out is null");
+    *out = nullptr;
+    if (max_batch == 0 || max_batch > 4096) return fail(OXI_ERR_BATCH, "oxi_create: max_batch must be 1..4096");
+    if (max_seq_len == 0 || max_seq_len > (1u << 22)) return fail(OXI_ERR_ARG, "oxi_create: max_seq_len out of range");
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || device < 0 || device >= ndev) {
+        cudaGetLastError();
+        return fail(OXI_ERR_NO_DEVICE, "oxi_create: no such CUDA device");
+    }
+    cudaDeviceProp prop;
+    OXI_CUDA(cudaGetDeviceProperties(&prop, device), "cudaGetDeviceProperties");
+    if (prop.major != 10) return fail(OXI_ERR_NO_DEVICE, "oxi_create: device is not sm_100 (B200)");
+    OXI_CUDA(cudaSetDevice(device), "cudaSetDevice");
+
+    oxi_handle* h = new (std::nothrow) oxi_handle();
+    if (!h) return fail(OXI_ERR_WORKSPACE, "oxi_create: host allocation failed");
+    memset(h, 0, sizeof(*h));
+    h->device = device;
+    h->num_sms = prop.multiProcessorCount;
+    h->max_batch = max_batch;
+    h->max_seq_len = max_seq_len;
+    h->max_prefill_rows = max_prefill_rows;
+
+    const uint32_t chunk = decode_chunk_keys();
+    const uint32_t max_chunks = (max_seq_len + chunk - 1) / chunk;
+    h->dws.max_chunks = max_chunks;
+    h->dws.max_seq_len = max_seq_len;
+    h->dws.num_sms = h->num_sms;
+    int32_t rc = OXI_OK;
+    const size_t slots = (size_t)max_batch * max_chunks * NQ;
+    if ((rc = dev_alloc(h, (void**)&h->dws.partial_acc, slots * HD * sizeof(float)))) goto bad;
+    if ((rc = dev_alloc(h, (void**)&h->dws.partial_stats, slots * 2 * sizeof(float)))) goto bad;
+    if ((rc = dev_alloc(h, (void**)&h->dws.counters, (size_t)max_batch * NKV * sizeof(uint32_t)))) goto bad;
+    if ((rc = dev_alloc(h, (void**)&h->dws.status, 256))) goto bad;
+    if (max_prefill_rows)
+        if ((rc = dev_alloc(h, &h->conv_stage, (size_t)max_prefill_rows * HIDDEN * CONV_S * 2))) goto bad;
+    for (int i = 0; i < 2; i++) {
+        if ((rc = dev_alloc(h, &h->stg_q[i], (size_t)max_batch * NQ * HD * 2))) goto bad;
+        if ((rc = dev_alloc(h, &h->stg_k[i], (size_t)max_batch * NKV * HD * 2))) goto bad;
+        if ((rc = dev_alloc(h, &h->stg_v[i], (size_t)max_batch * NKV * HD * 2))) goto bad;
+        if ((rc = dev_alloc(h, &h->stg_gate[i], (size_t)max_batch * NQ * 2))) goto bad;
+        if ((rc = dev_alloc(h, &h->stg_ctx[i], (size_t)max_batch * NQ * HD * 2))) goto bad;
+        if ((rc = dev_alloc(h, (void**)&h->stg_kp[i], (size_t)max_batch * 8))) goto bad;
+        if ((rc = dev_alloc(h, (void**)&h->stg_vp[i], (size_t)max_batch * 8))) goto bad;
+        if (cudaEventCreateWithFlags(&h->stg_free[i], cudaEventDisableTiming) != cudaSuccess) {
+            rc = cuda_fail(cudaGetLastError(), "cudaEventCreate");
+            goto bad;
+        }
+    }
+    if ((rc = dev_alloc(h, (void**)&h->stg_pos, (size_t)max_batch * 4))) goto bad;
+    if ((rc = dev_alloc(h, (void**)&h->stg_len, (size_t)max_batch * 4))) goto bad;
+    if (cudaMallocHost((void**)&h->host_len, (size_t)max_batch * 4) != cudaSuccess) {
+        rc = cuda_fail(cudaGetLastError(), "cudaMallocHost");
+        goto bad;
+    }
+    if (cudaMemset(h->dws.counters, 0, (size_t)max_batch * NKV * sizeof(uint32_t)) != cudaSuccess ||
+        cudaMemset(h->dws.status, 0, 256) != cudaSuccess) {
+        rc = cuda_fail(cudaGetLastError(), "cudaMemset");
+        goto bad;
+    }
+    {
+        cudaError_t e = decode_attn_init();
+        if (e == cudaSuccess) e = prefill_attn_init();
+        if (e != cudaSuccess) { rc = cuda_fail(e, "cudaFuncSetAttribute"); goto bad; }
+    }
+    OXI_CUDA(cudaDeviceSynchronize(), "oxi_create sync");
+    *out = h;
+    return OXI_OK;
+bad:
+    oxi_destroy(h);
+    return rc;
+}
+
+int32_t oxi_destroy(oxi_handle* h) {
+    if (!h) return OXI_OK;
+    cudaSetDevice(h->device);
+    cudaFree(h->dws.partial_acc);
+    cudaFree(h->dws.partial_stats);
+    cudaFree(h->dws.counters);
+    cudaFree(h->dws.status);
+    cudaFree(h->conv_stage);
+    for (int i = 0; i < 2; i++) {
+        cudaFree(h->stg_q[i]); cudaFree(h->stg_k[i]); cudaFree(h->stg_v[i]);
+        cudaFree(h->stg_gate[i]); cudaFree(h->stg_ctx[i]);
+        cudaFree(h->stg_kp[i]); cudaFree(h->stg_vp[i]);
+        if (h->stg_free[i]) cudaEventDestroy(h->stg_free[i]);
+    }
+    cudaFree(h->stg_pos);
+    cudaFree(h->stg_len);
+    if (h->host_len) cudaFreeHost(h->host_len);
+    cudaGetLastError();
+    delete h;
+    return OXI_OK;
+}
+
+size_t oxi_workspace_bytes(const oxi_handle* h) { return h ? h->bytes : 0; }
+
+int32_t oxi_device_status(oxi_handle* h, void* stream, uint32_t* bits_out) {
+    if (!h || !bits_out) return fail(OXI_ERR_NULL, "oxi_device_status: null argument");
+    cudaStream_t s = (cudaStream_t)stream;
+    uint32_t bits = 0;
+    OXI_CUDA(cudaMemcpyAsync(&bits, h->dws.status, 4, cudaMemcpyDeviceToHost, s), "status copy");
+    OXI_CUDA(cudaMemsetAsync(h->dws.status, 0, 4, s), "status clear");
+    OXI_CUDA(cudaStreamSynchronize(s), "status sync");
+    *bits_out = bits;
+    return OXI_OK;
+}
+
+#define REQ_HANDLE(name) \
+    if (!h) return fail(OXI_ERR_NULL, name ": handle is null")
+#define REQ_PTR(p, name) \
+    if (!(p)) return fail(OXI_ERR_NULL, name ": required pointer is null")
+#define REQ_BATCH(n, lim, name) \
+    if ((n) == 0 || (n) > (lim)) return fail(OXI_ERR_BATCH, name ": batch/rows is 0 or exceeds the handle limit")
+
+int32_t oxi_append(oxi_handle* h, void* stream, void* q_io, const void* k_in, const void* v_in,
+                   const void* q_norm_w, const void* k_norm_w, const void* cos_table,
+                   const void* sin_table, const uint32_t* pos_ids, const uint64_t* k_ptrs,
+                   const uint64_t* v_ptrs, uint32_t batch, float eps) {
+    REQ_HANDLE("oxi_append");
+    REQ_PTR(q_io && k_in && v_in && q_norm_w && k_norm_w && cos_table && sin_table && pos_ids &&
+                k_ptrs && v_ptrs, "oxi_append");
+    REQ_BATCH(batch, h->max_batch, "oxi_append");
+    if (!(eps >= 0.0f)) return fail(OXI_ERR_ARG, "oxi_append: eps must be >= 0");
+    OXI_CUDA(launch_append((cudaStream_t)stream, q_io, k_in, v_in, q_norm_w, k_norm_w, cos_table,
+                           sin_table, pos_ids, k_ptrs, v_ptrs, batch, eps, h->dws.status),
+             "append launch");
+    return OXI_OK;
+}
+
+int32_t oxi_decode_attn(oxi_handle* h, void* stream, void* ctx_out, const void* q,
+                        const void* gate, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
+                        const uint32_t* seq_lens, uint32_t batch, uint32_t window) {
+    REQ_HANDLE("oxi_decode_attn");
+    REQ_PTR(ctx_out && q && k_ptrs && v_ptrs && seq_lens, "oxi_decode_attn");
+    REQ_BATCH(batch, h->max_batch, "oxi_decode_attn");
+    OXI_CUDA(launch_decode_attn((cudaStream_t)stream, h->dws, ctx_out, q, gate, k_ptrs, v_ptrs,
+                                seq_lens, batch, window),
+             "decode_attn launch");
+    return OXI_OK;
+}
+
+int32_t oxi_append_decode(oxi_handle* h, void* stream, void* ctx_out, void* q_io, const void* k_in,
+                          const void* v_in, const void* gate, const void* q_norm_w,
+                          const void* k_norm_w, const void* cos_table, const void* sin_table,
+                          const uint32_t* pos_ids, const uint32_t* seq_lens,
+                          const uint64_t* k_ptrs, const uint64_t* v_ptrs, uint32_t batch,
+                          uint32_t window, float eps) {
+    int32_t rc = oxi_append(h, stream, q_io, k_in, v_in, q_norm_w, k_norm_w, cos_table, sin_table,
+                            pos_ids, k_ptrs, v_ptrs, batch, eps);
+    if (rc != OXI_OK) return rc;
+    return oxi_decode_attn(h, stream, ctx_out, q_io, gate, k_ptrs, v_ptrs, seq_lens, batch, window);
+}
+
+int32_t oxi_prefill_attn(oxi_handle* h, void* stream, void* ctx_out, const void* q,
+                         const void* gate, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
+                         const uint32_t* seq_lens, uint32_t rows, uint32_t window) {
+    REQ_HANDLE("oxi_prefill_attn");
+    REQ_PTR(ctx_out && q && k_ptrs && v_ptrs && seq_lens, "oxi_prefill_attn");
+    REQ_BATCH(rows, h->max_prefill_rows, "oxi_prefill_attn");
+    OXI_CUDA(launch_prefill_attn((cudaStream_t)stream, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens,
+                                 rows, window, h->dws.status, h->num_sms),
+             "prefill_attn launch");
+    return OXI_OK;
+}
+
+int32_t oxi_conv_decode(oxi_handle* h, void* stream, void* y_out, const uint64_t* conv_ptrs,
+                        const void* bcx, const void* conv_w, uint32_t batch) {
+    REQ_HANDLE("oxi_conv_decode");
+    REQ_PTR(y_out && conv_ptrs && bcx && conv_w, "oxi_conv_decode");
+    REQ_BATCH(batch, 65535u, "oxi_conv_decode");
+    OXI_CUDA(launch_conv_decode((cudaStream_t)stream, y_out, conv_ptrs, bcx, conv_w, batch,
+                                h->dws.status),
+             "conv_decode launch");
+    return OXI_OK;
+}
+
+int32_t oxi_conv_prefill(oxi_handle* h, void* stream, void* y_out, const uint64_t* carry_ptrs,
+                         const uint32_t* origin, const uint32_t* local_pos, const void* bcx,
+                         const void* conv_w, uint32_t rows) {
+    REQ_HANDLE("oxi_conv_prefill");
+    REQ_PTR(y_out && carry_ptrs && origin && local_pos && bcx && conv_w, "oxi_conv_prefill");
+    REQ_BATCH(rows, h->max_prefill_rows, "oxi_conv_prefill");
+    if (rows > 65535u) return fail(OXI_ERR_BATCH, "oxi_conv_prefill: at most 65535 rows per wave");
+    OXI_CUDA(launch_conv_prefill((cudaStream_t)stream, y_out, carry_ptrs, origin, local_pos, bcx,
+                                 conv_w, rows, h->conv_stage, h->dws.status),
+             "conv_prefill launch");
+    return OXI_OK;
+}
+
+int32_t oxi_qk_rmsnorm(oxi_handle* h, void* stream, void* x_io, const void* weight, float eps,
+                       uint32_t num_heads, uint32_t batch) {
+    REQ_HANDLE("oxi_qk_rmsnorm");
+    REQ_PTR(x_io && weight, "oxi_qk_rmsnorm");
+    if (batch == 0) return fail(OXI_ERR_BATCH, "oxi_qk_rmsnorm: batch is 0");
+    if (num_heads == 0 || num_heads > 1024) return fail(OXI_ERR_ARG, "oxi_qk_rmsnorm: num_heads out of range");
+    OXI_CUDA(launch_qk_rmsnorm((cudaStream_t)stream, x_io, weight, eps, num_heads, batch), "qk_rmsnorm launch");
+    return OXI_OK;
+}
+
+int32_t oxi_rope(oxi_handle* h, void* stream, void* x_io, const void* cos_table,
+                 const void* sin_table, const uint32_t* pos_ids, uint32_t num_heads,
+                 uint32_t batch) {
+    REQ_HANDLE("oxi_rope");
+    REQ_PTR(x_io && cos_table && sin_table && pos_ids, "oxi_rope");
+    if (batch == 0) return fail(OXI_ERR_BATCH, "oxi_rope: batch is 0");
+    if (num_heads == 0 || num_heads > 1024) return fail(OXI_ERR_ARG, "oxi_rope: num_heads out of range");
+    OXI_CUDA(launch_rope((cudaStream_t)stream, x_io, cos_table, sin_table, pos_ids, num_heads, batch), "rope launch");
+    return OXI_OK;
+}
+
+int32_t oxi_kv_copy(oxi_handle* h, void* stream, const uint64_t* dst_ptrs, const void* src,
+                    const uint32_t* pos_ids, uint32_t batch) {
+    REQ_HANDLE("oxi_kv_copy");
+    REQ_PTR(dst_ptrs && src && pos_ids, "oxi_kv_copy");
+    if (batch == 0) return fail(OXI_ERR_BATCH, "oxi_kv_copy: batch is 0");
+    OXI_CUDA(launch_kv_copy((cudaStream_t)stream, dst_ptrs, src, pos_ids, batch, h->dws.status), "kv_copy launch");
+    return OXI_OK;
+}
+
+int32_t oxi_sigmoid_gate(oxi_handle* h, void* stream, void* ctx_io, const void* gate,
+                         uint32_t batch) {
+    REQ_HANDLE("oxi_sigmoid_gate");
+    REQ_PTR(ctx_io && gate, "oxi_sigmoid_gate");
+    if (batch == 0) return fail(OXI_ERR_BATCH, "oxi_sigmoid_gate: batch is 0");
+    OXI_CUDA(launch_sigmoid_gate((cudaStream_t)stream, ctx_io, gate, batch), "sigmoid_gate launch");
+    return OXI_OK;
+}
+
+int32_t oxi_decode_step_host(oxi_handle* h, void* stream, void* ctx_host, const void* q_host,
+                             const void* k_host, const void* v_host, const void* gate_host,
+                             const void* q_norm_w_dev, const void* k_norm_w_dev,
+                             const void* cos_table_dev, const void* sin_table_dev,
+                             const uint32_t* pos_ids_host, const uint64_t* k_ptrs_host,
+                             const uint64_t* v_ptrs_host, uint32_t batch, uint32_t layers,
+                             uint32_t window, float eps) {
+    REQ_HANDLE("oxi_decode_step_host");
+    REQ_PTR(ctx_host && q_host && k_host && v_host && q_norm_w_dev && k_norm_w_dev &&
+                cos_table_dev && sin_table_dev && pos_ids_host && k_ptrs_host && v_ptrs_host,
+            "oxi_decode_step_host");
+    REQ_BATCH(batch, h->max_batch, "oxi_decode_step_host");
+    if (layers == 0 || layers > 4096) return fail(OXI_ERR_ARG, "oxi_decode_step_host: layers out of range");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t qb = (size_t)batch * NQ * HD * 2, kb = (size_t)batch * NKV * HD * 2;
+    const size_t gb = (size_t)batch * NQ * 2, tb = (size_t)batch * 8;
+    // step metadata: positions and lengths (seq_len counts the appended token)
+    for (uint32_t i = 0; i < batch; i++) h->host_len[i] = pos_ids_host[i] + 1u;
+    OXI_CUDA(cudaMemcpyAsync(h->stg_pos, pos_ids_host, (size_t)batch * 4, cudaMemcpyHostToDevice, s), "pos upload");
+    OXI_CUDA(cudaMemcpyAsync(h->stg_len, h->host_len, (size_t)batch * 4, cudaMemcpyHostToDevice, s), "len upload");
+    for (uint32_t l = 0; l < layers; l++) {
+        const int sb = l & 1;
+        const char* qh = (const char*)q_host + l * qb;
+        OXI_CUDA(cudaMemcpyAsync(h->stg_q[sb], qh, qb, cudaMemcpyHostToDevice, s), "q upload");
+        OXI_CUDA(cudaMemcpyAsync(h->stg_k[sb], (const char*)k_host + l * kb, kb, cudaMemcpyHostToDevice, s), "k upload");
+        OXI_CUDA(cudaMemcpyAsync(h->stg_v[sb], (const char*)v_host + l * kb, kb, cudaMemcpyHostToDevice, s), "v upload");
+        if (gate_host)
+            OXI_CUDA(cudaMemcpyAsync(h->stg_gate[sb], (const char*)gate_host + l * gb, gb, cudaMemcpyHostToDevice, s), "gate upload");
+        OXI_CUDA(cudaMemcpyAsync(h->stg_kp[sb], k_ptrs_host + (size_t)l * batch, tb, cudaMemcpyHostToDevice, s), "k_ptrs upload");
+        OXI_CUDA(cudaMemcpyAsync(h->stg_vp[sb], v_ptrs_host + (size_t)l * batch, tb, cudaMemcpyHostToDevice, s), "v_ptrs upload");
+        OXI_CUDA(launch_append(s, h->stg_q[sb], h->stg_k[sb], h->stg_v[sb],
+                               (const char*)q_norm_w_dev + (size_t)l * HD * 2,
+                               (const char*)k_norm_w_dev + (size_t)l * HD * 2, cos_table_dev,
+                               sin_table_dev, h->stg_pos, h->stg_kp[sb], h->stg_vp[sb], batch, eps,
+                               h->dws.status),
+                 "append launch");
+        OXI_CUDA(launch_decode_attn(s, h->dws, h->stg_ctx[sb], h->stg_q[sb],
+                                    gate_host ? h->stg_gate[sb] : nullptr, h->stg_kp[sb],
+                                    h->stg_vp[sb], h->stg_len, batch, window),
+                 "decode_attn launch");
+        OXI_CUDA(cudaMemcpyAsync((char*)ctx_host + l * qb, h->stg_ctx[sb], qb, cudaMemcpyDeviceToHost, s), "ctx download");
+    }
+    return OXI_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,147 @@
+"""Operators of the pointer-table KV-cache path on torch CUDA tensors.
+
+Each function forwards to the C ABI export of the same name (include/oxi_kv.h)
+on torch's current stream; torch supplies device memory and streams only.
+Argument names and layouts are the reference's (batch_engine.rs launch sites):
+``q`` [B,16,128], ``k``/``v`` [B,4,128], ``gate`` [B,16], fp16; ``k_ptrs`` /
+``v_ptrs`` / ``conv_ptrs`` int64 device tables of per-sequence device pointers;
+``pos_ids`` / ``seq_lens`` int32 device tensors (bit patterns of u32).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+
+class OxiError(RuntimeError):
+    def __init__(self, code: int, where: str):
+        lib = _lib.load()
+        msg = lib.oxi_last_error_string().decode() or lib.oxi_status_string(code).decode()
+        super().__init__(f"{where}: status {code}: {msg}")
+        self.code = code
+
+
+def _check(code: int, where: str) -> None:
+    if code != 0:
+        raise OxiError(code, where)
+
+
+def _p(t):
+    if t is None:
+        return None
+    if isinstance(t, torch.Tensor):
+        if not t.is_contiguous():
+            raise ValueError("tensors passed to liboxi_kv must be contiguous")
+        return t.data_ptr()
+    return t
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class KvPath:
+    """One per device: owns the library workspace (oxi_create / oxi_destroy)."""
+
+    def __init__(self, device: int = 0, max_batch: int = 128, max_seq_len: int = 8192,
+                 max_prefill_rows: int = 512):
+        self.lib = _lib.load()
+        h = C.c_void_p()
+        _check(self.lib.oxi_create(C.byref(h), device, max_batch, max_seq_len, max_prefill_rows),
+               "oxi_create")
+        self.h = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.oxi_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    @property
+    def workspace_bytes(self) -> int:
+        return int(self.lib.oxi_workspace_bytes(self.h))
+
+    def device_status(self) -> int:
+        bits = C.c_uint32(0)
+        _check(self.lib.oxi_device_status(self.h, _stream(), C.byref(bits)), "oxi_device_status")
+        return bits.value
+
+    # ---- fused operators
+    def append(self, q_io, k_in, v_in, q_norm_w, k_norm_w, cos, sin, pos_ids, k_ptrs, v_ptrs,
+               eps: float = 1e-5, batch: int | None = None):
+        b = q_io.shape[0] if batch is None else batch
+        _check(self.lib.oxi_append(self.h, _stream(), _p(q_io), _p(k_in), _p(v_in), _p(q_norm_w),
+                                   _p(k_norm_w), _p(cos), _p(sin), _p(pos_ids), _p(k_ptrs),
+                                   _p(v_ptrs), b, eps), "oxi_append")
+
+    def decode_attn(self, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, window: int = 0,
+                    batch: int | None = None):
+        b = q.shape[0] if batch is None else batch
+        _check(self.lib.oxi_decode_attn(self.h, _stream(), _p(ctx_out), _p(q), _p(gate),
+                                        _p(k_ptrs), _p(v_ptrs), _p(seq_lens), b, window),
+               "oxi_decode_attn")
+
+    def append_decode(self, ctx_out, q_io, k_in, v_in, gate, q_norm_w, k_norm_w, cos, sin, pos_ids,
+                      seq_lens, k_ptrs, v_ptrs, window: int = 0, eps: float = 1e-5):
+        _check(self.lib.oxi_append_decode(self.h, _stream(), _p(ctx_out), _p(q_io), _p(k_in),
+                                          _p(v_in), _p(gate), _p(q_norm_w), _p(k_norm_w), _p(cos),
+                                          _p(sin), _p(pos_ids), _p(seq_lens), _p(k_ptrs),
+                                          _p(v_ptrs), q_io.shape[0], window, eps),
+               "oxi_append_decode")
+
+    def prefill_attn(self, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, window: int = 0,
+                     rows: int | None = None):
+        n = q.shape[0] if rows is None else rows
+        _check(self.lib.oxi_prefill_attn(self.h, _stream(), _p(ctx_out), _p(q), _p(gate),
+                                         _p(k_ptrs), _p(v_ptrs), _p(seq_lens), n, window),
+               "oxi_prefill_attn")
+
+    def conv_decode(self, y_out, conv_ptrs, bcx, conv_w, batch: int | None = None):
+        b = bcx.shape[0] if batch is None else batch
+        _check(self.lib.oxi_conv_decode(self.h, _stream(), _p(y_out), _p(conv_ptrs), _p(bcx),
+                                        _p(conv_w), b), "oxi_conv_decode")
+
+    def conv_prefill(self, y_out, carry_ptrs, origin, local_pos, bcx, conv_w,
+                     rows: int | None = None):
+        n = bcx.shape[0] if rows is None else rows
+        _check(self.lib.oxi_conv_prefill(self.h, _stream(), _p(y_out), _p(carry_ptrs), _p(origin),
+                                         _p(local_pos), _p(bcx), _p(conv_w), n),
+               "oxi_conv_prefill")
+
+    # ---- unfused operators (reference semantics, one per PTX entry point)
+    def qk_rmsnorm(self, x_io, weight, eps: float = 1e-5):
+        b, heads = x_io.shape[0], x_io.shape[1]
+        _check(self.lib.oxi_qk_rmsnorm(self.h, _stream(), _p(x_io), _p(weight), eps, heads, b),
+               "oxi_qk_rmsnorm")
+
+    def rope(self, x_io, cos, sin, pos_ids):
+        b, heads = x_io.shape[0], x_io.shape[1]
+        _check(self.lib.oxi_rope(self.h, _stream(), _p(x_io), _p(cos), _p(sin), _p(pos_ids), heads,
+                                 b), "oxi_rope")
+
+    def kv_copy(self, dst_ptrs, src, pos_ids):
+        _check(self.lib.oxi_kv_copy(self.h, _stream(), _p(dst_ptrs), _p(src), _p(pos_ids),
+                                    src.shape[0]), "oxi_kv_copy")
+
+    def sigmoid_gate(self, ctx_io, gate):
+        _check(self.lib.oxi_sigmoid_gate(self.h, _stream(), _p(ctx_io), _p(gate), ctx_io.shape[0]),
+               "oxi_sigmoid_gate")
+
+    # ---- host-buffer entry
+    def decode_step_host(self, ctx_host, q_host, k_host, v_host, gate_host, q_norm_w, k_norm_w,
+                         cos, sin, pos_ids_host, k_ptrs_host, v_ptrs_host, batch: int, layers: int,
+                         window: int = 0, eps: float = 1e-5):
+        _check(self.lib.oxi_decode_step_host(self.h, _stream(), _p(ctx_host), _p(q_host),
+                                             _p(k_host), _p(v_host), _p(gate_host), _p(q_norm_w),
+                                             _p(k_norm_w), _p(cos), _p(sin), _p(pos_ids_host),
+                                             _p(k_ptrs_host), _p(v_ptrs_host), batch, layers,
+                                             window, eps), "oxi_decode_step_host")
