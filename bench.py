@@ -1,0 +1,418 @@
+#!/usr/bin/env python
+"""Benchmark of the KV-cache hot path: one decode step of 8 attention layers
+(fused RMSNorm+RoPE+KV append, then gated GQA decode attention) at batch 128 per
+GPU and 4096 keys per sequence, fp16 KV, per-sequence pointer tables.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line (rank 0).  `value` is algorithmic HBM bytes of the whole
+job per second (GB/s) with every input resident in HBM; `e2e` is the same metric
+through the host-buffer C-ABI entry (q/k/v/gate/tables copied from pinned host
+memory and ctx copied back inside the timed region; the KV cache itself is state
+that lives on the device).  Under torchrun each rank owns its own 128 sequences
+(replicas, no data-path collective); torch.distributed is used only for the
+barrier and the max-over-ranks of the device time.
+
+--impl reference runs the reference's own kernels (its PTX, prebuilt into
+oracle/_ref/*.cubin) on ONE B200 with the engine's launch sequence: 9 launches
+per layer.  The reference has no CPU implementation of this path; the CPU figure
+reported in `cpu_baseline` is the scalar oracle port on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+NQ, NKV, HD = 16, 4, 128
+LAYERS, BATCH, CTX = 8, 128, 4096
+ROW_BYTES = NKV * HD * 2
+# algorithmic bytes per (layer, sequence): K and V rows read once per GQA group plus the
+# step's q/k/v/gate, norm weights, cos/sin rows, K/V row writes, ctx write, table entries
+PER_SEQ_FIXED = 4096 + 1024 + 1024 + 32 + 512 + 512 + 2048 + 4096 + 28
+ATTN_FIXED = 4096 + 32 + 4096 + 20  # decode-attention kernel alone: q, gate, ctx, tables
+
+
+def alg_bytes_layer(seq_lens) -> int:
+    return int(sum(2 * ROW_BYTES * int(s) + PER_SEQ_FIXED for s in seq_lens))
+
+
+def attn_bytes_layer(seq_lens) -> int:
+    return int(sum(2 * ROW_BYTES * int(s) + ATTN_FIXED for s in seq_lens))
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.stop_flag, self.rows = index, False, []
+
+    def run(self):
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                      "--format=csv,noheader,nounits"], capture_output=True,
+                                     text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([x.strip() for x in out.split(",")])
+            except Exception:
+                pass
+            time.sleep(0.05)
+
+    def summary(self):
+        self.stop_flag = True
+        self.join(timeout=6)
+        sm = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        reasons = set()
+        for r in self.rows:
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                "sw_power_cap"), r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except Exception:
+            return local_rank
+    return local_rank
+
+
+def measured_peak_gbs():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def build_workload(torch, seq_len: int, batch: int, layers: int, seed: int):
+    """Per layer: one K and one V slab [batch][seq_len][4][128] f16 ~N(0,1) (each sequence its
+    own contiguous region, addressed through pointer tables), the step's q/k/v/gate ~N(0,1),
+    norm weights ~1+N(0,0.02), RoPE theta 1e6 at position seq_len-1."""
+    import numpy as np
+    from oxide_infer_b200 import rotary_tables
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    dev = "cuda"
+    w = type("W", (), {})()
+    w.batch, w.layers, w.seq_len = batch, layers, seq_len
+    w.k_slab, w.v_slab, w.k_ptrs, w.v_ptrs = [], [], [], []
+    stride = seq_len * ROW_BYTES
+    for _ in range(layers):
+        k = torch.empty(batch, seq_len, NKV, HD, dtype=torch.float16, device=dev).normal_(generator=g)
+        v = torch.empty(batch, seq_len, NKV, HD, dtype=torch.float16, device=dev).normal_(generator=g)
+        w.k_slab.append(k)
+        w.v_slab.append(v)
+        w.k_ptrs.append(torch.tensor([k.data_ptr() + i * stride for i in range(batch)], dtype=torch.int64, device=dev))
+        w.v_ptrs.append(torch.tensor([v.data_ptr() + i * stride for i in range(batch)], dtype=torch.int64, device=dev))
+    rn = lambda *s: torch.empty(*s, dtype=torch.float16, device=dev).normal_(generator=g)
+    w.q0 = rn(layers, batch, NQ, HD)
+    w.k = rn(layers, batch, NKV, HD)
+    w.v = rn(layers, batch, NKV, HD)
+    w.gate = rn(layers, batch, NQ)
+    w.q = w.q0.clone()
+    w.qw = (1 + 0.02 * torch.randn(layers, HD, device=dev, generator=g)).half()
+    w.kw = (1 + 0.02 * torch.randn(layers, HD, device=dev, generator=g)).half()
+    cos, sin = rotary_tables(seq_len, 1e6, 0.5)
+    w.cos, w.sin = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
+    w.pos = torch.full((batch,), seq_len - 1, dtype=torch.int32, device=dev)
+    w.lens = torch.full((batch,), seq_len, dtype=torch.int32, device=dev)
+    w.ctx = torch.zeros(layers, batch, NQ, HD, dtype=torch.float16, device=dev)
+    w.seq_lens_host = np.full(batch, seq_len, np.int64)
+    return w
+
+
+def cpu_baseline(seq_len: int, batch: int, budget_s: float = 12.0):
+    """The oracle's decode sequence for ONE layer of the workload on the host cores."""
+    import numpy as np
+    from oracle import cpu as O
+    O.build()
+    rng = np.random.default_rng(0)
+    f16 = lambda *s: rng.standard_normal(s, dtype=np.float32).astype(np.float16)
+    b = batch
+    kc = [f16(seq_len, NKV, HD) for _ in range(b)]
+    vc = [f16(seq_len, NKV, HD) for _ in range(b)]
+    q, k, v, gate = f16(b, NQ, HD), f16(b, NKV, HD), f16(b, NKV, HD), f16(b, NQ)
+    w = np.ones(HD, np.float16)
+    cos, sin = O.rope_table(seq_len)
+    pos = np.full(b, seq_len - 1, np.uint32)
+    kp, vp = O.ptr_table(kc), O.ptr_table(vc)
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        O.decode_layer(q.copy(), k.copy(), v, gate, w, w, cos, sin, pos, pos + 1, kp, vp)
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt > budget_s or reps >= 20:
+            break
+    gbs = alg_bytes_layer([seq_len] * b) * reps / dt / 1e9
+    return {"value": round(gbs, 3), "unit": "GB/s", "cores": O.num_threads(), "kind": "port",
+            "sample": f"1 of {LAYERS} layers (append + split/combine + gate), B={b}, ctx={seq_len}, "
+                      f"{reps} reps in {dt:.1f} s"}
+
+
+def run_ours(args, torch, rank, world, local_rank):
+    from oxide_infer_b200 import KvPath
+    kv = KvPath(local_rank, max_batch=BATCH, max_seq_len=CTX, max_prefill_rows=16)
+    w = build_workload(torch, CTX, BATCH, LAYERS, seed=1234 + rank)
+    stream = torch.cuda.current_stream()
+
+    def step(events=None, restore_q=False):
+        for l in range(LAYERS):
+            if restore_q:  # q is normalised in place; the timed steps simply re-normalise it
+                w.q[l].copy_(w.q0[l])
+            kv.append(w.q[l], w.k[l], w.v[l], w.qw[l], w.kw[l], w.cos, w.sin, w.pos, w.k_ptrs[l], w.v_ptrs[l])
+            if events is not None:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+            kv.decode_attn(w.ctx[l], w.q[l], w.gate[l], w.k_ptrs[l], w.v_ptrs[l], w.lens, 0)
+            if events is not None:
+                e1.record(stream)
+                events.append((e0, e1))
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(gpu_index(local_rank))
+    sampler.start()
+    ev, t0, t1 = [], torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record(stream)
+    for _ in range(args.steps):
+        step(ev)
+    t1.record(stream)
+    barrier()
+    ms = t0.elapsed_time(t1)
+    attn_ms = sum(a.elapsed_time(b) for a, b in ev) / len(ev)
+    clocks = sampler.summary()
+
+    if args.no_e2e:
+        if rank == 0:
+            attn_gbs = attn_bytes_layer(w.seq_lens_host) / (attn_ms * 1e-3) / 1e9
+            return {"profiling_case": True, "layers": LAYERS, "batch": BATCH, "ctx": CTX,
+                    "ms_per_step": round(ms / args.steps, 4), "decode_attn_us": round(attn_ms * 1e3, 2),
+                    "decode_attn_gbs": round(attn_gbs, 1), "clocks": clocks}
+        return None
+
+    # ---- end to end through the host-buffer entry
+    pin = lambda t: t.cpu().pin_memory()
+    hq, hk, hv, hg = pin(w.q0), pin(w.k), pin(w.v), pin(w.gate)
+    hctx = torch.zeros(LAYERS, BATCH, NQ, HD, dtype=torch.float16).pin_memory()
+    hpos = pin(w.pos)
+    hkp, hvp = pin(torch.stack(w.k_ptrs)), pin(torch.stack(w.v_ptrs))
+    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hg, hkp, hvp)) + 2 * hpos.numel() * 4
+    d2h = hctx.numel() * 2
+
+    def step_host():
+        kv.decode_step_host(hctx, hq, hk, hv, hg, w.qw, w.kw, w.cos, w.sin, hpos, hkp, hvp, BATCH, LAYERS)
+
+    for _ in range(max(3, args.warmup)):
+        step_host()
+    barrier()
+    t0.record(stream)
+    for _ in range(args.steps):
+        step_host()
+    t1.record(stream)
+    barrier()
+    ms_e2e = t0.elapsed_time(t1)
+    step(restore_q=True)  # untimed: same inputs as the host-buffer path, for the equality check
+    status = kv.device_status()
+    ctx_ok = bool(torch.isfinite(w.ctx.float()).all().item()) and bool(torch.isfinite(hctx.float()).all().item())
+    same = bool((hctx.cuda() == w.ctx).all().item())
+
+    times = torch.tensor([ms, ms_e2e, attn_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
+    ms, ms_e2e, attn_ms = (float(x) for x in times.tolist())
+    if rank != 0:
+        return None
+
+    step_bytes = LAYERS * alg_bytes_layer(w.seq_lens_host) * world
+    peak, peak_kind = measured_peak_gbs()
+    attn_gbs = attn_bytes_layer(w.seq_lens_host) / (attn_ms * 1e-3) / 1e9
+    line = {
+        "metric": "gqa_decode_step_hbm_gbs", "value": round(step_bytes * args.steps / (ms * 1e-3) / 1e9, 1),
+        "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms / args.steps, 4), "us_per_layer": round(ms / args.steps / LAYERS * 1e3, 2),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic",
+        "config": {"workload": f"decode_step_{LAYERS}_attention_layers_B{BATCH}_per_gpu_ctx{CTX}",
+                   "layers": LAYERS, "batch_per_gpu": BATCH, "seq_len": CTX, "heads": "16q/4kv x128",
+                   "kv_bytes_per_gpu": LAYERS * BATCH * CTX * 2 * ROW_BYTES,
+                   "l2": "inputs larger than L2 (1.07 GB of KV per layer, 8 distinct layers)",
+                   "parallelism": f"replicas x{world}, sequences partitioned, no collective"},
+        "e2e": {"value": round(step_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
+                "ms_per_step": round(ms_e2e / args.steps, 4), "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(d2h)},
+        "gpu_launches": 3 * LAYERS * args.steps,  # append, decode_attn, decode_merge per layer
+        "roofline": {"kernel": "decode_attn_kernel", "bound": "hbm", "achieved": round(attn_gbs, 1),
+                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(attn_gbs / peak, 4),
+                     "frac_of_8TBs_nominal": round(attn_gbs / 8000.0, 4), "us_per_launch": round(attn_ms * 1e3, 2),
+                     "traffic": TRAFFIC_PER_LAUNCH},
+        "clocks": clocks, "device_status": status, "finite": ctx_ok, "e2e_equals_device_path": same,
+    }
+    if world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline(CTX, BATCH)
+    return line
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_attn_kernel launch at the bench
+# workload, from the ncu capture summarised in profiles/ (None until captured)
+TRAFFIC_PER_LAUNCH = None
+
+
+def run_reference(args, torch, rank, world, local_rank):
+    """The reference's kernels on one B200 (rank 0 only), engine launch order, 9 per layer."""
+    if rank != 0:
+        return None
+    from oracle import refptx
+    if not refptx.available():
+        cb = cpu_baseline(CTX, BATCH)
+        return {"impl": "reference", "metric": "gqa_decode_step_hbm_gbs", "value": cb["value"], "unit": "GB/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
+                "scaling": "weak", "dtype": "f16", "data": "synthetic",
+                "config": {"workload": "decode_step_8_attention_layers_B128_per_gpu_ctx4096",
+                           "note": "reference cubins absent: CPU oracle port timed instead"},
+                "cpu_baseline": cb,
+                "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    ref = refptx.RefPtx()
+    w = build_workload(torch, CTX, BATCH, LAYERS, seed=1234)
+    stream = torch.cuda.current_stream()
+    nch = ref.nchunks_for(CTX, 0)
+    acc = torch.empty(BATCH * nch * NQ * HD, dtype=torch.float32, device="cuda")
+    stats = torch.empty(BATCH * nch * NQ * 2, dtype=torch.float32, device="cuda")
+    kbuf = w.k.clone()
+
+    def step():
+        for l in range(LAYERS):  # q and k are normalised in place; the timed steps re-normalise them
+            ref.append(w.q[l], kbuf[l], w.v[l], w.qw[l], w.kw[l], w.cos, w.sin, w.pos, w.k_ptrs[l], w.v_ptrs[l], BATCH)
+            ref.decode_attention(w.ctx[l], w.q[l], w.gate[l], w.k_ptrs[l], w.v_ptrs[l], w.lens, BATCH, 0, CTX, acc, stats)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(gpu_index(local_rank))
+    sampler.start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record(stream)
+    for _ in range(args.steps):
+        step()
+    t1.record(stream)
+    torch.cuda.synchronize()
+    ms = t0.elapsed_time(t1)
+    clocks = sampler.summary()
+
+    # end to end with the same host traffic as our arm: upload q/k/v/gate + tables, download ctx
+    pin = lambda t: t.cpu().pin_memory()
+    hq, hk, hv, hg = pin(w.q0), pin(w.k), pin(w.v), pin(w.gate)
+    hkp, hvp = pin(torch.stack(w.k_ptrs)), pin(torch.stack(w.v_ptrs))
+    hctx = torch.zeros(LAYERS, BATCH, NQ, HD, dtype=torch.float16).pin_memory()
+    dkp, dvp = torch.stack(w.k_ptrs).clone(), torch.stack(w.v_ptrs).clone()
+
+    def step_host():
+        for l in range(LAYERS):
+            w.q[l].copy_(hq[l], non_blocking=True)
+            kbuf[l].copy_(hk[l], non_blocking=True)
+            w.v[l].copy_(hv[l], non_blocking=True)
+            w.gate[l].copy_(hg[l], non_blocking=True)
+            dkp[l].copy_(hkp[l], non_blocking=True)
+            dvp[l].copy_(hvp[l], non_blocking=True)
+            ref.append(w.q[l], kbuf[l], w.v[l], w.qw[l], w.kw[l], w.cos, w.sin, w.pos, dkp[l], dvp[l], BATCH)
+            ref.decode_attention(w.ctx[l], w.q[l], w.gate[l], dkp[l], dvp[l], w.lens, BATCH, 0, CTX, acc, stats)
+            hctx[l].copy_(w.ctx[l], non_blocking=True)
+
+    for _ in range(3):
+        step_host()
+    torch.cuda.synchronize()
+    t0.record(stream)
+    for _ in range(args.steps):
+        step_host()
+    t1.record(stream)
+    torch.cuda.synchronize()
+    ms_e2e = t0.elapsed_time(t1)
+    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hg, hkp, hvp))
+    step_bytes = LAYERS * alg_bytes_layer(w.seq_lens_host)
+    line = {
+        "impl": "reference", "metric": "gqa_decode_step_hbm_gbs",
+        "value": round(step_bytes * args.steps / (ms * 1e-3) / 1e9, 1), "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
+        "us_per_layer": round(ms / args.steps / LAYERS * 1e3, 2), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "decode_step_8_attention_layers_B128_per_gpu_ctx4096", "layers": LAYERS,
+                   "batch_per_gpu": BATCH, "seq_len": CTX,
+                   "what": "reference PTX kernels (sm_80 text assembled for sm_100a) on one B200, "
+                           "engine launch sequence: 2 norm, 2 rope, 2 copy, split4, combine, gate",
+                   "parallelism": "single GPU (the reference has no multi-GPU path)"},
+        "e2e": {"value": round(step_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
+                "ms_per_step": round(ms_e2e / args.steps, 4), "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(hctx.numel() * 2)},
+        "gpu_launches": 9 * LAYERS * args.steps, "clocks": clocks,
+    }
+    if not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline(CTX, BATCH)
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="override for small profiling cases")
+    ap.add_argument("--batch", type=int, default=BATCH)
+    ap.add_argument("--ctx", type=int, default=CTX)
+    args = ap.parse_args()
+    globals().update(LAYERS=args.layers, BATCH=args.batch, CTX=args.ctx)
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference" and rank != 0:
+        return 0
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1 and args.impl == "ours":
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        line = (run_ours if args.impl == "ours" else run_reference)(args, torch, rank, world, local_rank)
+        if line is not None:
+            print(json.dumps(line), flush=True)
+    finally:
+        if world > 1 and args.impl == "ours" and torch.distributed.is_initialized():
+            torch.distributed.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -63,9 +63,9 @@ const char* oxi_status_string(int32_t status);
 /* Text of the last error raised on the calling thread ("" if none). */
 const char* oxi_last_error_string(void);
 
-/* Creates the per-device workspace (split-KV partials, arrival counters, conv
- * staging, host-entry staging).  Replaces the scratch half of
- * BatchEngine::new (batch_engine.rs:320-364).  max_batch <= 4096. */
+/* Creates the per-device workspace (split-KV partials, conv staging,
+ * host-entry staging).  Replaces the scratch half of BatchEngine::new
+ * (batch_engine.rs:320-364).  max_batch <= 2048. */
 int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_t max_seq_len,
                    uint32_t max_prefill_rows);
 int32_t oxi_destroy(oxi_handle* h);
@@ -92,9 +92,9 @@ int32_t oxi_append(oxi_handle* h, void* stream, void* q_io, const void* k_in, co
                    const void* sin_table, const uint32_t* pos_ids, const uint64_t* k_ptrs,
                    const uint64_t* v_ptrs, uint32_t batch, float eps);
 
-/* Batched GQA decode attention with the per-head sigmoid output gate in ONE
- * launch (split-KV flash-decode; the CTA finishing a row's last key range
- * merges the partials and applies the gate).
+/* Batched GQA decode attention with the per-head sigmoid output gate:
+ * split-KV flash-decode streaming kernel + a small merge kernel that also
+ * applies the gate (rows covered by one key range finish in the first kernel).
  * Replaces batched_gqa_attention_split4_fp16 + batched_gqa_attn_combine_fp16
  * (or batched_gqa_attention_online_fp16) + batched_sigmoid_gate_fp16
  * (batched_attn.rs:2665-3035, 1597-1717, 1194-1370, 583-655; launched at

@@ -17,36 +17,67 @@
 // warps, one per KV head, each serve the 4 query heads of their group from
 // that single K/V read: S = Q K^T and O += P V run on tensor cores
 // (mma.sync.m16n8k16, f16 in, f32 accumulate; the 4 heads are rows 0..3 of the
-// M=16 tile), the online-softmax row reductions are quad shuffles.  Rows are
-// stored with a 1040-byte pitch so the 8 row addresses of every ldmatrix phase
-// fall in distinct banks.
+// M=16 tile), the online-softmax row reductions are quad shuffles.  K/V rows
+// are copied in groups of 4 consecutive tokens (4 KB per bulk copy: large
+// copies keep the TMA issue rate off the critical path) and each group is
+// padded by 16 bytes in shared memory; an 8x8 ldmatrix tile takes its 8 rows
+// from 8 different groups (keys j, j+4, ..., j+28), so the 8 row addresses of
+// every ldmatrix phase fall in distinct banks.  The key order inside a stage is
+// therefore a permutation, applied consistently to the P columns and V rows.
 //
-// A row covered by one item is finished in registers.  Otherwise each consumer
-// warp writes its (max, sum, acc[128]) partials, bumps an arrival counter for
-// (row, kv head), and the warp that arrives last merges all partials of that
-// (row, kv head) in key-range order (deterministic), applies 1/sum, rounds to
-// f16, applies the gate exactly as the reference's gate kernel does on the f16
-// context, and resets the counter.  Nothing spins on another CTA.
+// The step's q row (4 KB: all 16 heads) rides with the first stage of each item
+// as one more bulk copy, and seq_lens are staged in shared memory, so a consumer
+// warp issues no global load of its own while streaming: under a saturated
+// memory pipe every dependent global access costs microseconds of queueing.
+//
+// A row covered by one item is finished in registers (1/sum, f16, gate).
+// Otherwise each consumer warp stores its (max, sum, acc[128]) partials and
+// moves on; a second, tiny kernel merges the partials of every multi-item row
+// in key-range order (deterministic), applies 1/sum, rounds to f16 and applies
+// the gate exactly as the reference's gate kernel does on the f16 context.
+// Nothing spins on another CTA and no atomics or fences sit on the stream.
 #include "common.cuh"
 #include "kernels.h"
+#ifdef OXI_EXP_TIMING
+#include <cstdio>
+#endif
 
 namespace oxi {
 
+#ifndef OXI_DEC_NSTAGE
+#define OXI_DEC_NSTAGE 3
+#endif
+#ifndef OXI_DEC_CTAS
+#define OXI_DEC_CTAS 1
+#endif
+#ifndef OXI_DEC_CHUNK
+#define OXI_DEC_CHUNK 256
+#endif
+#ifndef OXI_DEC_MAXROWS
+#define OXI_DEC_MAXROWS 2048
+#endif
+
 namespace dec {
 constexpr int KS = 32;                        // keys per pipeline stage
-constexpr int NSTAGE = 3;                     // ring depth
-constexpr int PITCH = KV_ROW_BYTES + 16;      // 1040 B per key row in shared memory
-constexpr int STAGE_BYTES = 2 * KS * PITCH;   // K rows then V rows
-constexpr int CHUNK = 256;                    // keys per work item
+constexpr int NSTAGE = OXI_DEC_NSTAGE;        // ring depth
+constexpr int GK = 4;                         // keys per bulk copy (one group)
+constexpr int GROUP_BYTES = GK * KV_ROW_BYTES;  // 4096 B copied at once
+constexpr int GPITCH = GROUP_BYTES + 16;      // group pitch in shared memory
+constexpr int NGROUP = KS / GK;               // 8 groups per stage = the 8 rows of an ldmatrix tile
+constexpr int HALF_BYTES = NGROUP * GPITCH;   // K part (then V part) of a stage
+constexpr int Q_BYTES = NQ * HD * 2;           // the row's q (all heads), carried by an item's first stage
+constexpr int STAGE_BYTES = 2 * HALF_BYTES + Q_BYTES;
+constexpr int CHUNK = OXI_DEC_CHUNK;          // keys per work item
 constexpr int N_CONSUMER_WARPS = NKV;         // one per KV head
 constexpr int THREADS = (N_CONSUMER_WARPS + 1) * 32;
-constexpr int MAX_ROWS = 4096;                // rows per launch (prefix array in shared memory)
-constexpr int CTAS_PER_SM = 1;
+constexpr int MAX_ROWS = OXI_DEC_MAXROWS;     // rows per launch (prefix array in shared memory)
+constexpr int CTAS_PER_SM = OXI_DEC_CTAS;
 constexpr float QK_SCALE_LOG2 = ATTN_SCALE * LOG2E;
 constexpr size_t SMEM_BYTES = (size_t)NSTAGE * STAGE_BYTES + 2 * NSTAGE * 8 + 16 +
-                              (MAX_ROWS + 1) * sizeof(uint32_t);
+                              (2 * MAX_ROWS + 1) * sizeof(uint32_t);
 static_assert(SMEM_BYTES <= 227 * 1024, "decode kernel shared memory");
 static_assert(CHUNK % KS == 0, "a work item is a whole number of stages");
+static_assert(NGROUP == 8, "ldmatrix tiles take one row from each of 8 groups");
 }  // namespace dec
 
 struct DecodeParams {
@@ -58,7 +89,6 @@ struct DecodeParams {
     const uint32_t* seq_lens;
     float* partial_acc;
     float* partial_stats;
-    uint32_t* counters;
     uint32_t* status;
     uint32_t batch;
     uint32_t window;
@@ -90,6 +120,7 @@ decode_attn_kernel(const DecodeParams p) {
     uint64_t* empty_bar = full_bar + NSTAGE;
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(empty_bar + NSTAGE);
     uint32_t* prefix = const_cast<uint32_t*>(reinterpret_cast<volatile uint32_t*>(abort_flag) + 4);
+    uint32_t* s_len = prefix + MAX_ROWS + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -114,6 +145,7 @@ decode_attn_kernel(const DecodeParams p) {
             n = row_chunks(slen, p.window);
         }
         prefix[b + 1] = n;
+        s_len[b] = slen;
     }
     __syncthreads();
     if (warp == 0) {
@@ -139,14 +171,27 @@ decode_attn_kernel(const DecodeParams p) {
         const uint64_t policy = l2_policy_evict_first();
         uint32_t fill = 0;
         bool ok = true;
+        // metadata of the item about to be streamed; the next item's is fetched one item ahead
+        uint32_t nb = 0, nslen = 0, nc = 0;
+        uint64_t nkp = 0, nvp = 0;
+        auto fetch = [&](uint32_t item) {
+            if (item < total_items) {
+                nb = find_row(prefix, p.batch, item);
+                nc = item - prefix[nb];
+                nslen = s_len[nb];
+                nkp = p.k_ptrs[nb];
+                nvp = p.v_ptrs[nb];
+            }
+        };
+        fetch(blockIdx.x);
         for (uint32_t item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-            const uint32_t b = find_row(prefix, p.batch, item);
-            const uint32_t c = item - prefix[b];
-            const uint32_t slen = p.seq_lens[b];
+            const uint32_t slen = nslen, c = nc;
+            const char* qp = reinterpret_cast<const char*>(p.q) + (size_t)nb * Q_BYTES;
+            const char* kp = reinterpret_cast<const char*>(nkp);
+            const char* vp = reinterpret_cast<const char*>(nvp);
+            fetch(item + gridDim.x);
             const uint32_t t0 = window_start(slen, p.window) + c * CHUNK;
             const uint32_t t1 = min(t0 + (uint32_t)CHUNK, slen);
-            const char* kp = reinterpret_cast<const char*>(p.k_ptrs[b]);
-            const char* vp = reinterpret_cast<const char*>(p.v_ptrs[b]);
             for (uint32_t t = t0; t < t1; t += KS, ++fill) {
                 const uint32_t slot = fill % NSTAGE;
                 if (fill >= NSTAGE) {
@@ -156,15 +201,22 @@ decode_attn_kernel(const DecodeParams p) {
                     }
                 }
                 const uint32_t nvalid = min((uint32_t)KS, t1 - t);
-                if (lane == 0) mbar_arrive_expect_tx(&full_bar[slot], nvalid * 2u * KV_ROW_BYTES);
+                const bool first = (t == t0);
+                if (lane == 0)
+                    mbar_arrive_expect_tx(&full_bar[slot], nvalid * 2u * KV_ROW_BYTES + (first ? Q_BYTES : 0));
                 __syncwarp();
                 const uint32_t sbase = smem_u32(stages + (size_t)slot * STAGE_BYTES);
-                for (uint32_t i = lane; i < 2u * nvalid; i += 32) {
-                    const bool is_v = i >= nvalid;
-                    const uint32_t key = is_v ? i - nvalid : i;
-                    const char* src = (is_v ? vp : kp) + (size_t)(t + key) * KV_ROW_BYTES;
-                    const uint32_t dst = sbase + (is_v ? KS * PITCH : 0) + key * PITCH;
-                    bulk_g2s_hint(dst, src, KV_ROW_BYTES, &full_bar[slot], policy);
+                if (first && lane == 2 * NGROUP) bulk_g2s(sbase + 2 * HALF_BYTES, qp, Q_BYTES, &full_bar[slot]);
+                // lanes 0..7 copy the K groups, lanes 8..15 the V groups (up to 4 KB each)
+                if (lane < 2 * NGROUP) {
+                    const uint32_t grp = lane & (NGROUP - 1);
+                    const bool is_v = lane >= NGROUP;
+                    if (grp * GK < nvalid) {
+                        const uint32_t nk = min((uint32_t)GK, nvalid - grp * GK);
+                        const char* src = (is_v ? vp : kp) + (size_t)(t + grp * GK) * KV_ROW_BYTES;
+                        bulk_g2s_hint(sbase + (is_v ? HALF_BYTES : 0) + grp * GPITCH, src,
+                                      nk * KV_ROW_BYTES, &full_bar[slot], policy);
+                    }
                 }
             }
         }
@@ -184,57 +236,66 @@ decode_attn_kernel(const DecodeParams p) {
     const int t4 = lane & 3;         // fragment column pair
     uint32_t take = 0;               // stages consumed so far (mirrors the producer's `fill`)
     bool ok = true;
+#ifdef OXI_EXP_TIMING
+    long long tw = 0, tc = 0, te = 0, tq = 0, t_mark = clock64(), t_start = t_mark; int nitems = 0;
+    const uint64_t g_start = global_timer_ns();
+#define TMARK(acc) do { long long now__ = clock64(); acc += now__ - t_mark; t_mark = now__; } while (0)
+#else
+#define TMARK(acc) do {} while (0)
+#endif
 
     for (uint32_t item = blockIdx.x; item < total_items; item += gridDim.x) {
         const uint32_t b = find_row(prefix, p.batch, item);
         const uint32_t c = item - prefix[b];
         const uint32_t nchunks = prefix[b + 1] - prefix[b];
-        const uint32_t slen = p.seq_lens[b];
+        const uint32_t slen = s_len[b];
         const uint32_t t0 = window_start(slen, p.window) + c * CHUNK;
         const uint32_t t1 = min(t0 + (uint32_t)CHUNK, slen);
-
-        // Q fragments (A operand, rows 0..3 = the group's heads, rows 4..15 zero)
-        uint32_t qa[8][2];
-        {
-            const uint16_t* qrow = p.q + ((size_t)b * NQ + kvh * 4 + (g & 3)) * HD;
-#pragma unroll
-            for (int ks = 0; ks < 8; ks++) {
-                uint32_t lo = 0, hi = 0;
-                if (g < 4) {
-                    lo = *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * t4);
-                    hi = *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 8 + 2 * t4);
-                }
-                qa[ks][0] = lo;
-                qa[ks][1] = hi;
-            }
-        }
+        uint32_t qa[8][2];  // Q fragments (A operand, rows 0..3 = the group's heads, rows 4..15 zero)
         float o[16][4];
 #pragma unroll
         for (int j = 0; j < 16; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
         float m_run = -1.0e30f, l_run = 0.0f;
+        TMARK(tq);
 
         for (uint32_t t = t0; t < t1; t += KS, ++take) {
             const uint32_t slot = take % NSTAGE;
             if (ok) ok = mbar_wait_bounded(&full_bar[slot], (take / NSTAGE) & 1u, abort_flag);
+            TMARK(tw);
+            if (t == t0) {  // the item's first stage carries the row's q
+                const unsigned char* qrow = stages + (size_t)slot * STAGE_BYTES + 2 * HALF_BYTES +
+                                            (kvh * 4 + (g & 3)) * (HD * 2);
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++) {
+                    uint32_t lo = 0, hi = 0;
+                    if (g < 4) {
+                        lo = *reinterpret_cast<const uint32_t*>(qrow + (16 * ks + 2 * t4) * 2);
+                        hi = *reinterpret_cast<const uint32_t*>(qrow + (16 * ks + 8 + 2 * t4) * 2);
+                    }
+                    qa[ks][0] = lo;
+                    qa[ks][1] = hi;
+                }
+            }
             const uint32_t nvalid = min((uint32_t)KS, t1 - t);
             unsigned char* kst = stages + (size_t)slot * STAGE_BYTES + kvh * (HD * 2);
-            unsigned char* vst = kst + KS * PITCH;
+            unsigned char* vst = kst + HALF_BYTES;
             if (nvalid < KS) {
                 // tail stage: rows past the range keep stale bytes; zero this head's V slice there
                 // so that 0 * stale can never produce NaN.
                 for (uint32_t i = lane; i < (KS - nvalid) * 16u; i += 32) {
                     const uint32_t row = nvalid + (i >> 4);
-                    *reinterpret_cast<uint4*>(vst + row * PITCH + (i & 15u) * 16u) = make_uint4(0, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(vst + (row >> 2) * GPITCH + (row & 3u) * KV_ROW_BYTES +
+                                              (i & 15u) * 16u) = make_uint4(0, 0, 0, 0);
                 }
                 __syncwarp();
             }
 
-            // ---- S = Q K^T for 32 keys: 4 n-blocks of 8 keys
+            // ---- S = Q K^T for 32 keys: n-block nb holds keys nb + 4*n (n = 0..7, one per group)
             float s[4][4];
 #pragma unroll
             for (int nb = 0; nb < 4; nb++) {
                 s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
-                const uint32_t kaddr = smem_u32(kst) + (nb * 8 + (lane & 7)) * PITCH + (lane >> 3) * 16;
+                const uint32_t kaddr = smem_u32(kst) + (lane & 7) * GPITCH + nb * KV_ROW_BYTES + (lane >> 3) * 16;
 #pragma unroll
                 for (int kk = 0; kk < 4; kk++) {
                     uint32_t r0, r1, r2, r3;
@@ -243,13 +304,13 @@ decode_attn_kernel(const DecodeParams p) {
                     mma_16816(s[nb], qa[2 * kk + 1][0], 0u, qa[2 * kk + 1][1], 0u, r2, r3);
                 }
             }
-            // ---- online softmax on row g (keys nb*8 + 2*t4 + {0,1})
+            // ---- online softmax on row g (this thread: keys nb + 4*(2*t4 + {0,1}))
             float mx = -1.0e30f;
 #pragma unroll
             for (int nb = 0; nb < 4; nb++) {
 #pragma unroll
                 for (int j = 0; j < 2; j++) {
-                    const uint32_t key = nb * 8 + 2 * t4 + j;
+                    const uint32_t key = nb + 4 * (2 * t4 + j);
                     float v = s[nb][j] * QK_SCALE_LOG2;
                     v = (key < nvalid) ? v : -INFINITY;
                     s[nb][j] = v;
@@ -274,12 +335,12 @@ decode_attn_kernel(const DecodeParams p) {
 #pragma unroll
             for (int j = 0; j < 16; j++) { o[j][0] *= corr; o[j][1] *= corr; }
 
-            // ---- O += P V : 2 k-steps of 16 keys, 16 n-blocks of 8 dims
+            // ---- O += P V : 2 k-steps of 16 keys (the keys of n-blocks 2*k2 and 2*k2+1, same
+            // permutation as P's columns), 16 n-blocks of 8 dims
 #pragma unroll
             for (int k2 = 0; k2 < 2; k2++) {
-                const uint32_t vaddr = smem_u32(vst) +
-                                       (k2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * PITCH +
-                                       (lane >> 4) * 16;
+                const uint32_t vaddr = smem_u32(vst) + (lane & 7) * GPITCH +
+                                       (2 * k2 + ((lane >> 3) & 1)) * KV_ROW_BYTES + (lane >> 4) * 16;
 #pragma unroll
                 for (int jn = 0; jn < 8; jn++) {
                     uint32_t r0, r1, r2, r3;
@@ -292,7 +353,11 @@ decode_attn_kernel(const DecodeParams p) {
             if (nvalid < KS) fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty_bar[slot]);
+            TMARK(tc);
         }
+#ifdef OXI_EXP_TIMING
+        nitems++;
+#endif
 
         // ---- finish the item: row sums across the quad
         l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
@@ -315,10 +380,11 @@ decode_attn_kernel(const DecodeParams p) {
                     *reinterpret_cast<uint32_t*>(out + 8 * j + 2 * t4) = (uint32_t)h0 | ((uint32_t)h1 << 16);
                 }
             }
+            TMARK(te);
             continue;
         }
 
-        // ---- several items cover this row: publish partials, last arrival merges
+        // ---- several items cover this row: store the partials for the merge kernel
         const size_t pbase = ((size_t)b * p.max_chunks + c) * NQ;
         if (g < 4) {
             float* pacc = p.partial_acc + (pbase + head) * HD;
@@ -329,51 +395,64 @@ decode_attn_kernel(const DecodeParams p) {
                 __stcg(reinterpret_cast<float2*>(p.partial_stats + (pbase + head) * 2),
                        make_float2(m_run, l_run));
         }
-        __threadfence();
-        __syncwarp();
-        uint32_t arrived = 0;
-        if (lane == 0) arrived = atomicAdd(&p.counters[b * NKV + kvh], 1u);
-        arrived = __shfl_sync(0xffffffffu, arrived, 0);
-        if (arrived != nchunks - 1) continue;
-
-        __threadfence();
-        // merge in key-range order; lane owns dims 4*lane .. 4*lane+3 of each head
-        for (int hh = 0; hh < 4; hh++) {
-            const uint32_t hd = kvh * 4 + hh;
-            float m = -1.0e30f, l = 0.0f;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (uint32_t cc = 0; cc < nchunks; cc++) {
-                const size_t pi = ((size_t)b * p.max_chunks + cc) * NQ + hd;
-                const float2 st = __ldcg(reinterpret_cast<const float2*>(p.partial_stats + pi * 2));
-                const float4 pv = __ldcg(reinterpret_cast<const float4*>(p.partial_acc + pi * HD) + lane);
-                const float m_new = fmaxf(m, st.x);
-                const float c_old = ex2_approx_ftz(m - m_new);
-                const float c_new = ex2_approx_ftz(st.x - m_new);
-                l = l * c_old + c_new * st.y;
-                acc.x = acc.x * c_old + c_new * pv.x;
-                acc.y = acc.y * c_old + c_new * pv.y;
-                acc.z = acc.z * c_old + c_new * pv.z;
-                acc.w = acc.w * c_old + c_new * pv.w;
-                m = m_new;
-            }
-            const float inv = rcp_approx_ftz(l);
-            uint16_t h[4] = {f2h(__fmul_rn(acc.x, inv)), f2h(__fmul_rn(acc.y, inv)),
-                             f2h(__fmul_rn(acc.z, inv)), f2h(__fmul_rn(acc.w, inv))};
-            if (p.gate) {
-                const float sig = sigmoid_ref(h2f(p.gate[(size_t)b * NQ + hd]));
-#pragma unroll
-                for (int i = 0; i < 4; i++) h[i] = f2h(__fmul_rn(h2f(h[i]), sig));
-            }
-            uint2 packed = make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16),
-                                      (uint32_t)h[2] | ((uint32_t)h[3] << 16));
-            *reinterpret_cast<uint2*>(p.ctx_out + ((size_t)b * NQ + hd) * HD + 4 * lane) = packed;
-        }
-        if (lane == 0) p.counters[b * NKV + kvh] = 0u;  // ready for the next launch
+        TMARK(te);
     }
+#ifdef OXI_EXP_TIMING
+    if (lane == 0 && warp == 0 && (blockIdx.x == 0 || blockIdx.x == 50 || blockIdx.x == 147))
+        printf("cta %d items %d total %lld cyc %llu ns: wait %lld compute %lld epilogue %lld qload %lld\n", blockIdx.x, nitems,
+               clock64() - t_start, (unsigned long long)(global_timer_ns() - g_start), tw, tc, te, tq);
+#endif
     if (!ok && lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
 }
 
+// Merges the partials of every row that was covered by more than one item.
+// grid = B*4 CTAs of 4 warps: warp = one query head of one row; lane owns dims
+// 4*lane .. 4*lane+3.  All loads are independent of the arithmetic, which runs
+// in key-range order, so the result does not depend on scheduling.
+__global__ void __launch_bounds__(128)
+decode_merge_kernel(const DecodeParams p) {
+    const uint32_t b = blockIdx.x >> 2;
+    const int lane = threadIdx.x & 31;
+    const uint32_t hd = (blockIdx.x & 3u) * 4 + (threadIdx.x >> 5);
+    const uint32_t slen = p.seq_lens[b];
+    if (slen == 0u || slen > p.max_seq_len) return;
+    if (((p.k_ptrs[b] | p.v_ptrs[b]) & 15ull) != 0ull) return;
+    const uint32_t nchunks = row_chunks(slen, p.window);
+    if (nchunks <= 1) return;
+    const float* stats = p.partial_stats + (((size_t)b * p.max_chunks) * NQ + hd) * 2;
+    const float* accs = p.partial_acc + (((size_t)b * p.max_chunks) * NQ + hd) * HD;
+    float m = -1.0e30f;
+    for (uint32_t cc = lane; cc < nchunks; cc += 32) m = fmaxf(m, __ldcg(stats + (size_t)cc * NQ * 2));
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    float l = 0.0f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (uint32_t cc = 0; cc < nchunks; cc++) {
+        const float2 st = __ldcg(reinterpret_cast<const float2*>(stats + (size_t)cc * NQ * 2));
+        const float4 pv = __ldcg(reinterpret_cast<const float4*>(accs + (size_t)cc * NQ * HD) + lane);
+        const float wgt = ex2_approx_ftz(st.x - m);
+        l = fmaf(wgt, st.y, l);
+        acc.x = fmaf(wgt, pv.x, acc.x);
+        acc.y = fmaf(wgt, pv.y, acc.y);
+        acc.z = fmaf(wgt, pv.z, acc.z);
+        acc.w = fmaf(wgt, pv.w, acc.w);
+    }
+    const float inv = rcp_approx_ftz(l);
+    uint16_t h[4] = {f2h(__fmul_rn(acc.x, inv)), f2h(__fmul_rn(acc.y, inv)),
+                     f2h(__fmul_rn(acc.z, inv)), f2h(__fmul_rn(acc.w, inv))};
+    if (p.gate) {
+        const float sig = sigmoid_ref(h2f(p.gate[(size_t)b * NQ + hd]));
+#pragma unroll
+        for (int i = 0; i < 4; i++) h[i] = f2h(__fmul_rn(h2f(h[i]), sig));
+    }
+    uint2 packed = make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16),
+                              (uint32_t)h[2] | ((uint32_t)h[3] << 16));
+    *reinterpret_cast<uint2*>(p.ctx_out + ((size_t)b * NQ + hd) * HD + 4 * lane) = packed;
+}
+
 uint32_t decode_chunk_keys() { return dec::CHUNK; }
+uint32_t decode_max_rows() { return dec::MAX_ROWS; }
 
 cudaError_t decode_attn_init() {
     return cudaFuncSetAttribute(decode_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -393,7 +472,6 @@ cudaError_t launch_decode_attn(cudaStream_t stream, const DecodeWorkspace& ws, v
     p.seq_lens = seq_lens;
     p.partial_acc = ws.partial_acc;
     p.partial_stats = ws.partial_stats;
-    p.counters = ws.counters;
     p.status = ws.status;
     p.batch = batch;
     p.window = window;
@@ -401,6 +479,9 @@ cudaError_t launch_decode_attn(cudaStream_t stream, const DecodeWorkspace& ws, v
     p.max_seq_len = ws.max_seq_len;
     const int grid = ws.num_sms * dec::CTAS_PER_SM;
     decode_attn_kernel<<<grid, dec::THREADS, dec::SMEM_BYTES, stream>>>(p);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    decode_merge_kernel<<<batch * NKV, 128, 0, stream>>>(p);
     return cudaGetLastError();
 }
 

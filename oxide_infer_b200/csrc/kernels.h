@@ -9,7 +9,6 @@ namespace oxi {
 struct DecodeWorkspace {
     float* partial_acc;     // [max_batch][max_chunks][16][128]
     float* partial_stats;   // [max_batch][max_chunks][16][2]  (running max in log2 units, sum)
-    uint32_t* counters;     // [max_batch][4] arrivals per (row, kv head); all zero between launches
     uint32_t* status;       // device status word (OR of DEV_* bits)
     uint32_t max_chunks;    // partial slots per row
     uint32_t max_seq_len;
@@ -35,6 +34,7 @@ cudaError_t launch_decode_attn(cudaStream_t stream, const DecodeWorkspace& ws, v
                                const uint64_t* v_ptrs, const uint32_t* seq_lens, uint32_t batch,
                                uint32_t window);
 uint32_t decode_chunk_keys();    // keys per split-KV work item
+uint32_t decode_max_rows();      // rows one launch can take
 
 cudaError_t prefill_attn_init();
 cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* q,

@@ -28,7 +28,6 @@ struct oxi_handle {
     uint32_t* stg_pos;    // [max_batch]
     uint32_t* stg_len;    // [max_batch]
     uint32_t* host_len;   // pinned [max_batch]
-    cudaEvent_t stg_free[2];
     size_t bytes;
 };
 
@@ -77,7 +76,8 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
                    uint32_t max_prefill_rows) {
     if (!out) return fail(OXI_ERR_NULL, "oxi_create: out is null");
     *out = nullptr;
-    if (max_batch == 0 || max_batch > 4096) return fail(OXI_ERR_BATCH, "oxi_create: max_batch must be 1..4096");
+    if (max_batch == 0 || max_batch > decode_max_rows())
+        return fail(OXI_ERR_BATCH, "oxi_create: max_batch must be 1..2048");
     if (max_seq_len == 0 || max_seq_len > (1u << 22)) return fail(OXI_ERR_ARG, "oxi_create: max_seq_len out of range");
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || device < 0 || device >= ndev) {
@@ -107,7 +107,6 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
     const size_t slots = (size_t)max_batch * max_chunks * NQ;
     if ((rc = dev_alloc(h, (void**)&h->dws.partial_acc, slots * HD * sizeof(float)))) goto bad;
     if ((rc = dev_alloc(h, (void**)&h->dws.partial_stats, slots * 2 * sizeof(float)))) goto bad;
-    if ((rc = dev_alloc(h, (void**)&h->dws.counters, (size_t)max_batch * NKV * sizeof(uint32_t)))) goto bad;
     if ((rc = dev_alloc(h, (void**)&h->dws.status, 256))) goto bad;
     if (max_prefill_rows)
         if ((rc = dev_alloc(h, &h->conv_stage, (size_t)max_prefill_rows * HIDDEN * CONV_S * 2))) goto bad;
@@ -119,10 +118,6 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
         if ((rc = dev_alloc(h, &h->stg_ctx[i], (size_t)max_batch * NQ * HD * 2))) goto bad;
         if ((rc = dev_alloc(h, (void**)&h->stg_kp[i], (size_t)max_batch * 8))) goto bad;
         if ((rc = dev_alloc(h, (void**)&h->stg_vp[i], (size_t)max_batch * 8))) goto bad;
-        if (cudaEventCreateWithFlags(&h->stg_free[i], cudaEventDisableTiming) != cudaSuccess) {
-            rc = cuda_fail(cudaGetLastError(), "cudaEventCreate");
-            goto bad;
-        }
     }
     if ((rc = dev_alloc(h, (void**)&h->stg_pos, (size_t)max_batch * 4))) goto bad;
     if ((rc = dev_alloc(h, (void**)&h->stg_len, (size_t)max_batch * 4))) goto bad;
@@ -130,8 +125,7 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
         rc = cuda_fail(cudaGetLastError(), "cudaMallocHost");
         goto bad;
     }
-    if (cudaMemset(h->dws.counters, 0, (size_t)max_batch * NKV * sizeof(uint32_t)) != cudaSuccess ||
-        cudaMemset(h->dws.status, 0, 256) != cudaSuccess) {
+    if (cudaMemset(h->dws.status, 0, 256) != cudaSuccess) {
         rc = cuda_fail(cudaGetLastError(), "cudaMemset");
         goto bad;
     }
@@ -153,14 +147,12 @@ int32_t oxi_destroy(oxi_handle* h) {
     cudaSetDevice(h->device);
     cudaFree(h->dws.partial_acc);
     cudaFree(h->dws.partial_stats);
-    cudaFree(h->dws.counters);
     cudaFree(h->dws.status);
     cudaFree(h->conv_stage);
     for (int i = 0; i < 2; i++) {
         cudaFree(h->stg_q[i]); cudaFree(h->stg_k[i]); cudaFree(h->stg_v[i]);
         cudaFree(h->stg_gate[i]); cudaFree(h->stg_ctx[i]);
         cudaFree(h->stg_kp[i]); cudaFree(h->stg_vp[i]);
-        if (h->stg_free[i]) cudaEventDestroy(h->stg_free[i]);
     }
     cudaFree(h->stg_pos);
     cudaFree(h->stg_len);
