@@ -1,4 +1,4 @@
-// Split-KV flash-decode GQA attention with the sigmoid output gate, one launch.
+// Split-KV flash-decode GQA attention with the sigmoid output gate.
 //
 // Replaces batched_gqa_attention_split4_fp16 + batched_gqa_attn_combine_fp16 +
 // batched_sigmoid_gate_fp16 (batched_attn.rs:2665-3035, 1597-1717, 583-655).
@@ -6,10 +6,12 @@
 // Work decomposition.  A work item is (row b, key range c) where the ranges
 // are fixed CHUNK-key slices of the row's own [window start, seq_len) interval,
 // so a row's arithmetic never depends on which other rows share the launch.
-// The grid is persistent (a fixed number of CTAs per SM); every CTA derives the
-// item list from seq_lens on the device (prefix sum of per-row chunk counts in
-// shared memory) and takes items blockIdx.x, +gridDim.x, ...  The host needs no
-// knowledge of the lengths and the launch shape never changes.
+// The grid is persistent (one CTA per SM); every CTA derives the item list from
+// seq_lens on the device (prefix sum of per-row range counts in shared memory),
+// takes item blockIdx.x first and then claims further items from a global work
+// counter (claimed two items ahead, so the claim's latency is off the critical
+// path).  The host needs no knowledge of the lengths, the launch shape never
+// changes, and SMs that receive less memory bandwidth simply claim fewer items.
 //
 // Inside a CTA: one producer warp streams K and V rows (1024 B each: all four
 // KV heads of one token are contiguous) into a ring of shared-memory stages
@@ -25,30 +27,25 @@
 // every ldmatrix phase fall in distinct banks.  The key order inside a stage is
 // therefore a permutation, applied consistently to the P columns and V rows.
 //
-// The step's q row (4 KB: all 16 heads) rides with the first stage of each item
-// as one more bulk copy, and seq_lens are staged in shared memory, so a consumer
-// warp issues no global load of its own while streaming: under a saturated
-// memory pipe every dependent global access costs microseconds of queueing.
+// Every stage carries a 16-byte descriptor written by the producer (row, range,
+// valid keys, first/last-of-item flags), and the first stage of an item also
+// carries the row's q (4 KB, one more bulk copy); seq_lens are staged in shared
+// memory.  A consumer warp therefore issues no global load of its own while
+// streaming: under a saturated memory pipe every dependent global access costs
+// microseconds of queueing behind the stream.
 //
 // A row covered by one item is finished in registers (1/sum, f16, gate).
 // Otherwise each consumer warp stores its (max, sum, acc[128]) partials and
 // moves on; a second, tiny kernel merges the partials of every multi-item row
 // in key-range order (deterministic), applies 1/sum, rounds to f16 and applies
-// the gate exactly as the reference's gate kernel does on the f16 context.
-// Nothing spins on another CTA and no atomics or fences sit on the stream.
+// the gate exactly as the reference's gate kernel does on the f16 context, and
+// resets the work counter.  Nothing spins on another CTA; the only waits are on
+// this CTA's own mbarriers and they are time-bounded.
 #include "common.cuh"
 #include "kernels.h"
-#ifdef OXI_EXP_TIMING
-#include <cstdio>
-#endif
-
-namespace oxi {
 
 #ifndef OXI_DEC_NSTAGE
 #define OXI_DEC_NSTAGE 3
-#endif
-#ifndef OXI_DEC_CTAS
-#define OXI_DEC_CTAS 1
 #endif
 #ifndef OXI_DEC_CHUNK
 #define OXI_DEC_CHUNK 256
@@ -57,27 +54,33 @@ namespace oxi {
 #define OXI_DEC_MAXROWS 2048
 #endif
 
+namespace oxi {
+
 namespace dec {
-constexpr int KS = 32;                        // keys per pipeline stage
-constexpr int NSTAGE = OXI_DEC_NSTAGE;        // ring depth
-constexpr int GK = 4;                         // keys per bulk copy (one group)
+constexpr int KS = 32;                          // keys per pipeline stage
+constexpr int NSTAGE = OXI_DEC_NSTAGE;          // ring depth
+constexpr int GK = 4;                           // keys per bulk copy (one group)
 constexpr int GROUP_BYTES = GK * KV_ROW_BYTES;  // 4096 B copied at once
-constexpr int GPITCH = GROUP_BYTES + 16;      // group pitch in shared memory
-constexpr int NGROUP = KS / GK;               // 8 groups per stage = the 8 rows of an ldmatrix tile
-constexpr int HALF_BYTES = NGROUP * GPITCH;   // K part (then V part) of a stage
-constexpr int Q_BYTES = NQ * HD * 2;           // the row's q (all heads), carried by an item's first stage
-constexpr int STAGE_BYTES = 2 * HALF_BYTES + Q_BYTES;
-constexpr int CHUNK = OXI_DEC_CHUNK;          // keys per work item
-constexpr int N_CONSUMER_WARPS = NKV;         // one per KV head
+constexpr int GPITCH = GROUP_BYTES + 16;        // group pitch in shared memory
+constexpr int NGROUP = KS / GK;                 // 8 groups per stage = the 8 rows of an ldmatrix tile
+constexpr int HALF_BYTES = NGROUP * GPITCH;     // K part (then V part) of a stage
+constexpr int Q_BYTES = NQ * HD * 2;            // the row's q (all heads), carried by an item's first stage
+constexpr int DESC_BYTES = 16;
+constexpr int STAGE_BYTES = 2 * HALF_BYTES + Q_BYTES + DESC_BYTES;
+constexpr int CHUNK = OXI_DEC_CHUNK;            // keys per work item
+constexpr int N_CONSUMER_WARPS = NKV;           // one per KV head
 constexpr int THREADS = (N_CONSUMER_WARPS + 1) * 32;
-constexpr int MAX_ROWS = OXI_DEC_MAXROWS;     // rows per launch (prefix array in shared memory)
-constexpr int CTAS_PER_SM = OXI_DEC_CTAS;
+constexpr int MAX_ROWS = OXI_DEC_MAXROWS;       // rows per launch (prefix + length arrays in shared memory)
 constexpr float QK_SCALE_LOG2 = ATTN_SCALE * LOG2E;
 constexpr size_t SMEM_BYTES = (size_t)NSTAGE * STAGE_BYTES + 2 * NSTAGE * 8 + 16 +
                               (2 * MAX_ROWS + 1) * sizeof(uint32_t);
 static_assert(SMEM_BYTES <= 227 * 1024, "decode kernel shared memory");
 static_assert(CHUNK % KS == 0, "a work item is a whole number of stages");
 static_assert(NGROUP == 8, "ldmatrix tiles take one row from each of 8 groups");
+static_assert(STAGE_BYTES % 16 == 0, "stage alignment");
+
+// stage descriptor flags (word z)
+constexpr uint32_t F_FIRST = 0x100u, F_LAST = 0x200u, F_END = 0x400u;
 }  // namespace dec
 
 struct DecodeParams {
@@ -89,6 +92,7 @@ struct DecodeParams {
     const uint32_t* seq_lens;
     float* partial_acc;
     float* partial_stats;
+    uint32_t* work_counter;
     uint32_t* status;
     uint32_t batch;
     uint32_t window;
@@ -111,7 +115,7 @@ __device__ __forceinline__ uint32_t find_row(const uint32_t* prefix, uint32_t ba
     return lo;
 }
 
-__global__ void __launch_bounds__(dec::THREADS, dec::CTAS_PER_SM)
+__global__ void __launch_bounds__(dec::THREADS, 1)
 decode_attn_kernel(const DecodeParams p) {
     using namespace dec;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -124,7 +128,7 @@ decode_attn_kernel(const DecodeParams p) {
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // ---- prologue: barriers, per-row chunk counts, prefix sum
+    // ---- prologue: barriers, per-row range counts, prefix sum, lengths into shared memory
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; s++) {
             mbar_init(&full_bar[s], 1);
@@ -171,43 +175,60 @@ decode_attn_kernel(const DecodeParams p) {
         const uint64_t policy = l2_policy_evict_first();
         uint32_t fill = 0;
         bool ok = true;
-        // metadata of the item about to be streamed; the next item's is fetched one item ahead
-        uint32_t nb = 0, nslen = 0, nc = 0;
-        uint64_t nkp = 0, nvp = 0;
-        auto fetch = [&](uint32_t item) {
-            if (item < total_items) {
-                nb = find_row(prefix, p.batch, item);
-                nc = item - prefix[nb];
+        // Item pipeline: `cur` is streamed now; `nxt` is known and its pointers are being
+        // fetched; the claim for the item after `nxt` is in flight (lane 0's `claim`).
+        uint32_t cur = blockIdx.x;
+        uint32_t cb = 0, cc = 0, cslen = 0;
+        uint64_t ckp = 0, cvp = 0;
+        if (cur < total_items) {
+            cb = find_row(prefix, p.batch, cur);
+            cc = cur - prefix[cb];
+            cslen = s_len[cb];
+            ckp = p.k_ptrs[cb];
+            cvp = p.v_ptrs[cb];
+        }
+        uint32_t claim = 0;
+        if (lane == 0 && cur < total_items) claim = atomicAdd(p.work_counter, 1u);
+
+        while (cur < total_items && ok) {
+            uint32_t nxt = __shfl_sync(0xffffffffu, claim, 0);
+            nxt = (nxt >= total_items) ? total_items : min(nxt + gridDim.x, total_items);
+            uint32_t nb = 0, nc = 0, nslen = 0;
+            uint64_t nkp = 0, nvp = 0;
+            claim = 0xffffffffu;  // "no more items" unless a new claim is made
+            if (nxt < total_items) {
+                if (lane == 0) claim = atomicAdd(p.work_counter, 1u);
+                nb = find_row(prefix, p.batch, nxt);
+                nc = nxt - prefix[nb];
                 nslen = s_len[nb];
                 nkp = p.k_ptrs[nb];
                 nvp = p.v_ptrs[nb];
             }
-        };
-        fetch(blockIdx.x);
-        for (uint32_t item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-            const uint32_t slen = nslen, c = nc;
-            const char* qp = reinterpret_cast<const char*>(p.q) + (size_t)nb * Q_BYTES;
-            const char* kp = reinterpret_cast<const char*>(nkp);
-            const char* vp = reinterpret_cast<const char*>(nvp);
-            fetch(item + gridDim.x);
-            const uint32_t t0 = window_start(slen, p.window) + c * CHUNK;
-            const uint32_t t1 = min(t0 + (uint32_t)CHUNK, slen);
+            const uint32_t nchunks = prefix[cb + 1] - prefix[cb];
+            const char* qp = reinterpret_cast<const char*>(p.q) + (size_t)cb * Q_BYTES;
+            const char* kp = reinterpret_cast<const char*>(ckp);
+            const char* vp = reinterpret_cast<const char*>(cvp);
+            const uint32_t t0 = window_start(cslen, p.window) + cc * CHUNK;
+            const uint32_t t1 = min(t0 + (uint32_t)CHUNK, cslen);
             for (uint32_t t = t0; t < t1; t += KS, ++fill) {
                 const uint32_t slot = fill % NSTAGE;
-                if (fill >= NSTAGE) {
-                    if (!mbar_wait_bounded(&empty_bar[slot], ((fill / NSTAGE) & 1u) ^ 1u, abort_flag)) {
-                        ok = false;
-                        break;
-                    }
+                if (fill >= NSTAGE &&
+                    !mbar_wait_bounded(&empty_bar[slot], ((fill / NSTAGE) & 1u) ^ 1u, abort_flag)) {
+                    ok = false;
+                    break;
                 }
                 const uint32_t nvalid = min((uint32_t)KS, t1 - t);
-                const bool first = (t == t0);
-                if (lane == 0)
+                const bool first = (t == t0), last = (t + KS >= t1);
+                unsigned char* sb = stages + (size_t)slot * STAGE_BYTES;
+                if (lane == 0) {
+                    *reinterpret_cast<uint4*>(sb + 2 * HALF_BYTES + Q_BYTES) =
+                        make_uint4(cb, cc | (nchunks << 16),
+                                   nvalid | (first ? F_FIRST : 0u) | (last ? F_LAST : 0u), 0u);
                     mbar_arrive_expect_tx(&full_bar[slot], nvalid * 2u * KV_ROW_BYTES + (first ? Q_BYTES : 0));
+                }
                 __syncwarp();
-                const uint32_t sbase = smem_u32(stages + (size_t)slot * STAGE_BYTES);
-                if (first && lane == 2 * NGROUP) bulk_g2s(sbase + 2 * HALF_BYTES, qp, Q_BYTES, &full_bar[slot]);
-                // lanes 0..7 copy the K groups, lanes 8..15 the V groups (up to 4 KB each)
+                const uint32_t sbase = smem_u32(sb);
+                // lanes 0..7 copy the K groups, lanes 8..15 the V groups (up to 4 KB each), lane 16 the q row
                 if (lane < 2 * NGROUP) {
                     const uint32_t grp = lane & (NGROUP - 1);
                     const bool is_v = lane >= NGROUP;
@@ -217,7 +238,24 @@ decode_attn_kernel(const DecodeParams p) {
                         bulk_g2s_hint(sbase + (is_v ? HALF_BYTES : 0) + grp * GPITCH, src,
                                       nk * KV_ROW_BYTES, &full_bar[slot], policy);
                     }
+                } else if (first && lane == 2 * NGROUP) {
+                    bulk_g2s(sbase + 2 * HALF_BYTES, qp, Q_BYTES, &full_bar[slot]);
                 }
+            }
+            cur = nxt; cb = nb; cc = nc; cslen = nslen; ckp = nkp; cvp = nvp;
+        }
+        if (ok) {
+            // end-of-work descriptor so the consumers leave their loop
+            const uint32_t slot = fill % NSTAGE;
+            if (fill < NSTAGE || mbar_wait_bounded(&empty_bar[slot], ((fill / NSTAGE) & 1u) ^ 1u, abort_flag)) {
+                if (lane == 0) {
+                    *reinterpret_cast<uint4*>(stages + (size_t)slot * STAGE_BYTES + 2 * HALF_BYTES + Q_BYTES) =
+                        make_uint4(0u, 0u, F_END, 0u);
+                    mbar_arrive(&full_bar[slot]);
+                }
+                ++fill;
+            } else {
+                ok = false;
             }
         }
         if (!ok) {
@@ -234,183 +272,163 @@ decode_attn_kernel(const DecodeParams p) {
     const int kvh = warp;            // this warp's KV head
     const int g = lane >> 2;         // fragment row (query head within the group when g < 4)
     const int t4 = lane & 3;         // fragment column pair
-    uint32_t take = 0;               // stages consumed so far (mirrors the producer's `fill`)
-    bool ok = true;
-#ifdef OXI_EXP_TIMING
-    long long tw = 0, tc = 0, te = 0, tq = 0, t_mark = clock64(), t_start = t_mark; int nitems = 0;
-    const uint64_t g_start = global_timer_ns();
-#define TMARK(acc) do { long long now__ = clock64(); acc += now__ - t_mark; t_mark = now__; } while (0)
-#else
-#define TMARK(acc) do {} while (0)
-#endif
+    const uint32_t head = kvh * 4 + (g & 3);
 
-    for (uint32_t item = blockIdx.x; item < total_items; item += gridDim.x) {
-        const uint32_t b = find_row(prefix, p.batch, item);
-        const uint32_t c = item - prefix[b];
-        const uint32_t nchunks = prefix[b + 1] - prefix[b];
-        const uint32_t slen = s_len[b];
-        const uint32_t t0 = window_start(slen, p.window) + c * CHUNK;
-        const uint32_t t1 = min(t0 + (uint32_t)CHUNK, slen);
-        uint32_t qa[8][2];  // Q fragments (A operand, rows 0..3 = the group's heads, rows 4..15 zero)
-        float o[16][4];
+    uint32_t qa[8][2];  // Q fragments (A operand, rows 0..3 = the group's heads, rows 4..15 zero)
+    float o[16][4];
+    float m_run = -1.0e30f, l_run = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 16; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
-        float m_run = -1.0e30f, l_run = 0.0f;
-        TMARK(tq);
+    for (int ks = 0; ks < 8; ks++) { qa[ks][0] = qa[ks][1] = 0u; }
+#pragma unroll
+    for (int j = 0; j < 16; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
 
-        for (uint32_t t = t0; t < t1; t += KS, ++take) {
-            const uint32_t slot = take % NSTAGE;
-            if (ok) ok = mbar_wait_bounded(&full_bar[slot], (take / NSTAGE) & 1u, abort_flag);
-            TMARK(tw);
-            if (t == t0) {  // the item's first stage carries the row's q
-                const unsigned char* qrow = stages + (size_t)slot * STAGE_BYTES + 2 * HALF_BYTES +
-                                            (kvh * 4 + (g & 3)) * (HD * 2);
-#pragma unroll
-                for (int ks = 0; ks < 8; ks++) {
-                    uint32_t lo = 0, hi = 0;
-                    if (g < 4) {
-                        lo = *reinterpret_cast<const uint32_t*>(qrow + (16 * ks + 2 * t4) * 2);
-                        hi = *reinterpret_cast<const uint32_t*>(qrow + (16 * ks + 8 + 2 * t4) * 2);
-                    }
-                    qa[ks][0] = lo;
-                    qa[ks][1] = hi;
-                }
-            }
-            const uint32_t nvalid = min((uint32_t)KS, t1 - t);
-            unsigned char* kst = stages + (size_t)slot * STAGE_BYTES + kvh * (HD * 2);
-            unsigned char* vst = kst + HALF_BYTES;
-            if (nvalid < KS) {
-                // tail stage: rows past the range keep stale bytes; zero this head's V slice there
-                // so that 0 * stale can never produce NaN.
-                for (uint32_t i = lane; i < (KS - nvalid) * 16u; i += 32) {
-                    const uint32_t row = nvalid + (i >> 4);
-                    *reinterpret_cast<uint4*>(vst + (row >> 2) * GPITCH + (row & 3u) * KV_ROW_BYTES +
-                                              (i & 15u) * 16u) = make_uint4(0, 0, 0, 0);
-                }
-                __syncwarp();
-            }
+    for (uint32_t take = 0;; ++take) {
+        const uint32_t slot = take % NSTAGE;
+        if (!mbar_wait_bounded(&full_bar[slot], (take / NSTAGE) & 1u, abort_flag)) {
+            if (lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
+            break;
+        }
+        unsigned char* sb = stages + (size_t)slot * STAGE_BYTES;
+        const uint4 desc = *reinterpret_cast<const uint4*>(sb + 2 * HALF_BYTES + Q_BYTES);
+        if (desc.z & F_END) break;
+        const uint32_t nvalid = desc.z & 0xffu;
+        unsigned char* kst = sb + kvh * (HD * 2);
+        unsigned char* vst = kst + HALF_BYTES;
 
-            // ---- S = Q K^T for 32 keys: n-block nb holds keys nb + 4*n (n = 0..7, one per group)
-            float s[4][4];
+        if (desc.z & F_FIRST) {  // new item: reset the running state, take the row's q from the stage
+            const unsigned char* qrow = sb + 2 * HALF_BYTES + head * (HD * 2);
 #pragma unroll
-            for (int nb = 0; nb < 4; nb++) {
-                s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
-                const uint32_t kaddr = smem_u32(kst) + (lane & 7) * GPITCH + nb * KV_ROW_BYTES + (lane >> 3) * 16;
-#pragma unroll
-                for (int kk = 0; kk < 4; kk++) {
-                    uint32_t r0, r1, r2, r3;
-                    ldmatrix_x4(kaddr + kk * 64, r0, r1, r2, r3);
-                    mma_16816(s[nb], qa[2 * kk][0], 0u, qa[2 * kk][1], 0u, r0, r1);
-                    mma_16816(s[nb], qa[2 * kk + 1][0], 0u, qa[2 * kk + 1][1], 0u, r2, r3);
+            for (int ks = 0; ks < 8; ks++) {
+                uint32_t lo = 0, hi = 0;
+                if (g < 4) {
+                    lo = *reinterpret_cast<const uint32_t*>(qrow + (16 * ks + 2 * t4) * 2);
+                    hi = *reinterpret_cast<const uint32_t*>(qrow + (16 * ks + 8 + 2 * t4) * 2);
                 }
+                qa[ks][0] = lo;
+                qa[ks][1] = hi;
             }
-            // ---- online softmax on row g (this thread: keys nb + 4*(2*t4 + {0,1}))
-            float mx = -1.0e30f;
 #pragma unroll
-            for (int nb = 0; nb < 4; nb++) {
-#pragma unroll
-                for (int j = 0; j < 2; j++) {
-                    const uint32_t key = nb + 4 * (2 * t4 + j);
-                    float v = s[nb][j] * QK_SCALE_LOG2;
-                    v = (key < nvalid) ? v : -INFINITY;
-                    s[nb][j] = v;
-                    mx = fmaxf(mx, v);
-                }
+            for (int j = 0; j < 16; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
+            m_run = -1.0e30f;
+            l_run = 0.0f;
+        }
+        if (nvalid < KS) {
+            // tail stage: rows past the range keep stale bytes; zero this head's V slice there
+            // so that 0 * stale can never produce NaN.
+            for (uint32_t i = lane; i < (KS - nvalid) * 16u; i += 32) {
+                const uint32_t row = nvalid + (i >> 4);
+                *reinterpret_cast<uint4*>(vst + (row >> 2) * GPITCH + (row & 3u) * KV_ROW_BYTES +
+                                          (i & 15u) * 16u) = make_uint4(0, 0, 0, 0);
             }
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-            const float m_new = fmaxf(m_run, mx);
-            const float corr = ex2_approx_ftz(m_run - m_new);
-            m_run = m_new;
-            float psum = 0.0f;
-            uint32_t pa[4];
-#pragma unroll
-            for (int nb = 0; nb < 4; nb++) {
-                const float p0 = ex2_approx_ftz(s[nb][0] - m_new);
-                const float p1 = ex2_approx_ftz(s[nb][1] - m_new);
-                psum += p0 + p1;
-                pa[nb] = pack_h2(p0, p1);
-            }
-            l_run = l_run * corr + psum;
-#pragma unroll
-            for (int j = 0; j < 16; j++) { o[j][0] *= corr; o[j][1] *= corr; }
-
-            // ---- O += P V : 2 k-steps of 16 keys (the keys of n-blocks 2*k2 and 2*k2+1, same
-            // permutation as P's columns), 16 n-blocks of 8 dims
-#pragma unroll
-            for (int k2 = 0; k2 < 2; k2++) {
-                const uint32_t vaddr = smem_u32(vst) + (lane & 7) * GPITCH +
-                                       (2 * k2 + ((lane >> 3) & 1)) * KV_ROW_BYTES + (lane >> 4) * 16;
-#pragma unroll
-                for (int jn = 0; jn < 8; jn++) {
-                    uint32_t r0, r1, r2, r3;
-                    ldmatrix_x4_trans(vaddr + jn * 32, r0, r1, r2, r3);
-                    mma_16816(o[2 * jn], pa[2 * k2], 0u, pa[2 * k2 + 1], 0u, r0, r1);
-                    mma_16816(o[2 * jn + 1], pa[2 * k2], 0u, pa[2 * k2 + 1], 0u, r2, r3);
-                }
-            }
-            // release the stage (generic writes of a tail stage are ordered before later bulk copies)
-            if (nvalid < KS) fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&empty_bar[slot]);
-            TMARK(tc);
         }
-#ifdef OXI_EXP_TIMING
-        nitems++;
-#endif
 
-        // ---- finish the item: row sums across the quad
-        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-        const uint32_t head = kvh * 4 + (g & 3);
-
-        if (nchunks == 1) {
-            if (g < 4) {
-                const float inv = rcp_approx_ftz(l_run);
-                const float sig = p.gate ? sigmoid_ref(h2f(p.gate[(size_t)b * NQ + head])) : 1.0f;
-                uint16_t* out = p.ctx_out + ((size_t)b * NQ + head) * HD;
+        // ---- S = Q K^T for 32 keys: n-block nb holds keys nb + 4*n (n = 0..7, one per group)
+        float s[4][4];
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    uint16_t h0 = f2h(__fmul_rn(o[j][0], inv));
-                    uint16_t h1 = f2h(__fmul_rn(o[j][1], inv));
-                    if (p.gate) {
-                        h0 = f2h(__fmul_rn(h2f(h0), sig));
-                        h1 = f2h(__fmul_rn(h2f(h1), sig));
-                    }
-                    *reinterpret_cast<uint32_t*>(out + 8 * j + 2 * t4) = (uint32_t)h0 | ((uint32_t)h1 << 16);
-                }
+        for (int nb = 0; nb < 4; nb++) {
+            s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
+            const uint32_t kaddr = smem_u32(kst) + (lane & 7) * GPITCH + nb * KV_ROW_BYTES + (lane >> 3) * 16;
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++) {
+                uint32_t r0, r1, r2, r3;
+                ldmatrix_x4(kaddr + kk * 64, r0, r1, r2, r3);
+                mma_16816(s[nb], qa[2 * kk][0], 0u, qa[2 * kk][1], 0u, r0, r1);
+                mma_16816(s[nb], qa[2 * kk + 1][0], 0u, qa[2 * kk + 1][1], 0u, r2, r3);
             }
-            TMARK(te);
-            continue;
         }
+        // ---- online softmax on row g (this thread: keys nb + 4*(2*t4 + {0,1}))
+        float mx = -1.0e30f;
+#pragma unroll
+        for (int nb = 0; nb < 4; nb++) {
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const uint32_t key = nb + 4 * (2 * t4 + j);
+                float v = s[nb][j] * QK_SCALE_LOG2;
+                v = (key < nvalid) ? v : -INFINITY;
+                s[nb][j] = v;
+                mx = fmaxf(mx, v);
+            }
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const float corr = ex2_approx_ftz(m_run - m_new);
+        m_run = m_new;
+        float psum = 0.0f;
+        uint32_t pa[4];
+#pragma unroll
+        for (int nb = 0; nb < 4; nb++) {
+            const float p0 = ex2_approx_ftz(s[nb][0] - m_new);
+            const float p1 = ex2_approx_ftz(s[nb][1] - m_new);
+            psum += p0 + p1;
+            pa[nb] = pack_h2(p0, p1);
+        }
+        l_run = l_run * corr + psum;
+#pragma unroll
+        for (int j = 0; j < 16; j++) { o[j][0] *= corr; o[j][1] *= corr; }
 
-        // ---- several items cover this row: store the partials for the merge kernel
-        const size_t pbase = ((size_t)b * p.max_chunks + c) * NQ;
-        if (g < 4) {
-            float* pacc = p.partial_acc + (pbase + head) * HD;
+        // ---- O += P V : 2 k-steps of 16 keys (the keys of n-blocks 2*k2 and 2*k2+1, same
+        // permutation as P's columns), 16 n-blocks of 8 dims
+#pragma unroll
+        for (int k2 = 0; k2 < 2; k2++) {
+            const uint32_t vaddr = smem_u32(vst) + (lane & 7) * GPITCH +
+                                   (2 * k2 + ((lane >> 3) & 1)) * KV_ROW_BYTES + (lane >> 4) * 16;
+#pragma unroll
+            for (int jn = 0; jn < 8; jn++) {
+                uint32_t r0, r1, r2, r3;
+                ldmatrix_x4_trans(vaddr + jn * 32, r0, r1, r2, r3);
+                mma_16816(o[2 * jn], pa[2 * k2], 0u, pa[2 * k2 + 1], 0u, r0, r1);
+                mma_16816(o[2 * jn + 1], pa[2 * k2], 0u, pa[2 * k2 + 1], 0u, r2, r3);
+            }
+        }
+        // release the stage (generic writes of a tail stage are ordered before later bulk copies)
+        if (nvalid < KS) fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[slot]);
+
+        if (!(desc.z & F_LAST)) continue;
+
+        // ---- the item is complete: row sums across the quad, then output or partials
+        const uint32_t b = desc.x, c = desc.y & 0xffffu, nchunks = desc.y >> 16;
+        float l_tot = l_run;
+        l_tot += __shfl_xor_sync(0xffffffffu, l_tot, 1);
+        l_tot += __shfl_xor_sync(0xffffffffu, l_tot, 2);
+        if (g >= 4) continue;
+        if (nchunks == 1) {
+            const float inv = rcp_approx_ftz(l_tot);
+            const float sig = p.gate ? sigmoid_ref(h2f(p.gate[(size_t)b * NQ + head])) : 1.0f;
+            uint16_t* out = p.ctx_out + ((size_t)b * NQ + head) * HD;
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                uint16_t h0 = f2h(__fmul_rn(o[j][0], inv));
+                uint16_t h1 = f2h(__fmul_rn(o[j][1], inv));
+                if (p.gate) {
+                    h0 = f2h(__fmul_rn(h2f(h0), sig));
+                    h1 = f2h(__fmul_rn(h2f(h1), sig));
+                }
+                *reinterpret_cast<uint32_t*>(out + 8 * j + 2 * t4) = (uint32_t)h0 | ((uint32_t)h1 << 16);
+            }
+        } else {
+            const size_t pslot = ((size_t)b * p.max_chunks + c) * NQ + head;
+            float* pacc = p.partial_acc + pslot * HD;
 #pragma unroll
             for (int j = 0; j < 16; j++)
                 __stcg(reinterpret_cast<float2*>(pacc + 8 * j + 2 * t4), make_float2(o[j][0], o[j][1]));
             if (t4 == 0)
-                __stcg(reinterpret_cast<float2*>(p.partial_stats + (pbase + head) * 2),
-                       make_float2(m_run, l_run));
+                __stcg(reinterpret_cast<float2*>(p.partial_stats + pslot * 2), make_float2(m_run, l_tot));
         }
-        TMARK(te);
     }
-#ifdef OXI_EXP_TIMING
-    if (lane == 0 && warp == 0 && (blockIdx.x == 0 || blockIdx.x == 50 || blockIdx.x == 147))
-        printf("cta %d items %d total %lld cyc %llu ns: wait %lld compute %lld epilogue %lld qload %lld\n", blockIdx.x, nitems,
-               clock64() - t_start, (unsigned long long)(global_timer_ns() - g_start), tw, tc, te, tq);
-#endif
-    if (!ok && lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
 }
 
-// Merges the partials of every row that was covered by more than one item.
+// Merges the partials of every row that was covered by more than one item, and
+// resets the work counter for the next launch.
 // grid = B*4 CTAs of 4 warps: warp = one query head of one row; lane owns dims
 // 4*lane .. 4*lane+3.  All loads are independent of the arithmetic, which runs
 // in key-range order, so the result does not depend on scheduling.
 __global__ void __launch_bounds__(128)
 decode_merge_kernel(const DecodeParams p) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) *p.work_counter = 0u;
     const uint32_t b = blockIdx.x >> 2;
     const int lane = threadIdx.x & 31;
     const uint32_t hd = (blockIdx.x & 3u) * 4 + (threadIdx.x >> 5);
@@ -472,13 +490,13 @@ cudaError_t launch_decode_attn(cudaStream_t stream, const DecodeWorkspace& ws, v
     p.seq_lens = seq_lens;
     p.partial_acc = ws.partial_acc;
     p.partial_stats = ws.partial_stats;
+    p.work_counter = ws.work_counter;
     p.status = ws.status;
     p.batch = batch;
     p.window = window;
     p.max_chunks = ws.max_chunks;
     p.max_seq_len = ws.max_seq_len;
-    const int grid = ws.num_sms * dec::CTAS_PER_SM;
-    decode_attn_kernel<<<grid, dec::THREADS, dec::SMEM_BYTES, stream>>>(p);
+    decode_attn_kernel<<<ws.num_sms, dec::THREADS, dec::SMEM_BYTES, stream>>>(p);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     decode_merge_kernel<<<batch * NKV, 128, 0, stream>>>(p);

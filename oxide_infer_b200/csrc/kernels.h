@@ -10,6 +10,7 @@ struct DecodeWorkspace {
     float* partial_acc;     // [max_batch][max_chunks][16][128]
     float* partial_stats;   // [max_batch][max_chunks][16][2]  (running max in log2 units, sum)
     uint32_t* status;       // device status word (OR of DEV_* bits)
+    uint32_t* work_counter; // items claimed beyond the first per CTA; zero between launches
     uint32_t max_chunks;    // partial slots per row
     uint32_t max_seq_len;
     int num_sms;

@@ -108,6 +108,7 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
     if ((rc = dev_alloc(h, (void**)&h->dws.partial_acc, slots * HD * sizeof(float)))) goto bad;
     if ((rc = dev_alloc(h, (void**)&h->dws.partial_stats, slots * 2 * sizeof(float)))) goto bad;
     if ((rc = dev_alloc(h, (void**)&h->dws.status, 256))) goto bad;
+    h->dws.work_counter = h->dws.status + 32;  // same zero-initialised 256-byte block, own 128-byte line
     if (max_prefill_rows)
         if ((rc = dev_alloc(h, &h->conv_stage, (size_t)max_prefill_rows * HIDDEN * CONV_S * 2))) goto bad;
     for (int i = 0; i < 2; i++) {
