@@ -70,12 +70,9 @@ class ClockSampler(threading.Thread):
             get = getattr(N, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
                 N.nvmlDeviceGetCurrentClocksThrottleReasons
             while not self.stop_flag:
-                self.sm.append(int(N.nvmlDeviceGetClockInfo(h, N.NVML_CLOCK_SM)))
-                bits = int(get(h))
-                for k, v in names.items():
-                    if bits & v:
-                        self.reasons.add(k)
-                time.sleep(0.002)
+                mhz, bits = int(N.nvmlDeviceGetClockInfo(h, N.NVML_CLOCK_SM)), int(get(h))
+                self.sm.append((time.perf_counter(), mhz, tuple(k for k, v in names.items() if bits & v)))
+                time.sleep(0.001)
         except Exception:
             self._run_smi()
 
@@ -90,22 +87,26 @@ class ClockSampler(threading.Thread):
                                      text=True, timeout=5).stdout.strip()
                 r = [x.strip() for x in out.split(",")]
                 if r and r[0].isdigit():
-                    self.sm.append(int(r[0]))
                     self.max_mhz = int(r[1])
-                    for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
-                                        "sw_power_cap"), r[2:6]):
-                        if v.lower().startswith("active"):
-                            self.reasons.add(name)
+                    self.sm.append((time.perf_counter(), int(r[0]),
+                                    tuple(n for n, v in zip(("hw_slowdown", "hw_thermal_slowdown",
+                                                             "sw_thermal_slowdown", "sw_power_cap"), r[2:6])
+                                          if v.lower().startswith("active"))))
             except Exception:
                 pass
             time.sleep(0.02)
 
-    def summary(self):
+    def window(self, t0: float, t1: float):
+        """Median/min SM clock and the reasons seen between two perf_counter() instants."""
+        rows = [r for r in list(self.sm) if t0 <= r[0] <= t1]
+        sm = sorted(r[1] for r in rows)
+        reasons = sorted({x for r in rows for x in r[2]})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_min_mhz": sm[0] if sm else None,
+                "sm_max_mhz": self.max_mhz, "samples": len(sm), "reasons": reasons}
+
+    def stop(self):
         self.stop_flag = True
         self.join(timeout=6)
-        sm = sorted(self.sm)
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_min_mhz": sm[0] if sm else None,
-                "sm_max_mhz": self.max_mhz, "samples": len(sm), "reasons": sorted(self.reasons)}
 
 
 def gpu_index(local_rank: int) -> int:
@@ -216,22 +217,25 @@ def run_ours(args, torch, rank, world, local_rank):
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(gpu_index(local_rank))
+    sampler.start()
     for _ in range(args.warmup):
         step()
     barrier()
-    sampler = ClockSampler(gpu_index(local_rank))
-    sampler.start()
     ev, t0, t1 = [], torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = time.perf_counter()
     t0.record(stream)
     for _ in range(args.steps):
         step(ev)
     t1.record(stream)
     barrier()
+    w1 = time.perf_counter()
     ms = t0.elapsed_time(t1)
     attn_ms = sum(a.elapsed_time(b) for a, b in ev) / len(ev)
-    clocks = sampler.summary()
+    clocks = sampler.window(w0, w1)
 
     if args.no_e2e:
+        sampler.stop()
         if rank == 0:
             attn_gbs = attn_bytes_layer(w.seq_lens_host) / (attn_ms * 1e-3) / 1e9
             return {"profiling_case": True, "layers": LAYERS, "batch": BATCH, "ctx": CTX,
@@ -260,6 +264,7 @@ def run_ours(args, torch, rank, world, local_rank):
     t1.record(stream)
     barrier()
     ms_e2e = t0.elapsed_time(t1)
+    sampler.stop()
     step(restore_q=True)  # untimed: same inputs as the host-buffer path, for the equality check
     status = kv.device_status()
     ctx_ok = bool(torch.isfinite(w.ctx.float()).all().item()) and bool(torch.isfinite(hctx.float()).all().item())
@@ -333,19 +338,22 @@ def run_reference(args, torch, rank, world, local_rank):
             ref.append(w.q[l], kbuf[l], w.v[l], w.qw[l], w.kw[l], w.cos, w.sin, w.pos, w.k_ptrs[l], w.v_ptrs[l], BATCH)
             ref.decode_attention(w.ctx[l], w.q[l], w.gate[l], w.k_ptrs[l], w.v_ptrs[l], w.lens, BATCH, 0, CTX, acc, stats)
 
+    sampler = ClockSampler(gpu_index(local_rank))
+    sampler.start()
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
-    sampler = ClockSampler(gpu_index(local_rank))
-    sampler.start()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = time.perf_counter()
     t0.record(stream)
     for _ in range(args.steps):
         step()
     t1.record(stream)
     torch.cuda.synchronize()
+    w1 = time.perf_counter()
     ms = t0.elapsed_time(t1)
-    clocks = sampler.summary()
+    clocks = sampler.window(w0, w1)
+    sampler.stop()
 
     # end to end with the same host traffic as our arm: upload q/k/v/gate + tables, download ctx
     pin = lambda t: t.cpu().pin_memory()

@@ -73,8 +73,10 @@ append_kernel(uint16_t* __restrict__ q_io, const uint16_t* __restrict__ k_in,
               uint32_t* __restrict__ status) {
     const uint32_t b = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
     const uint32_t pos = pos_ids[b];
     const uint64_t kp = k_ptrs[b], vp = v_ptrs[b];
+    pdl_wait();  // q/k/v come from the preceding kernel; the caches may still be read by it
     const bool aligned = ((kp | vp) & 15ull) == 0ull;
     if (!aligned && threadIdx.x == 0) atomicOr(status, DEV_MISALIGNED_PTR);
     const uint16_t* cos_row = cos_t + (size_t)pos * HD;
@@ -157,11 +159,10 @@ cudaError_t launch_append(cudaStream_t stream, void* q_io, const void* k_in, con
                           const void* q_norm_w, const void* k_norm_w, const void* cos_t,
                           const void* sin_t, const uint32_t* pos_ids, const uint64_t* k_ptrs,
                           const uint64_t* v_ptrs, uint32_t batch, float eps, uint32_t* status) {
-    append_kernel<<<batch, 640, 0, stream>>>(
-        (uint16_t*)q_io, (const uint16_t*)k_in, (const uint16_t*)v_in, (const uint16_t*)q_norm_w,
-        (const uint16_t*)k_norm_w, (const uint16_t*)cos_t, (const uint16_t*)sin_t, pos_ids, k_ptrs,
-        v_ptrs, eps, status);
-    return cudaGetLastError();
+    return launch_pdl(append_kernel, dim3(batch), dim3(640), 0, stream, (uint16_t*)q_io,
+                      (const uint16_t*)k_in, (const uint16_t*)v_in, (const uint16_t*)q_norm_w,
+                      (const uint16_t*)k_norm_w, (const uint16_t*)cos_t, (const uint16_t*)sin_t, pos_ids,
+                      k_ptrs, v_ptrs, eps, status);
 }
 
 cudaError_t launch_qk_rmsnorm(cudaStream_t stream, void* x_io, const void* w, float eps,

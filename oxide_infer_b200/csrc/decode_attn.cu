@@ -127,8 +127,10 @@ decode_attn_kernel(const DecodeParams p) {
     uint32_t* s_len = prefix + MAX_ROWS + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();  // the merge kernel may be scheduled now; it waits for this grid to finish
 
     // ---- prologue: barriers, per-row range counts, prefix sum, lengths into shared memory
+    // (reads only the step's tables, which no kernel writes)
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; s++) {
             mbar_init(&full_bar[s], 1);
@@ -169,6 +171,7 @@ decode_attn_kernel(const DecodeParams p) {
     }
     __syncthreads();
     const uint32_t total_items = prefix[p.batch];
+    pdl_wait();  // K/V rows and q written by the preceding kernel are visible from here on
 
     if (warp == N_CONSUMER_WARPS) {
         // =========================== producer warp ===========================
@@ -424,43 +427,61 @@ decode_attn_kernel(const DecodeParams p) {
 // Merges the partials of every row that was covered by more than one item, and
 // resets the work counter for the next launch.
 // grid = B*4 CTAs of 4 warps: warp = one query head of one row; lane owns dims
-// 4*lane .. 4*lane+3.  All loads are independent of the arithmetic, which runs
-// in key-range order, so the result does not depend on scheduling.
+// 4*lane .. 4*lane+3.  Loads are issued in blocks of 16 key ranges, all
+// independent of the arithmetic, which runs in key-range order, so the result
+// does not depend on scheduling and the kernel costs two memory round trips.
 __global__ void __launch_bounds__(128)
 decode_merge_kernel(const DecodeParams p) {
-    if (blockIdx.x == 0 && threadIdx.x == 0) *p.work_counter = 0u;
+    pdl_launch_dependents();
     const uint32_t b = blockIdx.x >> 2;
     const int lane = threadIdx.x & 31;
     const uint32_t hd = (blockIdx.x & 3u) * 4 + (threadIdx.x >> 5);
+    // step inputs (not written by any kernel): fetched while the streaming kernel drains
     const uint32_t slen = p.seq_lens[b];
-    if (slen == 0u || slen > p.max_seq_len) return;
-    if (((p.k_ptrs[b] | p.v_ptrs[b]) & 15ull) != 0ull) return;
+    const uint64_t kvp = p.k_ptrs[b] | p.v_ptrs[b];
+    const float gate_f = p.gate ? h2f(p.gate[(size_t)b * NQ + hd]) : 0.0f;
+    pdl_wait();
+    if (blockIdx.x == 0 && threadIdx.x == 0) *p.work_counter = 0u;
+    if (slen == 0u || slen > p.max_seq_len || (kvp & 15ull) != 0ull) return;
     const uint32_t nchunks = row_chunks(slen, p.window);
     if (nchunks <= 1) return;
     const float* stats = p.partial_stats + (((size_t)b * p.max_chunks) * NQ + hd) * 2;
     const float* accs = p.partial_acc + (((size_t)b * p.max_chunks) * NQ + hd) * HD;
     float m = -1.0e30f;
     for (uint32_t cc = lane; cc < nchunks; cc += 32) m = fmaxf(m, __ldcg(stats + (size_t)cc * NQ * 2));
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    constexpr int BLK = 16;
     float l = 0.0f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-    for (uint32_t cc = 0; cc < nchunks; cc++) {
-        const float2 st = __ldcg(reinterpret_cast<const float2*>(stats + (size_t)cc * NQ * 2));
-        const float4 pv = __ldcg(reinterpret_cast<const float4*>(accs + (size_t)cc * NQ * HD) + lane);
-        const float wgt = ex2_approx_ftz(st.x - m);
-        l = fmaf(wgt, st.y, l);
-        acc.x = fmaf(wgt, pv.x, acc.x);
-        acc.y = fmaf(wgt, pv.y, acc.y);
-        acc.z = fmaf(wgt, pv.z, acc.z);
-        acc.w = fmaf(wgt, pv.w, acc.w);
+    bool have_max = false;
+    for (uint32_t c0 = 0; c0 < nchunks; c0 += BLK) {
+        float2 st[BLK];
+        float4 pv[BLK];
+#pragma unroll
+        for (int i = 0; i < BLK; i++) {
+            const uint32_t cc = min(c0 + i, nchunks - 1);  // clamped loads; weights of clamped slots are dropped
+            st[i] = __ldcg(reinterpret_cast<const float2*>(stats + (size_t)cc * NQ * 2));
+            pv[i] = __ldcg(reinterpret_cast<const float4*>(accs + (size_t)cc * NQ * HD) + lane);
+        }
+        if (!have_max) {
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+            have_max = true;
+        }
+#pragma unroll
+        for (int i = 0; i < BLK; i++) {
+            const float wgt = (c0 + i < nchunks) ? ex2_approx_ftz(st[i].x - m) : 0.0f;
+            l = fmaf(wgt, st[i].y, l);
+            acc.x = fmaf(wgt, pv[i].x, acc.x);
+            acc.y = fmaf(wgt, pv[i].y, acc.y);
+            acc.z = fmaf(wgt, pv[i].z, acc.z);
+            acc.w = fmaf(wgt, pv[i].w, acc.w);
+        }
     }
     const float inv = rcp_approx_ftz(l);
     uint16_t h[4] = {f2h(__fmul_rn(acc.x, inv)), f2h(__fmul_rn(acc.y, inv)),
                      f2h(__fmul_rn(acc.z, inv)), f2h(__fmul_rn(acc.w, inv))};
     if (p.gate) {
-        const float sig = sigmoid_ref(h2f(p.gate[(size_t)b * NQ + hd]));
+        const float sig = sigmoid_ref(gate_f);
 #pragma unroll
         for (int i = 0; i < 4; i++) h[i] = f2h(__fmul_rn(h2f(h[i]), sig));
     }
@@ -496,11 +517,10 @@ cudaError_t launch_decode_attn(cudaStream_t stream, const DecodeWorkspace& ws, v
     p.window = window;
     p.max_chunks = ws.max_chunks;
     p.max_seq_len = ws.max_seq_len;
-    decode_attn_kernel<<<ws.num_sms, dec::THREADS, dec::SMEM_BYTES, stream>>>(p);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(decode_attn_kernel, dim3(ws.num_sms), dim3(dec::THREADS), dec::SMEM_BYTES,
+                               stream, p);
     if (e != cudaSuccess) return e;
-    decode_merge_kernel<<<batch * NKV, 128, 0, stream>>>(p);
-    return cudaGetLastError();
+    return launch_pdl(decode_merge_kernel, dim3(batch * NKV), dim3(128), 0, stream, p);
 }
 
 }  // namespace oxi

@@ -28,6 +28,10 @@ struct oxi_handle {
     uint32_t* stg_pos;    // [max_batch]
     uint32_t* stg_len;    // [max_batch]
     uint32_t* host_len;   // pinned [max_batch]
+    // copy streams and events of the host-buffer entry: uploads of layer l+1 and the
+    // download of layer l-1 overlap the kernels of layer l
+    cudaStream_t h2d, d2h;
+    cudaEvent_t ev_start, ev_up[2], ev_comp[2], ev_down[2];
     size_t bytes;
 };
 
@@ -126,6 +130,17 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
         rc = cuda_fail(cudaGetLastError(), "cudaMallocHost");
         goto bad;
     }
+    {
+        cudaError_t e = cudaStreamCreateWithFlags(&h->h2d, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->d2h, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_start, cudaEventDisableTiming);
+        for (int i = 0; i < 2 && e == cudaSuccess; i++) {
+            e = cudaEventCreateWithFlags(&h->ev_up[i], cudaEventDisableTiming);
+            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_comp[i], cudaEventDisableTiming);
+            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_down[i], cudaEventDisableTiming);
+        }
+        if (e != cudaSuccess) { rc = cuda_fail(e, "stream/event creation"); goto bad; }
+    }
     if (cudaMemset(h->dws.status, 0, 256) != cudaSuccess) {
         rc = cuda_fail(cudaGetLastError(), "cudaMemset");
         goto bad;
@@ -158,6 +173,14 @@ int32_t oxi_destroy(oxi_handle* h) {
     cudaFree(h->stg_pos);
     cudaFree(h->stg_len);
     if (h->host_len) cudaFreeHost(h->host_len);
+    if (h->h2d) cudaStreamDestroy(h->h2d);
+    if (h->d2h) cudaStreamDestroy(h->d2h);
+    if (h->ev_start) cudaEventDestroy(h->ev_start);
+    for (int i = 0; i < 2; i++) {
+        if (h->ev_up[i]) cudaEventDestroy(h->ev_up[i]);
+        if (h->ev_comp[i]) cudaEventDestroy(h->ev_comp[i]);
+        if (h->ev_down[i]) cudaEventDestroy(h->ev_down[i]);
+    }
     cudaGetLastError();
     delete h;
     return OXI_OK;
@@ -313,20 +336,30 @@ int32_t oxi_decode_step_host(oxi_handle* h, void* stream, void* ctx_host, const 
     cudaStream_t s = (cudaStream_t)stream;
     const size_t qb = (size_t)batch * NQ * HD * 2, kb = (size_t)batch * NKV * HD * 2;
     const size_t gb = (size_t)batch * NQ * 2, tb = (size_t)batch * 8;
+    const cudaMemcpyKind H2D = cudaMemcpyHostToDevice;
+    // the copy streams start after everything already enqueued on the caller's stream
+    OXI_CUDA(cudaEventRecord(h->ev_start, s), "event record");
+    OXI_CUDA(cudaStreamWaitEvent(h->h2d, h->ev_start, 0), "stream wait");
+    OXI_CUDA(cudaStreamWaitEvent(h->d2h, h->ev_start, 0), "stream wait");
     // step metadata: positions and lengths (seq_len counts the appended token)
     for (uint32_t i = 0; i < batch; i++) h->host_len[i] = pos_ids_host[i] + 1u;
-    OXI_CUDA(cudaMemcpyAsync(h->stg_pos, pos_ids_host, (size_t)batch * 4, cudaMemcpyHostToDevice, s), "pos upload");
-    OXI_CUDA(cudaMemcpyAsync(h->stg_len, h->host_len, (size_t)batch * 4, cudaMemcpyHostToDevice, s), "len upload");
+    OXI_CUDA(cudaMemcpyAsync(h->stg_pos, pos_ids_host, (size_t)batch * 4, H2D, h->h2d), "pos upload");
+    OXI_CUDA(cudaMemcpyAsync(h->stg_len, h->host_len, (size_t)batch * 4, H2D, h->h2d), "len upload");
     for (uint32_t l = 0; l < layers; l++) {
         const int sb = l & 1;
-        const char* qh = (const char*)q_host + l * qb;
-        OXI_CUDA(cudaMemcpyAsync(h->stg_q[sb], qh, qb, cudaMemcpyHostToDevice, s), "q upload");
-        OXI_CUDA(cudaMemcpyAsync(h->stg_k[sb], (const char*)k_host + l * kb, kb, cudaMemcpyHostToDevice, s), "k upload");
-        OXI_CUDA(cudaMemcpyAsync(h->stg_v[sb], (const char*)v_host + l * kb, kb, cudaMemcpyHostToDevice, s), "v upload");
+        // uploads of layer l reuse the staging set of layer l-2: wait until its kernels are done
+        if (l >= 2) OXI_CUDA(cudaStreamWaitEvent(h->h2d, h->ev_comp[sb], 0), "stream wait");
+        OXI_CUDA(cudaMemcpyAsync(h->stg_q[sb], (const char*)q_host + l * qb, qb, H2D, h->h2d), "q upload");
+        OXI_CUDA(cudaMemcpyAsync(h->stg_k[sb], (const char*)k_host + l * kb, kb, H2D, h->h2d), "k upload");
+        OXI_CUDA(cudaMemcpyAsync(h->stg_v[sb], (const char*)v_host + l * kb, kb, H2D, h->h2d), "v upload");
         if (gate_host)
-            OXI_CUDA(cudaMemcpyAsync(h->stg_gate[sb], (const char*)gate_host + l * gb, gb, cudaMemcpyHostToDevice, s), "gate upload");
-        OXI_CUDA(cudaMemcpyAsync(h->stg_kp[sb], k_ptrs_host + (size_t)l * batch, tb, cudaMemcpyHostToDevice, s), "k_ptrs upload");
-        OXI_CUDA(cudaMemcpyAsync(h->stg_vp[sb], v_ptrs_host + (size_t)l * batch, tb, cudaMemcpyHostToDevice, s), "v_ptrs upload");
+            OXI_CUDA(cudaMemcpyAsync(h->stg_gate[sb], (const char*)gate_host + l * gb, gb, H2D, h->h2d), "gate upload");
+        OXI_CUDA(cudaMemcpyAsync(h->stg_kp[sb], k_ptrs_host + (size_t)l * batch, tb, H2D, h->h2d), "k_ptrs upload");
+        OXI_CUDA(cudaMemcpyAsync(h->stg_vp[sb], v_ptrs_host + (size_t)l * batch, tb, H2D, h->h2d), "v_ptrs upload");
+        OXI_CUDA(cudaEventRecord(h->ev_up[sb], h->h2d), "event record");
+        OXI_CUDA(cudaStreamWaitEvent(s, h->ev_up[sb], 0), "stream wait");
+        // the ctx staging buffer of layer l-2 must have been downloaded
+        if (l >= 2) OXI_CUDA(cudaStreamWaitEvent(s, h->ev_down[sb], 0), "stream wait");
         OXI_CUDA(launch_append(s, h->stg_q[sb], h->stg_k[sb], h->stg_v[sb],
                                (const char*)q_norm_w_dev + (size_t)l * HD * 2,
                                (const char*)k_norm_w_dev + (size_t)l * HD * 2, cos_table_dev,
@@ -337,8 +370,15 @@ int32_t oxi_decode_step_host(oxi_handle* h, void* stream, void* ctx_host, const 
                                     gate_host ? h->stg_gate[sb] : nullptr, h->stg_kp[sb],
                                     h->stg_vp[sb], h->stg_len, batch, window),
                  "decode_attn launch");
-        OXI_CUDA(cudaMemcpyAsync((char*)ctx_host + l * qb, h->stg_ctx[sb], qb, cudaMemcpyDeviceToHost, s), "ctx download");
+        OXI_CUDA(cudaEventRecord(h->ev_comp[sb], s), "event record");
+        OXI_CUDA(cudaStreamWaitEvent(h->d2h, h->ev_comp[sb], 0), "stream wait");
+        OXI_CUDA(cudaMemcpyAsync((char*)ctx_host + l * qb, h->stg_ctx[sb], qb, cudaMemcpyDeviceToHost, h->d2h),
+                 "ctx download");
+        OXI_CUDA(cudaEventRecord(h->ev_down[sb], h->d2h), "event record");
     }
+    // the caller's stream completes only after the last downloads
+    OXI_CUDA(cudaStreamWaitEvent(s, h->ev_down[(layers - 1) & 1], 0), "stream wait");
+    if (layers >= 2) OXI_CUDA(cudaStreamWaitEvent(s, h->ev_down[layers & 1], 0), "stream wait");
     return OXI_OK;
 }
 
