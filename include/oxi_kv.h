@@ -178,6 +178,36 @@ int32_t oxi_decode_step_host(oxi_handle* h, void* stream, void* ctx_host, const 
                              const uint64_t* v_ptrs_host, uint32_t batch, uint32_t layers,
                              uint32_t window, float eps);
 
+/* ---- entry point that allocates nothing -------------------------------- */
+
+#define OXI_STATIC_MAX_BATCH 16u      /* rows per call                         */
+#define OXI_STATIC_MAX_SEQ_LEN 4096u  /* keys per row, the appended one included */
+
+/* oxi_decode_attn for callers that cannot allocate device memory (and hence
+ * cannot call oxi_create): plugins inside a foreign memory budget, callbacks
+ * that run while the application's allocator is locked, processes that gave
+ * all device memory to their own pool.  It has no counterpart in the
+ * reference, whose engine allocates all scratch in BatchEngine::new.
+ *
+ * Same inputs, outputs and arithmetic as oxi_decode_attn, no handle.  The
+ * split-KV partials, the work counter and the status word live in a ~2.1 MB
+ * array inside the library image (held by every GPU that loads the library
+ * until the process exits); the call performs no cudaMalloc / cudaFree and
+ * calls no allocating library routine.
+ *   - batch <= OXI_STATIC_MAX_BATCH, else OXI_ERR_BATCH; max_seq_len (the
+ *     caller's bound on every seq_lens[b]) <= OXI_STATIC_MAX_SEQ_LEN, else
+ *     OXI_ERR_ARG.  A row whose seq_len exceeds max_seq_len is skipped.
+ *   - The device current on the calling thread is used.  The FIRST call on a
+ *     device also resolves the array's device address and sets the kernel's
+ *     shared-memory attribute; make that first call outside any stream capture.
+ *   - All calls on one device share the array: calls whose kernels can overlap
+ *     on the GPU (different streams without ordering between them) race.  Calls
+ *     on one stream are ordered and safe. */
+int32_t oxi_decode_attn_static(void* stream, void* ctx_out, const void* q, const void* gate,
+                               const uint64_t* k_ptrs, const uint64_t* v_ptrs,
+                               const uint32_t* seq_lens, uint32_t batch, uint32_t max_seq_len,
+                               uint32_t window);
+
 #ifdef __cplusplus
 }
 #endif

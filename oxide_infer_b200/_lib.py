@@ -30,6 +30,7 @@ SIGNATURES = {
     "oxi_kv_copy": [_vp] * 5 + [_u32],
     "oxi_sigmoid_gate": [_vp] * 4 + [_u32],
     "oxi_decode_step_host": [_vp] * 14 + [_u32, _u32, _u32, _f32],
+    "oxi_decode_attn_static": [_vp] * 7 + [_u32, _u32, _u32],
 }
 _RESTYPE = {"oxi_status_string": C.c_char_p, "oxi_last_error_string": C.c_char_p,
             "oxi_workspace_bytes": C.c_size_t}

@@ -41,6 +41,9 @@
 // the gate exactly as the reference's gate kernel does on the f16 context, and
 // resets the work counter.  Nothing spins on another CTA; the only waits are on
 // this CTA's own mbarriers and they are time-bounded.
+#include <mutex>
+
+#include "../../include/oxi_kv.h"
 #include "common.cuh"
 #include "kernels.h"
 
@@ -524,3 +527,89 @@ cudaError_t launch_decode_attn(cudaStream_t stream, const DecodeWorkspace& ws, v
 }
 
 }  // namespace oxi
+
+// ---------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate device memory.
+//
+// Some hosts of this library may not call cudaMalloc at the point where they
+// need attention: a plugin running inside someone else's memory budget, a
+// callback that executes while the application's allocator is locked, a
+// process that handed all device memory to its own pool at start-up.  They
+// also cannot create an oxi_handle, because oxi_create allocates.  For them the
+// split-KV partials, the work counter and the status word live in the array
+// below, which is part of the library image: every GPU that loads liboxi_kv
+// holds these ~2.1 MB from module load until the process exits.
+namespace oxi {
+namespace nalloc {
+constexpr uint32_t MAX_ROWS = OXI_STATIC_MAX_BATCH;
+constexpr uint32_t MAX_CHUNKS = (OXI_STATIC_MAX_SEQ_LEN + dec::CHUNK - 1) / dec::CHUNK;
+constexpr size_t CTRL_BYTES = 256;  // status word at +0, work counter at +128
+constexpr size_t ACC_BYTES = (size_t)MAX_ROWS * MAX_CHUNKS * NQ * HD * sizeof(float);
+constexpr size_t STATS_BYTES = (size_t)MAX_ROWS * MAX_CHUNKS * NQ * 2 * sizeof(float);
+constexpr size_t TOTAL_BYTES = CTRL_BYTES + ACC_BYTES + STATS_BYTES;
+constexpr int MAX_DEVICES = 64;
+
+struct PerDevice {
+    bool ready = false;
+    unsigned char* base = nullptr;  // DEVICE address of g_scratch on that device
+    int num_sms = 0;
+};
+}  // namespace nalloc
+}  // namespace oxi
+
+// In host code this name is only a stand-in for the symbol; the device address is obtained
+// with cudaGetSymbolAddress below, once per device, and that address is what kernels receive.
+static __device__ __align__(256) unsigned char g_scratch[oxi::nalloc::TOTAL_BYTES];
+
+static oxi::nalloc::PerDevice g_nalloc_dev[oxi::nalloc::MAX_DEVICES];
+static std::mutex g_nalloc_mutex;
+
+extern "C" int32_t oxi_decode_attn_static(void* stream, void* ctx_out, const void* q, const void* gate,
+                                          const uint64_t* k_ptrs, const uint64_t* v_ptrs,
+                                          const uint32_t* seq_lens, uint32_t batch,
+                                          uint32_t max_seq_len, uint32_t window) {
+    using namespace oxi;
+    if (!ctx_out || !q || !k_ptrs || !v_ptrs || !seq_lens) return OXI_ERR_NULL;
+    if (batch == 0 || batch > nalloc::MAX_ROWS) return OXI_ERR_BATCH;
+    if (max_seq_len == 0 || max_seq_len > OXI_STATIC_MAX_SEQ_LEN) return OXI_ERR_ARG;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int32_t)e;
+    if (dev < 0 || dev >= nalloc::MAX_DEVICES) return OXI_ERR_NO_DEVICE;
+    nalloc::PerDevice& pd = g_nalloc_dev[dev];
+    {
+        // First call on this device: resolve the scratch array's device address and size the
+        // kernel's shared memory.  Neither call allocates; both must happen outside stream capture.
+        std::lock_guard<std::mutex> lock(g_nalloc_mutex);
+        if (!pd.ready) {
+            void* ptr = nullptr;
+            e = cudaGetSymbolAddress(&ptr, g_scratch);
+            if (e != cudaSuccess) return (int32_t)e;
+            int sms = 0, major = 0;
+            e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (e == cudaSuccess) e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+            if (e != cudaSuccess) return (int32_t)e;
+            if (major != 10) return OXI_ERR_NO_DEVICE;
+            e = decode_attn_init();
+            if (e != cudaSuccess) return (int32_t)e;
+            pd.base = static_cast<unsigned char*>(ptr);
+            pd.num_sms = sms;
+            pd.ready = true;
+        }
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // The array keeps whatever the previous call left: the control block must start at zero.
+    e = cudaMemsetAsync(pd.base, 0, nalloc::CTRL_BYTES, s);
+    if (e != cudaSuccess) return (int32_t)e;
+    DecodeWorkspace ws;
+    ws.status = reinterpret_cast<uint32_t*>(pd.base);
+    ws.work_counter = reinterpret_cast<uint32_t*>(pd.base + 128);
+    ws.partial_acc = reinterpret_cast<float*>(pd.base + nalloc::CTRL_BYTES);
+    ws.partial_stats = reinterpret_cast<float*>(pd.base + nalloc::CTRL_BYTES + nalloc::ACC_BYTES);
+    ws.max_chunks = nalloc::MAX_CHUNKS;
+    ws.max_seq_len = max_seq_len;
+    ws.num_sms = pd.num_sms;
+    e = launch_decode_attn(s, ws, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, batch, window);
+    return (int32_t)e;
+}
+
