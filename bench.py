@@ -406,6 +406,144 @@ def run_reference(args, torch, rank, world, local_rank):
     return line
 
 
+# ---------------------------------------------------------------------------
+# Secondary workloads (not the headline line): conv-state path (config 3) and the
+# chunked-prefill wave (config 4).  One GPU; both arms are timed in the same run.
+
+def _time_loop(torch, fn, steps, warmup):
+    stream = torch.cuda.current_stream()
+    for _ in range(max(3, warmup)):
+        fn()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record(stream)
+    for _ in range(steps):
+        fn()
+    t1.record(stream)
+    torch.cuda.synchronize()
+    return t0.elapsed_time(t1) / steps
+
+
+def run_conv(args, torch):
+    """Config 3: 16 conv layers, batch 128, 2048 channels, 7 taps, 6-slot fp16 carry state per
+    (layer, sequence) behind conv_ptrs; one decode update per layer."""
+    from oxide_infer_b200 import KvPath
+    from oracle import refptx
+    nl, b, hid = 16, 128, 2048
+    kv = KvPath(0, max_batch=b, max_seq_len=4096, max_prefill_rows=16)
+    g = torch.Generator(device="cuda").manual_seed(3)
+    rn = lambda *s, sc=1.0: (torch.randn(*s, device="cuda", generator=g) * sc).half()
+    state = rn(nl, b, hid, 6)
+    bcx = rn(nl, b, 3 * hid)
+    w = rn(nl, hid, 7, sc=0.1)
+    y = torch.zeros(nl, b, hid, dtype=torch.float16, device="cuda")
+    ptrs = torch.tensor([[state[l, i].data_ptr() for i in range(b)] for l in range(nl)], dtype=torch.int64, device="cuda")
+    sampler = ClockSampler(0)
+    sampler.start()
+
+    def ours():
+        for l in range(nl):
+            kv.conv_decode(y[l], ptrs[l], bcx[l], w[l])
+    w0 = time.perf_counter()
+    ms = _time_loop(torch, ours, args.steps, args.warmup)
+    clocks = sampler.window(w0, time.perf_counter())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ours()
+    ms_graph = _time_loop(torch, graph.replay, args.steps, args.warmup)
+    ms_ref = None
+    if refptx.available():
+        ref = refptx.RefPtx()
+        ms_ref = _time_loop(torch, lambda: [ref.conv_decode(y[l], ptrs[l], bcx[l], w[l], b) for l in range(nl)],
+                            args.steps, args.warmup)
+    sampler.stop()
+    step_bytes = nl * (b * 65536 + 28672)
+    peak, kind = measured_peak_gbs()
+    return {"metric": "conv_state_decode_hbm_gbs", "value": round(step_bytes / (ms_graph * 1e-3) / 1e9, 1), "unit": "GB/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_graph, 4),
+            "us_per_layer": round(ms_graph / nl * 1e3, 2), "us_per_layer_stream_launches": round(ms / nl * 1e3, 2),
+            "higher_is_better": True, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "conv_decode_16_layers_B128_2048ch_K7", "note": "value is the 16-layer sequence replayed as a CUDA graph"},
+            "roofline": {"kernel": "conv_decode_kernel", "bound": "hbm", "achieved": round(step_bytes / (ms_graph * 1e-3) / 1e9, 1),
+                         "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": round(step_bytes / (ms_graph * 1e-3) / 1e9 / peak, 4),
+                         "note": "8.4 MB per launch: launch-latency bound, not bandwidth bound"},
+            "reference_kernels_us_per_layer": None if ms_ref is None else round(ms_ref / nl * 1e3, 2),
+            "gpu_launches": nl * args.steps, "clocks": clocks, "device_status": kv.device_status()}
+
+
+def run_prefill(args, torch):
+    """Config 4: one wave of 128 new tokens for each of 32 sequences, prefixes uniform 0..8192
+    (seeded), one attention layer: append of the 4096 wave rows, then causal gated GQA attention."""
+    import numpy as np
+    from oxide_infer_b200 import KvPath, rotary_tables
+    from oracle import refptx
+    nseq, new = 32, 128
+    rows = nseq * new
+    rng = np.random.default_rng(4)
+    prefix = rng.integers(0, 8193, nseq)
+    kv = KvPath(0, max_batch=128, max_seq_len=8192 + new, max_prefill_rows=rows)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    rn = lambda *s: torch.empty(*s, dtype=torch.float16, device="cuda").normal_(generator=g)
+    kc = [rn(int(p) + new, NKV, HD) for p in prefix]
+    vc = [rn(int(p) + new, NKV, HD) for p in prefix]
+    q0, k, v, gate = rn(rows, NQ, HD), rn(rows, NKV, HD), rn(rows, NKV, HD), rn(rows, NQ)
+    q = q0.clone()
+    qw = (1 + 0.02 * torch.randn(HD, device="cuda", generator=g)).half()
+    kw = (1 + 0.02 * torch.randn(HD, device="cuda", generator=g)).half()
+    cos, sin = rotary_tables(8192 + new, 1e6, 0.5)
+    cos, sin = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
+    owner = np.repeat(np.arange(nseq), new)
+    pos = (prefix[owner] + np.tile(np.arange(new), nseq)).astype(np.int32)
+    kp = torch.tensor([kc[i].data_ptr() for i in owner], dtype=torch.int64, device="cuda")
+    vp = torch.tensor([vc[i].data_ptr() for i in owner], dtype=torch.int64, device="cuda")
+    dpos = torch.from_numpy(pos).cuda()
+    dlen = torch.from_numpy(pos + 1).cuda()
+    ctx = torch.zeros(rows, NQ, HD, dtype=torch.float16, device="cuda")
+    sampler = ClockSampler(0)
+    sampler.start()
+
+    def attn():
+        kv.prefill_attn(ctx, q, gate, kp, vp, dlen, 0)
+
+    def wave():
+        kv.append(q, k, v, qw, kw, cos, sin, dpos, kp, vp, batch=rows)
+        attn()
+    w0 = time.perf_counter()
+    ms_wave = _time_loop(torch, wave, args.steps, args.warmup)
+    ms_attn = _time_loop(torch, attn, args.steps, args.warmup)
+    clocks = sampler.window(w0, time.perf_counter())
+    ms_ref = None
+    if refptx.available():
+        ref = refptx.RefPtx()
+        rctx = torch.zeros_like(ctx)
+
+        def ref_attn():  # the reference's non-GEMM path: online kernel over all rows + gate (BE:1214-1239)
+            ref.attn_online(rctx, q, kp, vp, dlen, rows, 0)
+            ref.sigmoid_gate(rctx, gate, rows)
+        ms_ref = _time_loop(torch, ref_attn, max(3, args.steps // 4), 3)
+    sampler.stop()
+    flops = float(sum(8192 * (128 * int(p) + 8256) for p in prefix))
+    kv_bytes = float(sum(2048 * (int(p) + new) for p in prefix)) + rows * (4096 + 4096 + 32)
+    peak_tf = 1354.7
+    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    kind = "fallback"
+    if os.path.exists(pk):
+        try:
+            peak_tf, kind = float(json.load(open(pk))["bf16_tflops_sustained"]), "measured"
+        except Exception:
+            pass
+    tf = flops / (ms_attn * 1e-3) / 1e12
+    return {"metric": "prefill_attention_tflops", "value": round(tf, 2), "unit": "TFLOP/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_wave, 4),
+            "ms_attention_only": round(ms_attn, 4), "higher_is_better": True, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "prefill_wave_32seq_x128tok_prefix_U0_8192_one_layer", "rows": rows,
+                       "prefix_sum": int(prefix.sum()), "causal_exact_flops": flops, "algorithmic_bytes": kv_bytes},
+            "roofline": {"kernel": "prefill_attn_kernel", "bound": "tensor", "achieved": round(tf, 2), "peak": peak_tf,
+                         "peak_kind": kind, "unit": "TFLOP/s", "frac": round(tf / peak_tf, 4)},
+            "reference_online_plus_gate_ms": None if ms_ref is None else round(ms_ref, 4),
+            "gpu_launches": 3 * args.steps, "clocks": clocks, "device_status": kv.device_status()}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -417,6 +555,8 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="override for small profiling cases")
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--ctx", type=int, default=CTX)
+    ap.add_argument("--workload", default="decode", choices=["decode", "conv", "prefill"],
+                    help="decode = the headline line; conv / prefill = secondary single-GPU lines")
     args = ap.parse_args()
     globals().update(LAYERS=args.layers, BATCH=args.batch, CTX=args.ctx)
     args.warmup = max(args.warmup, 3)
@@ -434,7 +574,12 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        line = (run_ours if args.impl == "ours" else run_reference)(args, torch, rank, world, local_rank)
+        if args.workload == "conv":
+            line = run_conv(args, torch) if rank == 0 else None
+        elif args.workload == "prefill":
+            line = run_prefill(args, torch) if rank == 0 else None
+        else:
+            line = (run_ours if args.impl == "ours" else run_reference)(args, torch, rank, world, local_rank)
         if line is not None:
             print(json.dumps(line), flush=True)
     finally:

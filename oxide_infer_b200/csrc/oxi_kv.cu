@@ -213,7 +213,7 @@ int32_t oxi_append(oxi_handle* h, void* stream, void* q_io, const void* k_in, co
     REQ_HANDLE("oxi_append");
     REQ_PTR(q_io && k_in && v_in && q_norm_w && k_norm_w && cos_table && sin_table && pos_ids &&
                 k_ptrs && v_ptrs, "oxi_append");
-    REQ_BATCH(batch, h->max_batch, "oxi_append");
+    REQ_BATCH(batch, (h->max_batch > h->max_prefill_rows ? h->max_batch : h->max_prefill_rows), "oxi_append");
     if (!(eps >= 0.0f)) return fail(OXI_ERR_ARG, "oxi_append: eps must be >= 0");
     OXI_CUDA(launch_append((cudaStream_t)stream, q_io, k_in, v_in, q_norm_w, k_norm_w, cos_table,
                            sin_table, pos_ids, k_ptrs, v_ptrs, batch, eps, h->dws.status),
