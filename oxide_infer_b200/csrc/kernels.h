@@ -41,7 +41,9 @@ cudaError_t prefill_attn_init();
 cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* q,
                                 const void* gate, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
                                 const uint32_t* seq_lens, uint32_t rows, uint32_t window,
-                                uint32_t* status, int num_sms);
+                                uint32_t* status, int num_sms,
+                                uint32_t* order /* [ceil(rows/32)] block order scratch */,
+                                uint32_t* counter /* item claim counter */);
 
 cudaError_t launch_conv_decode(cudaStream_t stream, void* y_out, const uint64_t* conv_ptrs,
                                const void* bcx, const void* conv_w, uint32_t batch,

@@ -17,6 +17,7 @@ struct oxi_handle {
     uint32_t max_batch, max_seq_len, max_prefill_rows;
     DecodeWorkspace dws;
     void* conv_stage;     // [max_prefill_rows][2048][6] f16
+    uint32_t* pf_order;   // [ceil(max_prefill_rows/32)] prefill block order
     // staging for the host-buffer entry, one layer at a time, double buffered
     void* stg_q[2];       // [max_batch][16][128]
     void* stg_k[2];       // [max_batch][4][128]
@@ -113,8 +114,10 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
     if ((rc = dev_alloc(h, (void**)&h->dws.partial_stats, slots * 2 * sizeof(float)))) goto bad;
     if ((rc = dev_alloc(h, (void**)&h->dws.status, 256))) goto bad;
     h->dws.work_counter = h->dws.status + 32;  // same zero-initialised 256-byte block, own 128-byte line
-    if (max_prefill_rows)
+    if (max_prefill_rows) {
         if ((rc = dev_alloc(h, &h->conv_stage, (size_t)max_prefill_rows * HIDDEN * CONV_S * 2))) goto bad;
+        if ((rc = dev_alloc(h, (void**)&h->pf_order, ((size_t)max_prefill_rows / 32 + 1) * sizeof(uint32_t)))) goto bad;
+    }
     for (int i = 0; i < 2; i++) {
         if ((rc = dev_alloc(h, &h->stg_q[i], (size_t)max_batch * NQ * HD * 2))) goto bad;
         if ((rc = dev_alloc(h, &h->stg_k[i], (size_t)max_batch * NKV * HD * 2))) goto bad;
@@ -165,6 +168,7 @@ int32_t oxi_destroy(oxi_handle* h) {
     cudaFree(h->dws.partial_stats);
     cudaFree(h->dws.status);
     cudaFree(h->conv_stage);
+    cudaFree(h->pf_order);
     for (int i = 0; i < 2; i++) {
         cudaFree(h->stg_q[i]); cudaFree(h->stg_k[i]); cudaFree(h->stg_v[i]);
         cudaFree(h->stg_gate[i]); cudaFree(h->stg_ctx[i]);
@@ -252,7 +256,7 @@ int32_t oxi_prefill_attn(oxi_handle* h, void* stream, void* ctx_out, const void*
     REQ_PTR(ctx_out && q && k_ptrs && v_ptrs && seq_lens, "oxi_prefill_attn");
     REQ_BATCH(rows, h->max_prefill_rows, "oxi_prefill_attn");
     OXI_CUDA(launch_prefill_attn((cudaStream_t)stream, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens,
-                                 rows, window, h->dws.status, h->num_sms),
+                                 rows, window, h->dws.status, h->num_sms, h->pf_order, h->dws.status + 48),
              "prefill_attn launch");
     return OXI_OK;
 }

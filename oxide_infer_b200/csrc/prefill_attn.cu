@@ -22,9 +22,13 @@
 // from shared memory, both K-major with the 128-byte swizzle, D = S in TMEM)
 // -> each thread loads its S row (tcgen05.ld), applies scale, causal/window
 // mask and the online-softmax update, writes P as f16 back to TMEM
-// (tcgen05.st) -> O_tile = P V (tcgen05.mma, A = P from TMEM, B = V tile from
-// shared memory, MN-major) -> each thread adds its O_tile row into its f32
-// accumulator registers (rescaled by the softmax correction while the MMA runs).
+// (tcgen05.st) -> O += P V (tcgen05.mma, A = P from TMEM, B = V tile from shared
+// memory, MN-major, D = O accumulating in TMEM across all tiles).
+// The running maximum used for the exponentials is only raised when a tile's
+// maximum exceeds it by more than 2^8 (then the thread rescales its O row in
+// TMEM); otherwise the stale maximum is kept, which is exact after the final
+// division by the row sum and keeps O untouched between MMAs.
+// The tensor core runs PV(j) and QK(j+1) back to back while the threads wait;
 // K/V tiles are double buffered with cp.async (16-byte chunks written straight
 // into the swizzled layout, zero-filled past the run's last key).  Two CTAs are
 // resident per SM (256 of the 512 TMEM columns each), so one CTA's softmax
@@ -53,8 +57,9 @@ constexpr int KV_TILE = 2 * KV_SUB;          // 16 KB
 constexpr int STAGE = 2 * KV_TILE;           // K then V: 32 KB
 constexpr int NBUF = 2;
 constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + NBUF * STAGE;  // + slack for 1024-byte alignment
-constexpr uint32_t TMEM_COLS = 256;          // S [0,64) | O_tile [64,192) | P [192,224)
-constexpr uint32_t S_COL = 0, O_COL = 64, P_COL = 192;
+constexpr uint32_t TMEM_COLS = 256;          // S [0,64) | P [64,96) | O [128,256)
+constexpr uint32_t S_COL = 0, P_COL = 64, O_COL = 128;
+constexpr float RESCALE_THRESHOLD = 8.0f;    // log2 units: the stale maximum may lag by a factor 256
 constexpr float QK_SCALE_LOG2 = ATTN_SCALE * LOG2E;
 // instruction descriptors (kind::f16): D = f32, A = B = f16, M = 128
 constexpr uint32_t IDESC_QK = (1u << 4) | ((uint32_t)(TK >> 3) << 17) | ((uint32_t)(M >> 4) << 24);          // N = 64, A and B K-major
@@ -123,29 +128,115 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// Orders the 32-row blocks of the wave by decreasing work (key tiles to scan) with a counting
+// sort, so that the persistent CTAs of the main kernel claim the longest items first, and
+// resets the claim counter.  One CTA.
+__global__ void __launch_bounds__(1024)
+prefill_plan_kernel(const uint32_t* __restrict__ seq_lens, uint32_t rows, uint32_t window,
+                    uint32_t* __restrict__ order, uint32_t* __restrict__ counter) {
+    using namespace pf;
+    constexpr int NB = 1024;
+    __shared__ uint32_t hist[NB];
+    __shared__ uint32_t warp_tot[32];
+    const uint32_t nblocks = (rows + TOK - 1) / TOK;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    hist[tid] = 0u;
+    if (tid == 0) *counter = 0u;
+    __syncthreads();
+    auto key_of = [&](uint32_t blk) {
+        uint32_t lo = 0xffffffffu, hi = 0;
+        const uint32_t r1 = min(rows, (blk + 1) * TOK);
+        for (uint32_t r = blk * TOK; r < r1; r++) {
+            const uint32_t sl = seq_lens[r];
+            if (sl == 0) continue;
+            lo = min(lo, window_start(sl, window));
+            hi = max(hi, sl);
+        }
+        const uint32_t tiles = hi > lo ? (hi - lo + TK - 1) / TK : 0u;
+        return (uint32_t)(NB - 1) - min(tiles, (uint32_t)(NB - 1));  // bucket 0 = most work
+    };
+    for (uint32_t blk = tid; blk < nblocks; blk += 1024) atomicAdd(&hist[key_of(blk)], 1u);
+    __syncthreads();
+    // exclusive prefix sum of the 1024 buckets
+    uint32_t v = hist[tid], incl = v;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += t;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        uint32_t w = warp_tot[lane], wi = w;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const uint32_t t = __shfl_up_sync(0xffffffffu, wi, off);
+            if (lane >= off) wi += t;
+        }
+        warp_tot[lane] = wi - w;
+    }
+    __syncthreads();
+    hist[tid] = warp_tot[warp] + incl - v;
+    __syncthreads();
+    for (uint32_t blk = tid; blk < nblocks; blk += 1024) order[atomicAdd(&hist[key_of(blk)], 1u)] = blk;
+}
+
 __global__ void __launch_bounds__(pf::THREADS, 2)
 prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__ q,
                     const uint16_t* __restrict__ gate, const uint64_t* __restrict__ k_ptrs,
                     const uint64_t* __restrict__ v_ptrs, const uint32_t* __restrict__ seq_lens,
-                    uint32_t rows, uint32_t window, uint32_t* __restrict__ status) {
+                    uint32_t rows, uint32_t window, uint32_t* __restrict__ status,
+                    const uint32_t* __restrict__ order, uint32_t* __restrict__ counter) {
     using namespace pf;
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint64_t s_kp[TOK], s_vp[TOK];
     __shared__ uint32_t s_len[TOK];
     __shared__ __align__(8) uint64_t bar_s, bar_o;
-    __shared__ uint32_t s_tmem, s_abort;
+    __shared__ uint32_t s_tmem, s_abort, s_item;
 
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;  // 1024-byte aligned tiles
     const uint32_t q_s = sbase;
     const uint32_t kv_s = sbase + Q_BYTES;
-
-    const uint32_t row0 = blockIdx.x * TOK;
-    const int kvh = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t nitems = ((rows + TOK - 1) / TOK) * NKV;
+
+    // ---- once per CTA: TMEM allocation, barriers
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (tid == 0) {
+        mbar_init(&bar_s, 1);
+        mbar_init(&bar_o, 1);
+        s_abort = 0u;
+        mbar_fence_init();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+    uint32_t par_s = 0, par_o = 0;
+    bool ok = true;
+
+    // per-thread constants of the tile loaders: this thread copies chunk c of rows r0, r0+8, ...
+    const uint32_t ld_r0 = tid >> 4, ld_c = tid & 15u;
+    const uint32_t ld_soff = (ld_c >> 3) * KV_SUB + ld_r0 * ROW_B + (((ld_c & 7u) ^ (ld_r0 & 7u)) << 4);
+
+  // ======== persistent loop over (32-row block, KV head) items, longest first ========
+  for (;;) {
+    tc_fence_before();
+    __syncthreads();  // the previous item's tables, Q tile and TMEM contents are no longer in use
+    if (tid == 0) s_item = atomicAdd(counter, 1u);
+    __syncthreads();
+    const uint32_t item = s_item;
+    if (item >= nitems) break;
+    const uint32_t row0 = order[item >> 2] * TOK;
+    const int kvh = item & 3u;
     const int head = kvh * 4 + warp;          // this thread's query head
     const uint32_t nrows = min((uint32_t)TOK, rows - row0);
 
-    // ---- tables of the block's rows, TMEM allocation, barriers
+    // ---- tables of the block's rows
     if (tid < TOK) {
         uint64_t kp = 0, vp = 0;
         uint32_t sl = 0;
@@ -165,16 +256,6 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         s_vp[tid] = vp;
         s_len[tid] = sl;  // 0 marks a row that is skipped
     }
-    if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    if (tid == 0) {
-        mbar_init(&bar_s, 1);
-        mbar_init(&bar_o, 1);
-        s_abort = 0u;
-        mbar_fence_init();
-    }
     // ---- Q tile: row = head*32 + token, two 64-dim halves, 16-byte chunks swizzled by (row & 7)
     for (uint32_t i = tid; i < (uint32_t)M * 16u; i += THREADS) {
         const uint32_t r = i >> 4, c = i & 15u;
@@ -184,30 +265,36 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         cp_async_16(q_s + (c >> 3) * Q_SUB + r * ROW_B + (((c & 7u) ^ (r & 7u)) << 4), src, valid);
     }
     cp_async_commit();
-    tc_fence_before();
     __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = s_tmem;
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
 
-    float acc[HD];
+    float m_ref = -1.0e30f, l_run = 0.0f;  // maximum used for the exponentials (may be stale), row sum
+    bool o_valid = false;   // O in TMEM holds a sum (false until the CTA's first PV)
+    bool pv_pending = false;  // a PV MMA has been committed to bar_o and not yet waited for
+
+    auto issue_qk = [&](uint32_t ks) {  // S = Q K^T, 128 dims = 8 k-steps of 16
 #pragma unroll
-    for (int d = 0; d < HD; d++) acc[d] = 0.0f;
-    float m_run = -1.0e30f, l_run = 0.0f;
-    uint32_t par_s = 0, par_o = 0;
-    bool ok = true;
+        for (int kk = 0; kk < 8; kk++) {
+            const uint64_t ad = umma_desc(q_s + (kk >> 2) * Q_SUB + (kk & 3) * 32, 16, 1024);
+            const uint64_t bd = umma_desc(ks + (kk >> 2) * KV_SUB + (kk & 3) * 32, 16, 1024);
+            umma_ss(tmem + S_COL, ad, bd, IDESC_QK, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&bar_s);
+    };
 
     // ---- runs of rows that share one cache
     uint32_t run0 = 0;
     while (run0 < nrows) {
         uint32_t run1 = run0 + 1;
         while (run1 < nrows && s_kp[run1] == s_kp[run0] && s_vp[run1] == s_vp[run0]) run1++;
-        uint32_t lo = 0xffffffffu, hi = 0;
+        uint32_t lo = 0xffffffffu, hi = 0, lo_max = 0, hi_min = 0xffffffffu;
+        bool full_run = (run1 - run0 == (uint32_t)TOK);  // every row of the M tile belongs to the run
         for (uint32_t i = run0; i < run1; i++) {
             const uint32_t sl = s_len[i];
-            if (sl == 0) continue;
+            if (sl == 0) { full_run = false; continue; }
             lo = min(lo, window_start(sl, window));
             hi = max(hi, sl);
+            lo_max = max(lo_max, window_start(sl, window));
+            hi_min = min(hi_min, sl);
         }
         if (hi > lo) {
             // this thread's row (token = lane): valid key interval inside the run, empty if not in the run
@@ -218,136 +305,192 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
             const char* vbase = reinterpret_cast<const char*>(s_vp[run0]) + kvh * (HD * 2);
             const uint32_t ntiles = (hi - lo + TK - 1) / TK;
 
-            auto load_tile = [&](uint32_t tile, uint32_t buf) {
-                const uint32_t kbeg = lo + tile * TK;
-                const uint32_t ks = kv_s + buf * STAGE, vs = ks + KV_TILE;
-                for (uint32_t i = tid; i < (uint32_t)TK * 16u; i += THREADS) {
-                    const uint32_t r = i >> 4, c = i & 15u;
-                    const bool valid = kbeg + r < hi;
-                    const size_t goff = (size_t)(valid ? kbeg + r : lo) * KV_ROW_BYTES + c * 16;
-                    const uint32_t soff = (c >> 3) * KV_SUB + r * ROW_B + (((c & 7u) ^ (r & 7u)) << 4);
-                    cp_async_16(ks + soff, kbase + goff, valid);
-                    cp_async_16(vs + soff, vbase + goff, valid);
+            // K and V tiles have separate double buffers and separate cp.async groups: K(t+2) is
+            // requested when QK(t) has completed, V(t+1) when PV(t-1) has completed, so every load
+            // has a whole iteration to land.  One group is committed per call (possibly empty) so
+            // that wait_group counts stay uniform.
+            auto load_half = [&](uint32_t tile, uint32_t dst, const char* base) {
+                if (tile < ntiles) {
+                    const uint32_t kbeg = lo + tile * TK;
+                    const char* src = base + (size_t)(kbeg + ld_r0) * KV_ROW_BYTES + ld_c * 16;
+                    const uint32_t d = dst + ld_soff;
+                    if (kbeg + TK <= hi) {
+#pragma unroll
+                        for (int k = 0; k < TK / 8; k++)  // rows r0 + 8k: same swizzle phase, fixed strides
+                            cp_async_16(d + k * 8 * ROW_B, src + (size_t)k * 8 * KV_ROW_BYTES, true);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < TK / 8; k++) {
+                            const bool valid = kbeg + ld_r0 + 8 * k < hi;
+                            cp_async_16(d + k * 8 * ROW_B, valid ? src + (size_t)k * 8 * KV_ROW_BYTES : base, valid);
+                        }
+                    }
                 }
                 cp_async_commit();
             };
+            auto k_buf = [&](uint32_t tile) { return kv_s + (tile & 1u) * STAGE; };
+            auto v_buf = [&](uint32_t tile) { return kv_s + (tile & 1u) * STAGE + KV_TILE; };
 
-            load_tile(0, 0);
+            // The previous run's last PV may still be reading its V tile and P.
+            if (pv_pending) {
+                ok &= mbar_wait_bounded(&bar_o, par_o, &s_abort);
+                par_o ^= 1u;
+                pv_pending = false;
+                __syncwarp();
+                tc_fence_after();
+            }
+            // prologue of the run: K(0), V(0), K(1) requested; S(0) issued as soon as K(0) landed
+            load_half(0, k_buf(0), kbase);
+            load_half(0, v_buf(0), vbase);
+            load_half(1, k_buf(1), kbase);
+            cp_async_wait<2>();
+            fence_proxy_async_smem();  // cp.async-written tiles become visible to the tensor core
+            tc_fence_before();
+            __syncthreads();
+            if (tid == 0) {
+                tc_fence_after();
+                issue_qk(k_buf(0));
+            }
+
             for (uint32_t tile = 0; tile < ntiles; tile++) {
-                const uint32_t buf = tile & 1u;
-                if (tile + 1 < ntiles) {
-                    load_tile(tile + 1, buf ^ 1u);
-                    cp_async_wait<1>();
-                } else {
-                    cp_async_wait<0>();
-                }
-                fence_proxy_async_smem();  // cp.async-written tiles become visible to the tensor core
-                tc_fence_before();
-                __syncthreads();
-                const uint32_t ks = kv_s + buf * STAGE, vs = ks + KV_TILE;
-                if (tid == 0) {
-                    tc_fence_after();
-#pragma unroll
-                    for (int kk = 0; kk < 8; kk++) {  // 128 dims = 8 k-steps of 16
-                        const uint64_t ad = umma_desc(q_s + (kk >> 2) * Q_SUB + (kk & 3) * 32, 16, 1024);
-                        const uint64_t bd = umma_desc(ks + (kk >> 2) * KV_SUB + (kk & 3) * 32, 16, 1024);
-                        umma_ss(tmem + S_COL, ad, bd, IDESC_QK, kk > 0 ? 1u : 0u);
-                    }
-                    umma_commit(&bar_s);
-                }
-                // A wait that gives up (after ~1 s; cannot happen unless the MMA never completes)
+                // A wait that gives up (after ~1 s; cannot happen unless an MMA never completes)
                 // does not leave the loop: all threads keep the same barrier sequence, later
                 // waits return at once, the status word is set and no output is written.
                 ok &= mbar_wait_bounded(&bar_s, par_s, &s_abort);
                 par_s ^= 1u;
                 __syncwarp();
                 tc_fence_after();
+                load_half(tile + 2, k_buf(tile), kbase);  // QK(tile) is done with its K buffer
 
-                // ---- this thread's S row: scale, mask, online softmax, P -> TMEM as f16
+                // ---- this thread's S row: scale, mask, softmax weights against the reference maximum
                 const uint32_t kbeg = lo + tile * TK;
                 uint32_t sr[2][32];
                 tmem_ld32(lane_base + S_COL, sr[0]);
                 tmem_ld32(lane_base + S_COL + 32, sr[1]);
                 tmem_wait_ld();
+                // Interior tiles (every key valid for every row of the M tile) skip the masks.
+                const bool interior = full_run && kbeg >= lo_max && kbeg + TK <= hi_min;
                 float mx = -1.0e30f;
+                if (interior) {
 #pragma unroll
-                for (int c = 0; c < TK; c++) {
-                    const uint32_t key = kbeg + c;
-                    float v = __uint_as_float(sr[c >> 5][c & 31]) * QK_SCALE_LOG2;
-                    v = (key >= rlo && key < rhi) ? v : -INFINITY;
-                    sr[c >> 5][c & 31] = __float_as_uint(v);
-                    mx = fmaxf(mx, v);
+                    for (int c = 0; c < TK; c++) mx = fmaxf(mx, __uint_as_float(sr[c >> 5][c & 31]));
+                    mx *= QK_SCALE_LOG2;
+                } else {
+#pragma unroll
+                    for (int c = 0; c < TK; c++) {
+                        const uint32_t key = kbeg + c;
+                        float v = __uint_as_float(sr[c >> 5][c & 31]);
+                        v = (key >= rlo && key < rhi) ? v : -INFINITY;
+                        sr[c >> 5][c & 31] = __float_as_uint(v);
+                        mx = fmaxf(mx, v);
+                    }
+                    mx = mx > -1.0e29f ? mx * QK_SCALE_LOG2 : -1.0e30f;  // stays -1e30 when the whole row is masked
                 }
-                const float m_new = fmaxf(m_run, mx);
-                const float corr = ex2_approx_ftz(m_run - m_new);
-                m_run = m_new;
+                const bool raise = mx > m_ref + RESCALE_THRESHOLD;
+                const float corr = raise ? ex2_approx_ftz(m_ref - mx) : 1.0f;
+                if (raise) m_ref = mx;
                 float psum = 0.0f;
                 uint32_t pk[32];
+                const float neg_m = -m_ref;
 #pragma unroll
-                for (int c = 0; c < TK; c += 2) {
-                    const float p0 = ex2_approx_ftz(__uint_as_float(sr[c >> 5][c & 31]) - m_new);
-                    const float p1 = ex2_approx_ftz(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]) - m_new);
+                for (int c = 0; c < TK; c += 2) {  // p = 2^(s*scale*log2e - m): one fma + one ex2 per key
+                    const float p0 = ex2_approx_ftz(fmaf(__uint_as_float(sr[c >> 5][c & 31]), QK_SCALE_LOG2, neg_m));
+                    const float p1 = ex2_approx_ftz(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), QK_SCALE_LOG2, neg_m));
                     psum += p0 + p1;
                     pk[c >> 1] = pack_h2(p0, p1);
                 }
+                l_run = l_run * corr + psum;
+
+                // ---- PV(tile-1) must be complete before P is overwritten and before O is rescaled;
+                // its V stage is then free for tile+1 (tile 1 of a run was loaded in the prologue)
+                if (pv_pending) {
+                    ok &= mbar_wait_bounded(&bar_o, par_o, &s_abort);
+                    par_o ^= 1u;
+                    pv_pending = false;
+                    __syncwarp();
+                    tc_fence_after();
+                }
+                load_half(tile + 1, v_buf(tile + 1), vbase);  // PV(tile-1) is done with that V buffer
+                if (o_valid && __any_sync(0xffffffffu, raise)) {
+                    // rare: the reference maximum of some row of this warp moved; rescale the warp's O rows
+#pragma unroll
+                    for (int ch = 0; ch < 4; ch++) {
+                        uint32_t orow[32];
+                        tmem_ld32(lane_base + O_COL + ch * 32, orow);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * corr);
+                        tmem_st32(lane_base + O_COL + ch * 32, orow);
+                    }
+                }
                 tmem_st32(lane_base + P_COL, pk);
                 tmem_wait_st();
+                // V(tile) and K(tile+1) must have landed before the MMAs below; the two groups
+                // requested in this iteration may still be in flight
+                cp_async_wait<2>();
+                fence_proxy_async_smem();
                 tc_fence_before();
                 __syncthreads();
                 if (tid == 0) {
                     tc_fence_after();
+                    const uint32_t vs = v_buf(tile);
 #pragma unroll
                     for (int kk = 0; kk < TK / 16; kk++) {  // 64 keys = 4 k-steps of 16
                         const uint64_t bd = umma_desc(vs + kk * 16 * ROW_B, KV_SUB, 1024);
-                        umma_ts(tmem + O_COL, tmem + P_COL + kk * 8, bd, IDESC_PV, kk > 0 ? 1u : 0u);
+                        umma_ts(tmem + O_COL, tmem + P_COL + kk * 8, bd, IDESC_PV, (kk > 0 || o_valid) ? 1u : 0u);
                     }
                     umma_commit(&bar_o);
+                    if (tile + 1 < ntiles) issue_qk(k_buf(tile + 1));
                 }
-                // while the MMA runs: rescale the running accumulator
-                l_run = l_run * corr + psum;
-#pragma unroll
-                for (int d = 0; d < HD; d++) acc[d] *= corr;
-                ok &= mbar_wait_bounded(&bar_o, par_o, &s_abort);
-                par_o ^= 1u;
-                __syncwarp();
-                tc_fence_after();
-#pragma unroll
-                for (int ch = 0; ch < 4; ch++) {
-                    uint32_t orow[32];
-                    tmem_ld32(lane_base + O_COL + ch * 32, orow);
-                    tmem_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 32; i++) acc[ch * 32 + i] += __uint_as_float(orow[i]);
-                }
-                tc_fence_before();
+                o_valid = true;
+                pv_pending = true;
             }
         }
         run0 = run1;
     }
-    if (!ok && tid == 0) atomicOr(status, DEV_WAIT_TIMEOUT);
+    if (pv_pending) {
+        ok &= mbar_wait_bounded(&bar_o, par_o, &s_abort);
+        par_o ^= 1u;
+        pv_pending = false;
+        __syncwarp();
+        tc_fence_after();
+    }
 
-    // ---- epilogue: 1/sum, f16, gate on the f16 value (as online kernel + gate kernel)
-    if ((uint32_t)lane < nrows && s_len[lane] != 0 && ok) {
+    // ---- epilogue: O row from TMEM, 1/sum, f16, gate on the f16 value (as online kernel + gate kernel)
+    {
+        const bool write = (uint32_t)lane < nrows && s_len[lane] != 0 && ok && o_valid;
         const float inv = rcp_approx_ftz(l_run);
-        const size_t rh = (size_t)(row0 + lane) * NQ + head;
-        const float sig = gate ? sigmoid_ref(h2f(gate[rh])) : 1.0f;
+        const size_t rh = (size_t)(row0 + (write ? lane : 0)) * NQ + head;
+        const float sig = (gate && write) ? sigmoid_ref(h2f(gate[rh])) : 1.0f;
         uint4* out = reinterpret_cast<uint4*>(ctx_out + rh * HD);
+        if (o_valid) {
 #pragma unroll
-        for (int v8 = 0; v8 < HD / 8; v8++) {
-            uint32_t w[4];
+            for (int ch = 0; ch < 4; ch++) {
+                uint32_t orow[32];
+                tmem_ld32(lane_base + O_COL + ch * 32, orow);
+                tmem_wait_ld();
+                if (write) {
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                uint16_t h0 = f2h(__fmul_rn(acc[v8 * 8 + 2 * j], inv));
-                uint16_t h1 = f2h(__fmul_rn(acc[v8 * 8 + 2 * j + 1], inv));
-                if (gate) {
-                    h0 = f2h(__fmul_rn(h2f(h0), sig));
-                    h1 = f2h(__fmul_rn(h2f(h1), sig));
+                    for (int v8 = 0; v8 < 4; v8++) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            uint16_t h0 = f2h(__fmul_rn(__uint_as_float(orow[v8 * 8 + 2 * j]), inv));
+                            uint16_t h1 = f2h(__fmul_rn(__uint_as_float(orow[v8 * 8 + 2 * j + 1]), inv));
+                            if (gate) {
+                                h0 = f2h(__fmul_rn(h2f(h0), sig));
+                                h1 = f2h(__fmul_rn(h2f(h1), sig));
+                            }
+                            w[j] = (uint32_t)h0 | ((uint32_t)h1 << 16);
+                        }
+                        out[ch * 4 + v8] = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
                 }
-                w[j] = (uint32_t)h0 | ((uint32_t)h1 << 16);
             }
-            out[v8] = make_uint4(w[0], w[1], w[2], w[3]);
         }
     }
+  }  // item loop
+    if (!ok && tid == 0) atomicOr(status, DEV_WAIT_TIMEOUT);
     tc_fence_before();
     __syncthreads();
     if (warp == 0) {
@@ -364,12 +507,15 @@ cudaError_t prefill_attn_init() {
 cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* q,
                                 const void* gate, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
                                 const uint32_t* seq_lens, uint32_t rows, uint32_t window,
-                                uint32_t* status, int num_sms) {
-    (void)num_sms;
-    dim3 grid((rows + pf::TOK - 1) / pf::TOK, NKV);
+                                uint32_t* status, int num_sms, uint32_t* order, uint32_t* counter) {
+    const uint32_t nitems = ((rows + pf::TOK - 1) / pf::TOK) * NKV;
+    prefill_plan_kernel<<<1, 1024, 0, stream>>>(seq_lens, rows, window, order, counter);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    const uint32_t grid = nitems < (uint32_t)(2 * num_sms) ? nitems : (uint32_t)(2 * num_sms);
     prefill_attn_kernel<<<grid, pf::THREADS, pf::SMEM_BYTES, stream>>>(
         (uint16_t*)ctx_out, (const uint16_t*)q, (const uint16_t*)gate, k_ptrs, v_ptrs, seq_lens,
-        rows, window, status);
+        rows, window, status, order, counter);
     return cudaGetLastError();
 }
 
