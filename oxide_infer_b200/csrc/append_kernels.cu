@@ -11,13 +11,13 @@
 namespace oxi {
 
 // One warp normalises (and optionally rotates) one head held in registers.
-// x[i] is dim lane + 32*i.  Returns the f16 bit patterns in out[i].
+// x[i] is dim lane + 32*i; wv / cv / sv are the norm weight, cos and sin of the same dims
+// (already converted to f32 by the caller, which can fetch them early).  Returns the f16 bit
+// patterns in out[i].
 template <bool kNorm, bool kRope>
-__device__ __forceinline__ void head_norm_rope(const uint16_t* __restrict__ x_head,
-                                               const uint16_t* __restrict__ w, float eps,
-                                               const uint16_t* __restrict__ cos_row,
-                                               const uint16_t* __restrict__ sin_row, int lane,
-                                               uint16_t (&out)[4]) {
+__device__ __forceinline__ void head_norm_rope(const uint16_t* __restrict__ x_head, const float (&wv)[4],
+                                               float eps, const float (&cv)[4], const float (&sv)[4],
+                                               int lane, uint16_t (&out)[4]) {
     float x[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) x[i] = h2f(x_head[lane + 32 * i]);
@@ -34,10 +34,7 @@ __device__ __forceinline__ void head_norm_rope(const uint16_t* __restrict__ x_he
         float r = rsqrt_approx_ftz(mean);
         r = __shfl_sync(0xffffffffu, r, 0);
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            float fw = h2f(w[lane + 32 * i]);
-            y16[i] = f2h(__fmul_rn(__fmul_rn(x[i], r), fw));
-        }
+        for (int i = 0; i < 4; i++) y16[i] = f2h(__fmul_rn(__fmul_rn(x[i], r), wv[i]));
     } else {
 #pragma unroll
         for (int i = 0; i < 4; i++) y16[i] = x_head[lane + 32 * i];
@@ -49,17 +46,20 @@ __device__ __forceinline__ void head_norm_rope(const uint16_t* __restrict__ x_he
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             // dim d = lane + 32 i pairs with d + 64 (i < 2) or d - 64 (i >= 2)
-            float other = (i < 2) ? -y[i + 2] : y[i - 2];
-            float c = h2f(cos_row[lane + 32 * i]);
-            float s = h2f(sin_row[lane + 32 * i]);
-            float res = __fmul_rn(y[i], c);
-            res = __fmaf_rn(other, s, res);
+            const float other = (i < 2) ? -y[i + 2] : y[i - 2];
+            float res = __fmul_rn(y[i], cv[i]);
+            res = __fmaf_rn(other, sv[i], res);
             out[i] = f2h(res);
         }
     } else {
 #pragma unroll
         for (int i = 0; i < 4; i++) out[i] = y16[i];
     }
+}
+
+__device__ __forceinline__ void load4(const uint16_t* __restrict__ p, int lane, float (&v)[4]) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) v[i] = h2f(p[lane + 32 * i]);
 }
 
 // grid = B, block = 20 warps: warps 0..15 own the query heads, 16..19 the K
@@ -74,23 +74,27 @@ append_kernel(uint16_t* __restrict__ q_io, const uint16_t* __restrict__ k_in,
     const uint32_t b = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
+    // the step's tables, norm weights and RoPE rows are not written by any kernel: fetch them
+    // while the preceding kernel is still draining
     const uint32_t pos = pos_ids[b];
     const uint64_t kp = k_ptrs[b], vp = v_ptrs[b];
+    float wv[4], cv[4], sv[4];
+    load4(warp < NQ ? q_norm_w : k_norm_w, lane, wv);
+    load4(cos_t + (size_t)pos * HD, lane, cv);
+    load4(sin_t + (size_t)pos * HD, lane, sv);
     pdl_wait();  // q/k/v come from the preceding kernel; the caches may still be read by it
     const bool aligned = ((kp | vp) & 15ull) == 0ull;
     if (!aligned && threadIdx.x == 0) atomicOr(status, DEV_MISALIGNED_PTR);
-    const uint16_t* cos_row = cos_t + (size_t)pos * HD;
-    const uint16_t* sin_row = sin_t + (size_t)pos * HD;
     uint16_t out[4];
     if (warp < NQ) {
         uint16_t* xh = q_io + ((size_t)b * NQ + warp) * HD;
-        head_norm_rope<true, true>(xh, q_norm_w, eps, cos_row, sin_row, lane, out);
+        head_norm_rope<true, true>(xh, wv, eps, cv, sv, lane, out);
 #pragma unroll
         for (int i = 0; i < 4; i++) xh[lane + 32 * i] = out[i];
     } else {
         const int kh = warp - NQ;
         const uint16_t* xh = k_in + ((size_t)b * NKV + kh) * HD;
-        head_norm_rope<true, true>(xh, k_norm_w, eps, cos_row, sin_row, lane, out);
+        head_norm_rope<true, true>(xh, wv, eps, cv, sv, lane, out);
         if (aligned) {
             uint16_t* dst = reinterpret_cast<uint16_t*>(kp) + (size_t)pos * (NKV * HD) + kh * HD;
 #pragma unroll
@@ -112,7 +116,10 @@ qk_rmsnorm_kernel(uint16_t* __restrict__ x_io, const uint16_t* __restrict__ w, f
     uint16_t out[4];
     uint16_t* xh = x_io + (size_t)head * HD;
     const int lane = threadIdx.x & 31;
-    head_norm_rope<true, false>(xh, w, eps, nullptr, nullptr, lane, out);
+    float wv[4];
+    const float none[4] = {0.f, 0.f, 0.f, 0.f};
+    load4(w, lane, wv);
+    head_norm_rope<true, false>(xh, wv, eps, none, none, lane, out);
 #pragma unroll
     for (int i = 0; i < 4; i++) xh[lane + 32 * i] = out[i];
 }
@@ -127,8 +134,11 @@ rope_kernel(uint16_t* __restrict__ x_io, const uint16_t* __restrict__ cos_t,
     uint16_t out[4];
     uint16_t* xh = x_io + (size_t)head * HD;
     const int lane = threadIdx.x & 31;
-    head_norm_rope<false, true>(xh, nullptr, 0.0f, cos_t + (size_t)pos * HD,
-                                sin_t + (size_t)pos * HD, lane, out);
+    float cv[4], sv[4];
+    const float none[4] = {0.f, 0.f, 0.f, 0.f};
+    load4(cos_t + (size_t)pos * HD, lane, cv);
+    load4(sin_t + (size_t)pos * HD, lane, sv);
+    head_norm_rope<false, true>(xh, none, 0.0f, cv, sv, lane, out);
 #pragma unroll
     for (int i = 0; i < 4; i++) xh[lane + 32 * i] = out[i];
 }

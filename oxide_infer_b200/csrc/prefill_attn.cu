@@ -146,6 +146,7 @@ prefill_plan_kernel(const uint32_t* __restrict__ seq_lens, uint32_t rows, uint32
     auto key_of = [&](uint32_t blk) {
         uint32_t lo = 0xffffffffu, hi = 0;
         const uint32_t r1 = min(rows, (blk + 1) * TOK);
+#pragma unroll 8
         for (uint32_t r = blk * TOK; r < r1; r++) {
             const uint32_t sl = seq_lens[r];
             if (sl == 0) continue;
@@ -155,7 +156,15 @@ prefill_plan_kernel(const uint32_t* __restrict__ seq_lens, uint32_t rows, uint32
         const uint32_t tiles = hi > lo ? (hi - lo + TK - 1) / TK : 0u;
         return (uint32_t)(NB - 1) - min(tiles, (uint32_t)(NB - 1));  // bucket 0 = most work
     };
-    for (uint32_t blk = tid; blk < nblocks; blk += 1024) atomicAdd(&hist[key_of(blk)], 1u);
+    uint32_t my_key[4];  // keys of this thread's first blocks are kept for the scatter pass
+    {
+        int j = 0;
+        for (uint32_t blk = tid; blk < nblocks; blk += 1024, j++) {
+            const uint32_t k = key_of(blk);
+            if (j < 4) my_key[j] = k;
+            atomicAdd(&hist[k], 1u);
+        }
+    }
     __syncthreads();
     // exclusive prefix sum of the 1024 buckets
     uint32_t v = hist[tid], incl = v;
@@ -178,7 +187,11 @@ prefill_plan_kernel(const uint32_t* __restrict__ seq_lens, uint32_t rows, uint32
     __syncthreads();
     hist[tid] = warp_tot[warp] + incl - v;
     __syncthreads();
-    for (uint32_t blk = tid; blk < nblocks; blk += 1024) order[atomicAdd(&hist[key_of(blk)], 1u)] = blk;
+    {
+        int j = 0;
+        for (uint32_t blk = tid; blk < nblocks; blk += 1024, j++)
+            order[atomicAdd(&hist[j < 4 ? my_key[j] : key_of(blk)], 1u)] = blk;
+    }
 }
 
 __global__ void __launch_bounds__(pf::THREADS, 2)
