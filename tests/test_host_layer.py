@@ -1,0 +1,36 @@
+"""Compiles and runs the C++ tests of the host layer (oxide_infer_b200/csrc/host/kv_host.hpp)."""
+import os
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CPP = os.path.join(ROOT, "tests", "cpp")
+BUILD = os.path.join(CPP, "build")
+
+
+def _gxx():
+    return "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
+
+
+def test_host_layer_allocator_and_tables_cpu():
+    os.makedirs(BUILD, exist_ok=True)
+    exe = os.path.join(BUILD, "test_kv_host_cpu")
+    subprocess.run([_gxx(), "-std=c++17", "-O1", "-Wall", "-o", exe, os.path.join(CPP, "test_kv_host_cpu.cpp")], check=True)
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "passed" in r.stdout
+
+
+@pytest.mark.gpu
+def test_host_layer_decode_step_gpu():
+    from oxide_infer_b200 import build
+    so = build.build()
+    os.makedirs(BUILD, exist_ok=True)
+    exe = os.path.join(BUILD, "test_kv_host_gpu")
+    subprocess.run(["nvcc", "-std=c++17", "-O1", "-gencode", "arch=compute_100a,code=sm_100a", "-o", exe,
+                    os.path.join(CPP, "test_kv_host_gpu.cpp"), so, "-Xlinker", "-rpath", "-Xlinker",
+                    os.path.dirname(so)], check=True)
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "passed" in r.stdout
