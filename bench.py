@@ -544,6 +544,94 @@ def run_prefill(args, torch):
             "gpu_launches": 3 * args.steps, "clocks": clocks, "device_status": kv.device_status()}
 
 
+def run_serving_mix(args, torch, rank, world, local_rank):
+    """Config 5: 1,024 sequences with lognormal context lengths (median 2048, sigma 1.0 - the
+    spread is not given by the configuration and is chosen here -, clipped to [16, 32704]),
+    8 attention layers, 64 consecutive decode steps (append + gated GQA attention, positions
+    advancing).  The FIXED set of sequences is partitioned over the ranks by
+    oxide_infer_b200.shard.assign_sequences (strong scaling, replicas, no collective)."""
+    import numpy as np
+    from oxide_infer_b200 import KvPath, rotary_tables
+    from oxide_infer_b200.shard import assign_sequences, shard_keys
+    nseq, layers, steps = 1024, 8, 64
+    rng = np.random.default_rng(5)
+    lens_all = np.clip(np.round(np.exp(rng.normal(np.log(2048), 1.0, nseq))), 16, 32768 - 64).astype(np.int64)
+    parts = assign_sequences(lens_all, world)
+    mine = parts[rank]
+    lens = lens_all[mine]
+    b = len(mine)
+    cap = lens + steps + 1
+    kv = KvPath(local_rank, max_batch=max(b, 1), max_seq_len=32768 + steps, max_prefill_rows=0)
+    g = torch.Generator(device="cuda").manual_seed(50 + rank)
+    total_rows = int(cap.sum())
+    k_ptrs, v_ptrs, slabs = [], [], []
+    offs = np.concatenate([[0], np.cumsum(cap)[:-1]]) * ROW_BYTES
+    for _ in range(layers):
+        ks = torch.empty(total_rows, NKV, HD, dtype=torch.float16, device="cuda").normal_(generator=g)
+        vs = torch.empty(total_rows, NKV, HD, dtype=torch.float16, device="cuda").normal_(generator=g)
+        slabs.append((ks, vs))
+        k_ptrs.append(torch.from_numpy(ks.data_ptr() + offs).cuda())
+        v_ptrs.append(torch.from_numpy(vs.data_ptr() + offs).cuda())
+    rn = lambda *s: torch.empty(*s, dtype=torch.float16, device="cuda").normal_(generator=g)
+    q, k, v, gate = rn(layers, b, NQ, HD), rn(layers, b, NKV, HD), rn(layers, b, NKV, HD), rn(layers, b, NQ)
+    qw = torch.ones(HD, dtype=torch.float16, device="cuda")
+    cos, sin = rotary_tables(32768 + steps, 1e6, 0.5)
+    cos, sin = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
+    ctx = torch.zeros(layers, b, NQ, HD, dtype=torch.float16, device="cuda")
+    pos_steps = [torch.from_numpy((lens + s_).astype(np.int32)).cuda() for s_ in range(steps)]
+    len_steps = [p + 1 for p in pos_steps]
+    stream = torch.cuda.current_stream()
+
+    def run64():
+        for s_ in range(steps):
+            for l in range(layers):
+                kv.append_decode(ctx[l], q[l], k[l], v[l], gate[l], qw, qw, cos, sin, pos_steps[s_], len_steps[s_],
+                                 k_ptrs[l], v_ptrs[l])
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(gpu_index(local_rank))
+    sampler.start()
+    run64()  # warm-up pass (also the W >= 3 warm-up steps: 64 of them)
+    barrier()
+    reps = max(1, args.steps // steps)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = time.perf_counter()
+    t0.record(stream)
+    for _ in range(reps):
+        run64()
+    t1.record(stream)
+    barrier()
+    clocks = sampler.window(w0, time.perf_counter())
+    sampler.stop()
+    ms = t0.elapsed_time(t1) / reps
+    status = kv.device_status()
+    tt = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        torch.distributed.all_reduce(tt, op=torch.distributed.ReduceOp.MAX)
+    if rank != 0:
+        return None
+    ms = float(tt.item())
+    total_bytes = sum(layers * alg_bytes_layer(lens_all + s_ + 1) for s_ in range(steps))
+    keys = shard_keys(lens_all, parts)
+    peak, kind = measured_peak_gbs()
+    gbs = total_bytes / (ms * 1e-3) / 1e9
+    return {"metric": "serving_mix_64_decode_steps_hbm_gbs", "value": round(gbs, 1), "unit": "GB/s", "n_gpus": world,
+            "steps": steps * reps, "warmup": steps, "ms_per_step": round(ms / steps, 4), "ms_per_64_steps": round(ms, 3),
+            "tokens_per_s": round(nseq * steps / (ms * 1e-3), 1), "higher_is_better": True, "scaling": "strong",
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "serving_mix_1024seq_lognormal_median2048_sigma1_8layers_64steps",
+                       "sequences": nseq, "kv_bytes_total": int(lens_all.sum()) * layers * 2 * ROW_BYTES,
+                       "keys_per_gpu_min_max": [int(min(keys)), int(max(keys))],
+                       "parallelism": f"replicas x{world}, sequences partitioned longest-first, no collective"},
+            "roofline": {"bound": "hbm", "achieved": round(gbs / world, 1), "peak": peak, "peak_kind": kind,
+                         "unit": "GB/s per GPU", "frac": round(gbs / world / peak, 4)},
+            "gpu_launches": 3 * layers * steps * reps, "clocks": clocks, "device_status": status}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -555,7 +643,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="override for small profiling cases")
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--ctx", type=int, default=CTX)
-    ap.add_argument("--workload", default="decode", choices=["decode", "conv", "prefill"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "conv", "prefill", "serving_mix"],
                     help="decode = the headline line; conv / prefill = secondary single-GPU lines")
     args = ap.parse_args()
     globals().update(LAYERS=args.layers, BATCH=args.batch, CTX=args.ctx)
@@ -578,6 +666,8 @@ def main():
             line = run_conv(args, torch) if rank == 0 else None
         elif args.workload == "prefill":
             line = run_prefill(args, torch) if rank == 0 else None
+        elif args.workload == "serving_mix":
+            line = run_serving_mix(args, torch, rank, world, local_rank)
         else:
             line = (run_ours if args.impl == "ours" else run_reference)(args, torch, rank, world, local_rank)
         if line is not None:
