@@ -65,7 +65,7 @@ const char* oxi_last_error_string(void);
 
 /* Creates the per-device workspace (split-KV partials, conv staging,
  * host-entry staging).  Replaces the scratch half of BatchEngine::new
- * (batch_engine.rs:320-364).  max_batch <= 2048. */
+ * (batch_engine.rs:320-364).  max_batch <= 1024. */
 int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_t max_seq_len,
                    uint32_t max_prefill_rows);
 int32_t oxi_destroy(oxi_handle* h);
@@ -105,8 +105,15 @@ int32_t oxi_decode_attn(oxi_handle* h, void* stream, void* ctx_out, const void* 
                         const void* gate, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
                         const uint32_t* seq_lens, uint32_t batch, uint32_t window);
 
-/* oxi_append followed by oxi_decode_attn on the same stream (the whole
- * attention-layer hot path of one decode step, batch_engine.rs:941-1239). */
+/* The whole attention-layer hot path of one decode step (batch_engine.rs:941-1239)
+ * as ONE streaming kernel plus the merge kernel: RMSNorm + RoPE + KV append are
+ * fused into the decode-attention kernel, so q is normalised on chip and never
+ * makes a round trip through HBM.  Cache rows and ctx_out are byte-identical to
+ * oxi_append followed by oxi_decode_attn.  Differences from that pair: q_io is
+ * NOT modified (it is read as the raw projected q), and the position of the
+ * appended token is taken as seq_lens[b] - 1 (pos_ids must agree, as the engine
+ * guarantees, batch_engine.rs:689-691).  cos/sin tables, k_in and v_in must be
+ * 16-byte aligned. */
 int32_t oxi_append_decode(oxi_handle* h, void* stream, void* ctx_out, void* q_io, const void* k_in,
                           const void* v_in, const void* gate, const void* q_norm_w,
                           const void* k_norm_w, const void* cos_table, const void* sin_table,

@@ -34,6 +34,19 @@
 // streaming: under a saturated memory pipe every dependent global access costs
 // microseconds of queueing behind the stream.
 //
+// Fused variant (kFused, behind oxi_append_decode): the per-head Q/K RMSNorm + RoPE + KV append
+// of batched_attn.rs:13-287 runs inside this kernel, so q never makes a round trip through
+// HBM before it is used and the append launch disappears.  The producer delivers the RAW q
+// row plus the position's cos/sin rows with an item's first stage; each consumer warp
+// normalises and rotates its 4 query heads in shared memory with the append kernel's exact
+// arithmetic.  The item holding a row's LAST key range is the row's "owner": the key at
+// position seq_len-1 does not exist in the cache yet, so the producer copies one key less
+// and delivers the raw k/v rows instead; each consumer warp normalises/rotates its K head,
+// drops K and V into the stage at that key's place, and writes the cache row to global
+// memory.  No other item reads that cache row, so nothing waits on another CTA.  The caller's
+// q buffer is not modified.  Context and cache bytes are identical to append followed by the
+// unfused kernel.
+//
 // A row covered by one item is finished in registers (1/sum, f16, gate).
 // Otherwise each consumer warp stores its (max, sum, acc[128]) partials and
 // moves on; a second, tiny kernel merges the partials of every multi-item row
@@ -46,6 +59,7 @@
 #include "../../include/oxi_kv.h"
 #include "common.cuh"
 #include "kernels.h"
+#include "norm_rope.cuh"
 
 #ifndef OXI_DEC_NSTAGE
 #define OXI_DEC_NSTAGE 3
@@ -54,7 +68,7 @@
 #define OXI_DEC_CHUNK 256
 #endif
 #ifndef OXI_DEC_MAXROWS
-#define OXI_DEC_MAXROWS 2048
+#define OXI_DEC_MAXROWS 1024
 #endif
 
 namespace oxi {
@@ -68,14 +82,19 @@ constexpr int GPITCH = GROUP_BYTES + 16;        // group pitch in shared memory
 constexpr int NGROUP = KS / GK;                 // 8 groups per stage = the 8 rows of an ldmatrix tile
 constexpr int HALF_BYTES = NGROUP * GPITCH;     // K part (then V part) of a stage
 constexpr int Q_BYTES = NQ * HD * 2;            // the row's q (all heads), carried by an item's first stage
-constexpr int DESC_BYTES = 16;
-constexpr int STAGE_BYTES = 2 * HALF_BYTES + Q_BYTES + DESC_BYTES;
+// extra inputs of the fused variant: cos row, sin row (256 B each), raw k row, raw v row (1 KB each)
+constexpr int X_COS = 0, X_SIN = 256, X_K = 512, X_V = 512 + KV_ROW_BYTES;
+constexpr int X_BYTES = 512 + 2 * KV_ROW_BYTES;
+constexpr int DESC_BYTES = 32;
+constexpr int Q_OFF = 2 * HALF_BYTES, X_OFF = Q_OFF + Q_BYTES, DESC_OFF = X_OFF + X_BYTES;
+constexpr int STAGE_BYTES = DESC_OFF + DESC_BYTES;
 constexpr int CHUNK = OXI_DEC_CHUNK;            // keys per work item
 constexpr int N_CONSUMER_WARPS = NKV;           // one per KV head
 constexpr int THREADS = (N_CONSUMER_WARPS + 1) * 32;
 constexpr int MAX_ROWS = OXI_DEC_MAXROWS;       // rows per launch (prefix + length arrays in shared memory)
 constexpr float QK_SCALE_LOG2 = ATTN_SCALE * LOG2E;
-constexpr size_t SMEM_BYTES = (size_t)NSTAGE * STAGE_BYTES + 2 * NSTAGE * 8 + 16 +
+constexpr int W_BYTES = 2 * HD * 2;  // q and k norm weights (fused variant)
+constexpr size_t SMEM_BYTES = (size_t)NSTAGE * STAGE_BYTES + 2 * NSTAGE * 8 + 16 + W_BYTES +
                               (2 * MAX_ROWS + 1) * sizeof(uint32_t);
 static_assert(SMEM_BYTES <= 227 * 1024, "decode kernel shared memory");
 static_assert(CHUNK % KS == 0, "a work item is a whole number of stages");
@@ -84,6 +103,7 @@ static_assert(STAGE_BYTES % 16 == 0, "stage alignment");
 
 // stage descriptor flags (word z)
 constexpr uint32_t F_FIRST = 0x100u, F_LAST = 0x200u, F_END = 0x400u;
+constexpr uint32_t F_LASTRANGE = 0x800u;  // the item is its row's last key range (fused: the row's owner)
 }  // namespace dec
 
 struct DecodeParams {
@@ -101,6 +121,14 @@ struct DecodeParams {
     uint32_t window;
     uint32_t max_chunks;
     uint32_t max_seq_len;
+    // fused variant only (q is then the raw projected q)
+    const uint16_t* k_in;
+    const uint16_t* v_in;
+    const uint16_t* q_norm_w;
+    const uint16_t* k_norm_w;
+    const uint16_t* cos_t;
+    const uint16_t* sin_t;
+    float eps;
 };
 
 __device__ __forceinline__ uint32_t row_chunks(uint32_t slen, uint32_t window) {
@@ -118,6 +146,7 @@ __device__ __forceinline__ uint32_t find_row(const uint32_t* prefix, uint32_t ba
     return lo;
 }
 
+template <bool kFused>
 __global__ void __launch_bounds__(dec::THREADS, 1)
 decode_attn_kernel(const DecodeParams p) {
     using namespace dec;
@@ -126,7 +155,8 @@ decode_attn_kernel(const DecodeParams p) {
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)NSTAGE * STAGE_BYTES);
     uint64_t* empty_bar = full_bar + NSTAGE;
     volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(empty_bar + NSTAGE);
-    uint32_t* prefix = const_cast<uint32_t*>(reinterpret_cast<volatile uint32_t*>(abort_flag) + 4);
+    uint16_t* s_w = const_cast<uint16_t*>(reinterpret_cast<volatile uint16_t*>(abort_flag) + 8);  // [q_norm_w | k_norm_w]
+    uint32_t* prefix = reinterpret_cast<uint32_t*>(s_w + 2 * HD);
     uint32_t* s_len = prefix + MAX_ROWS + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -155,6 +185,10 @@ decode_attn_kernel(const DecodeParams p) {
         }
         prefix[b + 1] = n;
         s_len[b] = slen;
+    }
+    if (kFused) {
+        for (uint32_t i = threadIdx.x; i < 2u * HD; i += THREADS)
+            s_w[i] = i < (uint32_t)HD ? p.q_norm_w[i] : p.k_norm_w[i - HD];
     }
     __syncthreads();
     if (warp == 0) {
@@ -211,6 +245,8 @@ decode_attn_kernel(const DecodeParams p) {
                 nvp = p.v_ptrs[nb];
             }
             const uint32_t nchunks = prefix[cb + 1] - prefix[cb];
+            const bool last_range = (cc + 1 == nchunks);
+            const uint32_t pos = cslen - 1u;  // position of the token appended in this step
             const char* qp = reinterpret_cast<const char*>(p.q) + (size_t)cb * Q_BYTES;
             const char* kp = reinterpret_cast<const char*>(ckp);
             const char* vp = reinterpret_cast<const char*>(cvp);
@@ -225,27 +261,43 @@ decode_attn_kernel(const DecodeParams p) {
                 }
                 const uint32_t nvalid = min((uint32_t)KS, t1 - t);
                 const bool first = (t == t0), last = (t + KS >= t1);
+                // fused: the owner's last stage ends with the key being appended; it is not in the
+                // cache yet, so one key less is copied and the raw k/v rows are delivered instead
+                const bool owner = kFused && last && last_range;
+                const uint32_t ncopy = owner ? nvalid - 1u : nvalid;
                 unsigned char* sb = stages + (size_t)slot * STAGE_BYTES;
                 if (lane == 0) {
-                    *reinterpret_cast<uint4*>(sb + 2 * HALF_BYTES + Q_BYTES) =
+                    *reinterpret_cast<uint4*>(sb + DESC_OFF) =
                         make_uint4(cb, cc | (nchunks << 16),
-                                   nvalid | (first ? F_FIRST : 0u) | (last ? F_LAST : 0u), 0u);
-                    mbar_arrive_expect_tx(&full_bar[slot], nvalid * 2u * KV_ROW_BYTES + (first ? Q_BYTES : 0));
+                                   nvalid | (first ? F_FIRST : 0u) | (last ? F_LAST : 0u) |
+                                       (last_range ? F_LASTRANGE : 0u), pos);
+                    *reinterpret_cast<uint4*>(sb + DESC_OFF + 16) =
+                        make_uint4((uint32_t)ckp, (uint32_t)(ckp >> 32), (uint32_t)cvp, (uint32_t)(cvp >> 32));
+                    uint32_t bytes = ncopy * 2u * KV_ROW_BYTES + (first ? Q_BYTES : 0);
+                    if (kFused) bytes += ((first || owner) ? 512u : 0u) + (owner ? 2u * KV_ROW_BYTES : 0u);
+                    mbar_arrive_expect_tx(&full_bar[slot], bytes);
                 }
                 __syncwarp();
                 const uint32_t sbase = smem_u32(sb);
-                // lanes 0..7 copy the K groups, lanes 8..15 the V groups (up to 4 KB each), lane 16 the q row
+                // lanes 0..7 copy the K groups, lanes 8..15 the V groups (up to 4 KB each), lane 16 the q
+                // row; fused: lanes 17/18 the cos/sin rows, lanes 19/20 the raw k/v rows of the owner
                 if (lane < 2 * NGROUP) {
                     const uint32_t grp = lane & (NGROUP - 1);
                     const bool is_v = lane >= NGROUP;
-                    if (grp * GK < nvalid) {
-                        const uint32_t nk = min((uint32_t)GK, nvalid - grp * GK);
+                    if (grp * GK < ncopy) {
+                        const uint32_t nk = min((uint32_t)GK, ncopy - grp * GK);
                         const char* src = (is_v ? vp : kp) + (size_t)(t + grp * GK) * KV_ROW_BYTES;
                         bulk_g2s_hint(sbase + (is_v ? HALF_BYTES : 0) + grp * GPITCH, src,
                                       nk * KV_ROW_BYTES, &full_bar[slot], policy);
                     }
                 } else if (first && lane == 2 * NGROUP) {
-                    bulk_g2s(sbase + 2 * HALF_BYTES, qp, Q_BYTES, &full_bar[slot]);
+                    bulk_g2s(sbase + Q_OFF, qp, Q_BYTES, &full_bar[slot]);
+                } else if (kFused && (first || owner) && (lane == 17 || lane == 18)) {
+                    const uint16_t* tbl = (lane == 17) ? p.cos_t : p.sin_t;
+                    bulk_g2s(sbase + X_OFF + (lane == 17 ? X_COS : X_SIN), tbl + (size_t)pos * HD, 256, &full_bar[slot]);
+                } else if (kFused && owner && (lane == 19 || lane == 20)) {
+                    const uint16_t* src = (lane == 19 ? p.k_in : p.v_in) + (size_t)cb * (NKV * HD);
+                    bulk_g2s(sbase + X_OFF + (lane == 19 ? X_K : X_V), src, KV_ROW_BYTES, &full_bar[slot]);
                 }
             }
             cur = nxt; cb = nb; cc = nc; cslen = nslen; ckp = nkp; cvp = nvp;
@@ -255,7 +307,7 @@ decode_attn_kernel(const DecodeParams p) {
             const uint32_t slot = fill % NSTAGE;
             if (fill < NSTAGE || mbar_wait_bounded(&empty_bar[slot], ((fill / NSTAGE) & 1u) ^ 1u, abort_flag)) {
                 if (lane == 0) {
-                    *reinterpret_cast<uint4*>(stages + (size_t)slot * STAGE_BYTES + 2 * HALF_BYTES + Q_BYTES) =
+                    *reinterpret_cast<uint4*>(stages + (size_t)slot * STAGE_BYTES + DESC_OFF) =
                         make_uint4(0u, 0u, F_END, 0u);
                     mbar_arrive(&full_bar[slot]);
                 }
@@ -295,14 +347,32 @@ decode_attn_kernel(const DecodeParams p) {
             break;
         }
         unsigned char* sb = stages + (size_t)slot * STAGE_BYTES;
-        const uint4 desc = *reinterpret_cast<const uint4*>(sb + 2 * HALF_BYTES + Q_BYTES);
+        const uint4 desc = *reinterpret_cast<const uint4*>(sb + DESC_OFF);
         if (desc.z & F_END) break;
         const uint32_t nvalid = desc.z & 0xffu;
         unsigned char* kst = sb + kvh * (HD * 2);
         unsigned char* vst = kst + HALF_BYTES;
 
         if (desc.z & F_FIRST) {  // new item: reset the running state, take the row's q from the stage
-            const unsigned char* qrow = sb + 2 * HALF_BYTES + head * (HD * 2);
+            if (kFused) {
+                // raw q arrived: RMSNorm + RoPE of this group's 4 heads in place in the stage (same
+                // arithmetic and lane/dim mapping as the append kernel).  The q buffer in global memory
+                // is left untouched: other items of the row still read the raw row.
+                float cv[4], sv[4], wv[4];
+                load4(reinterpret_cast<const uint16_t*>(sb + X_OFF + X_COS), lane, cv);
+                load4(reinterpret_cast<const uint16_t*>(sb + X_OFF + X_SIN), lane, sv);
+                load4(s_w, lane, wv);
+#pragma unroll
+                for (int hh = 0; hh < 4; hh++) {
+                    uint16_t* qh = reinterpret_cast<uint16_t*>(sb + Q_OFF) + (kvh * 4 + hh) * HD;
+                    uint16_t out[4];
+                    head_norm_rope<true, true>(qh, wv, p.eps, cv, sv, lane, out);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) qh[lane + 32 * i] = out[i];
+                }
+                __syncwarp();
+            }
+            const unsigned char* qrow = sb + Q_OFF + head * (HD * 2);
 #pragma unroll
             for (int ks = 0; ks < 8; ks++) {
                 uint32_t lo = 0, hi = 0;
@@ -317,6 +387,33 @@ decode_attn_kernel(const DecodeParams p) {
             for (int j = 0; j < 16; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
             m_run = -1.0e30f;
             l_run = 0.0f;
+        }
+        const bool owner = kFused && (desc.z & F_LAST) && (desc.z & F_LASTRANGE);
+        if (owner) {
+            // the key being appended is the stage's last valid key: build its K (norm + rope) and V
+            // for this KV head in the stage, and write the cache row
+            const uint32_t kidx = nvalid - 1u;
+            float cv[4], sv[4], wv[4];
+            load4(reinterpret_cast<const uint16_t*>(sb + X_OFF + X_COS), lane, cv);
+            load4(reinterpret_cast<const uint16_t*>(sb + X_OFF + X_SIN), lane, sv);
+            load4(s_w + HD, lane, wv);
+            uint16_t out[4];
+            head_norm_rope<true, true>(reinterpret_cast<const uint16_t*>(sb + X_OFF + X_K) + kvh * HD, wv, p.eps, cv, sv,
+                                       lane, out);
+            const uint32_t roff = (kidx >> 2) * GPITCH + (kidx & 3u) * KV_ROW_BYTES;
+            uint16_t* krow_s = reinterpret_cast<uint16_t*>(kst + roff);
+            const uint64_t kp64 = *reinterpret_cast<const uint64_t*>(sb + DESC_OFF + 16);
+            const uint64_t vp64 = *reinterpret_cast<const uint64_t*>(sb + DESC_OFF + 24);
+            uint16_t* krow_g = reinterpret_cast<uint16_t*>(kp64 + (size_t)desc.w * KV_ROW_BYTES) + kvh * HD;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                krow_s[lane + 32 * i] = out[i];
+                krow_g[lane + 32 * i] = out[i];
+            }
+            const uint2 vv = *reinterpret_cast<const uint2*>(sb + X_OFF + X_V + kvh * (HD * 2) + lane * 8);
+            *reinterpret_cast<uint2*>(vst + roff + lane * 8) = vv;
+            *reinterpret_cast<uint2*>(vp64 + (size_t)desc.w * KV_ROW_BYTES + kvh * (HD * 2) + lane * 8) = vv;
+            __syncwarp();
         }
         if (nvalid < KS) {
             // tail stage: rows past the range keep stale bytes; zero this head's V slice there
@@ -389,7 +486,7 @@ decode_attn_kernel(const DecodeParams p) {
             }
         }
         // release the stage (generic writes of a tail stage are ordered before later bulk copies)
-        if (nvalid < KS) fence_proxy_async_smem();
+        if (nvalid < KS || owner || (kFused && (desc.z & F_FIRST))) fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty_bar[slot]);
 
@@ -497,15 +594,17 @@ uint32_t decode_chunk_keys() { return dec::CHUNK; }
 uint32_t decode_max_rows() { return dec::MAX_ROWS; }
 
 cudaError_t decode_attn_init() {
-    return cudaFuncSetAttribute(decode_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(decode_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)dec::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(decode_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)dec::SMEM_BYTES);
 }
 
-cudaError_t launch_decode_attn(cudaStream_t stream, const DecodeWorkspace& ws, void* ctx_out,
-                               const void* q, const void* gate, const uint64_t* k_ptrs,
-                               const uint64_t* v_ptrs, const uint32_t* seq_lens, uint32_t batch,
-                               uint32_t window) {
-    DecodeParams p;
+static DecodeParams make_params(const DecodeWorkspace& ws, void* ctx_out, const void* q, const void* gate,
+                                const uint64_t* k_ptrs, const uint64_t* v_ptrs, const uint32_t* seq_lens,
+                                uint32_t batch, uint32_t window) {
+    DecodeParams p = {};
     p.ctx_out = (uint16_t*)ctx_out;
     p.q = (const uint16_t*)q;
     p.gate = (const uint16_t*)gate;
@@ -520,7 +619,34 @@ cudaError_t launch_decode_attn(cudaStream_t stream, const DecodeWorkspace& ws, v
     p.window = window;
     p.max_chunks = ws.max_chunks;
     p.max_seq_len = ws.max_seq_len;
-    cudaError_t e = launch_pdl(decode_attn_kernel, dim3(ws.num_sms), dim3(dec::THREADS), dec::SMEM_BYTES,
+    return p;
+}
+
+cudaError_t launch_decode_attn(cudaStream_t stream, const DecodeWorkspace& ws, void* ctx_out,
+                               const void* q, const void* gate, const uint64_t* k_ptrs,
+                               const uint64_t* v_ptrs, const uint32_t* seq_lens, uint32_t batch,
+                               uint32_t window) {
+    const DecodeParams p = make_params(ws, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, batch, window);
+    cudaError_t e = launch_pdl(decode_attn_kernel<false>, dim3(ws.num_sms), dim3(dec::THREADS), dec::SMEM_BYTES,
+                               stream, p);
+    if (e != cudaSuccess) return e;
+    return launch_pdl(decode_merge_kernel, dim3(batch * NKV), dim3(128), 0, stream, p);
+}
+
+cudaError_t launch_append_decode(cudaStream_t stream, const DecodeWorkspace& ws, void* ctx_out, const void* q_io,
+                                 const void* k_in, const void* v_in, const void* gate, const void* q_norm_w,
+                                 const void* k_norm_w, const void* cos_t, const void* sin_t,
+                                 const uint32_t* seq_lens, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
+                                 uint32_t batch, uint32_t window, float eps) {
+    DecodeParams p = make_params(ws, ctx_out, q_io, gate, k_ptrs, v_ptrs, seq_lens, batch, window);
+    p.k_in = (const uint16_t*)k_in;
+    p.v_in = (const uint16_t*)v_in;
+    p.q_norm_w = (const uint16_t*)q_norm_w;
+    p.k_norm_w = (const uint16_t*)k_norm_w;
+    p.cos_t = (const uint16_t*)cos_t;
+    p.sin_t = (const uint16_t*)sin_t;
+    p.eps = eps;
+    cudaError_t e = launch_pdl(decode_attn_kernel<true>, dim3(ws.num_sms), dim3(dec::THREADS), dec::SMEM_BYTES,
                                stream, p);
     if (e != cudaSuccess) return e;
     return launch_pdl(decode_merge_kernel, dim3(batch * NKV), dim3(128), 0, stream, p);

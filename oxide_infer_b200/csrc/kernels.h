@@ -34,6 +34,12 @@ cudaError_t launch_decode_attn(cudaStream_t stream, const DecodeWorkspace& ws, v
                                const void* q, const void* gate, const uint64_t* k_ptrs,
                                const uint64_t* v_ptrs, const uint32_t* seq_lens, uint32_t batch,
                                uint32_t window);
+// Fused RMSNorm + RoPE + KV append + gated decode attention (positions are seq_lens - 1).
+cudaError_t launch_append_decode(cudaStream_t stream, const DecodeWorkspace& ws, void* ctx_out, const void* q_io,
+                                 const void* k_in, const void* v_in, const void* gate, const void* q_norm_w,
+                                 const void* k_norm_w, const void* cos_t, const void* sin_t,
+                                 const uint32_t* seq_lens, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
+                                 uint32_t batch, uint32_t window, float eps);
 uint32_t decode_chunk_keys();    // keys per split-KV work item
 uint32_t decode_max_rows();      // rows one launch can take
 

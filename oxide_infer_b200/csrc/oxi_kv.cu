@@ -82,7 +82,7 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
     if (!out) return fail(OXI_ERR_NULL, "oxi_create: out is null");
     *out = nullptr;
     if (max_batch == 0 || max_batch > decode_max_rows())
-        return fail(OXI_ERR_BATCH, "oxi_create: max_batch must be 1..2048");
+        return fail(OXI_ERR_BATCH, "oxi_create: max_batch must be 1..1024");
     if (max_seq_len == 0 || max_seq_len > (1u << 22)) return fail(OXI_ERR_ARG, "oxi_create: max_seq_len out of range");
     int ndev = 0;
     if (cudaGetDeviceCount(&ndev) != cudaSuccess || device < 0 || device >= ndev) {
@@ -243,10 +243,15 @@ int32_t oxi_append_decode(oxi_handle* h, void* stream, void* ctx_out, void* q_io
                           const uint32_t* pos_ids, const uint32_t* seq_lens,
                           const uint64_t* k_ptrs, const uint64_t* v_ptrs, uint32_t batch,
                           uint32_t window, float eps) {
-    int32_t rc = oxi_append(h, stream, q_io, k_in, v_in, q_norm_w, k_norm_w, cos_table, sin_table,
-                            pos_ids, k_ptrs, v_ptrs, batch, eps);
-    if (rc != OXI_OK) return rc;
-    return oxi_decode_attn(h, stream, ctx_out, q_io, gate, k_ptrs, v_ptrs, seq_lens, batch, window);
+    REQ_HANDLE("oxi_append_decode");
+    REQ_PTR(ctx_out && q_io && k_in && v_in && q_norm_w && k_norm_w && cos_table && sin_table && pos_ids &&
+                seq_lens && k_ptrs && v_ptrs, "oxi_append_decode");
+    REQ_BATCH(batch, h->max_batch, "oxi_append_decode");
+    if (!(eps >= 0.0f)) return fail(OXI_ERR_ARG, "oxi_append_decode: eps must be >= 0");
+    OXI_CUDA(launch_append_decode((cudaStream_t)stream, h->dws, ctx_out, q_io, k_in, v_in, gate, q_norm_w,
+                                  k_norm_w, cos_table, sin_table, seq_lens, k_ptrs, v_ptrs, batch, window, eps),
+             "append_decode launch");
+    return OXI_OK;
 }
 
 int32_t oxi_prefill_attn(oxi_handle* h, void* stream, void* ctx_out, const void* q,
@@ -364,16 +369,12 @@ int32_t oxi_decode_step_host(oxi_handle* h, void* stream, void* ctx_host, const 
         OXI_CUDA(cudaStreamWaitEvent(s, h->ev_up[sb], 0), "stream wait");
         // the ctx staging buffer of layer l-2 must have been downloaded
         if (l >= 2) OXI_CUDA(cudaStreamWaitEvent(s, h->ev_down[sb], 0), "stream wait");
-        OXI_CUDA(launch_append(s, h->stg_q[sb], h->stg_k[sb], h->stg_v[sb],
-                               (const char*)q_norm_w_dev + (size_t)l * HD * 2,
-                               (const char*)k_norm_w_dev + (size_t)l * HD * 2, cos_table_dev,
-                               sin_table_dev, h->stg_pos, h->stg_kp[sb], h->stg_vp[sb], batch, eps,
-                               h->dws.status),
-                 "append launch");
-        OXI_CUDA(launch_decode_attn(s, h->dws, h->stg_ctx[sb], h->stg_q[sb],
-                                    gate_host ? h->stg_gate[sb] : nullptr, h->stg_kp[sb],
-                                    h->stg_vp[sb], h->stg_len, batch, window),
-                 "decode_attn launch");
+        OXI_CUDA(launch_append_decode(s, h->dws, h->stg_ctx[sb], h->stg_q[sb], h->stg_k[sb], h->stg_v[sb],
+                                      gate_host ? h->stg_gate[sb] : nullptr,
+                                      (const char*)q_norm_w_dev + (size_t)l * HD * 2,
+                                      (const char*)k_norm_w_dev + (size_t)l * HD * 2, cos_table_dev,
+                                      sin_table_dev, h->stg_len, h->stg_kp[sb], h->stg_vp[sb], batch, window, eps),
+                 "append_decode launch");
         OXI_CUDA(cudaEventRecord(h->ev_comp[sb], s), "event record");
         OXI_CUDA(cudaStreamWaitEvent(h->d2h, h->ev_comp[sb], 0), "stream wait");
         OXI_CUDA(cudaMemcpyAsync((char*)ctx_host + l * qb, h->stg_ctx[sb], qb, cudaMemcpyDeviceToHost, h->d2h),

@@ -38,7 +38,7 @@ def test_create_argument_errors_need_no_device(lib):
     h = C.c_void_p()
     assert lib.oxi_create(None, 0, 8, 1024, 0) == -1
     assert lib.oxi_create(C.byref(h), 0, 0, 1024, 0) == -2
-    assert lib.oxi_create(C.byref(h), 0, 2049, 1024, 0) == -2
+    assert lib.oxi_create(C.byref(h), 0, 1025, 1024, 0) == -2
     assert lib.oxi_create(C.byref(h), 0, 8, 0, 0) == -3
     assert h.value is None
     assert lib.oxi_destroy(None) == 0

@@ -426,3 +426,49 @@ def test_prefill_attn(kv, ref, O, chunks, window):
         ref.sigmoid_gate(rctx, dg, rows)
         torch.cuda.synchronize()
         assert np.abs(mine - _np(rctx).astype(np.float32)).max() <= ATTN_TOL
+
+
+# ------------------------------------------------- fused append + decode --
+
+@pytest.mark.parametrize("lens,window", [([64, 100, 511, 300, 77, 256, 255, 129], 0),
+                                         ([0, 1, 2, 31, 32, 33], 0), ([255, 256, 257, 511, 512, 513], 256),
+                                         ([1023, 1024, 1025, 4095], 0), ([300, 700, 5], 128)])
+def test_fused_append_decode_matches_unfused_bitwise(kv, lens, window):
+    """oxi_append_decode (RMSNorm + RoPE + KV append inside the attention kernel) must leave the
+    same cache bytes and the same context bytes as oxi_append followed by oxi_decode_attn, and
+    must not modify q."""
+    case = DecodeCase(lens, seed=31 + len(lens) + window)
+    a, f = case.device(), case.device()
+    kv.append(a.q, a.k, a.v, a.q_norm_w, a.k_norm_w, a.cos, a.sin, a.pos_ids, a.k_ptrs, a.v_ptrs)
+    kv.decode_attn(a.ctx, a.q, a.gate, a.k_ptrs, a.v_ptrs, a.seq_lens, window)
+    q_before = f.q.clone()
+    kv.append_decode(f.ctx, f.q, f.k, f.v, f.gate, f.q_norm_w, f.k_norm_w, f.cos, f.sin, f.pos_ids, f.seq_lens,
+                     f.k_ptrs, f.v_ptrs, window)
+    torch.cuda.synchronize()
+    assert torch.equal(a.ctx.view(torch.int16), f.ctx.view(torch.int16))
+    assert torch.equal(f.q.view(torch.int16), q_before.view(torch.int16))
+    for i in range(case.b):
+        assert torch.equal(a.k_cache[i].view(torch.int16), f.k_cache[i].view(torch.int16))
+        assert torch.equal(a.v_cache[i].view(torch.int16), f.v_cache[i].view(torch.int16))
+
+
+def test_fused_append_decode_ragged_batch128(kv, ref):
+    lens = np.random.default_rng(7).integers(1024, 4097, 128) - 1
+    case = DecodeCase(lens, seed=7)
+    f = case.device()
+    kv.append_decode(f.ctx, f.q, f.k, f.v, f.gate, f.q_norm_w, f.k_norm_w, f.cos, f.sin, f.pos_ids, f.seq_lens,
+                     f.k_ptrs, f.v_ptrs, 0)
+    a = case.device()
+    kv.append(a.q, a.k, a.v, a.q_norm_w, a.k_norm_w, a.cos, a.sin, a.pos_ids, a.k_ptrs, a.v_ptrs)
+    kv.decode_attn(a.ctx, a.q, a.gate, a.k_ptrs, a.v_ptrs, a.seq_lens, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(a.ctx.view(torch.int16), f.ctx.view(torch.int16))
+    if ref is not None:
+        r = case.device()
+        ref.append(r.q, r.k, r.v, r.q_norm_w, r.k_norm_w, r.cos, r.sin, r.pos_ids, r.k_ptrs, r.v_ptrs, 128)
+        ref.decode_attention(r.ctx, r.q, r.gate, r.k_ptrs, r.v_ptrs, r.seq_lens, 128, 0, int(case.seq_lens.max()))
+        torch.cuda.synchronize()
+        assert np.abs(_np(f.ctx).astype(np.float32) - _np(r.ctx).astype(np.float32)).max() <= ATTN_TOL
+        for i in (0, 50, 127):
+            assert torch.equal(f.k_cache[i].view(torch.int16), r.k_cache[i].view(torch.int16))
+            assert torch.equal(f.v_cache[i].view(torch.int16), r.v_cache[i].view(torch.int16))
