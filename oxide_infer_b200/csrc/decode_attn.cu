@@ -331,6 +331,7 @@ decode_attn_kernel(const DecodeParams p) {
     const int g = lane >> 2;         // fragment row (query head within the group when g < 4)
     const int t4 = lane & 3;         // fragment column pair
     const uint32_t head = kvh * 4 + (g & 3);
+    const uint64_t keep_policy = l2_policy_evict_last();
 
     uint32_t qa[8][2];  // Q fragments (A operand, rows 0..3 = the group's heads, rows 4..15 zero)
     float o[16][4];
@@ -516,10 +517,10 @@ decode_attn_kernel(const DecodeParams p) {
             const size_t pslot = ((size_t)b * p.max_chunks + c) * NQ + head;
             float* pacc = p.partial_acc + pslot * HD;
 #pragma unroll
-            for (int j = 0; j < 16; j++)
-                __stcg(reinterpret_cast<float2*>(pacc + 8 * j + 2 * t4), make_float2(o[j][0], o[j][1]));
-            if (t4 == 0)
-                __stcg(reinterpret_cast<float2*>(p.partial_stats + pslot * 2), make_float2(m_run, l_tot));
+            // partials are read back by the merge kernel a few microseconds later: ask L2 to keep
+            // them while the K/V stream (evict_first) passes through
+            for (int j = 0; j < 16; j++) st_global_f2_hint(pacc + 8 * j + 2 * t4, o[j][0], o[j][1], keep_policy);
+            if (t4 == 0) st_global_f2_hint(p.partial_stats + pslot * 2, m_run, l_tot, keep_policy);
         }
     }
 }
