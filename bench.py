@@ -308,7 +308,7 @@ def run_ours(args, torch, rank, world, local_rank):
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_attn_kernel launch at the bench
 # workload, from the ncu capture summarised in profiles/decode_attn_kernel_B128_ctx4096.md
-TRAFFIC_PER_LAUNCH = 1074310000 + 7559168
+TRAFFIC_PER_LAUNCH = 1074318000 + 3661568
 
 
 def run_reference(args, torch, rank, world, local_rank):
