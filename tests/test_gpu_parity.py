@@ -472,3 +472,58 @@ def test_fused_append_decode_ragged_batch128(kv, ref):
         for i in (0, 50, 127):
             assert torch.equal(f.k_cache[i].view(torch.int16), r.k_cache[i].view(torch.int16))
             assert torch.equal(f.v_cache[i].view(torch.int16), r.v_cache[i].view(torch.int16))
+
+
+def test_decode_long_context_and_wide_batch(kv, ref):
+    """Maximum sizes: one 40,000-key row (157 key ranges) next to short rows, and a 256-row batch."""
+    case = DecodeCase([39999, 3, 20000, 511], seed=41)
+    d = case.device()
+    kv.append_decode(d.ctx, d.q, d.k, d.v, d.gate, d.q_norm_w, d.k_norm_w, d.cos, d.sin, d.pos_ids, d.seq_lens,
+                     d.k_ptrs, d.v_ptrs, 0)
+    torch.cuda.synchronize()
+    assert torch.isfinite(d.ctx.float()).all()
+    if ref is not None:
+        r = case.device()
+        ref.append(r.q, r.k, r.v, r.q_norm_w, r.k_norm_w, r.cos, r.sin, r.pos_ids, r.k_ptrs, r.v_ptrs, case.b)
+        ref.decode_attention(r.ctx, r.q, r.gate, r.k_ptrs, r.v_ptrs, r.seq_lens, case.b, 0, 40000)
+        torch.cuda.synchronize()
+        assert np.abs(_np(d.ctx).astype(np.float32) - _np(r.ctx).astype(np.float32)).max() <= ATTN_TOL
+    lens = np.random.default_rng(42).integers(1, 700, 256)
+    case = DecodeCase(lens, seed=42)
+    d = case.device()
+    kv.append_decode(d.ctx, d.q, d.k, d.v, d.gate, d.q_norm_w, d.k_norm_w, d.cos, d.sin, d.pos_ids, d.seq_lens,
+                     d.k_ptrs, d.v_ptrs, 256)
+    torch.cuda.synchronize()
+    if ref is not None:
+        r = case.device()
+        ref.append(r.q, r.k, r.v, r.q_norm_w, r.k_norm_w, r.cos, r.sin, r.pos_ids, r.k_ptrs, r.v_ptrs, 256)
+        ref.decode_attention(r.ctx, r.q, r.gate, r.k_ptrs, r.v_ptrs, r.seq_lens, 256, 256, int(case.seq_lens.max()))
+        torch.cuda.synchronize()
+        assert np.abs(_np(d.ctx).astype(np.float32) - _np(r.ctx).astype(np.float32)).max() <= ATTN_TOL
+
+
+def test_decode_step_replays_from_a_cuda_graph(kv):
+    """The fused step (programmatic dependent launches included) can be captured once and replayed:
+    a replay on fresh inputs equals the eager result byte for byte."""
+    case = DecodeCase([300, 1200, 64, 2047], seed=43)
+    e, g = case.device(), case.device()
+    kv.append_decode(e.ctx, e.q, e.k, e.v, e.gate, e.q_norm_w, e.k_norm_w, e.cos, e.sin, e.pos_ids, e.seq_lens,
+                     e.k_ptrs, e.v_ptrs, 0)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        # warm-up on the capture stream, then restore the cache rows the warm-up appended
+        with torch.cuda.graph(graph, stream=side):
+            kv.append_decode(g.ctx, g.q, g.k, g.v, g.gate, g.q_norm_w, g.k_norm_w, g.cos, g.sin, g.pos_ids,
+                             g.seq_lens, g.k_ptrs, g.v_ptrs, 0)
+    g.ctx.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(e.ctx.view(torch.int16), g.ctx.view(torch.int16))
+    for i in range(case.b):
+        assert torch.equal(e.k_cache[i].view(torch.int16), g.k_cache[i].view(torch.int16))
+    g.ctx.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(e.ctx.view(torch.int16), g.ctx.view(torch.int16))
