@@ -28,7 +28,9 @@
 // maximum exceeds it by more than 2^8 (then the thread rescales its O row in
 // TMEM); otherwise the stale maximum is kept, which is exact after the final
 // division by the row sum and keeps O untouched between MMAs.
-// The tensor core runs PV(j) and QK(j+1) back to back while the threads wait;
+// S is double buffered in TMEM and P(t) is written over the first columns of S(t): QK(t+1)
+// is issued before the threads start the softmax of tile t, so the tensor core computes the
+// next scores while the CUDA cores work, and PV(t) follows as soon as P(t) is stored;
 // K/V tiles are double buffered with cp.async (16-byte chunks written straight
 // into the swizzled layout, zero-filled past the run's last key).  Two CTAs are
 // resident per SM (256 of the 512 TMEM columns each), so one CTA's softmax
@@ -57,8 +59,8 @@ constexpr int KV_TILE = 2 * KV_SUB;          // 16 KB
 constexpr int STAGE = 2 * KV_TILE;           // K then V: 32 KB
 constexpr int NBUF = 2;
 constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + NBUF * STAGE;  // + slack for 1024-byte alignment
-constexpr uint32_t TMEM_COLS = 256;          // S [0,64) | P [64,96) | O [128,256)
-constexpr uint32_t S_COL = 0, P_COL = 64, O_COL = 128;
+constexpr uint32_t TMEM_COLS = 256;          // S0 [0,64) | S1 [64,128) | O [128,256); P(t) overwrites the head of S(t)
+constexpr uint32_t S_COL = 0, O_COL = 128;
 constexpr float RESCALE_THRESHOLD = 8.0f;    // log2 units: the stale maximum may lag by a factor 256
 constexpr float QK_SCALE_LOG2 = ATTN_SCALE * LOG2E;
 // instruction descriptors (kind::f16): D = f32, A = B = f16, M = 128
@@ -204,7 +206,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint64_t s_kp[TOK], s_vp[TOK];
     __shared__ uint32_t s_len[TOK];
-    __shared__ __align__(8) uint64_t bar_s, bar_o;
+    __shared__ __align__(8) uint64_t bar_s[2], bar_o;
     __shared__ uint32_t s_tmem, s_abort, s_item;
 
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;  // 1024-byte aligned tiles
@@ -219,7 +221,8 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     if (tid == 0) {
-        mbar_init(&bar_s, 1);
+        mbar_init(&bar_s[0], 1);
+        mbar_init(&bar_s[1], 1);
         mbar_init(&bar_o, 1);
         s_abort = 0u;
         mbar_fence_init();
@@ -229,7 +232,8 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     tc_fence_after();
     const uint32_t tmem = s_tmem;
     const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-    uint32_t par_s = 0, par_o = 0;
+    uint32_t gt = 0;      // tiles processed by this CTA so far: S buffer gt & 1, its barrier phase (gt >> 1) & 1
+    uint32_t par_o = 0;
     bool ok = true;
 
     // per-thread constants of the tile loaders: this thread copies chunk c of rows r0, r0+8, ...
@@ -284,14 +288,14 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     bool o_valid = false;   // O in TMEM holds a sum (false until the CTA's first PV)
     bool pv_pending = false;  // a PV MMA has been committed to bar_o and not yet waited for
 
-    auto issue_qk = [&](uint32_t ks) {  // S = Q K^T, 128 dims = 8 k-steps of 16
+    auto issue_qk = [&](uint32_t ks, uint32_t sbuf) {  // S[sbuf] = Q K^T, 128 dims = 8 k-steps of 16
 #pragma unroll
         for (int kk = 0; kk < 8; kk++) {
             const uint64_t ad = umma_desc(q_s + (kk >> 2) * Q_SUB + (kk & 3) * 32, 16, 1024);
             const uint64_t bd = umma_desc(ks + (kk >> 2) * KV_SUB + (kk & 3) * 32, 16, 1024);
-            umma_ss(tmem + S_COL, ad, bd, IDESC_QK, kk > 0 ? 1u : 0u);
+            umma_ss(tmem + S_COL + sbuf * TK, ad, bd, IDESC_QK, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&bar_s);
+        umma_commit(&bar_s[sbuf]);
     };
 
     // ---- runs of rows that share one cache
@@ -356,38 +360,49 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
             load_half(0, k_buf(0), kbase);
             load_half(0, v_buf(0), vbase);
             load_half(1, k_buf(1), kbase);
-            cp_async_wait<2>();
+            cp_async_wait<0>();
             fence_proxy_async_smem();  // cp.async-written tiles become visible to the tensor core
             tc_fence_before();
             __syncthreads();
             if (tid == 0) {
                 tc_fence_after();
-                issue_qk(k_buf(0));
+                issue_qk(k_buf(0), gt & 1u);
             }
 
             for (uint32_t tile = 0; tile < ntiles; tile++) {
                 // A wait that gives up (after ~1 s; cannot happen unless an MMA never completes)
                 // does not leave the loop: all threads keep the same barrier sequence, later
                 // waits return at once, the status word is set and no output is written.
-                ok &= mbar_wait_bounded(&bar_s, par_s, &s_abort);
-                par_s ^= 1u;
+                const uint32_t sbuf = gt & 1u;
+                ok &= mbar_wait_bounded(&bar_s[sbuf], (gt >> 1) & 1u, &s_abort);
                 __syncwarp();
                 tc_fence_after();
                 load_half(tile + 2, k_buf(tile), kbase);  // QK(tile) is done with its K buffer
+                // K(tile+1) (requested one iteration ago) must have landed: QK(tile+1) is issued now, into
+                // the other S buffer, so that it runs while the threads do the softmax of this tile
+                cp_async_wait<2>();
+                fence_proxy_async_smem();
+                tc_fence_before();
+                __syncthreads();
+                if (tid == 0 && tile + 1 < ntiles) {
+                    tc_fence_after();
+                    issue_qk(k_buf(tile + 1), sbuf ^ 1u);
+                }
 
                 // ---- this thread's S row: scale, mask, softmax weights against the reference maximum
                 const uint32_t kbeg = lo + tile * TK;
                 uint32_t sr[2][32];
-                tmem_ld32(lane_base + S_COL, sr[0]);
-                tmem_ld32(lane_base + S_COL + 32, sr[1]);
+                tmem_ld32(lane_base + S_COL + sbuf * TK, sr[0]);
+                tmem_ld32(lane_base + S_COL + sbuf * TK + 32, sr[1]);
                 tmem_wait_ld();
                 // Interior tiles (every key valid for every row of the M tile) skip the masks.
                 const bool interior = full_run && kbeg >= lo_max && kbeg + TK <= hi_min;
-                float mx = -1.0e30f;
+                // four independent accumulators keep the max / sum dependency chains short (one warp
+                // per scheduler per CTA: latency, not issue bandwidth, is what limits this loop)
+                float mxa[4] = {-1.0e30f, -1.0e30f, -1.0e30f, -1.0e30f};
                 if (interior) {
 #pragma unroll
-                    for (int c = 0; c < TK; c++) mx = fmaxf(mx, __uint_as_float(sr[c >> 5][c & 31]));
-                    mx *= QK_SCALE_LOG2;
+                    for (int c = 0; c < TK; c++) mxa[c & 3] = fmaxf(mxa[c & 3], __uint_as_float(sr[c >> 5][c & 31]));
                 } else {
 #pragma unroll
                     for (int c = 0; c < TK; c++) {
@@ -395,23 +410,25 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                         float v = __uint_as_float(sr[c >> 5][c & 31]);
                         v = (key >= rlo && key < rhi) ? v : -INFINITY;
                         sr[c >> 5][c & 31] = __float_as_uint(v);
-                        mx = fmaxf(mx, v);
+                        mxa[c & 3] = fmaxf(mxa[c & 3], v);
                     }
-                    mx = mx > -1.0e29f ? mx * QK_SCALE_LOG2 : -1.0e30f;  // stays -1e30 when the whole row is masked
                 }
+                float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
+                mx = mx > -1.0e29f ? mx * QK_SCALE_LOG2 : -1.0e30f;  // stays -1e30 when the whole row is masked
                 const bool raise = mx > m_ref + RESCALE_THRESHOLD;
                 const float corr = raise ? ex2_approx_ftz(m_ref - mx) : 1.0f;
                 if (raise) m_ref = mx;
-                float psum = 0.0f;
+                float psa[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 uint32_t pk[32];
                 const float neg_m = -m_ref;
 #pragma unroll
                 for (int c = 0; c < TK; c += 2) {  // p = 2^(s*scale*log2e - m): one fma + one ex2 per key
                     const float p0 = ex2_approx_ftz(fmaf(__uint_as_float(sr[c >> 5][c & 31]), QK_SCALE_LOG2, neg_m));
                     const float p1 = ex2_approx_ftz(fmaf(__uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]), QK_SCALE_LOG2, neg_m));
-                    psum += p0 + p1;
+                    psa[(c >> 1) & 3] += p0 + p1;
                     pk[c >> 1] = pack_h2(p0, p1);
                 }
+                const float psum = (psa[0] + psa[1]) + (psa[2] + psa[3]);
                 l_run = l_run * corr + psum;
 
                 // ---- PV(tile-1) must be complete before P is overwritten and before O is rescaled;
@@ -436,10 +453,10 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                         tmem_st32(lane_base + O_COL + ch * 32, orow);
                     }
                 }
-                tmem_st32(lane_base + P_COL, pk);
+                tmem_st32(lane_base + S_COL + sbuf * TK, pk);  // P(tile) over the head of S(tile)
                 tmem_wait_st();
-                // V(tile) and K(tile+1) must have landed before the MMAs below; the two groups
-                // requested in this iteration may still be in flight
+                // V(tile) must have landed before PV(tile); the two groups requested in this
+                // iteration may still be in flight
                 cp_async_wait<2>();
                 fence_proxy_async_smem();
                 tc_fence_before();
@@ -450,13 +467,13 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
 #pragma unroll
                     for (int kk = 0; kk < TK / 16; kk++) {  // 64 keys = 4 k-steps of 16
                         const uint64_t bd = umma_desc(vs + kk * 16 * ROW_B, KV_SUB, 1024);
-                        umma_ts(tmem + O_COL, tmem + P_COL + kk * 8, bd, IDESC_PV, (kk > 0 || o_valid) ? 1u : 0u);
+                        umma_ts(tmem + O_COL, tmem + S_COL + sbuf * TK + kk * 8, bd, IDESC_PV, (kk > 0 || o_valid) ? 1u : 0u);
                     }
                     umma_commit(&bar_o);
-                    if (tile + 1 < ntiles) issue_qk(k_buf(tile + 1));
                 }
                 o_valid = true;
                 pv_pending = true;
+                ++gt;
             }
         }
         run0 = run1;
