@@ -1,7 +1,7 @@
 // Chunked-prefill causal GQA attention with the sigmoid gate over per-row
 // pointer tables, as one fused flash-attention kernel on the 5th-generation
-// tensor cores: tcgen05.mma with accumulators in tensor memory (TMEM).  Scores
-// and weights stay on chip.
+// tensor cores: tcgen05.mma with accumulators, weights and the query tile in
+// tensor memory (TMEM).  Scores and weights stay on chip.
 //
 // Replaces BatchEngine::gemm_attention_chunk (batch_engine.rs:439-592: pack_q,
 // cuBLASLt QK^T to f32 scores in HBM, softmax_mask to f16 weights in HBM,
@@ -12,55 +12,63 @@
 // the cache k_ptrs[r] / v_ptrs[r]; all rows' K/V were appended before the call,
 // so causality is the per-row upper bound.
 //
-// A CTA owns 32 consecutive wave rows (tokens) and one KV head: its M = 128
-// tile is (4 query heads of the group) x (32 tokens), row = head*32 + token, so
-// a K/V tile is read once for 128 (token, head) pairs and warp w / lane l of the
-// CTA owns exactly row (head w, token l) of the accumulator, which is TMEM lane
-// 32*w + l: the softmax is thread-local, no shuffles.
+// Work item = 64 consecutive wave rows (tokens) and one KV head, processed by one
+// persistent CTA per SM as TWO M = 128 query tiles (tokens 0-31 and 32-63; a tile is
+// (4 query heads of the group) x (32 tokens), row = head*32 + token) that share every
+// K/V tile brought into shared memory.  Warp roles:
+//   warps 0-3   softmax of query tile 0: warp w / lane l owns accumulator row (head w,
+//               token l) = TMEM lane 32*w + l, so the softmax is thread-local, no shuffles
+//   warps 4-7   softmax of query tile 1 (same TMEM lanes, other columns)
+//   warp 8      issues every tcgen05.mma (one elected lane, warp-uniform control flow)
+//   warp 9 / 10 K / V tile loaders: cp.async 16-byte chunks written straight into the
+//               128-byte-swizzled layout (zero-filled past the run's last key), a ring of
+//               4 stages each, 3 tiles in flight
+// all connected by mbarriers only (no CTA-wide barrier inside an item).
 //
-// Per 64-key tile:  S = Q K^T  (tcgen05.mma, A = Q from shared memory, B = K tile
-// from shared memory, both K-major with the 128-byte swizzle, D = S in TMEM)
-// -> each thread loads its S row (tcgen05.ld), applies scale, causal/window
-// mask and the online-softmax update, writes P as f16 back to TMEM
-// (tcgen05.st) -> O += P V (tcgen05.mma, A = P from TMEM, B = V tile from shared
-// memory, MN-major, D = O accumulating in TMEM across all tiles).
+// Per 64-key tile and query tile j:  S_j = Q_j K^T  (A = Q_j from TMEM, B = K tile from
+// shared memory, K-major, D = S_j in TMEM) -> each softmax thread loads its S row
+// (tcgen05.ld), applies scale, causal/window mask and the online-softmax update, writes P
+// as f16 over the first columns of S_j (tcgen05.st) -> O_j += P_j V  (A = P_j from TMEM,
+// B = V tile from shared memory, MN-major, D = O_j accumulating in TMEM across all tiles).
+// The tensor pipe runs  PV_0(t-1) QK_0(t) | PV_1(t-1) QK_1(t) | ...  so that the softmax
+// of one query tile overlaps the MMAs of the other.
 // The running maximum used for the exponentials is only raised when a tile's
 // maximum exceeds it by more than 2^8 (then the thread rescales its O row in
 // TMEM); otherwise the stale maximum is kept, which is exact after the final
 // division by the row sum and keeps O untouched between MMAs.
-// S is double buffered in TMEM and P(t) is written over the first columns of S(t): QK(t+1)
-// is issued before the threads start the softmax of tile t, so the tensor core computes the
-// next scores while the CUDA cores work, and PV(t) follows as soon as P(t) is stored;
-// K/V tiles are double buffered with cp.async (16-byte chunks written straight
-// into the swizzled layout, zero-filled past the run's last key).  Two CTAs are
-// resident per SM (256 of the 512 TMEM columns each), so one CTA's softmax
-// overlaps the other's MMAs.
 //
-// Rows of a 32-row block that point at different caches are processed as
+// TMEM (all 512 columns, one CTA per SM): Q_0 Q_1 (64 each: 128 dims as f16 pairs) |
+// S_0 S_1 (64 each) | O_0 O_1 (128 each).
+//
+// Rows of a 64-row block that point at different caches are processed as
 // separate runs of equal pointers (rows outside the run are masked), so any
 // table contents are legal; the engine's waves (consecutive positions of one
 // request per chunk) give one run per block except where a chunk boundary falls
 // inside a block.
+//
+// Every wait is bounded (about one second); a wait that gives up sets a CTA-wide flag that
+// makes every later wait return at once, the kernel then finishes its control flow without
+// writing output and reports OXI_DEV_WAIT_TIMEOUT in the status word.
 #include "common.cuh"
 #include "kernels.h"
 
 namespace oxi {
 
 namespace pf {
-constexpr int TOK = 32;                      // wave rows per CTA
+constexpr int TOK = 32;                      // wave rows per query tile
+constexpr int BLK = 64;                      // wave rows per work item (two query tiles)
 constexpr int M = 128;                       // accumulator rows = 4 heads x 32 tokens
 constexpr int TK = 64;                       // keys per tile
-constexpr int THREADS = 128;
+constexpr int THREADS = 384;                 // 8 softmax warps, MMA warp, K loader, V loader, one idle warp
+constexpr int W_MMA = 8, W_KLOAD = 9, W_VLOAD = 10;
 constexpr int ROW_B = 128;                   // bytes per swizzled row (64 f16)
-constexpr int Q_SUB = M * ROW_B;             // one 64-dim half of Q: 16 KB
-constexpr int Q_BYTES = 2 * Q_SUB;           // 32 KB
 constexpr int KV_SUB = TK * ROW_B;           // one 64-dim half of a K (or V) tile: 8 KB
 constexpr int KV_TILE = 2 * KV_SUB;          // 16 KB
-constexpr int STAGE = 2 * KV_TILE;           // K then V: 32 KB
-constexpr int NBUF = 2;
-constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + NBUF * STAGE;  // + slack for 1024-byte alignment
-constexpr uint32_t TMEM_COLS = 256;          // S0 [0,64) | S1 [64,128) | O [128,256); P(t) overwrites the head of S(t)
-constexpr uint32_t S_COL = 0, O_COL = 128;
+constexpr int NS = 4;                        // ring stages, for K and for V
+constexpr int DEPTH = 3;                     // tiles a loader keeps in flight
+constexpr size_t SMEM_BYTES = 1024 + 2 * NS * KV_TILE;  // + slack for 1024-byte alignment; > half an SM: one CTA per SM
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t Q_COL = 0, S_COL = 128, O_COL = 256;  // + j*64, + j*64, + j*128 for query tile j
 constexpr float RESCALE_THRESHOLD = 8.0f;    // log2 units: the stale maximum may lag by a factor 256
 constexpr float QK_SCALE_LOG2 = ATTN_SCALE * LOG2E;
 // instruction descriptors (kind::f16): D = f32, A = B = f16, M = 128
@@ -136,7 +144,7 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// Orders the 32-row blocks of the wave by decreasing work (key tiles to scan) with a counting
+// Orders the 64-row blocks of the wave by decreasing work (key tiles to scan) with a counting
 // sort, so that the persistent CTAs of the main kernel claim the longest items first, and
 // resets the claim counter.  One CTA.
 __global__ void __launch_bounds__(1024)
@@ -146,16 +154,16 @@ prefill_plan_kernel(const uint32_t* __restrict__ seq_lens, uint32_t rows, uint32
     constexpr int NB = 1024;
     __shared__ uint32_t hist[NB];
     __shared__ uint32_t warp_tot[32];
-    const uint32_t nblocks = (rows + TOK - 1) / TOK;
+    const uint32_t nblocks = (rows + BLK - 1) / BLK;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     hist[tid] = 0u;
     if (tid == 0) *counter = 0u;
     __syncthreads();
     auto key_of = [&](uint32_t blk) {
         uint32_t lo = 0xffffffffu, hi = 0;
-        const uint32_t r1 = min(rows, (blk + 1) * TOK);
+        const uint32_t r1 = min(rows, (blk + 1) * BLK);
 #pragma unroll 8
-        for (uint32_t r = blk * TOK; r < r1; r++) {
+        for (uint32_t r = blk * BLK; r < r1; r++) {
             const uint32_t sl = seq_lens[r];
             if (sl == 0) continue;
             lo = min(lo, window_start(sl, window));
@@ -202,7 +210,40 @@ prefill_plan_kernel(const uint32_t* __restrict__ seq_lens, uint32_t rows, uint32
     }
 }
 
-__global__ void __launch_bounds__(pf::THREADS, 2)
+// A run of consecutive block rows that share one cache, with the union of their key intervals.
+struct PfRun {
+    uint32_t r0, r1, lo, hi;
+};
+
+// Finds the next run at or after row `next` that has keys to scan.  Every thread of the CTA walks
+// the same tables, so all warp roles see the same sequence of runs and tiles.
+__device__ __forceinline__ bool pf_next_run(uint32_t& next, uint32_t nrows, const uint64_t* s_kp,
+                                            const uint64_t* s_vp, const uint32_t* s_len,
+                                            uint32_t window, PfRun& run) {
+    while (next < nrows) {
+        const uint32_t r0 = next;
+        uint32_t r1 = r0 + 1;
+        while (r1 < nrows && s_kp[r1] == s_kp[r0] && s_vp[r1] == s_vp[r0]) r1++;
+        next = r1;
+        uint32_t lo = 0xffffffffu, hi = 0;
+        for (uint32_t i = r0; i < r1; i++) {
+            const uint32_t sl = s_len[i];
+            if (sl == 0) continue;  // skipped row
+            lo = min(lo, window_start(sl, window));
+            hi = max(hi, sl);
+        }
+        if (hi > lo) {
+            run.r0 = r0;
+            run.r1 = r1;
+            run.lo = lo;
+            run.hi = hi;
+            return true;
+        }
+    }
+    return false;
+}
+
+__global__ void __launch_bounds__(pf::THREADS, 1)
 prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__ q,
                     const uint16_t* __restrict__ gate, const uint64_t* __restrict__ k_ptrs,
                     const uint64_t* __restrict__ v_ptrs, const uint32_t* __restrict__ seq_lens,
@@ -210,30 +251,39 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                     const uint32_t* __restrict__ order, uint32_t* __restrict__ counter) {
     using namespace pf;
     extern __shared__ unsigned char smem_raw[];
-    __shared__ uint64_t s_kp[TOK], s_vp[TOK];
-    __shared__ uint32_t s_len[TOK];
-    __shared__ __align__(8) uint64_t bar_s[2], bar_o;
+    __shared__ uint64_t s_kp[BLK], s_vp[BLK];
+    __shared__ uint32_t s_len[BLK];
+    // loaders -> MMA warp (32 arrivals) and back (tcgen05.commit)
+    __shared__ __align__(8) uint64_t bar_kfull[NS], bar_kempty[NS], bar_vfull[NS], bar_vempty[NS];
+    // per query tile: S ready (commit), P stored (128 arrivals), Q stored (128 arrivals), O final (commit)
+    __shared__ __align__(8) uint64_t bar_sfull[2], bar_pfull[2], bar_qfull[2], bar_ofull[2];
     __shared__ uint32_t s_tmem, s_abort, s_item;
 
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;  // 1024-byte aligned tiles
-    const uint32_t q_s = sbase;
-    const uint32_t kv_s = sbase + Q_BYTES;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // The MMAs are issued by one elected lane of warp 0 inside warp-uniform control flow, with
-    // descriptors derived from values the compiler can prove uniform (a shuffle from lane 0):
-    // issued under `if (tid == 0)` the same 12 MMAs per tile took ~1100 clocks instead of ~550.
+    const uint32_t k_s = sbase, v_s = sbase + NS * KV_TILE;
+    const int tid = threadIdx.x, lane = tid & 31;
+    // warp index the compiler can prove uniform: role branches and MMA issue stay in uniform control flow
     const int warp_u = __shfl_sync(0xffffffffu, tid >> 5, 0);
-    const uint32_t nitems = ((rows + TOK - 1) / TOK) * NKV;
+    const uint32_t nitems = ((rows + BLK - 1) / BLK) * NKV;
 
-    // ---- once per CTA: TMEM allocation, barriers
-    if (warp == 0) {
+    // ---- once per CTA: TMEM allocation (all 512 columns; one CTA per SM), barriers
+    if (warp_u == W_MMA) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     if (tid == 0) {
-        mbar_init(&bar_s[0], 1);
-        mbar_init(&bar_s[1], 1);
-        mbar_init(&bar_o, 1);
+        for (int s = 0; s < NS; s++) {
+            mbar_init(&bar_kfull[s], 32);
+            mbar_init(&bar_vfull[s], 32);
+            mbar_init(&bar_kempty[s], 1);
+            mbar_init(&bar_vempty[s], 1);
+        }
+        for (int j = 0; j < 2; j++) {
+            mbar_init(&bar_sfull[j], 1);
+            mbar_init(&bar_pfull[j], M);
+            mbar_init(&bar_qfull[j], M);
+            mbar_init(&bar_ofull[j], 1);
+        }
         s_abort = 0u;
         mbar_fence_init();
     }
@@ -241,30 +291,26 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = __shfl_sync(0xffffffffu, s_tmem, 0);
-    const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-    uint32_t gt = 0;      // tiles processed by this CTA so far: S buffer gt & 1, its barrier phase (gt >> 1) & 1
-    uint32_t par_o = 0;
+
+    // Every role counts the same sequence of K/V tiles: tile gk uses ring stage gk % NS in its
+    // (gk / NS)-th use and phase gk & 1 of the per-tile barriers.
+    uint32_t gk = 0;
+    uint32_t n_o = 0;  // items of this CTA that had tiles (phase of bar_ofull)
     bool ok = true;
 
-    // per-thread constants of the tile loaders: this thread copies chunk c of rows r0, r0+8, ...
-    const uint32_t ld_r0 = tid >> 4, ld_c = tid & 15u;
-    const uint32_t ld_soff = (ld_c >> 3) * KV_SUB + ld_r0 * ROW_B + (((ld_c & 7u) ^ (ld_r0 & 7u)) << 4);
-
-  // ======== persistent loop over (32-row block, KV head) items, longest first ========
-  for (;;) {
-    tc_fence_before();
-    __syncthreads();  // the previous item's tables, Q tile and TMEM contents are no longer in use
+  // ======== persistent loop over (64-row block, KV head) items, longest first ========
+  for (uint32_t it = 0;; ++it) {
+    __syncthreads();  // the previous item's tables are no longer in use
     if (tid == 0) s_item = atomicAdd(counter, 1u);
     __syncthreads();
     const uint32_t item = s_item;
     if (item >= nitems) break;
-    const uint32_t row0 = order[item >> 2] * TOK;
+    const uint32_t row0 = order[item >> 2] * BLK;
     const int kvh = item & 3u;
-    const int head = kvh * 4 + warp;          // this thread's query head
-    const uint32_t nrows = min((uint32_t)TOK, rows - row0);
+    const uint32_t nrows = min((uint32_t)BLK, rows - row0);
 
     // ---- tables of the block's rows
-    if (tid < TOK) {
+    if (tid < BLK) {
         uint64_t kp = 0, vp = 0;
         uint32_t sl = 0;
         if ((uint32_t)tid < nrows) {
@@ -283,141 +329,71 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         s_vp[tid] = vp;
         s_len[tid] = sl;  // 0 marks a row that is skipped
     }
-    // ---- Q tile: row = head*32 + token, two 64-dim halves, 16-byte chunks swizzled by (row & 7)
-    for (uint32_t i = tid; i < (uint32_t)M * 16u; i += THREADS) {
-        const uint32_t r = i >> 4, c = i & 15u;
-        const uint32_t hh = r >> 5, tok = r & 31u;
-        const bool valid = tok < nrows;
-        const uint16_t* src = q + ((size_t)(row0 + (valid ? tok : 0u)) * NQ + kvh * 4 + hh) * HD + c * 8;
-        cp_async_16(q_s + (c >> 3) * Q_SUB + r * ROW_B + (((c & 7u) ^ (r & 7u)) << 4), src, valid);
-    }
-    cp_async_commit();
     __syncthreads();
 
-    float m_ref = -1.0e30f, l_run = 0.0f;  // maximum used for the exponentials (may be stale), row sum
-    bool o_valid = false;   // O in TMEM holds a sum (false until the CTA's first PV)
-    bool pv_pending = false;  // a PV MMA has been committed to bar_o and not yet waited for
-
-    // descriptors of the tiles at the start of each buffer; a sub-tile / k-step / stage is an
-    // offset added to the 16-byte-unit start address field (no carry: shared addresses < 256 KB)
-    const uint64_t q_desc = umma_desc(q_s, 16, 1024);
-    const uint64_t k_desc0 = umma_desc(kv_s, 16, 1024);                // K tiles: K-major
-    const uint64_t v_desc0 = umma_desc(kv_s + KV_TILE, KV_SUB, 1024);  // V tiles: MN-major
-    auto issue_qk = [&](uint32_t stage, uint32_t sbuf) {  // whole warp 0; S[sbuf] = Q K^T, 128 dims = 8 k-steps of 16
-        const uint64_t kd = k_desc0 + (uint64_t)(stage * (STAGE >> 4));
-        if (elect_one()) {
+    if (warp_u < 8) {
+        // ================= softmax warps: query tile j, accumulator row (head hw, token lane) =================
+        const int j = warp_u >> 2, hw = warp_u & 3;
+        const uint32_t tok = (uint32_t)(j * TOK + lane);
+        const int head = kvh * 4 + hw;
+        const uint32_t lane_base = tmem + ((uint32_t)(hw * 32) << 16);
+        const uint32_t q_t = lane_base + Q_COL + j * 64, s_t = lane_base + S_COL + j * 64;
+        const uint32_t o_t = lane_base + O_COL + j * 128;
+        // This thread's query row goes to TMEM as the A operand of the score MMAs (128 dims = 64
+        // columns of f16 pairs).  The previous item's MMAs on this query tile completed before
+        // this warp left that item's epilogue.
+        {
+            const bool valid = tok < nrows;
+            const uint4* src = reinterpret_cast<const uint4*>(q + ((size_t)(row0 + (valid ? tok : 0u)) * NQ + head) * HD);
 #pragma unroll
-            for (int kk = 0; kk < 8; kk++) {
-                const uint32_t qoff = (uint32_t)(((kk >> 2) * Q_SUB + (kk & 3) * 32) >> 4);
-                const uint32_t koff = (uint32_t)(((kk >> 2) * KV_SUB + (kk & 3) * 32) >> 4);
-                umma_ss(tmem + S_COL + sbuf * TK, q_desc + qoff, kd + koff, IDESC_QK, kk > 0 ? 1u : 0u);
-            }
-            umma_commit(&bar_s[sbuf]);
-        }
-        __syncwarp();
-    };
-
-    // ---- runs of rows that share one cache
-    uint32_t run0 = 0;
-    while (run0 < nrows) {
-        uint32_t run1 = run0 + 1;
-        while (run1 < nrows && s_kp[run1] == s_kp[run0] && s_vp[run1] == s_vp[run0]) run1++;
-        uint32_t lo = 0xffffffffu, hi = 0, lo_max = 0, hi_min = 0xffffffffu;
-        bool full_run = (run1 - run0 == (uint32_t)TOK);  // every row of the M tile belongs to the run
-        for (uint32_t i = run0; i < run1; i++) {
-            const uint32_t sl = s_len[i];
-            if (sl == 0) { full_run = false; continue; }
-            lo = min(lo, window_start(sl, window));
-            hi = max(hi, sl);
-            lo_max = max(lo_max, window_start(sl, window));
-            hi_min = min(hi_min, sl);
-        }
-        if (hi > lo) {
-            // this thread's row (token = lane): valid key interval inside the run, empty if not in the run
-            const bool in = (uint32_t)lane >= run0 && (uint32_t)lane < run1 && s_len[lane] != 0;
-            const uint32_t rhi = in ? s_len[lane] : 0u;
-            const uint32_t rlo = in ? window_start(s_len[lane], window) : 0u;
-            const char* kbase = reinterpret_cast<const char*>(s_kp[run0]) + kvh * (HD * 2);
-            const char* vbase = reinterpret_cast<const char*>(s_vp[run0]) + kvh * (HD * 2);
-            const uint32_t ntiles = (hi - lo + TK - 1) / TK;
-
-            // K and V tiles have separate double buffers and separate cp.async groups: K(t+2) is
-            // requested when QK(t) has completed, V(t+1) when PV(t-1) has completed, so every load
-            // has a whole iteration to land.  One group is committed per call (possibly empty) so
-            // that wait_group counts stay uniform.
-            auto load_half = [&](uint32_t tile, uint32_t dst, const char* base) {
-                if (tile < ntiles) {
-                    const uint32_t kbeg = lo + tile * TK;
-                    const char* src = base + (size_t)(kbeg + ld_r0) * KV_ROW_BYTES + ld_c * 16;
-                    const uint32_t d = dst + ld_soff;
-                    if (kbeg + TK <= hi) {
+            for (int hf = 0; hf < 2; hf++) {
+                uint32_t qr[32];
 #pragma unroll
-                        for (int k = 0; k < TK / 8; k++)  // rows r0 + 8k: same swizzle phase, fixed strides
-                            cp_async_16(d + k * 8 * ROW_B, src + (size_t)k * 8 * KV_ROW_BYTES, true);
-                    } else {
-#pragma unroll
-                        for (int k = 0; k < TK / 8; k++) {
-                            const bool valid = kbeg + ld_r0 + 8 * k < hi;
-                            cp_async_16(d + k * 8 * ROW_B, valid ? src + (size_t)k * 8 * KV_ROW_BYTES : base, valid);
-                        }
-                    }
+                for (int i = 0; i < 8; i++) {
+                    const uint4 v = valid ? __ldg(src + hf * 8 + i) : make_uint4(0u, 0u, 0u, 0u);
+                    qr[4 * i] = v.x;
+                    qr[4 * i + 1] = v.y;
+                    qr[4 * i + 2] = v.z;
+                    qr[4 * i + 3] = v.w;
                 }
-                cp_async_commit();
-            };
-            auto k_buf = [&](uint32_t tile) { return kv_s + (tile & 1u) * STAGE; };
-            auto v_buf = [&](uint32_t tile) { return kv_s + (tile & 1u) * STAGE + KV_TILE; };
-
-            // The previous run's last PV may still be reading its V tile and P.
-            if (pv_pending) {
-                ok &= mbar_wait_bounded(&bar_o, par_o, &s_abort);
-                par_o ^= 1u;
-                pv_pending = false;
-                __syncwarp();
-                tc_fence_after();
+                tmem_st32(q_t + hf * 32, qr);
             }
-            // prologue of the run: K(0), V(0), K(1) requested; S(0) issued as soon as K(0) landed
-            load_half(0, k_buf(0), kbase);
-            load_half(0, v_buf(0), vbase);
-            load_half(1, k_buf(1), kbase);
-            cp_async_wait<0>();
-            fence_proxy_async_smem();  // cp.async-written tiles become visible to the tensor core
+            tmem_wait_st();
             tc_fence_before();
-            __syncthreads();
-            if (warp_u == 0) {
-                tc_fence_after();
-                issue_qk(0u, gt & 1u);
-            }
+            mbar_arrive(&bar_qfull[j]);
+        }
 
+        float m_ref = -1.0e30f, l_run = 0.0f;  // maximum used for the exponentials (may be stale), row sum
+        bool o_valid = false;                  // O in TMEM holds a sum (false until the item's first PV)
+        uint32_t next = 0;
+        PfRun run;
+        while (pf_next_run(next, nrows, s_kp, s_vp, s_len, window, run)) {
+            // this thread's row: valid key interval inside the run, empty if not in the run
+            const bool in = tok >= run.r0 && tok < run.r1 && s_len[tok] != 0;
+            const uint32_t rhi = in ? s_len[tok] : 0u;
+            const uint32_t rlo = in ? window_start(s_len[tok], window) : 0u;
+            // key range that is valid for every row of this query tile (mask-free tiles)
+            uint32_t lo_max = 0, hi_min = 0xffffffffu;
+            bool full = run.r0 <= (uint32_t)(j * TOK) && run.r1 >= (uint32_t)(j * TOK + TOK);
+            if (full) {
+                for (int i = j * TOK; i < j * TOK + TOK; i++) {
+                    const uint32_t sl = s_len[i];
+                    if (sl == 0) full = false;
+                    lo_max = max(lo_max, window_start(sl, window));
+                    hi_min = min(hi_min, sl);
+                }
+            }
+            const uint32_t ntiles = (run.hi - run.lo + TK - 1) / TK;
             for (uint32_t tile = 0; tile < ntiles; tile++) {
-                // A wait that gives up (after ~1 s; cannot happen unless an MMA never completes)
-                // does not leave the loop: all threads keep the same barrier sequence, later
-                // waits return at once, the status word is set and no output is written.
-                const uint32_t sbuf = gt & 1u;
-                ok &= mbar_wait_bounded(&bar_s[sbuf], (gt >> 1) & 1u, &s_abort);
+                ok &= mbar_wait_bounded(&bar_sfull[j], gk & 1u, &s_abort);  // S_j(tile) complete, and PV_j of the tile before
                 __syncwarp();
                 tc_fence_after();
-                load_half(tile + 2, k_buf(tile), kbase);  // QK(tile) is done with its K buffer
-                // K(tile+1) (requested one iteration ago) must have landed: QK(tile+1) is issued now, into
-                // the other S buffer, so that it runs while the threads do the softmax of this tile
-                cp_async_wait<2>();
-                fence_proxy_async_smem();
-                tc_fence_before();
-                __syncthreads();
-                if (warp_u == 0 && tile + 1 < ntiles) {
-                    tc_fence_after();
-                    issue_qk((tile + 1) & 1u, sbuf ^ 1u);
-                }
-
-                // ---- this thread's S row: scale, mask, softmax weights against the reference maximum
-                const uint32_t kbeg = lo + tile * TK;
+                const uint32_t kbeg = run.lo + tile * TK;
                 uint32_t sr[2][32];
-                tmem_ld32(lane_base + S_COL + sbuf * TK, sr[0]);
-                tmem_ld32(lane_base + S_COL + sbuf * TK + 32, sr[1]);
+                tmem_ld32(s_t, sr[0]);
+                tmem_ld32(s_t + 32, sr[1]);
                 tmem_wait_ld();
-                // Interior tiles (every key valid for every row of the M tile) skip the masks.
-                const bool interior = full_run && kbeg >= lo_max && kbeg + TK <= hi_min;
-                // four independent accumulators keep the max / sum dependency chains short (one warp
-                // per scheduler per CTA: latency, not issue bandwidth, is what limits this loop)
+                const bool interior = full && kbeg >= lo_max && kbeg + TK <= hi_min;
                 float mxa[4] = {-1.0e30f, -1.0e30f, -1.0e30f, -1.0e30f};
                 if (interior) {
 #pragma unroll
@@ -447,104 +423,214 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                     psa[(c >> 1) & 3] += p0 + p1;
                     pk[c >> 1] = pack_h2(p0, p1);
                 }
-                const float psum = (psa[0] + psa[1]) + (psa[2] + psa[3]);
-                l_run = l_run * corr + psum;
-
-                // ---- PV(tile-1) must be complete before P is overwritten and before O is rescaled;
-                // its V stage is then free for tile+1 (tile 1 of a run was loaded in the prologue)
-                if (pv_pending) {
-                    ok &= mbar_wait_bounded(&bar_o, par_o, &s_abort);
-                    par_o ^= 1u;
-                    pv_pending = false;
-                    __syncwarp();
-                    tc_fence_after();
-                }
-                load_half(tile + 1, v_buf(tile + 1), vbase);  // PV(tile-1) is done with that V buffer
+                l_run = l_run * corr + ((psa[0] + psa[1]) + (psa[2] + psa[3]));
                 if (o_valid && __any_sync(0xffffffffu, raise)) {
                     // rare: the reference maximum of some row of this warp moved; rescale the warp's O rows
+                    // (no MMA touches O_j between the completion seen above and the arrival below)
 #pragma unroll
                     for (int ch = 0; ch < 4; ch++) {
                         uint32_t orow[32];
-                        tmem_ld32(lane_base + O_COL + ch * 32, orow);
+                        tmem_ld32(o_t + ch * 32, orow);
                         tmem_wait_ld();
 #pragma unroll
                         for (int i = 0; i < 32; i++) orow[i] = __float_as_uint(__uint_as_float(orow[i]) * corr);
-                        tmem_st32(lane_base + O_COL + ch * 32, orow);
+                        tmem_st32(o_t + ch * 32, orow);
                     }
                 }
-                tmem_st32(lane_base + S_COL + sbuf * TK, pk);  // P(tile) over the head of S(tile)
+                tmem_st32(s_t, pk);  // P_j(tile) over the head of S_j(tile)
                 tmem_wait_st();
-                // V(tile) must have landed before PV(tile); the two groups requested in this
-                // iteration may still be in flight
-                cp_async_wait<2>();
-                fence_proxy_async_smem();
                 tc_fence_before();
-                __syncthreads();
-                if (warp_u == 0) {
-                    tc_fence_after();
-                    const uint64_t vd = v_desc0 + (uint64_t)((tile & 1u) * (STAGE >> 4));
-                    if (elect_one()) {
-#pragma unroll
-                        for (int kk = 0; kk < TK / 16; kk++)  // 64 keys = 4 k-steps of 16
-                            umma_ts(tmem + O_COL, tmem + S_COL + sbuf * TK + kk * 8,
-                                    vd + (uint32_t)((kk * 16 * ROW_B) >> 4), IDESC_PV, (kk > 0 || o_valid) ? 1u : 0u);
-                        umma_commit(&bar_o);
-                    }
-                    __syncwarp();
-                }
+                mbar_arrive(&bar_pfull[j]);
                 o_valid = true;
-                pv_pending = true;
-                ++gt;
+                ++gk;
             }
         }
-        run0 = run1;
-    }
-    if (pv_pending) {
-        ok &= mbar_wait_bounded(&bar_o, par_o, &s_abort);
-        par_o ^= 1u;
-        pv_pending = false;
-        __syncwarp();
-        tc_fence_after();
-    }
 
-    // ---- epilogue: O row from TMEM, 1/sum, f16, gate on the f16 value (as online kernel + gate kernel)
-    {
-        const bool write = (uint32_t)lane < nrows && s_len[lane] != 0 && ok && o_valid;
-        const float inv = rcp_approx_ftz(l_run);
-        const size_t rh = (size_t)(row0 + (write ? lane : 0)) * NQ + head;
-        const float sig = (gate && write) ? sigmoid_ref(h2f(gate[rh])) : 1.0f;
-        uint4* out = reinterpret_cast<uint4*>(ctx_out + rh * HD);
+        // ---- epilogue: O row from TMEM, 1/sum, f16, gate on the f16 value (as online kernel + gate kernel)
         if (o_valid) {
+            ok &= mbar_wait_bounded(&bar_ofull[j], n_o & 1u, &s_abort);
+            ++n_o;
+            __syncwarp();
+            tc_fence_after();
+            const bool write = tok < nrows && s_len[tok] != 0 && ok;
+            const float inv = rcp_approx_ftz(l_run);
+            const size_t rh = (size_t)(row0 + (write ? tok : 0u)) * NQ + head;
+            const float sig = (gate && write) ? sigmoid_ref(h2f(gate[rh])) : 1.0f;
+            uint4* out = reinterpret_cast<uint4*>(ctx_out + rh * HD);
 #pragma unroll
             for (int ch = 0; ch < 4; ch++) {
                 uint32_t orow[32];
-                tmem_ld32(lane_base + O_COL + ch * 32, orow);
+                tmem_ld32(o_t + ch * 32, orow);
                 tmem_wait_ld();
                 if (write) {
 #pragma unroll
                     for (int v8 = 0; v8 < 4; v8++) {
                         uint32_t w[4];
 #pragma unroll
-                        for (int j = 0; j < 4; j++) {
-                            uint16_t h0 = f2h(__fmul_rn(__uint_as_float(orow[v8 * 8 + 2 * j]), inv));
-                            uint16_t h1 = f2h(__fmul_rn(__uint_as_float(orow[v8 * 8 + 2 * j + 1]), inv));
+                        for (int jj = 0; jj < 4; jj++) {
+                            uint16_t h0 = f2h(__fmul_rn(__uint_as_float(orow[v8 * 8 + 2 * jj]), inv));
+                            uint16_t h1 = f2h(__fmul_rn(__uint_as_float(orow[v8 * 8 + 2 * jj + 1]), inv));
                             if (gate) {
                                 h0 = f2h(__fmul_rn(h2f(h0), sig));
                                 h1 = f2h(__fmul_rn(h2f(h1), sig));
                             }
-                            w[j] = (uint32_t)h0 | ((uint32_t)h1 << 16);
+                            w[jj] = (uint32_t)h0 | ((uint32_t)h1 << 16);
                         }
                         out[ch * 4 + v8] = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
             }
         }
+    } else if (warp_u == W_MMA) {
+        // ================= MMA warp: one elected lane issues, the whole warp waits =================
+        ok &= mbar_wait_bounded(&bar_qfull[0], it & 1u, &s_abort);
+        ok &= mbar_wait_bounded(&bar_qfull[1], it & 1u, &s_abort);
+        __syncwarp();
+        tc_fence_after();
+        // descriptors of ring stage 0; a stage / sub-tile / k-step is an offset added to the
+        // 16-byte-unit start address field (no carry: shared addresses < 256 KB)
+        const uint64_t k_desc0 = umma_desc(k_s, 16, 1024);      // K tiles: K-major
+        const uint64_t v_desc0 = umma_desc(v_s, KV_SUB, 1024);  // V tiles: MN-major
+        auto qk = [&](uint32_t j, uint32_t stage) {  // S_j = Q_j K^T: 128 dims = 8 k-steps of 16
+            const uint64_t kd = k_desc0 + (uint64_t)(stage * (KV_TILE >> 4));
+#pragma unroll
+            for (int kk = 0; kk < 8; kk++) {
+                const uint32_t koff = (uint32_t)(((kk >> 2) * KV_SUB + (kk & 3) * 32) >> 4);
+                umma_ts(tmem + S_COL + j * 64, tmem + Q_COL + j * 64 + kk * 8, kd + koff, IDESC_QK, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(&bar_sfull[j]);
+        };
+        auto pv = [&](uint32_t j, uint32_t stage, bool acc) {  // O_j (+)= P_j V: 64 keys = 4 k-steps of 16
+            const uint64_t vd = v_desc0 + (uint64_t)(stage * (KV_TILE >> 4));
+#pragma unroll
+            for (int kk = 0; kk < TK / 16; kk++)
+                umma_ts(tmem + O_COL + j * 128, tmem + S_COL + j * 64 + kk * 8,
+                        vd + (uint32_t)((kk * 16 * ROW_B) >> 4), IDESC_PV, (kk > 0 || acc) ? 1u : 0u);
+        };
+        uint32_t nt = 0;  // tiles of this item whose score MMAs have been issued
+        uint32_t next = 0;
+        PfRun run;
+        while (pf_next_run(next, nrows, s_kp, s_vp, s_len, window, run)) {
+            const uint32_t ntiles = (run.hi - run.lo + TK - 1) / TK;
+            for (uint32_t tile = 0; tile < ntiles; tile++) {
+                const uint32_t sk = gk % NS;
+                ok &= mbar_wait_bounded(&bar_kfull[sk], (gk / NS) & 1u, &s_abort);
+                if (nt > 0) {
+                    // tensor pipe order: PV_0(prev) QK_0(this) | PV_1(prev) QK_1(this)
+                    const uint32_t gp = gk - 1, sp = gp % NS;
+                    ok &= mbar_wait_bounded(&bar_vfull[sp], (gp / NS) & 1u, &s_abort);
+                    ok &= mbar_wait_bounded(&bar_pfull[0], gp & 1u, &s_abort);
+                    __syncwarp();
+                    tc_fence_after();
+                    if (elect_one()) {
+                        pv(0, sp, nt > 1);
+                        qk(0, sk);
+                    }
+                    __syncwarp();
+                    ok &= mbar_wait_bounded(&bar_pfull[1], gp & 1u, &s_abort);
+                    __syncwarp();
+                    tc_fence_after();
+                    if (elect_one()) {
+                        pv(1, sp, nt > 1);
+                        umma_commit(&bar_vempty[sp]);
+                        qk(1, sk);
+                        umma_commit(&bar_kempty[sk]);
+                    }
+                    __syncwarp();
+                } else {
+                    __syncwarp();
+                    tc_fence_after();
+                    if (elect_one()) {
+                        qk(0, sk);
+                        qk(1, sk);
+                        umma_commit(&bar_kempty[sk]);
+                    }
+                    __syncwarp();
+                }
+                ++nt;
+                ++gk;
+            }
+        }
+        if (nt > 0) {  // the item's last tile: PV only, then the O accumulators are final
+            const uint32_t gp = gk - 1, sp = gp % NS;
+            ok &= mbar_wait_bounded(&bar_vfull[sp], (gp / NS) & 1u, &s_abort);
+            ok &= mbar_wait_bounded(&bar_pfull[0], gp & 1u, &s_abort);
+            __syncwarp();
+            tc_fence_after();
+            if (elect_one()) {
+                pv(0, sp, nt > 1);
+                umma_commit(&bar_ofull[0]);
+            }
+            __syncwarp();
+            ok &= mbar_wait_bounded(&bar_pfull[1], gp & 1u, &s_abort);
+            __syncwarp();
+            tc_fence_after();
+            if (elect_one()) {
+                pv(1, sp, nt > 1);
+                umma_commit(&bar_vempty[sp]);
+                umma_commit(&bar_ofull[1]);
+            }
+            __syncwarp();
+            ++n_o;
+        }
+    } else if (warp_u == W_KLOAD || warp_u == W_VLOAD) {
+        // ================= loader warps: one for the K ring, one for the V ring =================
+        const bool is_k = warp_u == W_KLOAD;
+        uint64_t* full = is_k ? bar_kfull : bar_vfull;
+        uint64_t* empty = is_k ? bar_kempty : bar_vempty;
+        const uint32_t ring = is_k ? k_s : v_s;
+        // lane copies 16-byte chunk c of rows r0, r0+2, ...; chunk c of row r lands in sub-tile c/8 at
+        // row r, chunk position (c%8) ^ (r%8)
+        const uint32_t c = lane & 15u, r0 = lane >> 4;
+        uint32_t pending = 0;  // tiles requested whose full barrier has not been signalled yet
+        uint32_t next = 0;
+        PfRun run;
+        while (pf_next_run(next, nrows, s_kp, s_vp, s_len, window, run)) {
+            const char* base = reinterpret_cast<const char*>(is_k ? s_kp[run.r0] : s_vp[run.r0]) + kvh * (HD * 2);
+            const uint32_t ntiles = (run.hi - run.lo + TK - 1) / TK;
+            for (uint32_t tile = 0; tile < ntiles; tile++) {
+                const uint32_t st = gk % NS;
+                // the MMAs that read this stage's previous tile have completed (first use: passes at once)
+                ok &= mbar_wait_bounded(&empty[st], ((gk / NS) & 1u) ^ 1u, &s_abort);
+                const uint32_t kbeg = run.lo + tile * TK;
+                const uint32_t dst = ring + st * KV_TILE + (c >> 3) * KV_SUB;
+                const char* src = base + (size_t)(kbeg + r0) * KV_ROW_BYTES + c * 16;
+                if (kbeg + TK <= run.hi) {
+#pragma unroll
+                    for (int k = 0; k < TK / 2; k++) {
+                        const uint32_t row = r0 + 2 * k;
+                        cp_async_16(dst + row * ROW_B + (((c & 7u) ^ (row & 7u)) << 4), src + (size_t)k * 2 * KV_ROW_BYTES, true);
+                    }
+                } else {
+#pragma unroll
+                    for (int k = 0; k < TK / 2; k++) {
+                        const uint32_t row = r0 + 2 * k;
+                        const bool valid = kbeg + row < run.hi;  // rows past the run's last key are zero-filled
+                        cp_async_16(dst + row * ROW_B + (((c & 7u) ^ (row & 7u)) << 4),
+                                    valid ? src + (size_t)k * 2 * KV_ROW_BYTES : base, valid);
+                    }
+                }
+                cp_async_commit();
+                ++pending;
+                ++gk;
+                if (pending == DEPTH) {  // the oldest tile in flight has landed: publish it to the tensor core
+                    cp_async_wait<DEPTH - 1>();
+                    fence_proxy_async_smem();
+                    mbar_arrive(&full[(gk - DEPTH) % NS]);
+                    --pending;
+                }
+            }
+        }
+        cp_async_wait<0>();
+        fence_proxy_async_smem();
+        for (; pending > 0; --pending) mbar_arrive(&full[(gk - pending) % NS]);
     }
   }  // item loop
-    if (!ok && tid == 0) atomicOr(status, DEV_WAIT_TIMEOUT);
+
+    if (!ok) atomicOr(status, DEV_WAIT_TIMEOUT);
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) {
+    if (warp_u == W_MMA) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
@@ -559,11 +645,11 @@ cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* 
                                 const void* gate, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
                                 const uint32_t* seq_lens, uint32_t rows, uint32_t window,
                                 uint32_t* status, int num_sms, uint32_t* order, uint32_t* counter) {
-    const uint32_t nitems = ((rows + pf::TOK - 1) / pf::TOK) * NKV;
+    const uint32_t nitems = ((rows + pf::BLK - 1) / pf::BLK) * NKV;
     prefill_plan_kernel<<<1, 1024, 0, stream>>>(seq_lens, rows, window, order, counter);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    const uint32_t grid = nitems < (uint32_t)(2 * num_sms) ? nitems : (uint32_t)(2 * num_sms);
+    const uint32_t grid = nitems < (uint32_t)num_sms ? nitems : (uint32_t)num_sms;
     prefill_attn_kernel<<<grid, pf::THREADS, pf::SMEM_BYTES, stream>>>(
         (uint16_t*)ctx_out, (const uint16_t*)q, (const uint16_t*)gate, k_ptrs, v_ptrs, seq_lens,
         rows, window, status, order, counter);
