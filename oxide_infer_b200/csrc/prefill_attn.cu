@@ -59,16 +59,19 @@ constexpr int TOK = 32;                      // wave rows per query tile
 constexpr int BLK = 64;                      // wave rows per work item (two query tiles)
 constexpr int M = 128;                       // accumulator rows = 4 heads x 32 tokens
 constexpr int TK = 64;                       // keys per tile
-constexpr int THREADS = 384;                 // 8 softmax warps, MMA warp, K loader, V loader, one idle warp
-constexpr int W_MMA = 8, W_KLOAD = 9, W_VLOAD = 10;
+constexpr int THREADS = 384;                 // 8 softmax warps, 2 MMA warps, K loader, V loader
+constexpr int W_MMA0 = 8, W_KLOAD = 9, W_VLOAD = 10, W_MMA1 = 11;
 constexpr int ROW_B = 128;                   // bytes per swizzled row (64 f16)
 constexpr int KV_SUB = TK * ROW_B;           // one 64-dim half of a K (or V) tile: 8 KB
 constexpr int KV_TILE = 2 * KV_SUB;          // 16 KB
 constexpr int NS = 4;                        // ring stages, for K and for V
 constexpr int DEPTH = 3;                     // tiles a loader keeps in flight
-constexpr size_t SMEM_BYTES = 1024 + 2 * NS * KV_TILE;  // + slack for 1024-byte alignment; > half an SM: one CTA per SM
+constexpr int Q_SUB = M * ROW_B;             // one 64-dim half of a query tile in shared memory: 16 KB
+constexpr int Q_BYTES = 2 * Q_SUB;           // 32 KB
+constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + 2 * NS * KV_TILE;  // + slack for 1024-byte alignment; > half an SM: one CTA per SM
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t Q_COL = 0, S_COL = 128, O_COL = 256;  // + j*64, + j*64, + j*128 for query tile j
+// Q_0 (64) | S_0 S_1 (64 each) | P_0 P_1 (32 each) | O_0 O_1 (128 each); Q_1 does not fit and stays in shared memory
+constexpr uint32_t Q0_COL = 0, S_COL = 64, P_COL = 192, O_COL = 256;  // S + j*64, P + j*32, O + j*128 for query tile j
 constexpr float RESCALE_THRESHOLD = 8.0f;    // log2 units: the stale maximum may lag by a factor 256
 constexpr float QK_SCALE_LOG2 = ATTN_SCALE * LOG2E;
 // instruction descriptors (kind::f16): D = f32, A = B = f16, M = 128
@@ -253,21 +256,23 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint64_t s_kp[BLK], s_vp[BLK];
     __shared__ uint32_t s_len[BLK];
-    // loaders -> MMA warp (32 arrivals) and back (tcgen05.commit)
+    // loaders -> MMA warps (32 arrivals) and back (one tcgen05.commit from each MMA warp)
     __shared__ __align__(8) uint64_t bar_kfull[NS], bar_kempty[NS], bar_vfull[NS], bar_vempty[NS];
-    // per query tile: S ready (commit), P stored (128 arrivals), Q stored (128 arrivals), O final (commit)
-    __shared__ __align__(8) uint64_t bar_sfull[2], bar_pfull[2], bar_qfull[2], bar_ofull[2];
+    // per query tile: S ready (commit), S read into registers (128 arrivals), P stored (128 arrivals),
+    // PV of a tile complete (commit), Q stored (128 arrivals), O final (commit)
+    __shared__ __align__(8) uint64_t bar_sfull[2], bar_sfree[2], bar_pfull[2], bar_pvdone[2], bar_qfull[2], bar_ofull[2];
+    __shared__ __align__(8) uint64_t bar_tok[2];  // issue token of MMA warp j
     __shared__ uint32_t s_tmem, s_abort, s_item;
 
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;  // 1024-byte aligned tiles
-    const uint32_t k_s = sbase, v_s = sbase + NS * KV_TILE;
+    const uint32_t q1_s = sbase, k_s = sbase + Q_BYTES, v_s = k_s + NS * KV_TILE;
     const int tid = threadIdx.x, lane = tid & 31;
     // warp index the compiler can prove uniform: role branches and MMA issue stay in uniform control flow
     const int warp_u = __shfl_sync(0xffffffffu, tid >> 5, 0);
     const uint32_t nitems = ((rows + BLK - 1) / BLK) * NKV;
 
     // ---- once per CTA: TMEM allocation (all 512 columns; one CTA per SM), barriers
-    if (warp_u == W_MMA) {
+    if (warp_u == W_MMA0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -275,14 +280,17 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         for (int s = 0; s < NS; s++) {
             mbar_init(&bar_kfull[s], 32);
             mbar_init(&bar_vfull[s], 32);
-            mbar_init(&bar_kempty[s], 1);
-            mbar_init(&bar_vempty[s], 1);
+            mbar_init(&bar_kempty[s], 2);  // one commit from each MMA warp
+            mbar_init(&bar_vempty[s], 2);
         }
         for (int j = 0; j < 2; j++) {
             mbar_init(&bar_sfull[j], 1);
+            mbar_init(&bar_sfree[j], M);
             mbar_init(&bar_pfull[j], M);
+            mbar_init(&bar_pvdone[j], 1);
             mbar_init(&bar_qfull[j], M);
             mbar_init(&bar_ofull[j], 1);
+            mbar_init(&bar_tok[j], 1);
         }
         s_abort = 0u;
         mbar_fence_init();
@@ -296,6 +304,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     // (gk / NS)-th use and phase gk & 1 of the per-tile barriers.
     uint32_t gk = 0;
     uint32_t n_o = 0;  // items of this CTA that had tiles (phase of bar_ofull)
+    uint32_t n_burst = 0;  // MMA warps: bursts issued so far (phase of bar_tok)
     bool ok = true;
 
   // ======== persistent loop over (64-row block, KV head) items, longest first ========
@@ -337,29 +346,41 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         const uint32_t tok = (uint32_t)(j * TOK + lane);
         const int head = kvh * 4 + hw;
         const uint32_t lane_base = tmem + ((uint32_t)(hw * 32) << 16);
-        const uint32_t q_t = lane_base + Q_COL + j * 64, s_t = lane_base + S_COL + j * 64;
+        const uint32_t s_t = lane_base + S_COL + j * 64, p_t = lane_base + P_COL + j * 32;
         const uint32_t o_t = lane_base + O_COL + j * 128;
-        // This thread's query row goes to TMEM as the A operand of the score MMAs (128 dims = 64
-        // columns of f16 pairs).  The previous item's MMAs on this query tile completed before
+        // This thread's query row becomes a row of the A operand of the score MMAs: in TMEM for
+        // query tile 0 (128 dims = 64 columns of f16 pairs), in shared memory (K-major, 128-byte
+        // swizzle) for query tile 1.  The previous item's MMAs on this query tile completed before
         // this warp left that item's epilogue.
         {
             const bool valid = tok < nrows;
             const uint4* src = reinterpret_cast<const uint4*>(q + ((size_t)(row0 + (valid ? tok : 0u)) * NQ + head) * HD);
+            if (j == 0) {
 #pragma unroll
-            for (int hf = 0; hf < 2; hf++) {
-                uint32_t qr[32];
+                for (int hf = 0; hf < 2; hf++) {
+                    uint32_t qr[32];
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const uint4 v = valid ? __ldg(src + hf * 8 + i) : make_uint4(0u, 0u, 0u, 0u);
-                    qr[4 * i] = v.x;
-                    qr[4 * i + 1] = v.y;
-                    qr[4 * i + 2] = v.z;
-                    qr[4 * i + 3] = v.w;
+                    for (int i = 0; i < 8; i++) {
+                        const uint4 v = valid ? __ldg(src + hf * 8 + i) : make_uint4(0u, 0u, 0u, 0u);
+                        qr[4 * i] = v.x;
+                        qr[4 * i + 1] = v.y;
+                        qr[4 * i + 2] = v.z;
+                        qr[4 * i + 3] = v.w;
+                    }
+                    tmem_st32(lane_base + Q0_COL + hf * 32, qr);
                 }
-                tmem_st32(q_t + hf * 32, qr);
+                tmem_wait_st();
+                tc_fence_before();
+            } else {
+                const uint32_t r = (uint32_t)(hw * 32 + lane);
+#pragma unroll
+                for (uint32_t c = 0; c < 16; c++) {
+                    const uint4 v = valid ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
+                    const uint32_t dst = q1_s + (c >> 3) * Q_SUB + r * ROW_B + (((c & 7u) ^ (r & 7u)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+                }
+                fence_proxy_async_smem();
             }
-            tmem_wait_st();
-            tc_fence_before();
             mbar_arrive(&bar_qfull[j]);
         }
 
@@ -385,7 +406,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
             }
             const uint32_t ntiles = (run.hi - run.lo + TK - 1) / TK;
             for (uint32_t tile = 0; tile < ntiles; tile++) {
-                ok &= mbar_wait_bounded(&bar_sfull[j], gk & 1u, &s_abort);  // S_j(tile) complete, and PV_j of the tile before
+                ok &= mbar_wait_bounded(&bar_sfull[j], gk & 1u, &s_abort);  // S_j(tile) complete
                 __syncwarp();
                 tc_fence_after();
                 const uint32_t kbeg = run.lo + tile * TK;
@@ -393,6 +414,10 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                 tmem_ld32(s_t, sr[0]);
                 tmem_ld32(s_t + 32, sr[1]);
                 tmem_wait_ld();
+                tc_fence_before();
+                mbar_arrive(&bar_sfree[j]);  // the next tile's scores may overwrite S_j now
+                // PV_j of the tile before has long completed as a rule: polled here, needed before P is stored
+                const bool pv_prev_done = mbar_try_wait(&bar_pvdone[j], (gk - 1u) & 1u);
                 const bool interior = full && kbeg >= lo_max && kbeg + TK <= hi_min;
                 float mxa[4] = {-1.0e30f, -1.0e30f, -1.0e30f, -1.0e30f};
                 if (interior) {
@@ -424,6 +449,10 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                     pk[c >> 1] = pack_h2(p0, p1);
                 }
                 l_run = l_run * corr + ((psa[0] + psa[1]) + (psa[2] + psa[3]));
+                // P_j and O_j are free once PV_j of the tile before is complete (first tile of the CTA: passes)
+                if (!pv_prev_done) ok &= mbar_wait_bounded(&bar_pvdone[j], (gk - 1u) & 1u, &s_abort);
+                __syncwarp();
+                tc_fence_after();
                 if (o_valid && __any_sync(0xffffffffu, raise)) {
                     // rare: the reference maximum of some row of this warp moved; rescale the warp's O rows
                     // (no MMA touches O_j between the completion seen above and the arrival below)
@@ -437,7 +466,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                         tmem_st32(o_t + ch * 32, orow);
                     }
                 }
-                tmem_st32(s_t, pk);  // P_j(tile) over the head of S_j(tile)
+                tmem_st32(p_t, pk);
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&bar_pfull[j]);
@@ -481,31 +510,79 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                 }
             }
         }
-    } else if (warp_u == W_MMA) {
-        // ================= MMA warp: one elected lane issues, the whole warp waits =================
-        ok &= mbar_wait_bounded(&bar_qfull[0], it & 1u, &s_abort);
-        ok &= mbar_wait_bounded(&bar_qfull[1], it & 1u, &s_abort);
+    } else if (warp_u == W_MMA0 || warp_u == W_MMA1) {
+        // ================= MMA warps: warp W_MMAj issues the MMAs of query tile j =================
+        // One elected lane issues, the whole warp waits.  The tensor pipe accepts an MMA only when
+        // the one before has started, so the issuing thread is held for about the MMAs' execution
+        // time and every barrier wait between two bursts would leave the pipe idle.  Hence two
+        // issuing warps that alternate strictly (a token passed through bar_tok): while one warp
+        // issues its burst, the other one waits for the data of its next burst.  Bursts are never
+        // interleaved: MMAs that accumulate into the same tile stay back to back on the pipe.
+        const uint32_t j = warp_u == W_MMA0 ? 0u : 1u;
+        ok &= mbar_wait_bounded(&bar_qfull[j], it & 1u, &s_abort);
         __syncwarp();
         tc_fence_after();
         // descriptors of ring stage 0; a stage / sub-tile / k-step is an offset added to the
         // 16-byte-unit start address field (no carry: shared addresses < 256 KB)
         const uint64_t k_desc0 = umma_desc(k_s, 16, 1024);      // K tiles: K-major
         const uint64_t v_desc0 = umma_desc(v_s, KV_SUB, 1024);  // V tiles: MN-major
-        auto qk = [&](uint32_t j, uint32_t stage) {  // S_j = Q_j K^T: 128 dims = 8 k-steps of 16
+        const uint64_t q1_desc = umma_desc(q1_s, 16, 1024);     // query tile 1: K-major
+        auto qk = [&](uint32_t stage) {  // S_j = Q_j K^T: 128 dims = 8 k-steps of 16
             const uint64_t kd = k_desc0 + (uint64_t)(stage * (KV_TILE >> 4));
 #pragma unroll
             for (int kk = 0; kk < 8; kk++) {
                 const uint32_t koff = (uint32_t)(((kk >> 2) * KV_SUB + (kk & 3) * 32) >> 4);
-                umma_ts(tmem + S_COL + j * 64, tmem + Q_COL + j * 64 + kk * 8, kd + koff, IDESC_QK, kk > 0 ? 1u : 0u);
+                if (j == 0)
+                    umma_ts(tmem + S_COL, tmem + Q0_COL + kk * 8, kd + koff, IDESC_QK, kk > 0 ? 1u : 0u);
+                else
+                    umma_ss(tmem + S_COL + 64, q1_desc + (uint32_t)(((kk >> 2) * Q_SUB + (kk & 3) * 32) >> 4), kd + koff,
+                            IDESC_QK, kk > 0 ? 1u : 0u);
             }
             umma_commit(&bar_sfull[j]);
+            umma_commit(&bar_kempty[stage]);
         };
-        auto pv = [&](uint32_t j, uint32_t stage, bool acc) {  // O_j (+)= P_j V: 64 keys = 4 k-steps of 16
+        auto pv = [&](uint32_t stage, bool acc) {  // O_j (+)= P_j V: 64 keys = 4 k-steps of 16
             const uint64_t vd = v_desc0 + (uint64_t)(stage * (KV_TILE >> 4));
 #pragma unroll
             for (int kk = 0; kk < TK / 16; kk++)
-                umma_ts(tmem + O_COL + j * 128, tmem + S_COL + j * 64 + kk * 8,
+                umma_ts(tmem + O_COL + j * 128, tmem + P_COL + j * 32 + kk * 8,
                         vd + (uint32_t)((kk * 16 * ROW_B) >> 4), IDESC_PV, (kk > 0 || acc) ? 1u : 0u);
+            umma_commit(&bar_pvdone[j]);
+            umma_commit(&bar_vempty[stage]);
+        };
+        // Tile t of the item has global index g0 + t.  Step t of this warp is one burst: PV_j(t-2),
+        // which needs P_j(t-2) stored, then QK_j(t), which needs S_j(t-1) read into registers by the
+        // softmax warps - scores are produced one tile ahead of the softmax, so that the softmax warps
+        // do not wait for the tensor pipe in steady state.  Steps G and G+1 drain the last two PVs.
+        const uint32_t g0 = gk;
+        auto step = [&](uint32_t t, bool has_pv, bool has_qk, bool last) {
+            uint32_t sv = 0, sk = 0;
+            if (has_pv) {
+                const uint32_t g = g0 + t - 2;
+                sv = g % NS;
+                ok &= mbar_wait_bounded(&bar_vfull[sv], (g / NS) & 1u, &s_abort);
+                ok &= mbar_wait_bounded(&bar_pfull[j], g & 1u, &s_abort);
+            }
+            if (has_qk) {
+                const uint32_t g = g0 + t;
+                sk = g % NS;
+                ok &= mbar_wait_bounded(&bar_kfull[sk], (g / NS) & 1u, &s_abort);
+                if (t >= 1) ok &= mbar_wait_bounded(&bar_sfree[j], (g - 1u) & 1u, &s_abort);
+            }
+            // the token: warp 0's n-th burst follows warp 1's (n-1)-th, warp 1's n-th follows warp 0's n-th
+            ok &= mbar_wait_bounded(&bar_tok[j], (j == 0 ? n_burst + 1u : n_burst) & 1u, &s_abort);
+            __syncwarp();
+            tc_fence_after();
+            if (elect_one()) {
+                if (has_pv) {
+                    pv(sv, t > 2);
+                    if (last) umma_commit(&bar_ofull[j]);
+                }
+                if (has_qk) qk(sk);
+                mbar_arrive(&bar_tok[j ^ 1u]);
+            }
+            __syncwarp();
+            ++n_burst;
         };
         uint32_t nt = 0;  // tiles of this item whose score MMAs have been issued
         uint32_t next = 0;
@@ -513,64 +590,14 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         while (pf_next_run(next, nrows, s_kp, s_vp, s_len, window, run)) {
             const uint32_t ntiles = (run.hi - run.lo + TK - 1) / TK;
             for (uint32_t tile = 0; tile < ntiles; tile++) {
-                const uint32_t sk = gk % NS;
-                ok &= mbar_wait_bounded(&bar_kfull[sk], (gk / NS) & 1u, &s_abort);
-                if (nt > 0) {
-                    // tensor pipe order: PV_0(prev) QK_0(this) | PV_1(prev) QK_1(this)
-                    const uint32_t gp = gk - 1, sp = gp % NS;
-                    ok &= mbar_wait_bounded(&bar_vfull[sp], (gp / NS) & 1u, &s_abort);
-                    ok &= mbar_wait_bounded(&bar_pfull[0], gp & 1u, &s_abort);
-                    __syncwarp();
-                    tc_fence_after();
-                    if (elect_one()) {
-                        pv(0, sp, nt > 1);
-                        qk(0, sk);
-                    }
-                    __syncwarp();
-                    ok &= mbar_wait_bounded(&bar_pfull[1], gp & 1u, &s_abort);
-                    __syncwarp();
-                    tc_fence_after();
-                    if (elect_one()) {
-                        pv(1, sp, nt > 1);
-                        umma_commit(&bar_vempty[sp]);
-                        qk(1, sk);
-                        umma_commit(&bar_kempty[sk]);
-                    }
-                    __syncwarp();
-                } else {
-                    __syncwarp();
-                    tc_fence_after();
-                    if (elect_one()) {
-                        qk(0, sk);
-                        qk(1, sk);
-                        umma_commit(&bar_kempty[sk]);
-                    }
-                    __syncwarp();
-                }
+                step(nt, nt >= 2, true, false);
                 ++nt;
                 ++gk;
             }
         }
-        if (nt > 0) {  // the item's last tile: PV only, then the O accumulators are final
-            const uint32_t gp = gk - 1, sp = gp % NS;
-            ok &= mbar_wait_bounded(&bar_vfull[sp], (gp / NS) & 1u, &s_abort);
-            ok &= mbar_wait_bounded(&bar_pfull[0], gp & 1u, &s_abort);
-            __syncwarp();
-            tc_fence_after();
-            if (elect_one()) {
-                pv(0, sp, nt > 1);
-                umma_commit(&bar_ofull[0]);
-            }
-            __syncwarp();
-            ok &= mbar_wait_bounded(&bar_pfull[1], gp & 1u, &s_abort);
-            __syncwarp();
-            tc_fence_after();
-            if (elect_one()) {
-                pv(1, sp, nt > 1);
-                umma_commit(&bar_vempty[sp]);
-                umma_commit(&bar_ofull[1]);
-            }
-            __syncwarp();
+        if (nt > 0) {
+            step(nt, nt >= 2, false, false);
+            step(nt + 1, true, false, true);
             ++n_o;
         }
     } else if (warp_u == W_KLOAD || warp_u == W_VLOAD) {
@@ -630,7 +657,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     if (!ok) atomicOr(status, DEV_WAIT_TIMEOUT);
     tc_fence_before();
     __syncthreads();
-    if (warp_u == W_MMA) {
+    if (warp_u == W_MMA0) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
     }
