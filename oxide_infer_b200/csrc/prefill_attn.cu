@@ -19,26 +19,30 @@
 //   warps 0-3   softmax of query tile 0: warp w / lane l owns accumulator row (head w,
 //               token l) = TMEM lane 32*w + l, so the softmax is thread-local, no shuffles
 //   warps 4-7   softmax of query tile 1 (same TMEM lanes, other columns)
-//   warp 8      issues every tcgen05.mma (one elected lane, warp-uniform control flow)
+//   warp 8 / 11 issue the tcgen05.mma of query tile 0 / 1 (one elected lane, warp-uniform
+//               control flow), alternating strictly by a token so that bursts never interleave
 //   warp 9 / 10 K / V tile loaders: cp.async 16-byte chunks written straight into the
 //               128-byte-swizzled layout (zero-filled past the run's last key), a ring of
 //               4 stages each, 3 tiles in flight
 // all connected by mbarriers only (no CTA-wide barrier inside an item).
 //
-// Per 64-key tile and query tile j:  S_j = Q_j K^T  (A = Q_j from TMEM, B = K tile from
-// shared memory, K-major, D = S_j in TMEM) -> each softmax thread loads its S row
-// (tcgen05.ld), applies scale, causal/window mask and the online-softmax update, writes P
-// as f16 over the first columns of S_j (tcgen05.st) -> O_j += P_j V  (A = P_j from TMEM,
-// B = V tile from shared memory, MN-major, D = O_j accumulating in TMEM across all tiles).
-// The tensor pipe runs  PV_0(t-1) QK_0(t) | PV_1(t-1) QK_1(t) | ...  so that the softmax
-// of one query tile overlaps the MMAs of the other.
+// Per 64-key tile and query tile j:  S_j = Q_j K^T  (B = K tile from shared memory, K-major,
+// D = S_j in TMEM; A = Q_0 from TMEM for tile 0, Q_1 from shared memory for tile 1, which does
+// not fit into TMEM) -> each softmax thread loads its S row (tcgen05.ld) and at once hands S_j
+// back, applies scale, causal/window mask and the online-softmax update, writes P as f16 to
+// its own TMEM columns (tcgen05.st) -> O_j += P_j V  (A = P_j from TMEM, B = V tile from shared
+// memory, MN-major, D = O_j accumulating in TMEM across all tiles).
+// Scores run one tile ahead of the softmax: MMA warp j's step t is the burst PV_j(t-2), QK_j(t),
+// and QK_j(t) only needs S_j(t-1) to have been read into registers.  In steady state the softmax
+// warps therefore find their next scores ready, and the two query tiles keep the tensor pipe and
+// the special-function units busy at the same time.
 // The running maximum used for the exponentials is only raised when a tile's
 // maximum exceeds it by more than 2^8 (then the thread rescales its O row in
 // TMEM); otherwise the stale maximum is kept, which is exact after the final
 // division by the row sum and keeps O untouched between MMAs.
 //
-// TMEM (all 512 columns, one CTA per SM): Q_0 Q_1 (64 each: 128 dims as f16 pairs) |
-// S_0 S_1 (64 each) | O_0 O_1 (128 each).
+// TMEM (all 512 columns, one CTA per SM): Q_0 (64: 128 dims as f16 pairs) | S_0 S_1 (64 each) |
+// P_0 P_1 (32 each) | O_0 O_1 (128 each).
 //
 // Rows of a 64-row block that point at different caches are processed as
 // separate runs of equal pointers (rows outside the run are masked), so any
