@@ -38,15 +38,10 @@ ROW_BYTES = NKV * HD * 2
 # algorithmic bytes per (layer, sequence): K and V rows read once per GQA group plus the
 # step's q/k/v/gate, norm weights, cos/sin rows, K/V row writes, ctx write, table entries
 PER_SEQ_FIXED = 4096 + 1024 + 1024 + 32 + 512 + 512 + 2048 + 4096 + 28
-ATTN_FIXED = 4096 + 32 + 4096 + 20  # decode-attention kernel alone: q, gate, ctx, tables
 
 
 def alg_bytes_layer(seq_lens) -> int:
     return int(sum(2 * ROW_BYTES * int(s) + PER_SEQ_FIXED for s in seq_lens))
-
-
-def attn_bytes_layer(seq_lens) -> int:
-    return int(sum(2 * ROW_BYTES * int(s) + ATTN_FIXED for s in seq_lens))
 
 
 class ClockSampler(threading.Thread):
@@ -681,7 +676,7 @@ def run_serving_mix(args, torch, rank, world, local_rank):
                        "parallelism": f"replicas x{world}, sequences partitioned longest-first, no collective"},
             "roofline": {"bound": "hbm", "achieved": round(gbs / world, 1), "peak": peak, "peak_kind": kind,
                          "unit": "GB/s per GPU", "frac": round(gbs / world / peak, 4)},
-            "gpu_launches": 3 * layers * steps * reps, "clocks": clocks, "device_status": status}
+            "gpu_launches": 2 * layers * steps * reps, "clocks": clocks, "device_status": status}
 
 
 def main():
