@@ -53,7 +53,8 @@ enum {
 enum {
     OXI_DEV_MISALIGNED_PTR = 1u, /* a K/V/state pointer was not 16-byte aligned; row skipped */
     OXI_DEV_BAD_SEQ_LEN = 2u,    /* seq_len 0 or beyond the handle's max_seq_len; row skipped */
-    OXI_DEV_WAIT_TIMEOUT = 4u    /* an in-kernel pipeline wait gave up (internal error)       */
+    OXI_DEV_WAIT_TIMEOUT = 4u,   /* an in-kernel pipeline wait gave up (internal error)       */
+    OXI_DEV_BAD_TOKEN = 8u       /* a token id was beyond the embedding table; row zero-filled */
 };
 
 typedef struct oxi_handle oxi_handle;
@@ -153,6 +154,23 @@ int32_t oxi_conv_decode(oxi_handle* h, void* stream, void* y_out, const uint64_t
 int32_t oxi_conv_prefill(oxi_handle* h, void* stream, void* y_out, const uint64_t* carry_ptrs,
                          const uint32_t* origin, const uint32_t* local_pos, const void* bcx,
                          const void* conv_w, uint32_t rows);
+
+/* ---- the sampling side of a decode step: the file's two other table kernels */
+/* out[b][:] = table[token_ids[b]][:] (f16 rows of `hidden` elements).
+ * Replaces batched_embed_lookup_fp16 (batched_attn.rs:664-714, launched at
+ * batch_engine.rs:765-779).  The reference does not check the ids; here an id
+ * >= table_rows zero-fills the row and sets OXI_DEV_BAD_TOKEN. */
+int32_t oxi_embed_lookup(oxi_handle* h, void* stream, void* out, const void* table,
+                         const uint32_t* token_ids, uint32_t hidden, uint32_t table_rows,
+                         uint32_t batch);
+/* tokens_out[b] = argmax_v logits[b][v], logits [batch][vocab] f16, batch <= max_batch.
+ * Replaces batched_argmax_direct_f16 (batched_attn.rs:890-1023, launched with
+ * 256 threads per row at batch_engine.rs:1367-1378) and returns the same index
+ * as that launch for every input, ties included: the reference resolves equal
+ * maxima by its scan order and reduction tree (not by the lowest index), NaN
+ * never wins, a row without any value above -1e30 yields 0. */
+int32_t oxi_argmax(oxi_handle* h, void* stream, uint32_t* tokens_out, const void* logits,
+                   uint32_t vocab, uint32_t batch);
 
 /* ---- unfused operators with the reference's exact semantics ------------ */
 /* Same contract as the PTX entry of the same name, so a harness can swap the

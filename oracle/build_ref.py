@@ -33,6 +33,8 @@ WANTED = [
     "BATCHED_GQA_ATTENTION_SPLIT4_PTX", "BATCHED_SIGMOID_GATE_PTX", "BATCHED_CONV_PTR_PTX",
     "CONV_STATE_PREFILL_PTX", "BATCHED_ATTN_PACK_Q_PTX", "BATCHED_ATTN_SOFTMAX_MASK_PTX",
     "BATCHED_ATTN_GATE_SCATTER_PTX",
+    # the two other table-driven kernels of the same file (sampling side of a decode step)
+    "BATCHED_EMBED_LOOKUP_PTX", "BATCHED_ARGMAX_DIRECT_PTX",
 ]
 
 

@@ -216,6 +216,23 @@ def conv_prefill_wave(carry_tbl, origin, local_pos, bcx, conv_w):
     return y
 
 
+def embed_lookup(table, token_ids):
+    """out[b] = table[token_ids[b]] (batched_embed_lookup_fp16)."""
+    table = np.ascontiguousarray(table, np.float16)
+    tok = np.ascontiguousarray(token_ids, np.uint32)
+    out = np.empty((tok.shape[0], table.shape[1]), np.float16)
+    lib().orc_embed_lookup(_p(out), _p(table), _p(tok), _u32(table.shape[1]), _u32(tok.shape[0]))
+    return out
+
+
+def argmax(logits, nthreads=256):
+    """Per-row argmax with the reference kernel's scan order and reduction tree (batched_argmax_direct_f16)."""
+    logits = np.ascontiguousarray(logits, np.float16)
+    out = np.empty(logits.shape[0], np.uint32)
+    lib().orc_argmax(_p(out), _p(logits), _u32(logits.shape[1]), _u32(logits.shape[0]), _u32(nthreads))
+    return out
+
+
 # ------------------------------------------------ f64 mathematical model --
 
 def attention_f64(q, k_cache, v_cache, slen, window=0, gate=None):

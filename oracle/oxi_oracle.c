@@ -529,6 +529,86 @@ void orc_conv_prefill_wave(uint16_t* y, uint16_t* pool, const uint64_t* carry_tb
     free(ptrs);
 }
 
+/* ---- sampling-side table kernels of the same file (next to the KV path) ------------------- */
+
+/* batched_embed_lookup_fp16 (batched_attn.rs:664-714; launched batch_engine.rs:778):
+ * out[b][:] = table[token_ids[b]][:], hidden f16 per row, no bounds check in the reference. */
+void orc_embed_lookup(uint16_t* out, const uint16_t* table, const uint32_t* token_ids,
+                      uint32_t hidden, uint32_t batch) {
+    for (uint32_t b = 0; b < batch; b++)
+        memcpy(out + (size_t)b * hidden, table + (size_t)token_ids[b] * hidden, (size_t)hidden * 2);
+}
+
+/* batched_argmax_direct_f16 (batched_attn.rs:890-1023), one block of `nthreads` threads per row
+ * (256 at batch_engine.rs:1377).  Thread t scans t, t+nthreads, ... keeping the FIRST strict
+ * maximum (start -1e30, index 0; NaN never wins: setp.gt is false).  Then the shuffle-down tree
+ * inside each warp (offsets 16..1; a lane takes its partner's pair only if strictly greater; a
+ * partner past lane 31 returns the lane's own value), lane 0 of each warp to shared memory, and
+ * the same tree with offsets 4, 2, 1 over the 8 warp results.  Ties are therefore resolved by the
+ * tree, not by the lowest index - restated literally here. */
+void orc_argmax(uint32_t* tokens_out, const uint16_t* logits, uint32_t vocab, uint32_t batch,
+                uint32_t nthreads) {
+#pragma omp parallel for schedule(static)
+    for (int64_t bb = 0; bb < (int64_t)batch; bb++) {
+        const uint16_t* row = logits + (size_t)bb * vocab;
+        float* mx = (float*)malloc(sizeof(float) * nthreads);
+        uint32_t* bi = (uint32_t*)malloc(sizeof(uint32_t) * nthreads);
+        for (uint32_t t = 0; t < nthreads; t++) {
+            float m = -1.0e30f;
+            uint32_t best = 0;
+            for (uint32_t i = t; i < vocab; i += nthreads) {
+                const float f = orc_h2f(row[i]);
+                if (f > m) {
+                    m = f;
+                    best = i;
+                }
+            }
+            mx[t] = m;
+            bi[t] = best;
+        }
+        const uint32_t nwarps = nthreads / 32;
+        float wm[8] = {0};
+        uint32_t wi[8] = {0};
+        for (uint32_t w = 0; w < nwarps && w < 8; w++) {
+            float v[32];
+            uint32_t ix[32];
+            for (int l = 0; l < 32; l++) {
+                v[l] = mx[w * 32 + l];
+                ix[l] = bi[w * 32 + l];
+            }
+            for (int off = 16; off >= 1; off >>= 1) {
+                float nv[32];
+                uint32_t ni[32];
+                for (int l = 0; l < 32; l++) {
+                    const int p = l + off <= 31 ? l + off : l;
+                    const int take = v[p] > v[l];
+                    nv[l] = take ? v[p] : v[l];
+                    ni[l] = take ? ix[p] : ix[l];
+                }
+                memcpy(v, nv, sizeof v);
+                memcpy(ix, ni, sizeof ix);
+            }
+            wm[w] = v[0];
+            wi[w] = ix[0];
+        }
+        for (int off = 4; off >= 1; off >>= 1) {  /* threads 0..7; only lane 0's result is used */
+            float nv[8];
+            uint32_t ni[8];
+            for (int l = 0; l < 8; l++) {
+                const int p = l + off;
+                const int take = p < 8 && wm[p] > wm[l];
+                nv[l] = take ? wm[p] : wm[l];
+                ni[l] = take ? wi[p] : wi[l];
+            }
+            memcpy(wm, nv, sizeof wm);
+            memcpy(wi, ni, sizeof wi);
+        }
+        tokens_out[bb] = wi[0];
+        free(mx);
+        free(bi);
+    }
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
     extern int omp_get_max_threads(void);

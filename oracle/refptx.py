@@ -41,6 +41,8 @@ class RefPtx:
         "batched_attn_pack_q_fp16": "BATCHED_ATTN_PACK_Q_PTX",
         "batched_attn_softmax_mask_fp16": "BATCHED_ATTN_SOFTMAX_MASK_PTX",
         "batched_attn_gate_scatter_fp16": "BATCHED_ATTN_GATE_SCATTER_PTX",
+        "batched_embed_lookup_fp16": "BATCHED_EMBED_LOOKUP_PTX",
+        "batched_argmax_direct_f16": "BATCHED_ARGMAX_DIRECT_PTX",
     }
 
     def __init__(self):
@@ -121,6 +123,15 @@ class RefPtx:
         self.launch("batched_sigmoid_gate_fp16", (NQ, batch, 1), (HD, 1, 1),
                     [(C.c_void_p, ctx_io), (C.c_void_p, gate), (C.c_uint32, NQ), (C.c_uint32, HD),
                      (C.c_uint32, batch)])
+
+    def embed_lookup(self, out, table, token_ids, hidden, batch):  # BE:765-779
+        self.launch("batched_embed_lookup_fp16", (batch, 1, 1), (256, 1, 1),
+                    [(C.c_void_p, out), (C.c_void_p, table), (C.c_void_p, token_ids),
+                     (C.c_uint32, hidden), (C.c_uint32, batch)])
+
+    def argmax(self, tokens_out, logits, vocab, batch):  # BE:1367-1378
+        self.launch("batched_argmax_direct_f16", (batch, 1, 1), (256, 1, 1),
+                    [(C.c_void_p, tokens_out), (C.c_void_p, logits), (C.c_uint32, vocab)])
 
     def conv_decode(self, y, state_ptrs, bcx, conv_w, batch):  # BE:840-899
         self.launch("batched_fused_causal_conv1d_gating_ptr_fp16", (HIDDEN // 128, batch, 1),

@@ -20,6 +20,7 @@ constexpr float LOG2E = 1.44269504f;
 constexpr uint32_t DEV_MISALIGNED_PTR = 1u;
 constexpr uint32_t DEV_BAD_SEQ_LEN = 2u;
 constexpr uint32_t DEV_WAIT_TIMEOUT = 4u;
+constexpr uint32_t DEV_BAD_TOKEN = 8u;
 
 // ---- approximate instructions the reference uses (kept as PTX so results match bit for bit)
 __device__ __forceinline__ float ex2_approx_ftz(float x) {

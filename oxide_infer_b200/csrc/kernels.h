@@ -59,4 +59,14 @@ cudaError_t launch_conv_prefill(cudaStream_t stream, void* y_out, const uint64_t
                                 const void* bcx, const void* conv_w, uint32_t rows,
                                 void* stage /* [rows][2048][6] f16 */, uint32_t* status);
 
+// Sampling-side table kernels.
+cudaError_t launch_embed_lookup(cudaStream_t stream, void* out, const void* table,
+                                const uint32_t* token_ids, uint32_t hidden, uint32_t table_rows,
+                                uint32_t batch, uint32_t* status);
+cudaError_t launch_argmax(cudaStream_t stream, uint32_t* tokens_out, const void* logits, uint32_t vocab,
+                          uint32_t batch, int num_sms,
+                          void* cand_scratch /* [batch][argmax_max_splits()][256] (float, uint32) */,
+                          uint32_t* counters /* [batch], zero between launches */);
+uint32_t argmax_max_splits();
+
 }  // namespace oxi

@@ -18,6 +18,8 @@ struct oxi_handle {
     DecodeWorkspace dws;
     void* conv_stage;     // [max_prefill_rows][2048][6] f16
     uint32_t* pf_order;   // [ceil(max_prefill_rows/32)] prefill block order
+    void* am_cand;        // [max_batch][argmax_max_splits()][256] argmax candidates of the row splits
+    uint32_t* am_count;   // [max_batch] arrival counters, zero between launches
     // staging for the host-buffer entry, one layer at a time, double buffered
     void* stg_q[2];       // [max_batch][16][128]
     void* stg_k[2];       // [max_batch][4][128]
@@ -114,6 +116,12 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
     if ((rc = dev_alloc(h, (void**)&h->dws.partial_stats, slots * 2 * sizeof(float)))) goto bad;
     if ((rc = dev_alloc(h, (void**)&h->dws.status, 256))) goto bad;
     h->dws.work_counter = h->dws.status + 32;  // same zero-initialised 256-byte block, own 128-byte line
+    if ((rc = dev_alloc(h, &h->am_cand, (size_t)max_batch * argmax_max_splits() * 256 * 8))) goto bad;
+    if ((rc = dev_alloc(h, (void**)&h->am_count, (size_t)max_batch * 4))) goto bad;
+    if (cudaMemset(h->am_count, 0, (size_t)max_batch * 4) != cudaSuccess) {
+        rc = cuda_fail(cudaGetLastError(), "cudaMemset");
+        goto bad;
+    }
     if (max_prefill_rows) {
         if ((rc = dev_alloc(h, &h->conv_stage, (size_t)max_prefill_rows * HIDDEN * CONV_S * 2))) goto bad;
         if ((rc = dev_alloc(h, (void**)&h->pf_order, ((size_t)max_prefill_rows / 32 + 1) * sizeof(uint32_t)))) goto bad;
@@ -169,6 +177,8 @@ int32_t oxi_destroy(oxi_handle* h) {
     cudaFree(h->dws.status);
     cudaFree(h->conv_stage);
     cudaFree(h->pf_order);
+    cudaFree(h->am_cand);
+    cudaFree(h->am_count);
     for (int i = 0; i < 2; i++) {
         cudaFree(h->stg_q[i]); cudaFree(h->stg_k[i]); cudaFree(h->stg_v[i]);
         cudaFree(h->stg_gate[i]); cudaFree(h->stg_ctx[i]);
@@ -287,6 +297,28 @@ int32_t oxi_conv_prefill(oxi_handle* h, void* stream, void* y_out, const uint64_
     OXI_CUDA(launch_conv_prefill((cudaStream_t)stream, y_out, carry_ptrs, origin, local_pos, bcx,
                                  conv_w, rows, h->conv_stage, h->dws.status),
              "conv_prefill launch");
+    return OXI_OK;
+}
+
+int32_t oxi_embed_lookup(oxi_handle* h, void* stream, void* out, const void* table,
+                         const uint32_t* token_ids, uint32_t hidden, uint32_t table_rows, uint32_t batch) {
+    REQ_HANDLE("oxi_embed_lookup");
+    REQ_PTR(out && table && token_ids, "oxi_embed_lookup");
+    REQ_BATCH(batch, 65535u, "oxi_embed_lookup");
+    if (hidden == 0 || table_rows == 0) return fail(OXI_ERR_ARG, "oxi_embed_lookup: hidden and table_rows must be positive");
+    OXI_CUDA(launch_embed_lookup((cudaStream_t)stream, out, table, token_ids, hidden, table_rows, batch, h->dws.status),
+             "embed_lookup launch");
+    return OXI_OK;
+}
+
+int32_t oxi_argmax(oxi_handle* h, void* stream, uint32_t* tokens_out, const void* logits, uint32_t vocab,
+                   uint32_t batch) {
+    REQ_HANDLE("oxi_argmax");
+    REQ_PTR(tokens_out && logits, "oxi_argmax");
+    REQ_BATCH(batch, h->max_batch, "oxi_argmax");
+    if (vocab == 0 || vocab > 0x7fffff00u) return fail(OXI_ERR_ARG, "oxi_argmax: vocab out of range");
+    OXI_CUDA(launch_argmax((cudaStream_t)stream, tokens_out, logits, vocab, batch, h->num_sms, h->am_cand, h->am_count),
+             "argmax launch");
     return OXI_OK;
 }
 

@@ -117,6 +117,21 @@ class KvPath:
                                          _p(local_pos), _p(bcx), _p(conv_w), n),
                "oxi_conv_prefill")
 
+    # ---- sampling side of a decode step
+    def embed_lookup(self, out, table, token_ids, batch: int | None = None):
+        """out[b] = table[token_ids[b]] (batched_embed_lookup_fp16; ids beyond the table zero-fill
+        the row and set OXI_DEV_BAD_TOKEN)."""
+        b = token_ids.shape[0] if batch is None else batch
+        _check(self.lib.oxi_embed_lookup(self.h, _stream(), _p(out), _p(table), _p(token_ids),
+                                         table.shape[1], table.shape[0], b), "oxi_embed_lookup")
+
+    def argmax(self, tokens_out, logits, batch: int | None = None):
+        """tokens_out[b] = argmax of logits[b] with the reference kernel's tie resolution
+        (batched_argmax_direct_f16)."""
+        b = logits.shape[0] if batch is None else batch
+        _check(self.lib.oxi_argmax(self.h, _stream(), _p(tokens_out), _p(logits), logits.shape[1], b),
+               "oxi_argmax")
+
     # ---- unfused operators (reference semantics, one per PTX entry point)
     def qk_rmsnorm(self, x_io, weight, eps: float = 1e-5):
         b, heads = x_io.shape[0], x_io.shape[1]
