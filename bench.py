@@ -518,6 +518,71 @@ def run_conv(args, torch):
             "gpu_launches": nl * args.steps, "clocks": clocks, "device_status": kv.device_status()}
 
 
+def run_sample(args, torch):
+    """Sampling side of a decode step at the reference's sizes: argmax over 128,000 f16 logits for
+    each of 128 rows (batch_engine.rs:75, :1367-1378) and the embedding gather of the 128 chosen
+    rows of a [128000][2048] table.  Eight distinct logits buffers (262 MB) rotate so that no launch
+    finds its input in L2."""
+    from oxide_infer_b200 import KvPath
+    from oracle import refptx
+    b, vocab, hid, nbuf = 128, 128000, 2048, 8
+    kv = KvPath(0, max_batch=b, max_seq_len=256, max_prefill_rows=0)
+    g = torch.Generator(device="cuda").manual_seed(6)
+    logits = [torch.empty(b, vocab, dtype=torch.float16, device="cuda").normal_(generator=g) for _ in range(nbuf)]
+    table = torch.empty(vocab, hid, dtype=torch.float16, device="cuda").normal_(generator=g)
+    tok = torch.zeros(nbuf, b, dtype=torch.int32, device="cuda")
+    hidden = torch.zeros(b, hid, dtype=torch.float16, device="cuda")
+    sampler = ClockSampler(0)
+    sampler.start()
+
+    def ours():
+        for i in range(nbuf):
+            kv.argmax(tok[i], logits[i])
+            kv.embed_lookup(hidden, table, tok[i])
+    w0 = time.perf_counter()
+    ms = _time_loop(torch, ours, args.steps, args.warmup)
+    ms_am = _time_loop(torch, lambda: [kv.argmax(tok[i], logits[i]) for i in range(nbuf)], args.steps, args.warmup)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ours()
+    ms_graph = _time_loop(torch, graph.replay, max(args.steps, 200), args.warmup)
+    graph_am = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph_am):
+        for i in range(nbuf):
+            kv.argmax(tok[i], logits[i])
+    ms_am_graph = _time_loop(torch, graph_am.replay, max(args.steps, 200), args.warmup)
+    clocks = sampler.window(w0, time.perf_counter())
+    want = torch.stack([x.float().argmax(1) for x in logits]).int()  # random normal f16 logits: ties are possible but
+    agree = float((want == tok).float().mean().item())              # rare; parity proper is in tests/test_gpu_sample.py
+    ms_ref = None
+    if refptx.available():
+        ref = refptx.RefPtx()
+        rt = torch.zeros(b, dtype=torch.int32, device="cuda")
+
+        def ref_pair():
+            for i in range(nbuf):
+                ref.argmax(rt, logits[i], vocab, b)
+                ref.embed_lookup(hidden, table, rt, hid, b)
+        ms_ref = _time_loop(torch, ref_pair, max(3, args.steps // 2), 3)
+    sampler.stop()
+    pair_bytes = b * vocab * 2 + b * 4 + b * (4 + 2 * hid * 2)   # logits once, ids out; ids in, row in, row out
+    am_bytes = b * vocab * 2 + b * 4
+    peak, kind = measured_peak_gbs()
+    gbs = nbuf * pair_bytes / (ms_graph * 1e-3) / 1e9
+    am_gbs = nbuf * am_bytes / (ms_am_graph * 1e-3) / 1e9
+    return {"metric": "argmax_embed_hbm_gbs", "value": round(gbs, 1), "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_graph, 4), "us_per_pair": round(ms_graph / nbuf * 1e3, 2),
+            "us_per_pair_stream_launches": round(ms / nbuf * 1e3, 2), "us_per_argmax_stream_launches": round(ms_am / nbuf * 1e3, 2), "us_per_argmax": round(ms_am_graph / nbuf * 1e3, 2),
+            "higher_is_better": True, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "argmax_B128_vocab128000_plus_embed_gather_hidden2048", "buffers": nbuf,
+                       "l2": "8 distinct logits buffers (262 MB) rotate", "note": "value is the 8 pairs replayed as a CUDA graph"},
+            "roofline": {"kernel": "argmax_kernel", "bound": "hbm", "achieved": round(am_gbs, 1), "peak": peak, "peak_kind": kind,
+                         "unit": "GB/s", "frac": round(am_gbs / peak, 4), "bytes_per_launch": am_bytes},
+            "reference_kernels_us_per_pair": None if ms_ref is None else round(ms_ref / nbuf * 1e3, 2),
+            "agreement_with_torch_argmax": agree,
+            "gpu_launches": 2 * nbuf * args.steps, "clocks": clocks, "device_status": kv.device_status()}
+
+
 def run_prefill(args, torch):
     """Config 4: one wave of 128 new tokens for each of 32 sequences, prefixes uniform 0..8192
     (seeded), one attention layer: append of the 4096 wave rows, then causal gated GQA attention."""
@@ -690,8 +755,8 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="override for small profiling cases")
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--ctx", type=int, default=CTX)
-    ap.add_argument("--workload", default="decode", choices=["decode", "conv", "prefill", "serving_mix"],
-                    help="decode = the headline line; conv / prefill = secondary single-GPU lines")
+    ap.add_argument("--workload", default="decode", choices=["decode", "conv", "prefill", "serving_mix", "sample"],
+                    help="decode = the headline line; conv / prefill / sample = secondary single-GPU lines")
     args = ap.parse_args()
     globals().update(LAYERS=args.layers, BATCH=args.batch, CTX=args.ctx)
     args.warmup = max(args.warmup, 3)
@@ -713,6 +778,8 @@ def main():
             line = run_conv(args, torch) if rank == 0 else None
         elif args.workload == "prefill":
             line = run_prefill(args, torch) if rank == 0 else None
+        elif args.workload == "sample":
+            line = run_sample(args, torch) if rank == 0 else None
         elif args.workload == "serving_mix":
             line = run_serving_mix(args, torch, rank, world, local_rank)
         else:

@@ -200,7 +200,8 @@ cudaError_t launch_embed_lookup(cudaStream_t stream, void* out, const void* tabl
 
 cudaError_t launch_argmax(cudaStream_t stream, uint32_t* tokens_out, const void* logits, uint32_t vocab,
                           uint32_t batch, int num_sms, void* cand_scratch, uint32_t* counters) {
-    // enough CTAs for two per SM, but no split shorter than 32 k-rows (8192 logits)
+    // enough CTAs for two per SM (six per SM measured slower: the merge of the splits grows), but no
+    // split shorter than 32 k-rows (8192 logits)
     uint32_t splits = (uint32_t)(2 * num_sms + (int)batch - 1) / batch;
     const uint32_t nk = (vocab + sm::VT - 1) / sm::VT;
     const uint32_t by_len = nk / 32u;
