@@ -54,7 +54,8 @@ enum {
     OXI_DEV_MISALIGNED_PTR = 1u, /* a K/V/state pointer was not 16-byte aligned; row skipped */
     OXI_DEV_BAD_SEQ_LEN = 2u,    /* seq_len 0 or beyond the handle's max_seq_len; row skipped */
     OXI_DEV_WAIT_TIMEOUT = 4u,   /* an in-kernel pipeline wait gave up (internal error)       */
-    OXI_DEV_BAD_TOKEN = 8u       /* a token id was beyond the embedding table; row zero-filled */
+    OXI_DEV_BAD_TOKEN = 8u,      /* a token id was beyond the embedding table; row zero-filled */
+    OXI_DEV_BAD_BLOCK = 16u      /* a block id in a paged layout's table was >= num_blocks      */
 };
 
 typedef struct oxi_handle oxi_handle;
@@ -154,6 +155,45 @@ int32_t oxi_conv_decode(oxi_handle* h, void* stream, void* y_out, const uint64_t
 int32_t oxi_conv_prefill(oxi_handle* h, void* stream, void* y_out, const uint64_t* carry_ptrs,
                          const uint32_t* origin, const uint32_t* local_pos, const void* bcx,
                          const void* conv_w, uint32_t rows);
+
+/* ---- paged K/V layout: block tables instead of one contiguous lease ---- */
+/* The reference's stated next milestone (docs/SCALE_AND_OPTIMIZATION_ROADMAP.md:42-43):
+ * its PagedKvPool (core/src/paged_pool.rs:10-25), PagedBlockManager
+ * (scheduler/src/block_manager.rs, block_size 16) and the argument list of its
+ * paged_attention_decode_v1 stub (kernels/src/attention.rs:9-27: k_cache,
+ * v_cache, block_tables [batch][max_blocks], context_lens, max_blocks,
+ * block_size) exist, the kernel body does not.  The three entry points below
+ * are the pointer-table path's operators over that layout; heads, head dim and
+ * scale are the path's constants.  Token t of row b lives in block
+ * block_tables[b][t / block_size] at slot t % block_size; block i's rows start
+ * at pool + i * block_stride_bytes, one row = 4 KV heads x 128 f16 (1024 bytes)
+ * - with block_stride_bytes the reference's pool (all layers, K and V inside a
+ * block) is addressed by pointing k_pool / v_pool at the layer's K / V rows of
+ * block 0.  Results are bit-identical to the contiguous entry points on the
+ * same keys.  A block id >= num_blocks sets OXI_DEV_BAD_BLOCK (block 0 is read
+ * instead, nothing is written); a row that needs more than max_blocks blocks
+ * sets OXI_DEV_BAD_SEQ_LEN and is skipped. */
+typedef struct oxi_paged_layout {
+    const void* k_pool;            /* device, 16-byte aligned */
+    const void* v_pool;
+    const uint32_t* block_tables;  /* device [batch][max_blocks] */
+    uint64_t block_stride_bytes;   /* multiple of 16, >= block_size * 1024 */
+    uint32_t max_blocks;
+    uint32_t block_size;           /* tokens per block: 16, 32, 64, 128 or 256 */
+    uint32_t num_blocks;
+} oxi_paged_layout;
+int32_t oxi_append_paged(oxi_handle* h, void* stream, void* q_io, const void* k_in, const void* v_in,
+                         const void* q_norm_w, const void* k_norm_w, const void* cos_table,
+                         const void* sin_table, const uint32_t* pos_ids, const oxi_paged_layout* layout,
+                         uint32_t batch, float eps);
+int32_t oxi_decode_attn_paged(oxi_handle* h, void* stream, void* ctx_out, const void* q, const void* gate,
+                              const oxi_paged_layout* layout, const uint32_t* seq_lens, uint32_t batch,
+                              uint32_t window);
+int32_t oxi_append_decode_paged(oxi_handle* h, void* stream, void* ctx_out, void* q_io, const void* k_in,
+                                const void* v_in, const void* gate, const void* q_norm_w,
+                                const void* k_norm_w, const void* cos_table, const void* sin_table,
+                                const uint32_t* seq_lens, const oxi_paged_layout* layout, uint32_t batch,
+                                uint32_t window, float eps);
 
 /* ---- the sampling side of a decode step: the file's two other table kernels */
 /* out[b][:] = table[token_ids[b]][:] (f16 rows of `hidden` elements).

@@ -19,21 +19,44 @@ append_kernel(uint16_t* __restrict__ q_io, const uint16_t* __restrict__ k_in,
               const uint16_t* __restrict__ k_norm_w, const uint16_t* __restrict__ cos_t,
               const uint16_t* __restrict__ sin_t, const uint32_t* __restrict__ pos_ids,
               const uint64_t* __restrict__ k_ptrs, const uint64_t* __restrict__ v_ptrs, float eps,
-              uint32_t* __restrict__ status) {
+              uint32_t* __restrict__ status, const PagedMap pm) {
     const uint32_t b = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_launch_dependents();
     // the step's tables, norm weights and RoPE rows are not written by any kernel: fetch them
     // while the preceding kernel is still draining
     const uint32_t pos = pos_ids[b];
-    const uint64_t kp = k_ptrs[b], vp = v_ptrs[b];
+    uint64_t kp, vp;
+    bool page_ok = true;
+    if (pm.block_tables) {
+        // paged: the base that puts row `pos` at its slot of its block (base + pos * row bytes, as below)
+        const uint32_t pg = pos >> pm.lbs;
+        uint32_t id = 0;
+        if (pg >= pm.max_blocks) {
+            page_ok = false;
+            if (threadIdx.x == 0) atomicOr(status, DEV_BAD_SEQ_LEN);
+        } else {
+            id = pm.block_tables[(size_t)b * pm.max_blocks + pg];
+            if (id >= pm.num_blocks) {
+                page_ok = false;
+                if (threadIdx.x == 0) atomicOr(status, DEV_BAD_BLOCK);
+            }
+        }
+        const uint64_t off = (uint64_t)id * pm.block_stride + (uint64_t)(pos & ((1u << pm.lbs) - 1u)) * KV_ROW_BYTES -
+                             (uint64_t)pos * KV_ROW_BYTES;
+        kp = (uint64_t)(uintptr_t)pm.k_pool + off;
+        vp = (uint64_t)(uintptr_t)pm.v_pool + off;
+    } else {
+        kp = k_ptrs[b];
+        vp = v_ptrs[b];
+    }
     float wv[4], cv[4], sv[4];
     load4(warp < NQ ? q_norm_w : k_norm_w, lane, wv);
     load4(cos_t + (size_t)pos * HD, lane, cv);
     load4(sin_t + (size_t)pos * HD, lane, sv);
     pdl_wait();  // q/k/v come from the preceding kernel; the caches may still be read by it
-    const bool aligned = ((kp | vp) & 15ull) == 0ull;
-    if (!aligned && threadIdx.x == 0) atomicOr(status, DEV_MISALIGNED_PTR);
+    const bool aligned = page_ok && ((kp | vp) & 15ull) == 0ull;
+    if (!aligned && page_ok && threadIdx.x == 0) atomicOr(status, DEV_MISALIGNED_PTR);
     uint16_t out[4];
     if (warp < NQ) {
         uint16_t* xh = q_io + ((size_t)b * NQ + warp) * HD;
@@ -121,7 +144,17 @@ cudaError_t launch_append(cudaStream_t stream, void* q_io, const void* k_in, con
     return launch_pdl(append_kernel, dim3(batch), dim3(640), 0, stream, (uint16_t*)q_io,
                       (const uint16_t*)k_in, (const uint16_t*)v_in, (const uint16_t*)q_norm_w,
                       (const uint16_t*)k_norm_w, (const uint16_t*)cos_t, (const uint16_t*)sin_t, pos_ids,
-                      k_ptrs, v_ptrs, eps, status);
+                      k_ptrs, v_ptrs, eps, status, PagedMap{});
+}
+
+cudaError_t launch_append_paged(cudaStream_t stream, void* q_io, const void* k_in, const void* v_in,
+                                const void* q_norm_w, const void* k_norm_w, const void* cos_t,
+                                const void* sin_t, const uint32_t* pos_ids, const PagedMap& pm,
+                                uint32_t batch, float eps, uint32_t* status) {
+    return launch_pdl(append_kernel, dim3(batch), dim3(640), 0, stream, (uint16_t*)q_io,
+                      (const uint16_t*)k_in, (const uint16_t*)v_in, (const uint16_t*)q_norm_w,
+                      (const uint16_t*)k_norm_w, (const uint16_t*)cos_t, (const uint16_t*)sin_t, pos_ids,
+                      (const uint64_t*)nullptr, (const uint64_t*)nullptr, eps, status, pm);
 }
 
 cudaError_t launch_qk_rmsnorm(cudaStream_t stream, void* x_io, const void* w, float eps,

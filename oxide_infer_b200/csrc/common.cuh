@@ -21,6 +21,20 @@ constexpr uint32_t DEV_MISALIGNED_PTR = 1u;
 constexpr uint32_t DEV_BAD_SEQ_LEN = 2u;
 constexpr uint32_t DEV_WAIT_TIMEOUT = 4u;
 constexpr uint32_t DEV_BAD_TOKEN = 8u;
+constexpr uint32_t DEV_BAD_BLOCK = 16u;
+
+// Paged K/V layout of one layer: token t of row b lives in block block_tables[b][t >> lbs] at slot
+// t & (2^lbs - 1); block i's K rows start at k_pool + i * block_stride (V: v_pool), one row =
+// 4 KV heads x 128 f16 = 1024 bytes.  block_tables == nullptr means "not paged".
+struct PagedMap {
+    const unsigned char* k_pool;
+    const unsigned char* v_pool;
+    const uint32_t* block_tables;  // [batch][max_blocks]
+    uint64_t block_stride;         // bytes between consecutive blocks of one pool (multiple of 16)
+    uint32_t max_blocks;           // columns of block_tables
+    uint32_t lbs;                  // log2(block size in tokens), 4 ... 8
+    uint32_t num_blocks;           // blocks in the pool: larger ids are rejected
+};
 
 // ---- approximate instructions the reference uses (kept as PTX so results match bit for bit)
 __device__ __forceinline__ float ex2_approx_ftz(float x) {

@@ -121,6 +121,9 @@ struct DecodeParams {
     uint32_t window;
     uint32_t max_chunks;
     uint32_t max_seq_len;
+    // paged variant only: K/V rows live in fixed-size blocks of a pool, block_tables[b][i] is the
+    // block that holds tokens [i*bs, (i+1)*bs) of row b (k_ptrs / v_ptrs are then unused)
+    PagedMap paged;
     // fused variant only (q is then the raw projected q)
     const uint16_t* k_in;
     const uint16_t* v_in;
@@ -146,7 +149,7 @@ __device__ __forceinline__ uint32_t find_row(const uint32_t* prefix, uint32_t ba
     return lo;
 }
 
-template <bool kFused>
+template <bool kFused, bool kPaged>
 __global__ void __launch_bounds__(dec::THREADS, 1)
 decode_attn_kernel(const DecodeParams p) {
     using namespace dec;
@@ -178,7 +181,9 @@ decode_attn_kernel(const DecodeParams p) {
         uint32_t n = 0;
         if (slen == 0u || slen > p.max_seq_len) {
             if (blockIdx.x == 0) atomicOr(p.status, DEV_BAD_SEQ_LEN);
-        } else if (((p.k_ptrs[b] | p.v_ptrs[b]) & 15ull) != 0ull) {
+        } else if (kPaged && ((slen - 1u) >> p.paged.lbs) >= p.paged.max_blocks) {
+            if (blockIdx.x == 0) atomicOr(p.status, DEV_BAD_SEQ_LEN);  // more blocks than the table has columns
+        } else if (!kPaged && ((p.k_ptrs[b] | p.v_ptrs[b]) & 15ull) != 0ull) {
             if (blockIdx.x == 0) atomicOr(p.status, DEV_MISALIGNED_PTR);
         } else {
             n = row_chunks(slen, p.window);
@@ -220,12 +225,34 @@ decode_attn_kernel(const DecodeParams p) {
         uint32_t cur = blockIdx.x;
         uint32_t cb = 0, cc = 0, cslen = 0;
         uint64_t ckp = 0, cvp = 0;
+        // paged: lane l holds the block of the item's l-th page (an item spans at most CHUNK / 16 + 1 = 17
+        // pages), fetched one item ahead like the row pointers
+        uint32_t cpg = 0, cfp = 0;
+        auto fetch_pages = [&](uint32_t b, uint32_t c, uint32_t slen, uint32_t& first_page) -> uint32_t {
+            const uint32_t t0 = window_start(slen, p.window) + c * CHUNK;
+            const uint32_t t1 = min(t0 + (uint32_t)CHUNK, slen);
+            first_page = t0 >> p.paged.lbs;
+            const uint32_t pg = first_page + (uint32_t)lane;
+            uint32_t id = 0;
+            if (pg <= ((t1 - 1u) >> p.paged.lbs)) {
+                id = __ldg(p.paged.block_tables + (size_t)b * p.paged.max_blocks + pg);
+                if (id >= p.paged.num_blocks) {
+                    atomicOr(p.status, DEV_BAD_BLOCK);
+                    id = 0;
+                }
+            }
+            return id;
+        };
         if (cur < total_items) {
             cb = find_row(prefix, p.batch, cur);
             cc = cur - prefix[cb];
             cslen = s_len[cb];
-            ckp = p.k_ptrs[cb];
-            cvp = p.v_ptrs[cb];
+            if (kPaged) {
+                cpg = fetch_pages(cb, cc, cslen, cfp);
+            } else {
+                ckp = p.k_ptrs[cb];
+                cvp = p.v_ptrs[cb];
+            }
         }
         uint32_t claim = 0;
         if (lane == 0 && cur < total_items) claim = atomicAdd(p.work_counter, 1u);
@@ -233,7 +260,7 @@ decode_attn_kernel(const DecodeParams p) {
         while (cur < total_items && ok) {
             uint32_t nxt = __shfl_sync(0xffffffffu, claim, 0);
             nxt = (nxt >= total_items) ? total_items : min(nxt + gridDim.x, total_items);
-            uint32_t nb = 0, nc = 0, nslen = 0;
+            uint32_t nb = 0, nc = 0, nslen = 0, npg = 0, nfp = 0;
             uint64_t nkp = 0, nvp = 0;
             claim = 0xffffffffu;  // "no more items" unless a new claim is made
             if (nxt < total_items) {
@@ -241,8 +268,12 @@ decode_attn_kernel(const DecodeParams p) {
                 nb = find_row(prefix, p.batch, nxt);
                 nc = nxt - prefix[nb];
                 nslen = s_len[nb];
-                nkp = p.k_ptrs[nb];
-                nvp = p.v_ptrs[nb];
+                if (kPaged) {
+                    npg = fetch_pages(nb, nc, nslen, nfp);
+                } else {
+                    nkp = p.k_ptrs[nb];
+                    nvp = p.v_ptrs[nb];
+                }
             }
             const uint32_t nchunks = prefix[cb + 1] - prefix[cb];
             const bool last_range = (cc + 1 == nchunks);
@@ -252,6 +283,16 @@ decode_attn_kernel(const DecodeParams p) {
             const char* vp = reinterpret_cast<const char*>(cvp);
             const uint32_t t0 = window_start(cslen, p.window) + cc * CHUNK;
             const uint32_t t1 = min(t0 + (uint32_t)CHUNK, cslen);
+            const uint32_t bs_mask = kPaged ? (1u << p.paged.lbs) - 1u : 0u;
+            if (kPaged && kFused) {
+                // the consumers write the appended row at base + pos * row bytes: give them the base that
+                // makes this the row's place in its block (only meaningful in the row's last range)
+                const uint32_t pid = __shfl_sync(0xffffffffu, cpg, ((pos >> p.paged.lbs) - cfp) & 31u);
+                const uint64_t off = (uint64_t)pid * p.paged.block_stride + (uint64_t)(pos & bs_mask) * KV_ROW_BYTES -
+                                     (uint64_t)pos * KV_ROW_BYTES;
+                ckp = (uint64_t)(uintptr_t)p.paged.k_pool + off;
+                cvp = (uint64_t)(uintptr_t)p.paged.v_pool + off;
+            }
             for (uint32_t t = t0; t < t1; t += KS, ++fill) {
                 const uint32_t slot = fill % NSTAGE;
                 if (fill >= NSTAGE &&
@@ -281,14 +322,32 @@ decode_attn_kernel(const DecodeParams p) {
                 const uint32_t sbase = smem_u32(sb);
                 // lanes 0..7 copy the K groups, lanes 8..15 the V groups (up to 4 KB each), lane 16 the q
                 // row; fused: lanes 17/18 the cos/sin rows, lanes 19/20 the raw k/v rows of the owner
+                // paged: a group of 4 tokens lies in one block or straddles two (blocks hold >= 16 tokens)
+                uint32_t pid0 = 0, pid1 = 0;
+                if (kPaged) {
+                    const uint32_t pi = ((t + (lane & (NGROUP - 1)) * GK) >> p.paged.lbs) - cfp;
+                    pid0 = __shfl_sync(0xffffffffu, cpg, pi & 31u);
+                    pid1 = __shfl_sync(0xffffffffu, cpg, (pi + 1u) & 31u);
+                }
                 if (lane < 2 * NGROUP) {
                     const uint32_t grp = lane & (NGROUP - 1);
                     const bool is_v = lane >= NGROUP;
                     if (grp * GK < ncopy) {
                         const uint32_t nk = min((uint32_t)GK, ncopy - grp * GK);
-                        const char* src = (is_v ? vp : kp) + (size_t)(t + grp * GK) * KV_ROW_BYTES;
-                        bulk_g2s_hint(sbase + (is_v ? HALF_BYTES : 0) + grp * GPITCH, src,
-                                      nk * KV_ROW_BYTES, &full_bar[slot], policy);
+                        const uint32_t dst = sbase + (is_v ? HALF_BYTES : 0) + grp * GPITCH;
+                        if (kPaged) {
+                            const unsigned char* pool = is_v ? p.paged.v_pool : p.paged.k_pool;
+                            const uint32_t off = (t + grp * GK) & bs_mask;
+                            const uint32_t n1 = min(nk, bs_mask + 1u - off);
+                            bulk_g2s_hint(dst, pool + (size_t)pid0 * p.paged.block_stride + (size_t)off * KV_ROW_BYTES,
+                                          n1 * KV_ROW_BYTES, &full_bar[slot], policy);
+                            if (n1 < nk)
+                                bulk_g2s_hint(dst + n1 * KV_ROW_BYTES, pool + (size_t)pid1 * p.paged.block_stride,
+                                              (nk - n1) * KV_ROW_BYTES, &full_bar[slot], policy);
+                        } else {
+                            const char* src = (is_v ? vp : kp) + (size_t)(t + grp * GK) * KV_ROW_BYTES;
+                            bulk_g2s_hint(dst, src, nk * KV_ROW_BYTES, &full_bar[slot], policy);
+                        }
                     }
                 } else if (first && lane == 2 * NGROUP) {
                     bulk_g2s(sbase + Q_OFF, qp, Q_BYTES, &full_bar[slot]);
@@ -300,7 +359,7 @@ decode_attn_kernel(const DecodeParams p) {
                     bulk_g2s(sbase + X_OFF + (lane == 19 ? X_K : X_V), src, KV_ROW_BYTES, &full_bar[slot]);
                 }
             }
-            cur = nxt; cb = nb; cc = nc; cslen = nslen; ckp = nkp; cvp = nvp;
+            cur = nxt; cb = nb; cc = nc; cslen = nslen; ckp = nkp; cvp = nvp; cpg = npg; cfp = nfp;
         }
         if (ok) {
             // end-of-work descriptor so the consumers leave their loop
@@ -539,11 +598,12 @@ decode_merge_kernel(const DecodeParams p) {
     const uint32_t hd = (blockIdx.x & 3u) * 4 + (threadIdx.x >> 5);
     // step inputs (not written by any kernel): fetched while the streaming kernel drains
     const uint32_t slen = p.seq_lens[b];
-    const uint64_t kvp = p.k_ptrs[b] | p.v_ptrs[b];
+    const uint64_t kvp = p.paged.block_tables ? 0ull : (p.k_ptrs[b] | p.v_ptrs[b]);
     const float gate_f = p.gate ? h2f(p.gate[(size_t)b * NQ + hd]) : 0.0f;
     pdl_wait();
     if (blockIdx.x == 0 && threadIdx.x == 0) *p.work_counter = 0u;
     if (slen == 0u || slen > p.max_seq_len || (kvp & 15ull) != 0ull) return;
+    if (p.paged.block_tables && ((slen - 1u) >> p.paged.lbs) >= p.paged.max_blocks) return;
     const uint32_t nchunks = row_chunks(slen, p.window);
     if (nchunks <= 1) return;
     const float* stats = p.partial_stats + (((size_t)b * p.max_chunks) * NQ + hd) * 2;
@@ -595,11 +655,15 @@ uint32_t decode_chunk_keys() { return dec::CHUNK; }
 uint32_t decode_max_rows() { return dec::MAX_ROWS; }
 
 cudaError_t decode_attn_init() {
-    cudaError_t e = cudaFuncSetAttribute(decode_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(decode_attn_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)dec::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(decode_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)dec::SMEM_BYTES);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(decode_attn_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dec::SMEM_BYTES);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(decode_attn_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dec::SMEM_BYTES);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(decode_attn_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dec::SMEM_BYTES);
+    return e;
 }
 
 static DecodeParams make_params(const DecodeWorkspace& ws, void* ctx_out, const void* q, const void* gate,
@@ -628,7 +692,7 @@ cudaError_t launch_decode_attn(cudaStream_t stream, const DecodeWorkspace& ws, v
                                const uint64_t* v_ptrs, const uint32_t* seq_lens, uint32_t batch,
                                uint32_t window) {
     const DecodeParams p = make_params(ws, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, batch, window);
-    cudaError_t e = launch_pdl(decode_attn_kernel<false>, dim3(ws.num_sms), dim3(dec::THREADS), dec::SMEM_BYTES,
+    cudaError_t e = launch_pdl(decode_attn_kernel<false, false>, dim3(ws.num_sms), dim3(dec::THREADS), dec::SMEM_BYTES,
                                stream, p);
     if (e != cudaSuccess) return e;
     return launch_pdl(decode_merge_kernel, dim3(batch * NKV), dim3(128), 0, stream, p);
@@ -647,7 +711,38 @@ cudaError_t launch_append_decode(cudaStream_t stream, const DecodeWorkspace& ws,
     p.cos_t = (const uint16_t*)cos_t;
     p.sin_t = (const uint16_t*)sin_t;
     p.eps = eps;
-    cudaError_t e = launch_pdl(decode_attn_kernel<true>, dim3(ws.num_sms), dim3(dec::THREADS), dec::SMEM_BYTES,
+    cudaError_t e = launch_pdl(decode_attn_kernel<true, false>, dim3(ws.num_sms), dim3(dec::THREADS), dec::SMEM_BYTES,
+                               stream, p);
+    if (e != cudaSuccess) return e;
+    return launch_pdl(decode_merge_kernel, dim3(batch * NKV), dim3(128), 0, stream, p);
+}
+
+cudaError_t launch_decode_attn_paged(cudaStream_t stream, const DecodeWorkspace& ws, void* ctx_out, const void* q,
+                                     const void* gate, const PagedMap& pm, const uint32_t* seq_lens, uint32_t batch,
+                                     uint32_t window) {
+    DecodeParams p = make_params(ws, ctx_out, q, gate, nullptr, nullptr, seq_lens, batch, window);
+    p.paged = pm;
+    cudaError_t e = launch_pdl(decode_attn_kernel<false, true>, dim3(ws.num_sms), dim3(dec::THREADS), dec::SMEM_BYTES,
+                               stream, p);
+    if (e != cudaSuccess) return e;
+    return launch_pdl(decode_merge_kernel, dim3(batch * NKV), dim3(128), 0, stream, p);
+}
+
+cudaError_t launch_append_decode_paged(cudaStream_t stream, const DecodeWorkspace& ws, void* ctx_out, const void* q_io,
+                                       const void* k_in, const void* v_in, const void* gate, const void* q_norm_w,
+                                       const void* k_norm_w, const void* cos_t, const void* sin_t,
+                                       const uint32_t* seq_lens, const PagedMap& pm, uint32_t batch, uint32_t window,
+                                       float eps) {
+    DecodeParams p = make_params(ws, ctx_out, q_io, gate, nullptr, nullptr, seq_lens, batch, window);
+    p.paged = pm;
+    p.k_in = (const uint16_t*)k_in;
+    p.v_in = (const uint16_t*)v_in;
+    p.q_norm_w = (const uint16_t*)q_norm_w;
+    p.k_norm_w = (const uint16_t*)k_norm_w;
+    p.cos_t = (const uint16_t*)cos_t;
+    p.sin_t = (const uint16_t*)sin_t;
+    p.eps = eps;
+    cudaError_t e = launch_pdl(decode_attn_kernel<true, true>, dim3(ws.num_sms), dim3(dec::THREADS), dec::SMEM_BYTES,
                                stream, p);
     if (e != cudaSuccess) return e;
     return launch_pdl(decode_merge_kernel, dim3(batch * NKV), dim3(128), 0, stream, p);

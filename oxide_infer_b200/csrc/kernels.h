@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "common.cuh"
+
 namespace oxi {
 
 struct DecodeWorkspace {
@@ -58,6 +60,20 @@ cudaError_t launch_conv_prefill(cudaStream_t stream, void* y_out, const uint64_t
                                 const uint32_t* origin, const uint32_t* local_pos,
                                 const void* bcx, const void* conv_w, uint32_t rows,
                                 void* stage /* [rows][2048][6] f16 */, uint32_t* status);
+
+// Paged K/V layout (block tables instead of one contiguous lease per sequence).
+cudaError_t launch_append_paged(cudaStream_t stream, void* q_io, const void* k_in, const void* v_in,
+                                const void* q_norm_w, const void* k_norm_w, const void* cos_t,
+                                const void* sin_t, const uint32_t* pos_ids, const PagedMap& pm,
+                                uint32_t batch, float eps, uint32_t* status);
+cudaError_t launch_decode_attn_paged(cudaStream_t stream, const DecodeWorkspace& ws, void* ctx_out, const void* q,
+                                     const void* gate, const PagedMap& pm, const uint32_t* seq_lens, uint32_t batch,
+                                     uint32_t window);
+cudaError_t launch_append_decode_paged(cudaStream_t stream, const DecodeWorkspace& ws, void* ctx_out, const void* q_io,
+                                       const void* k_in, const void* v_in, const void* gate, const void* q_norm_w,
+                                       const void* k_norm_w, const void* cos_t, const void* sin_t,
+                                       const uint32_t* seq_lens, const PagedMap& pm, uint32_t batch, uint32_t window,
+                                       float eps);
 
 // Sampling-side table kernels.
 cudaError_t launch_embed_lookup(cudaStream_t stream, void* out, const void* table,

@@ -264,6 +264,74 @@ int32_t oxi_append_decode(oxi_handle* h, void* stream, void* ctx_out, void* q_io
     return OXI_OK;
 }
 
+// Validates a paged layout and converts it to the kernels' form.
+static int32_t paged_map(const oxi_paged_layout* l, const char* who, PagedMap* pm) {
+    if (!l || !l->k_pool || !l->v_pool || !l->block_tables) return fail(OXI_ERR_NULL, who);
+    uint32_t lbs = 0;
+    while ((1u << lbs) < l->block_size && lbs < 31) lbs++;
+    if (l->block_size < 16 || l->block_size > 256 || (1u << lbs) != l->block_size)
+        return fail(OXI_ERR_ARG, "paged layout: block_size must be 16, 32, 64, 128 or 256 tokens");
+    if (l->max_blocks == 0 || l->num_blocks == 0) return fail(OXI_ERR_ARG, "paged layout: max_blocks and num_blocks must be positive");
+    if ((l->block_stride_bytes & 15ull) != 0ull || l->block_stride_bytes < (uint64_t)l->block_size * KV_ROW_BYTES)
+        return fail(OXI_ERR_ARG, "paged layout: block_stride_bytes must be a multiple of 16 and hold block_size rows of 1024 bytes");
+    if ((((uintptr_t)l->k_pool | (uintptr_t)l->v_pool) & 15u) != 0) return fail(OXI_ERR_ARG, "paged layout: pools must be 16-byte aligned");
+    pm->k_pool = (const unsigned char*)l->k_pool;
+    pm->v_pool = (const unsigned char*)l->v_pool;
+    pm->block_tables = l->block_tables;
+    pm->block_stride = l->block_stride_bytes;
+    pm->max_blocks = l->max_blocks;
+    pm->lbs = lbs;
+    pm->num_blocks = l->num_blocks;
+    return OXI_OK;
+}
+
+int32_t oxi_append_paged(oxi_handle* h, void* stream, void* q_io, const void* k_in, const void* v_in,
+                         const void* q_norm_w, const void* k_norm_w, const void* cos_table,
+                         const void* sin_table, const uint32_t* pos_ids, const oxi_paged_layout* layout,
+                         uint32_t batch, float eps) {
+    REQ_HANDLE("oxi_append_paged");
+    REQ_PTR(q_io && k_in && v_in && q_norm_w && k_norm_w && cos_table && sin_table && pos_ids, "oxi_append_paged");
+    REQ_BATCH(batch, h->max_batch, "oxi_append_paged");
+    if (!(eps >= 0.0f)) return fail(OXI_ERR_ARG, "oxi_append_paged: eps must be >= 0");
+    PagedMap pm;
+    if (int32_t rc = paged_map(layout, "oxi_append_paged", &pm)) return rc;
+    OXI_CUDA(launch_append_paged((cudaStream_t)stream, q_io, k_in, v_in, q_norm_w, k_norm_w, cos_table, sin_table,
+                                 pos_ids, pm, batch, eps, h->dws.status),
+             "append_paged launch");
+    return OXI_OK;
+}
+
+int32_t oxi_decode_attn_paged(oxi_handle* h, void* stream, void* ctx_out, const void* q, const void* gate,
+                              const oxi_paged_layout* layout, const uint32_t* seq_lens, uint32_t batch,
+                              uint32_t window) {
+    REQ_HANDLE("oxi_decode_attn_paged");
+    REQ_PTR(ctx_out && q && seq_lens, "oxi_decode_attn_paged");
+    REQ_BATCH(batch, h->max_batch, "oxi_decode_attn_paged");
+    PagedMap pm;
+    if (int32_t rc = paged_map(layout, "oxi_decode_attn_paged", &pm)) return rc;
+    OXI_CUDA(launch_decode_attn_paged((cudaStream_t)stream, h->dws, ctx_out, q, gate, pm, seq_lens, batch, window),
+             "decode_attn_paged launch");
+    return OXI_OK;
+}
+
+int32_t oxi_append_decode_paged(oxi_handle* h, void* stream, void* ctx_out, void* q_io, const void* k_in,
+                                const void* v_in, const void* gate, const void* q_norm_w,
+                                const void* k_norm_w, const void* cos_table, const void* sin_table,
+                                const uint32_t* seq_lens, const oxi_paged_layout* layout, uint32_t batch,
+                                uint32_t window, float eps) {
+    REQ_HANDLE("oxi_append_decode_paged");
+    REQ_PTR(ctx_out && q_io && k_in && v_in && q_norm_w && k_norm_w && cos_table && sin_table && seq_lens,
+            "oxi_append_decode_paged");
+    REQ_BATCH(batch, h->max_batch, "oxi_append_decode_paged");
+    if (!(eps >= 0.0f)) return fail(OXI_ERR_ARG, "oxi_append_decode_paged: eps must be >= 0");
+    PagedMap pm;
+    if (int32_t rc = paged_map(layout, "oxi_append_decode_paged", &pm)) return rc;
+    OXI_CUDA(launch_append_decode_paged((cudaStream_t)stream, h->dws, ctx_out, q_io, k_in, v_in, gate, q_norm_w,
+                                        k_norm_w, cos_table, sin_table, seq_lens, pm, batch, window, eps),
+             "append_decode_paged launch");
+    return OXI_OK;
+}
+
 int32_t oxi_prefill_attn(oxi_handle* h, void* stream, void* ctx_out, const void* q,
                          const void* gate, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
                          const uint32_t* seq_lens, uint32_t rows, uint32_t window) {

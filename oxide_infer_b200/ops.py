@@ -16,6 +16,27 @@ import torch
 from . import _lib
 
 
+class PagedLayout(C.Structure):
+    """oxi_paged_layout of include/oxi_kv.h: one layer's K/V pools and the rows' block tables."""
+    _fields_ = [("k_pool", C.c_void_p), ("v_pool", C.c_void_p), ("block_tables", C.c_void_p),
+                ("block_stride_bytes", C.c_uint64), ("max_blocks", C.c_uint32), ("block_size", C.c_uint32),
+                ("num_blocks", C.c_uint32)]
+
+    @classmethod
+    def of(cls, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor, block_size: int,
+           block_stride_bytes: int | None = None, num_blocks: int | None = None) -> "PagedLayout":
+        """k_pool / v_pool [num_blocks][block_size][4][128] f16 (or views with the given stride),
+        block_tables [batch][max_blocks] int32."""
+        if not block_tables.is_contiguous():
+            raise ValueError("block_tables must be contiguous")
+        stride = block_stride_bytes if block_stride_bytes is not None else k_pool.stride(0) * k_pool.element_size()
+        nb = num_blocks if num_blocks is not None else k_pool.shape[0]
+        out = cls(k_pool.data_ptr(), v_pool.data_ptr(), block_tables.data_ptr(), stride, block_tables.shape[1],
+                  block_size, nb)
+        out._keep = (k_pool, v_pool, block_tables)
+        return out
+
+
 class OxiError(RuntimeError):
     def __init__(self, code: int, where: str):
         lib = _lib.load()
@@ -97,6 +118,25 @@ class KvPath:
                                           _p(sin), _p(pos_ids), _p(seq_lens), _p(k_ptrs),
                                           _p(v_ptrs), q_io.shape[0], window, eps),
                "oxi_append_decode")
+
+    # ---- paged K/V layout (block tables)
+    def append_paged(self, q_io, k_in, v_in, q_norm_w, k_norm_w, cos, sin, pos_ids, layout: PagedLayout,
+                     eps: float = 1e-5):
+        _check(self.lib.oxi_append_paged(self.h, _stream(), _p(q_io), _p(k_in), _p(v_in), _p(q_norm_w),
+                                         _p(k_norm_w), _p(cos), _p(sin), _p(pos_ids), C.addressof(layout),
+                                         q_io.shape[0], eps), "oxi_append_paged")
+
+    def decode_attn_paged(self, ctx_out, q, gate, layout: PagedLayout, seq_lens, window: int = 0):
+        _check(self.lib.oxi_decode_attn_paged(self.h, _stream(), _p(ctx_out), _p(q), _p(gate),
+                                              C.addressof(layout), _p(seq_lens), q.shape[0], window),
+               "oxi_decode_attn_paged")
+
+    def append_decode_paged(self, ctx_out, q_io, k_in, v_in, gate, q_norm_w, k_norm_w, cos, sin, seq_lens,
+                            layout: PagedLayout, window: int = 0, eps: float = 1e-5):
+        _check(self.lib.oxi_append_decode_paged(self.h, _stream(), _p(ctx_out), _p(q_io), _p(k_in), _p(v_in),
+                                                _p(gate), _p(q_norm_w), _p(k_norm_w), _p(cos), _p(sin),
+                                                _p(seq_lens), C.addressof(layout), q_io.shape[0], window, eps),
+               "oxi_append_decode_paged")
 
     def prefill_attn(self, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, window: int = 0,
                      rows: int | None = None):

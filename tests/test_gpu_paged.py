@@ -1,0 +1,152 @@
+"""The paged K/V entry points through the C ABI: the same keys stored in blocks of a pool behind
+block tables must give results that are bit-identical to the contiguous pointer-table entry points
+(the work items are the same 256-key ranges in the same order), and the appended rows must land
+in the right slot of the right block."""
+import numpy as np
+import pytest
+
+from oracle import cpu as O
+from tests.kvcase import DecodeCase, NKV, HD
+
+pytestmark = pytest.mark.gpu
+
+LENS = [0, 1, 14, 15, 16, 17, 255, 256, 257, 1000, 2047, 4095]
+
+
+@pytest.fixture(scope="module")
+def kv():
+    from oxide_infer_b200 import KvPath
+    return KvPath(0, max_batch=64, max_seq_len=8192, max_prefill_rows=0)
+
+
+def _paged(case, d, block_size, seed, layers_in_block=1, layer=0):
+    """Scatters the case's contiguous device caches into blocks of one pool.  With layers_in_block > 1
+    the pool has the reference's shape (paged_pool.rs:20-24): every block holds K and V of all
+    layers, so the block stride is 2 * layers * block_size rows and the layer's K / V rows start
+    inside the block."""
+    import torch
+    from oxide_infer_b200 import PagedLayout
+    rng = np.random.default_rng(seed)
+    need = [(int(n) + 1 + block_size - 1) // block_size for n in case.lens]  # blocks incl. the appended token
+    total = sum(need) + 3
+    perm = rng.permutation(total).astype(np.int32)
+    max_blocks = max(need) + 1
+    tables = np.full((case.b, max_blocks), 0, np.int32)
+    rows_per_block = 2 * layers_in_block * block_size
+    pool = torch.zeros(total, rows_per_block, NKV, HD, dtype=torch.float16, device="cuda")
+    k_view = pool[:, (2 * layer) * block_size:(2 * layer + 1) * block_size]
+    v_view = pool[:, (2 * layer + 1) * block_size:(2 * layer + 2) * block_size]
+    o = 0
+    for i, n in enumerate(case.lens):
+        ids = perm[o:o + need[i]]
+        o += need[i]
+        tables[i, :need[i]] = ids
+        for j, bid in enumerate(ids):
+            lo, hi = j * block_size, min((j + 1) * block_size, int(n))
+            if hi > lo:
+                k_view[bid, :hi - lo] = d.k_cache[i][lo:hi]
+                v_view[bid, :hi - lo] = d.v_cache[i][lo:hi]
+    dt = torch.from_numpy(tables).cuda()
+    lay = PagedLayout.of(k_view, v_view, dt, block_size, block_stride_bytes=rows_per_block * NKV * HD * 2, num_blocks=total)
+    return lay, pool, k_view, v_view, tables
+
+
+@pytest.mark.parametrize("block_size", [16, 64, 256])
+@pytest.mark.parametrize("window", [0, 300])
+def test_paged_append_then_attention_equals_contiguous(kv, block_size, window):
+    import torch
+    case = DecodeCase(LENS, seed=41)
+    d = case.device()
+    lay, pool, k_view, v_view, tables = _paged(case, d, block_size, seed=42)
+    # contiguous path
+    kv.append(d.q, d.k, d.v, d.q_norm_w, d.k_norm_w, d.cos, d.sin, d.pos_ids, d.k_ptrs, d.v_ptrs)
+    kv.decode_attn(d.ctx, d.q, d.gate, d.k_ptrs, d.v_ptrs, d.seq_lens, window)
+    # paged path on fresh inputs
+    d2 = case.device()
+    kv.append_paged(d2.q, d2.k, d2.v, d2.q_norm_w, d2.k_norm_w, d2.cos, d2.sin, d2.pos_ids, lay)
+    kv.decode_attn_paged(d2.ctx, d2.q, d2.gate, lay, d2.seq_lens, window)
+    torch.cuda.synchronize()
+    assert kv.device_status() == 0
+    assert torch.equal(d.q, d2.q)
+    for i, n in enumerate(case.lens):
+        bid, slot = tables[i, int(n) // block_size], int(n) % block_size
+        assert torch.equal(k_view[bid, slot], d.k_cache[i][int(n)]), i
+        assert torch.equal(v_view[bid, slot], d.v_cache[i][int(n)]), i
+    assert torch.equal(d.ctx.view(torch.int16), d2.ctx.view(torch.int16))
+    # and against the oracle on the contiguous copy
+    h = case.host()
+    O.qk_rmsnorm(h.q, case.q_norm_w)
+    O.qk_rmsnorm(h.k, case.k_norm_w)
+    O.rope(h.q, case.cos, case.sin, case.pos_ids)
+    O.rope(h.k, case.cos, case.sin, case.pos_ids)
+    O.kv_copy(h.k_ptrs, h.k, case.pos_ids)
+    O.kv_copy(h.v_ptrs, h.v, case.pos_ids)
+    want = O.decode_attn(h.q, case.gate, h.k_ptrs, h.v_ptrs, case.seq_lens, window)
+    err = np.abs(d2.ctx.cpu().numpy().astype(np.float32) - want.astype(np.float32)).max()
+    assert err <= 2e-3, err
+
+
+@pytest.mark.parametrize("block_size", [16, 128])
+def test_paged_fused_step_equals_contiguous_fused_step(kv, block_size):
+    import torch
+    case = DecodeCase(LENS, seed=43)
+    d = case.device()
+    kv.append_decode(d.ctx, d.q, d.k, d.v, d.gate, d.q_norm_w, d.k_norm_w, d.cos, d.sin, d.pos_ids, d.seq_lens,
+                     d.k_ptrs, d.v_ptrs, 0)
+    d2 = case.device()
+    lay, pool, k_view, v_view, tables = _paged(case, d2, block_size, seed=44)
+    kv.append_decode_paged(d2.ctx, d2.q, d2.k, d2.v, d2.gate, d2.q_norm_w, d2.k_norm_w, d2.cos, d2.sin, d2.seq_lens, lay, 0)
+    torch.cuda.synchronize()
+    assert kv.device_status() == 0
+    assert torch.equal(d.ctx.view(torch.int16), d2.ctx.view(torch.int16))
+    for i, n in enumerate(case.lens):
+        bid, slot = tables[i, int(n) // block_size], int(n) % block_size
+        assert torch.equal(k_view[bid, slot], d.k_cache[i][int(n)]), i
+        assert torch.equal(v_view[bid, slot], d.v_cache[i][int(n)]), i
+
+
+def test_paged_reference_pool_shape(kv):
+    """Blocks that hold K and V of 3 layers (block stride = 6 * block_size rows), layer 1 addressed."""
+    import torch
+    case = DecodeCase([100, 700, 31], seed=45)
+    d = case.device()
+    kv.append(d.q, d.k, d.v, d.q_norm_w, d.k_norm_w, d.cos, d.sin, d.pos_ids, d.k_ptrs, d.v_ptrs)
+    kv.decode_attn(d.ctx, d.q, d.gate, d.k_ptrs, d.v_ptrs, d.seq_lens, 0)
+    d2 = case.device()
+    lay, pool, k_view, v_view, tables = _paged(case, d2, 16, seed=46, layers_in_block=3, layer=1)
+    before = pool.clone()
+    kv.append_paged(d2.q, d2.k, d2.v, d2.q_norm_w, d2.k_norm_w, d2.cos, d2.sin, d2.pos_ids, lay)
+    kv.decode_attn_paged(d2.ctx, d2.q, d2.gate, lay, d2.seq_lens, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(d.ctx.view(torch.int16), d2.ctx.view(torch.int16))
+    changed = (pool != before).any(dim=(2, 3))  # [block][row in block]
+    assert int(changed.sum()) <= 2 * case.b     # only the appended K and V rows
+    assert not changed[:, :32].any() and not changed[:, 64:].any()  # layers 0 and 2 untouched
+
+
+def test_paged_bad_tables_are_flagged_not_followed(kv):
+    import torch
+    from oxide_infer_b200 import OxiError, PagedLayout
+    case = DecodeCase([40, 90], seed=47)
+    d = case.device()
+    lay, pool, k_view, v_view, tables = _paged(case, d, 16, seed=48)
+    bad = tables.copy()
+    bad[1, 2] = 10 ** 6  # beyond the pool
+    dt = torch.from_numpy(bad).cuda()
+    lay_bad = PagedLayout.of(k_view, v_view, dt, 16, block_stride_bytes=lay.block_stride_bytes, num_blocks=lay.num_blocks)
+    kv.decode_attn_paged(d.ctx, d.q, d.gate, lay_bad, d.seq_lens, 0)
+    torch.cuda.synchronize()
+    assert kv.device_status() & 16  # OXI_DEV_BAD_BLOCK
+    # a table with too few columns for the row: flagged, row skipped
+    short = torch.from_numpy(np.ascontiguousarray(tables[:, :3])).cuda()
+    lay_short = PagedLayout.of(k_view, v_view, short, 16, block_stride_bytes=lay.block_stride_bytes, num_blocks=lay.num_blocks)
+    d.ctx.fill_(7.0)
+    kv.decode_attn_paged(d.ctx, d.q, d.gate, lay_short, d.seq_lens, 0)
+    torch.cuda.synchronize()
+    assert kv.device_status() & 2   # OXI_DEV_BAD_SEQ_LEN
+    assert bool((d.ctx[1] == 7.0).all())  # 91 keys need 6 blocks, the table has 3 columns
+    # host-side validation
+    with pytest.raises(OxiError):
+        kv.decode_attn_paged(d.ctx, d.q, d.gate, PagedLayout.of(k_view, v_view, dt, 8, block_stride_bytes=lay.block_stride_bytes), d.seq_lens, 0)
+    with pytest.raises(OxiError):
+        kv.decode_attn_paged(d.ctx, d.q, d.gate, PagedLayout.of(k_view, v_view, dt, 16, block_stride_bytes=1000), d.seq_lens, 0)
