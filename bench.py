@@ -583,6 +583,62 @@ def run_sample(args, torch):
             "gpu_launches": 2 * nbuf * args.steps, "clocks": clocks, "device_status": kv.device_status()}
 
 
+def run_decode_paged(args, torch):
+    """The headline decode step (8 layers, batch 128, context 4096, fused append + attention) with
+    the K/V rows behind block tables: the same slabs seen as pools of 16- or 256-token blocks, every
+    sequence's pages scattered over the pool by a seeded permutation.  Contiguous step timed beside
+    it in the same process; all as CUDA-graph replays."""
+    import numpy as np
+    from oxide_infer_b200 import KvPath, PagedLayout
+    w = build_workload(torch, CTX, BATCH, LAYERS, 1)
+    kv = KvPath(0, max_batch=BATCH, max_seq_len=CTX, max_prefill_rows=0)
+    sampler = ClockSampler(0)
+    sampler.start()
+    w0 = time.perf_counter()
+
+    def timed(step):
+        for _ in range(3):
+            step()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        return _time_loop(torch, graph.replay, args.steps, args.warmup)
+
+    def contiguous():
+        for l in range(LAYERS):
+            kv.append_decode(w.ctx[l], w.q[l], w.k[l], w.v[l], w.gate[l], w.qw[l], w.kw[l], w.cos, w.sin, w.pos, w.lens,
+                             w.k_ptrs[l], w.v_ptrs[l])
+    res = {"contiguous": timed(contiguous)}
+    rng = np.random.default_rng(7)
+    for bs in (16, 256):
+        per_seq = CTX // bs
+        nblk = BATCH * per_seq
+        table = torch.from_numpy(rng.permutation(nblk).astype(np.int32).reshape(BATCH, per_seq)).cuda()
+        lays = [PagedLayout.of(w.k_slab[l].view(nblk, bs, NKV, HD), w.v_slab[l].view(nblk, bs, NKV, HD), table, bs)
+                for l in range(LAYERS)]
+
+        def paged():
+            for l in range(LAYERS):
+                kv.append_decode_paged(w.ctx[l], w.q[l], w.k[l], w.v[l], w.gate[l], w.qw[l], w.kw[l], w.cos, w.sin,
+                                       w.lens, lays[l])
+        res[f"paged_{bs}"] = timed(paged)
+    clocks = sampler.window(w0, time.perf_counter())
+    sampler.stop()
+    step_bytes = LAYERS * alg_bytes_layer(w.seq_lens_host)
+    peak, kind = measured_peak_gbs()
+    gbs = {k: step_bytes / (ms * 1e-3) / 1e9 for k, ms in res.items()}
+    return {"metric": "gqa_decode_step_paged_hbm_gbs", "value": round(gbs["paged_16"], 1), "unit": "GB/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(res["paged_16"], 4),
+            "us_per_layer": {k: round(ms / LAYERS * 1e3, 2) for k, ms in res.items()},
+            "gbs": {k: round(v, 1) for k, v in gbs.items()}, "higher_is_better": True, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": "decode_step_8_attention_layers_B128_ctx4096_paged_kv", "block_sizes": [16, 256],
+                       "tables": "seeded permutation of all blocks of the pool", "launch": "cuda graph replay"},
+            "roofline": {"kernel": "decode_attn_kernel<fused append, paged> + decode_merge_kernel", "bound": "hbm",
+                         "achieved": round(gbs["paged_16"], 1), "peak": peak, "peak_kind": kind, "unit": "GB/s",
+                         "frac": round(gbs["paged_16"] / peak, 4)},
+            "gpu_launches": 2 * LAYERS * args.steps, "clocks": clocks, "device_status": kv.device_status()}
+
+
 def run_prefill(args, torch):
     """Config 4: one wave of 128 new tokens for each of 32 sequences, prefixes uniform 0..8192
     (seeded), one attention layer: append of the 4096 wave rows, then causal gated GQA attention."""
@@ -755,7 +811,7 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="override for small profiling cases")
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--ctx", type=int, default=CTX)
-    ap.add_argument("--workload", default="decode", choices=["decode", "conv", "prefill", "serving_mix", "sample"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "conv", "prefill", "serving_mix", "sample", "decode_paged"],
                     help="decode = the headline line; conv / prefill / sample = secondary single-GPU lines")
     args = ap.parse_args()
     globals().update(LAYERS=args.layers, BATCH=args.batch, CTX=args.ctx)
@@ -780,6 +836,8 @@ def main():
             line = run_prefill(args, torch) if rank == 0 else None
         elif args.workload == "sample":
             line = run_sample(args, torch) if rank == 0 else None
+        elif args.workload == "decode_paged":
+            line = run_decode_paged(args, torch) if rank == 0 else None
         elif args.workload == "serving_mix":
             line = run_serving_mix(args, torch, rank, world, local_rank)
         else:
