@@ -156,6 +156,16 @@ int32_t oxi_conv_prefill(oxi_handle* h, void* stream, void* y_out, const uint64_
                          const uint32_t* origin, const uint32_t* local_pos, const void* bcx,
                          const void* conv_w, uint32_t rows);
 
+/* ---- step tables that advance on the device ----------------------------- */
+/* pos_ids[b] += delta and seq_lens[b] += delta in place (either pointer may be
+ * null).  The engine rebuilds and uploads its tables for every step
+ * (batch_engine.rs:709-740); while the batch membership is unchanged only the
+ * positions move, so with this call a captured CUDA graph of the whole decode
+ * step (all layers + this call) can be replayed token after token without any
+ * host-to-device copy.  No counterpart in the reference. */
+int32_t oxi_advance_step(oxi_handle* h, void* stream, uint32_t* pos_ids, uint32_t* seq_lens, uint32_t batch,
+                         uint32_t delta);
+
 /* ---- paged K/V layout: block tables instead of one contiguous lease ---- */
 /* The reference's stated next milestone (docs/SCALE_AND_OPTIMIZATION_ROADMAP.md:42-43):
  * its PagedKvPool (core/src/paged_pool.rs:10-25), PagedBlockManager

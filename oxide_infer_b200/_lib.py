@@ -25,6 +25,7 @@ SIGNATURES = {
     "oxi_prefill_attn": [_vp] * 8 + [_u32, _u32],
     "oxi_conv_decode": [_vp] * 6 + [_u32],
     "oxi_conv_prefill": [_vp] * 8 + [_u32],
+    "oxi_advance_step": [_vp] * 4 + [_u32, _u32],
     "oxi_append_paged": [_vp] * 11 + [_u32, _f32],
     "oxi_decode_attn_paged": [_vp] * 7 + [_u32, _u32],
     "oxi_append_decode_paged": [_vp] * 13 + [_u32, _u32, _f32],

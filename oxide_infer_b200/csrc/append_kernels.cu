@@ -137,6 +137,25 @@ sigmoid_gate_kernel(uint16_t* __restrict__ ctx_io, const uint16_t* __restrict__ 
     *p = f2h(__fmul_rn(h2f(*p), sig));
 }
 
+// pos_ids[b] += delta, seq_lens[b] += delta: the step tables advance on the device, so a captured
+// graph of a decode step can be replayed for consecutive tokens without any upload.
+__global__ void __launch_bounds__(256)
+advance_step_kernel(uint32_t* __restrict__ pos_ids, uint32_t* __restrict__ seq_lens, uint32_t batch, uint32_t delta) {
+    const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();  // the preceding step's kernels still read the tables
+    if (b < batch) {
+        if (pos_ids) pos_ids[b] += delta;
+        if (seq_lens) seq_lens[b] += delta;
+    }
+}
+
+cudaError_t launch_advance_step(cudaStream_t stream, uint32_t* pos_ids, uint32_t* seq_lens, uint32_t batch,
+                                uint32_t delta) {
+    return launch_pdl(advance_step_kernel, dim3((batch + 255) / 256), dim3(256), 0, stream, pos_ids, seq_lens, batch,
+                      delta);
+}
+
 cudaError_t launch_append(cudaStream_t stream, void* q_io, const void* k_in, const void* v_in,
                           const void* q_norm_w, const void* k_norm_w, const void* cos_t,
                           const void* sin_t, const uint32_t* pos_ids, const uint64_t* k_ptrs,

@@ -288,6 +288,8 @@ class StepTables {
     const uint64_t* conv_ptrs(size_t layer) const { return d_conv_ + layer * batch_; }
     const uint32_t* pos_ids() const { return d_pos_; }
     const uint32_t* seq_lens() const { return d_len_; }
+    uint32_t* pos_ids_mut() { return d_pos_; }
+    uint32_t* seq_lens_mut() { return d_len_; }
 
   private:
     static void check(cudaError_t e, const char* what) {
@@ -322,6 +324,12 @@ class KvPathEngine {
     // batch_engine.rs:840-899 for conv layer `layer` (decode rows).
     void conv_decode(cudaStream_t s, const StepTables& t, size_t layer, void* y, const void* bcx, const void* conv_w) {
         ok(oxi_conv_decode(h_, s, y, t.conv_ptrs(layer), bcx, conv_w, (uint32_t)t.batch()), "oxi_conv_decode");
+    }
+    // Moves every row of the tables one token ahead on the device.  While the batch membership is
+    // unchanged, a captured graph of (all layers + this call) replays step after step with no upload
+    // (the engine re-uploads its tables every step, batch_engine.rs:709-740).
+    void advance(cudaStream_t s, StepTables& t, uint32_t delta = 1) {
+        ok(oxi_advance_step(h_, s, t.pos_ids_mut(), t.seq_lens_mut(), (uint32_t)t.batch(), delta), "oxi_advance_step");
     }
     uint32_t device_status(cudaStream_t s) {
         uint32_t bits = 0;

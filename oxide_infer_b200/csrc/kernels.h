@@ -22,6 +22,8 @@ cudaError_t launch_append(cudaStream_t stream, void* q_io, const void* k_in, con
                           const void* q_norm_w, const void* k_norm_w, const void* cos_t,
                           const void* sin_t, const uint32_t* pos_ids, const uint64_t* k_ptrs,
                           const uint64_t* v_ptrs, uint32_t batch, float eps, uint32_t* status);
+cudaError_t launch_advance_step(cudaStream_t stream, uint32_t* pos_ids, uint32_t* seq_lens, uint32_t batch,
+                                uint32_t delta);
 cudaError_t launch_qk_rmsnorm(cudaStream_t stream, void* x_io, const void* w, float eps,
                               uint32_t heads, uint32_t batch);
 cudaError_t launch_rope(cudaStream_t stream, void* x_io, const void* cos_t, const void* sin_t,

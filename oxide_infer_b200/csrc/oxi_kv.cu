@@ -264,6 +264,15 @@ int32_t oxi_append_decode(oxi_handle* h, void* stream, void* ctx_out, void* q_io
     return OXI_OK;
 }
 
+int32_t oxi_advance_step(oxi_handle* h, void* stream, uint32_t* pos_ids, uint32_t* seq_lens, uint32_t batch,
+                         uint32_t delta) {
+    REQ_HANDLE("oxi_advance_step");
+    REQ_PTR(pos_ids || seq_lens, "oxi_advance_step");
+    if (batch == 0) return fail(OXI_ERR_BATCH, "oxi_advance_step: batch is 0");
+    OXI_CUDA(launch_advance_step((cudaStream_t)stream, pos_ids, seq_lens, batch, delta), "advance_step launch");
+    return OXI_OK;
+}
+
 // Validates a paged layout and converts it to the kernels' form.
 static int32_t paged_map(const oxi_paged_layout* l, const char* who, PagedMap* pm) {
     if (!l || !l->k_pool || !l->v_pool || !l->block_tables) return fail(OXI_ERR_NULL, who);

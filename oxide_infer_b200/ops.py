@@ -119,6 +119,12 @@ class KvPath:
                                           _p(v_ptrs), q_io.shape[0], window, eps),
                "oxi_append_decode")
 
+    def advance_step(self, pos_ids, seq_lens, delta: int = 1, batch: int | None = None):
+        """pos_ids += delta, seq_lens += delta on the device (graph-capturable)."""
+        t = pos_ids if pos_ids is not None else seq_lens
+        b = t.shape[0] if batch is None else batch
+        _check(self.lib.oxi_advance_step(self.h, _stream(), _p(pos_ids), _p(seq_lens), b, delta), "oxi_advance_step")
+
     # ---- paged K/V layout (block tables)
     def append_paged(self, q_io, k_in, v_in, q_norm_w, k_norm_w, cos, sin, pos_ids, layout: PagedLayout,
                      eps: float = 1e-5):

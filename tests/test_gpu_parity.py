@@ -527,3 +527,54 @@ def test_decode_step_replays_from_a_cuda_graph(kv):
     graph.replay()
     torch.cuda.synchronize()
     assert torch.equal(e.ctx.view(torch.int16), g.ctx.view(torch.int16))
+
+
+@pytest.mark.gpu
+def test_graph_of_whole_step_replays_token_after_token_without_uploads():
+    """A captured graph of (fused step of 3 layers + oxi_advance_step) replayed 12 times must leave
+    the same caches and the same last ctx as 12 eager steps whose tables come from the host."""
+    import torch
+    from oxide_infer_b200 import KvPath
+    steps, layers = 12, 3
+    lens = [5, 250, 251, 1020]
+    case = DecodeCase(lens, seed=71, spare_rows=steps + 1, max_pos=max(lens) + steps + 2)
+    kv = KvPath(0, max_batch=8, max_seq_len=2048, max_prefill_rows=0)
+
+    def fresh():
+        ds = [case.device() for _ in range(layers)]
+        return ds
+
+    # eager: host-built tables per step
+    de = fresh()
+    for s in range(steps):
+        pos = u32(case.lens + s)
+        sl = u32(case.lens + s + 1)
+        for l in range(layers):
+            d = de[l]
+            kv.append_decode(d.ctx, d.q, d.k, d.v, d.gate, d.q_norm_w, d.k_norm_w, d.cos, d.sin, pos, sl, d.k_ptrs, d.v_ptrs, 0)
+    torch.cuda.synchronize()
+    # graph: tables live on the device and advance there
+    dg = fresh()
+    pos, sl = u32(case.lens.copy()), u32(case.lens + 1)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        def step():
+            for l in range(layers):
+                d = dg[l]
+                kv.append_decode(d.ctx, d.q, d.k, d.v, d.gate, d.q_norm_w, d.k_norm_w, d.cos, d.sin, pos, sl, d.k_ptrs, d.v_ptrs, 0)
+            kv.advance_step(pos, sl, 1)
+        step()  # the first token eagerly on the capture stream (also loads everything)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            step()
+        for _ in range(steps - 1):  # capturing records the step, it does not run it
+            graph.replay()
+    torch.cuda.synchronize()
+    assert kv.device_status() == 0
+    assert np.array_equal(pos.cpu().numpy().view(np.uint32), case.lens + steps)
+    for l in range(layers):
+        assert torch.equal(de[l].ctx.view(torch.int16), dg[l].ctx.view(torch.int16)), l
+        for i in range(len(lens)):
+            assert torch.equal(de[l].k_cache[i], dg[l].k_cache[i]), (l, i)
+            assert torch.equal(de[l].v_cache[i], dg[l].v_cache[i]), (l, i)
