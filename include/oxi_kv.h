@@ -199,6 +199,14 @@ int32_t oxi_append_paged(oxi_handle* h, void* stream, void* q_io, const void* k_
 int32_t oxi_decode_attn_paged(oxi_handle* h, void* stream, void* ctx_out, const void* q, const void* gate,
                               const oxi_paged_layout* layout, const uint32_t* seq_lens, uint32_t batch,
                               uint32_t window);
+/* Chunked-prefill attention over the paged layout: wave row r reads the keys of
+ * table row row_seq[r] (consecutive rows with equal row_seq form one request's
+ * chunk, as equal k_ptrs / v_ptrs do for oxi_prefill_attn); the rows' K/V were
+ * appended before (oxi_append_paged).  Bit-identical to oxi_prefill_attn on the
+ * same keys. */
+int32_t oxi_prefill_attn_paged(oxi_handle* h, void* stream, void* ctx_out, const void* q, const void* gate,
+                               const oxi_paged_layout* layout, const uint32_t* row_seq, const uint32_t* seq_lens,
+                               uint32_t rows, uint32_t window);
 int32_t oxi_append_decode_paged(oxi_handle* h, void* stream, void* ctx_out, void* q_io, const void* k_in,
                                 const void* v_in, const void* gate, const void* q_norm_w,
                                 const void* k_norm_w, const void* cos_table, const void* sin_table,

@@ -29,6 +29,7 @@ SIGNATURES = {
     "oxi_append_paged": [_vp] * 11 + [_u32, _f32],
     "oxi_decode_attn_paged": [_vp] * 7 + [_u32, _u32],
     "oxi_append_decode_paged": [_vp] * 13 + [_u32, _u32, _f32],
+    "oxi_prefill_attn_paged": [_vp] * 8 + [_u32, _u32],
     "oxi_embed_lookup": [_vp] * 5 + [_u32, _u32, _u32],
     "oxi_argmax": [_vp] * 4 + [_u32, _u32],
     "oxi_qk_rmsnorm": [_vp, _vp, _vp, _vp, _f32, _u32, _u32],

@@ -53,7 +53,9 @@ cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* 
                                 const uint32_t* seq_lens, uint32_t rows, uint32_t window,
                                 uint32_t* status, int num_sms,
                                 uint32_t* order /* [ceil(rows/32)] block order scratch */,
-                                uint32_t* counter /* item claim counter */);
+                                uint32_t* counter /* item claim counter */,
+                                const PagedMap* pm = nullptr /* paged K/V: k_ptrs / v_ptrs unused */,
+                                const uint32_t* row_seq = nullptr /* paged: table row of each wave row */);
 
 cudaError_t launch_conv_decode(cudaStream_t stream, void* y_out, const uint64_t* conv_ptrs,
                                const void* bcx, const void* conv_w, uint32_t batch,

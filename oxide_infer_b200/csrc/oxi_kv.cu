@@ -341,6 +341,20 @@ int32_t oxi_append_decode_paged(oxi_handle* h, void* stream, void* ctx_out, void
     return OXI_OK;
 }
 
+int32_t oxi_prefill_attn_paged(oxi_handle* h, void* stream, void* ctx_out, const void* q, const void* gate,
+                               const oxi_paged_layout* layout, const uint32_t* row_seq, const uint32_t* seq_lens,
+                               uint32_t rows, uint32_t window) {
+    REQ_HANDLE("oxi_prefill_attn_paged");
+    REQ_PTR(ctx_out && q && row_seq && seq_lens, "oxi_prefill_attn_paged");
+    REQ_BATCH(rows, h->max_prefill_rows, "oxi_prefill_attn_paged");
+    PagedMap pm;
+    if (int32_t rc = paged_map(layout, "oxi_prefill_attn_paged", &pm)) return rc;
+    OXI_CUDA(launch_prefill_attn((cudaStream_t)stream, ctx_out, q, gate, nullptr, nullptr, seq_lens, rows, window,
+                                 h->dws.status, h->num_sms, h->pf_order, h->dws.status + 48, &pm, row_seq),
+             "prefill_attn_paged launch");
+    return OXI_OK;
+}
+
 int32_t oxi_prefill_attn(oxi_handle* h, void* stream, void* ctx_out, const void* q,
                          const void* gate, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
                          const uint32_t* seq_lens, uint32_t rows, uint32_t window) {

@@ -296,8 +296,11 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                     const uint16_t* __restrict__ gate, const uint64_t* __restrict__ k_ptrs,
                     const uint64_t* __restrict__ v_ptrs, const uint32_t* __restrict__ seq_lens,
                     uint32_t rows, uint32_t window, uint32_t* __restrict__ status,
-                    const uint32_t* __restrict__ order, uint32_t* __restrict__ counter) {
+                    const uint32_t* __restrict__ order, uint32_t* __restrict__ counter,
+                    const PagedMap pm, const uint32_t* __restrict__ row_seq) {
     using namespace pf;
+    // paged K/V: k_ptrs / v_ptrs are unused, wave row r reads row row_seq[r] of pm.block_tables
+    const bool paged = pm.block_tables != nullptr;
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint64_t s_kp[BLK], s_vp[BLK];
     __shared__ uint32_t s_len[BLK];
@@ -370,14 +373,23 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         uint32_t sl = 0;
         if ((uint32_t)tid < nrows) {
             const uint32_t r = row0 + tid;
-            kp = k_ptrs[r];
-            vp = v_ptrs[r];
             sl = seq_lens[r];
+            bool too_long = false;
+            if (paged) {
+                // the run logic below only compares these two words: (table row + 1) * 16 keeps rows of one
+                // sequence equal, non-zero and "aligned"
+                kp = vp = ((uint64_t)row_seq[r] + 1ull) << 4;
+                too_long = sl != 0u && ((sl - 1u) >> pm.lbs) >= pm.max_blocks;  // more blocks than the table has columns
+            } else {
+                kp = k_ptrs[r];
+                vp = v_ptrs[r];
+            }
             if (((kp | vp) & 15ull) != 0ull) {
                 if (kvh == 0) atomicOr(status, DEV_MISALIGNED_PTR);
                 sl = 0;
-            } else if (sl == 0u) {
+            } else if (sl == 0u || too_long) {
                 if (kvh == 0) atomicOr(status, DEV_BAD_SEQ_LEN);
+                sl = 0;
             }
         }
         s_kp[tid] = kp;
@@ -659,8 +671,26 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         uint32_t next = 0;
         PfRun run;
         while (pf_next_run(next, nrows, s_kp, s_vp, s_len, window, run)) {
-            const char* base = reinterpret_cast<const char*>(is_k ? s_kp[run.r0] : s_vp[run.r0]) + kvh * (HD * 2);
+            const char* base = paged ? reinterpret_cast<const char*>(is_k ? pm.k_pool : pm.v_pool) + kvh * (HD * 2)
+                                     : reinterpret_cast<const char*>(is_k ? s_kp[run.r0] : s_vp[run.r0]) + kvh * (HD * 2);
             const uint32_t ntiles = (run.hi - run.lo + TK - 1) / TK;
+            // paged: lane l holds the block of page (tile's first page + l); a 64-key tile spans at most 5
+            // blocks of >= 16 tokens; the next tile's entries are fetched while this tile is copied
+            const uint32_t* trow = paged ? pm.block_tables + (size_t)((s_kp[run.r0] >> 4) - 1ull) * pm.max_blocks : nullptr;
+            const uint32_t last_page = paged ? (run.hi - 1u) >> pm.lbs : 0u;
+            auto fetch_pages = [&](uint32_t kb) -> uint32_t {
+                const uint32_t pg = (kb >> pm.lbs) + (uint32_t)lane;
+                uint32_t id = 0;
+                if (lane < 8 && pg <= last_page) {
+                    id = __ldg(trow + pg);
+                    if (id >= pm.num_blocks) {
+                        atomicOr(status, DEV_BAD_BLOCK);
+                        id = 0;
+                    }
+                }
+                return id;
+            };
+            uint32_t pg_next = paged ? fetch_pages(run.lo) : 0u;
             for (uint32_t tile = 0; tile < ntiles; tile++) {
                 const uint32_t st = gk % NS;
                 // the MMAs that read this stage's previous tile have completed (first use: passes at once)
@@ -668,7 +698,20 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                 const uint32_t kbeg = run.lo + tile * TK;
                 const uint32_t dst = ring + st * KV_TILE + (c >> 3) * KV_SUB;
                 const char* src = base + (size_t)(kbeg + r0) * KV_ROW_BYTES + c * 16;
-                if (kbeg + TK <= run.hi) {
+                if (paged) {
+                    const uint32_t pg_cur = pg_next;
+                    if (tile + 1 < ntiles) pg_next = fetch_pages(kbeg + TK);
+                    const uint32_t p0 = kbeg >> pm.lbs, mask = (1u << pm.lbs) - 1u;
+#pragma unroll 8
+                    for (int k = 0; k < TK / 2; k++) {
+                        const uint32_t row = r0 + 2 * k, tkn = kbeg + row;
+                        const uint32_t pid = __shfl_sync(0xffffffffu, pg_cur, ((tkn >> pm.lbs) - p0) & 31u);
+                        const bool valid = tkn < run.hi;  // rows past the run's last key are zero-filled
+                        cp_async_16(dst + row * ROW_B + (((c & 7u) ^ (row & 7u)) << 4),
+                                    valid ? base + (size_t)pid * pm.block_stride + (size_t)(tkn & mask) * KV_ROW_BYTES + c * 16 : base,
+                                    valid);
+                    }
+                } else if (kbeg + TK <= run.hi) {
 #pragma unroll
                     for (int k = 0; k < TK / 2; k++) {
                         const uint32_t row = r0 + 2 * k;
@@ -717,7 +760,8 @@ cudaError_t prefill_attn_init() {
 cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* q,
                                 const void* gate, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
                                 const uint32_t* seq_lens, uint32_t rows, uint32_t window,
-                                uint32_t* status, int num_sms, uint32_t* order, uint32_t* counter) {
+                                uint32_t* status, int num_sms, uint32_t* order, uint32_t* counter,
+                                const PagedMap* pm, const uint32_t* row_seq) {
     const uint32_t nitems = ((rows + pf::BLK - 1) / pf::BLK) * NKV;
     if ((rows + pf::BLK - 1) / pf::BLK <= 1024u)
         prefill_plan_small_kernel<<<1, 1024, 0, stream>>>(seq_lens, rows, window, order, counter);
@@ -729,7 +773,7 @@ cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* 
     // programmatic dependent of the plan kernel: TMEM allocation and barrier set-up overlap it
     return launch_pdl(prefill_attn_kernel, dim3(grid), dim3(pf::THREADS), pf::SMEM_BYTES, stream,
                       (uint16_t*)ctx_out, (const uint16_t*)q, (const uint16_t*)gate, k_ptrs, v_ptrs, seq_lens, rows,
-                      window, status, (const uint32_t*)order, counter);
+                      window, status, (const uint32_t*)order, counter, pm ? *pm : PagedMap{}, row_seq);
 }
 
 }  // namespace oxi

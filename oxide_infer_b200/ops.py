@@ -144,6 +144,12 @@ class KvPath:
                                                 _p(seq_lens), C.addressof(layout), q_io.shape[0], window, eps),
                "oxi_append_decode_paged")
 
+    def prefill_attn_paged(self, ctx_out, q, gate, layout: PagedLayout, row_seq, seq_lens, window: int = 0,
+                           rows: int | None = None):
+        n = q.shape[0] if rows is None else rows
+        _check(self.lib.oxi_prefill_attn_paged(self.h, _stream(), _p(ctx_out), _p(q), _p(gate), C.addressof(layout),
+                                               _p(row_seq), _p(seq_lens), n, window), "oxi_prefill_attn_paged")
+
     def prefill_attn(self, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, window: int = 0,
                      rows: int | None = None):
         n = q.shape[0] if rows is None else rows

@@ -150,3 +150,49 @@ def test_paged_bad_tables_are_flagged_not_followed(kv):
         kv.decode_attn_paged(d.ctx, d.q, d.gate, PagedLayout.of(k_view, v_view, dt, 8, block_stride_bytes=lay.block_stride_bytes), d.seq_lens, 0)
     with pytest.raises(OxiError):
         kv.decode_attn_paged(d.ctx, d.q, d.gate, PagedLayout.of(k_view, v_view, dt, 16, block_stride_bytes=1000), d.seq_lens, 0)
+
+
+@pytest.mark.parametrize("block_size,window", [(16, 0), (64, 0), (16, 200), (256, 0)])
+def test_paged_prefill_equals_contiguous_prefill(block_size, window):
+    """A wave of chunks (ragged lengths, prefixes that are not multiples of anything) over paged
+    caches: ctx must be bit-identical to oxi_prefill_attn over contiguous copies of the same keys."""
+    import torch
+    from oxide_infer_b200 import KvPath, PagedLayout
+    rng = np.random.default_rng(61)
+    chunks = [(0, 70), (333, 128), (1000, 1), (77, 64), (2049, 129)]  # (prefix, new rows)
+    rows = sum(n for _, n in chunks)
+    kvp = KvPath(0, max_batch=8, max_seq_len=4096, max_prefill_rows=rows)
+    g = torch.Generator(device="cuda").manual_seed(61)
+    rn = lambda *s: torch.empty(*s, dtype=torch.float16, device="cuda").normal_(generator=g)
+    kc = [rn(p + n, NKV, HD) for p, n in chunks]
+    vc = [rn(p + n, NKV, HD) for p, n in chunks]
+    q, gate = rn(rows, 16, HD), rn(rows, 16)
+    owner = np.concatenate([np.full(n, i) for i, (_, n) in enumerate(chunks)])
+    lens = np.concatenate([p + 1 + np.arange(n) for p, n in chunks]).astype(np.int32)
+    kp = torch.tensor([kc[i].data_ptr() for i in owner], dtype=torch.int64, device="cuda")
+    vp = torch.tensor([vc[i].data_ptr() for i in owner], dtype=torch.int64, device="cuda")
+    dlen = torch.from_numpy(lens).cuda()
+    ctx = torch.zeros(rows, 16, HD, dtype=torch.float16, device="cuda")
+    kvp.prefill_attn(ctx, q, gate, kp, vp, dlen, window)
+    # the same keys in scattered blocks
+    need = [(p + n + block_size - 1) // block_size for p, n in chunks]
+    total = sum(need) + 2
+    perm = rng.permutation(total).astype(np.int32)
+    tables = np.zeros((len(chunks), max(need)), np.int32)
+    kpool = torch.zeros(total, block_size, NKV, HD, dtype=torch.float16, device="cuda")
+    vpool = torch.zeros_like(kpool)
+    o = 0
+    for i, (p, n) in enumerate(chunks):
+        ids = perm[o:o + need[i]]
+        o += need[i]
+        tables[i, :need[i]] = ids
+        for j, bid in enumerate(ids):
+            lo, hi = j * block_size, min((j + 1) * block_size, p + n)
+            kpool[bid, :hi - lo] = kc[i][lo:hi]
+            vpool[bid, :hi - lo] = vc[i][lo:hi]
+    lay = PagedLayout.of(kpool, vpool, torch.from_numpy(tables).cuda(), block_size)
+    ctx2 = torch.zeros_like(ctx)
+    kvp.prefill_attn_paged(ctx2, q, gate, lay, torch.from_numpy(owner.astype(np.int32)).cuda(), dlen, window)
+    torch.cuda.synchronize()
+    assert kvp.device_status() == 0
+    assert torch.equal(ctx.view(torch.int16), ctx2.view(torch.int16))
