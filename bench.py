@@ -34,6 +34,7 @@ if ROOT not in sys.path:
 
 NQ, NKV, HD = 16, 4, 128
 LAYERS, BATCH, CTX = 8, 128, 4096
+RAGGED = False  # --ragged: context lengths uniform 1024..4096 instead of 4096 for every sequence
 ROW_BYTES = NKV * HD * 2
 # algorithmic bytes per (layer, sequence): K and V rows read once per GQA group plus the
 # step's q/k/v/gate, norm weights, cos/sin rows, K/V row writes, ctx write, table entries
@@ -153,10 +154,14 @@ def build_workload(torch, seq_len: int, batch: int, layers: int, seed: int):
     w.kw = (1 + 0.02 * torch.randn(layers, HD, device=dev, generator=g)).half()
     cos, sin = rotary_tables(seq_len, 1e6, 0.5)
     w.cos, w.sin = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
-    w.pos = torch.full((batch,), seq_len - 1, dtype=torch.int32, device=dev)
-    w.lens = torch.full((batch,), seq_len, dtype=torch.int32, device=dev)
+    if RAGGED:  # configuration 2's ragged variant: old lengths uniform 1024..4096 (seeded), capacity seq_len each
+        lens_np = np.minimum(np.random.default_rng(seed).integers(1024, 4097, batch) + 1, seq_len).astype(np.int64)
+    else:
+        lens_np = np.full(batch, seq_len, np.int64)
+    w.pos = torch.from_numpy((lens_np - 1).astype(np.int32)).to(dev)
+    w.lens = torch.from_numpy(lens_np.astype(np.int32)).to(dev)
     w.ctx = torch.zeros(layers, batch, NQ, HD, dtype=torch.float16, device=dev)
-    w.seq_lens_host = np.full(batch, seq_len, np.int64)
+    w.seq_lens_host = lens_np
     return w
 
 
@@ -330,9 +335,10 @@ def run_ours(args, torch, rank, world, local_rank):
         "ms_per_step": round(ms / args.steps, 4), "us_per_layer": round(ms / args.steps / LAYERS * 1e3, 2),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
-        "config": {"workload": f"decode_step_{LAYERS}_attention_layers_B{BATCH}_per_gpu_ctx{CTX}",
+        "config": {"workload": f"decode_step_{LAYERS}_attention_layers_B{BATCH}_per_gpu_ctx{CTX}" +
+                               ("_ragged_lengths_uniform_1024_4096" if RAGGED else ""),
                    "layers": LAYERS, "batch_per_gpu": BATCH, "seq_len": CTX, "heads": "16q/4kv x128",
-                   "kv_bytes_per_gpu": LAYERS * BATCH * CTX * 2 * ROW_BYTES,
+                   "kv_bytes_per_gpu": int(LAYERS * w.seq_lens_host.sum() * 2 * ROW_BYTES),
                    "l2": "inputs larger than L2 (1.07 GB of KV per layer, 8 distinct layers)",
                    "launch": launch_mode,
                    "parallelism": f"replicas x{world}, sequences partitioned, no collective"},
@@ -811,10 +817,12 @@ def main():
     ap.add_argument("--layers", type=int, default=LAYERS, help="override for small profiling cases")
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--ctx", type=int, default=CTX)
+    ap.add_argument("--ragged", action="store_true",
+                    help="decode workload with context lengths uniform 1024..4096 (configuration 2's ragged variant)")
     ap.add_argument("--workload", default="decode", choices=["decode", "conv", "prefill", "serving_mix", "sample", "decode_paged"],
                     help="decode = the headline line; conv / prefill / sample = secondary single-GPU lines")
     args = ap.parse_args()
-    globals().update(LAYERS=args.layers, BATCH=args.batch, CTX=args.ctx)
+    globals().update(LAYERS=args.layers, BATCH=args.batch, CTX=args.ctx, RAGGED=args.ragged)
     args.warmup = max(args.warmup, 3)
 
     import torch

@@ -89,7 +89,6 @@ def test_embed_lookup(kv):
 
 def test_embed_lookup_odd_hidden_and_bad_id(kv):
     import torch
-    from oxide_infer_b200 import _lib
     rng = np.random.default_rng(33)
     table = rng.standard_normal((40, 100), dtype=np.float32).astype(np.float16)  # 200-byte rows: scalar path
     ids = np.array([39, 0, 40, 12], np.uint32)  # 40 is beyond the table
@@ -100,5 +99,4 @@ def test_embed_lookup_odd_hidden_and_bad_id(kv):
     got = out.cpu().numpy()
     assert np.array_equal(got[[0, 1, 3]], table[[39, 0, 12]])
     assert not got[2].any()
-    assert kv.device_status() & 8  # OXI_DEV_BAD_TOKEN
-    kv.clear_device_status() if hasattr(kv, "clear_device_status") else None
+    assert kv.device_status() & 8  # OXI_DEV_BAD_TOKEN (reading the status clears it)
