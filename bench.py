@@ -349,7 +349,8 @@ def run_ours(args, torch, rank, world, local_rank):
         "roofline": {"kernel": "decode_attn_kernel<fused append> + decode_merge_kernel", "bound": "hbm", "achieved": round(attn_gbs, 1),
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(attn_gbs / peak, 4),
                      "frac_of_8TBs_nominal": round(attn_gbs / 8000.0, 4), "us_per_launch": round(attn_ms * 1e3, 2),
-                     "traffic": TRAFFIC_PER_LAUNCH},
+                     # the ncu capture was taken at the default sizes only
+                     "traffic": TRAFFIC_PER_LAUNCH if (not RAGGED and (LAYERS, BATCH, CTX) == (8, 128, 4096)) else None},
         "clocks": clocks, "device_status": status, "finite": ctx_ok, "e2e_equals_device_path": same,
         "cuda_graph_replay_ms_per_step": round(ms_graph / args.steps, 4) if ms_graph != float("inf") else None,
         "stream_launch_ms_per_step": round(ms_stream / args.steps, 4),
