@@ -1,7 +1,9 @@
-"""Closed-loop greedy decode: 64 consecutive steps of append + gated GQA attention over
-several layers, with a fixed seeded "glue" (embedding, q/k/v/gate projections, output
-projection, LM head as torch fp16 matmuls) shared by every side, so that any token
-divergence is attributable to the KV-path kernels.  Bar: identical argmax tokens over the
+"""Closed-loop greedy decode: 64 consecutive steps of embedding gather, append + gated GQA
+attention over several layers and vocabulary argmax, with a fixed seeded "glue" (q/k/v/gate
+projections, output projection, LM head as torch fp16 matmuls) shared by every side, so that
+any token divergence is attributable to the path's kernels: each side uses its own embedding
+gather, append, attention and argmax (this library through the C ABI, the reference's kernels,
+the CPU oracle).  Bar: identical argmax tokens over the
 64 steps between this library, the reference's kernels and the CPU oracle.  The top-1 /
 top-2 logit margin of every step is tracked so that a flip could be classified."""
 import numpy as np
@@ -36,8 +38,9 @@ def _initial_caches(lens, seed):
     return [[(mk(int(n)), mk(int(n))) for n in lens] for _ in range(LAYERS)]
 
 
-def _run(layer_fn, w, lens, caches, cos, sin, tok0):
-    """layer_fn(l, q, k, v, gate, pos, seq_lens, k_ptrs, v_ptrs) -> ctx [B,16,128] (may modify q in place)."""
+def _run(layer_fn, w, lens, caches, cos, sin, tok0, embed_fn, argmax_fn):
+    """layer_fn(l, q, k, v, gate, pos, seq_lens, k_ptrs, v_ptrs) -> ctx [B,16,128] (may modify q in place);
+    embed_fn(table, tok int32 [B]) -> x [B,HID] f16; argmax_fn(logits f16 [B,VOCAB]) -> tok int32 [B]."""
     caches = [[(k.clone(), v.clone()) for k, v in layer] for layer in caches]
     kp = [dev_ptr_table([k for k, _ in layer]) for layer in caches]
     vp = [dev_ptr_table([v for _, v in layer]) for layer in caches]
@@ -46,7 +49,7 @@ def _run(layer_fn, w, lens, caches, cos, sin, tok0):
     for step in range(STEPS):
         pos = torch.from_numpy((lens + step).astype(np.int32)).cuda()
         sl = pos + 1
-        x = w["E"][tok]
+        x = embed_fn(w["E"], tok)
         for l in range(LAYERS):
             q = (x @ w[f"q{l}"]).view(NSEQ, NQ, HD).contiguous()
             k = (x @ w[f"k{l}"]).view(NSEQ, NKV, HD).contiguous()
@@ -54,9 +57,9 @@ def _run(layer_fn, w, lens, caches, cos, sin, tok0):
             gate = (x @ w[f"g{l}"]).contiguous()
             ctx = layer_fn(l, q, k, v, gate, pos, sl, kp[l], vp[l], caches[l])
             x = x + ctx.view(NSEQ, NQ * HD) @ w[f"o{l}"]
-        logits = (x @ w["out"]).float()
-        top = logits.topk(2, dim=-1)
-        tok = top.indices[:, 0]
+        logits16 = (x @ w["out"]).contiguous()
+        tok = argmax_fn(logits16)
+        top = logits16.float().topk(2, dim=-1)
         toks.append(tok.cpu().numpy().copy())
         margins.append((top.values[:, 0] - top.values[:, 1]).cpu().numpy())
     return np.stack(toks), np.stack(margins)
@@ -72,7 +75,7 @@ def test_greedy_64_steps_identical_tokens():
     caches = _initial_caches(lens, 6)
     cos_np, sin_np = O.rope_table(int(lens.max()) + STEPS + 2)
     cos, sin = torch.from_numpy(cos_np).cuda(), torch.from_numpy(sin_np).cuda()
-    tok0 = torch.from_numpy(rng.integers(0, VOCAB, NSEQ)).cuda()
+    tok0 = torch.from_numpy(rng.integers(0, VOCAB, NSEQ).astype(np.int32)).cuda()
     kv = KvPath(0, max_batch=NSEQ, max_seq_len=4096, max_prefill_rows=0)
 
     def ours(l, q, k, v, gate, pos, sl, kp, vp, cache):
@@ -80,7 +83,17 @@ def test_greedy_64_steps_identical_tokens():
         kv.append_decode(ctx, q, k, v, gate, w[f"qn{l}"], w[f"kn{l}"], cos, sin, pos, sl, kp, vp)
         return ctx
 
-    t_ours, m_ours = _run(ours, w, lens, caches, cos, sin, tok0)
+    def our_embed(table, tok):
+        x = torch.empty(NSEQ, HID, dtype=torch.float16, device="cuda")
+        kv.embed_lookup(x, table, tok)
+        return x
+
+    def our_argmax(logits):
+        tok = torch.empty(NSEQ, dtype=torch.int32, device="cuda")
+        kv.argmax(tok, logits)
+        return tok
+
+    t_ours, m_ours = _run(ours, w, lens, caches, cos, sin, tok0, our_embed, our_argmax)
     assert kv.device_status() == 0
     assert len({tuple(r) for r in t_ours.T}) > 1          # the loop is not degenerate
 
@@ -93,7 +106,17 @@ def test_greedy_64_steps_identical_tokens():
             ref.decode_attention(ctx, q, gate, kp, vp, sl, NSEQ, 0, int(sl.max().item()))
             return ctx
 
-        t_ref, m_ref = _run(theirs, w, lens, caches, cos, sin, tok0)
+        def ref_embed(table, tok):
+            x = torch.empty(NSEQ, HID, dtype=torch.float16, device="cuda")
+            ref.embed_lookup(x, table, tok, HID, NSEQ)
+            return x
+
+        def ref_argmax(logits):
+            tok = torch.empty(NSEQ, dtype=torch.int32, device="cuda")
+            ref.argmax(tok, logits, VOCAB, NSEQ)
+            return tok
+
+        t_ref, m_ref = _run(theirs, w, lens, caches, cos, sin, tok0, ref_embed, ref_argmax)
         bad = np.argwhere(t_ours != t_ref)
         assert bad.size == 0, f"first divergence at step/seq {bad[0]}, margin {m_ref[tuple(bad[0])]:.4g}"
 
@@ -109,7 +132,15 @@ def test_greedy_64_steps_identical_tokens():
             c[1][int(p[i])].copy_(torch.from_numpy(hv[i][int(p[i])]))
         return torch.from_numpy(ctx).cuda()
 
-    t_or, m_or = _run(oracle, w, lens, caches, cos, sin, tok0)
+    e_np = w["E"].cpu().numpy()
+
+    def or_embed(table, tok):
+        return torch.from_numpy(O.embed_lookup(e_np, tok.cpu().numpy().astype(np.uint32))).cuda()
+
+    def or_argmax(logits):
+        return torch.from_numpy(O.argmax(logits.cpu().numpy()).astype(np.int32)).cuda()
+
+    t_or, m_or = _run(oracle, w, lens, caches, cos, sin, tok0, or_embed, or_argmax)
     bad = np.argwhere(t_ours != t_or)
     assert bad.size == 0, f"first divergence vs oracle at step/seq {bad[0]}, margin {m_or[tuple(bad[0])]:.4g}"
     assert np.median(m_ours) > 0.05  # margins dwarf the 2e-3 attention tolerance
