@@ -54,6 +54,13 @@ def test_create_without_gpu_fails_cleanly(lib):
     # operators reject a null handle before touching CUDA
     assert lib.oxi_append(None, *([None] * 11), 1, 1e-5) == -1
     assert lib.oxi_decode_attn(None, *([None] * 7), 1, 0) == -1
+    assert lib.oxi_argmax(None, None, None, None, 128000, 1) == -1
+    assert lib.oxi_embed_lookup(None, None, None, None, None, 2048, 128000, 1) == -1
+    assert lib.oxi_advance_step(None, None, None, None, 1, 1) == -1
+    assert lib.oxi_append_paged(None, *([None] * 10), 1, 1e-5) == -1
+    assert lib.oxi_decode_attn_paged(None, *([None] * 6), 1, 0) == -1
+    assert lib.oxi_append_decode_paged(None, *([None] * 12), 1, 0, 1e-5) == -1
+    assert lib.oxi_prefill_attn_paged(None, *([None] * 7), 1, 0) == -1
 
 
 def test_package_has_no_fallback(monkeypatch):
