@@ -291,6 +291,7 @@ __device__ __forceinline__ bool pf_next_run(uint32_t& next, uint32_t nrows, cons
     return false;
 }
 
+template <bool kPaged>
 __global__ void __launch_bounds__(pf::THREADS, 1)
 prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__ q,
                     const uint16_t* __restrict__ gate, const uint64_t* __restrict__ k_ptrs,
@@ -300,7 +301,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                     const PagedMap pm, const uint32_t* __restrict__ row_seq) {
     using namespace pf;
     // paged K/V: k_ptrs / v_ptrs are unused, wave row r reads row row_seq[r] of pm.block_tables
-    const bool paged = pm.block_tables != nullptr;
+    constexpr bool paged = kPaged;
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint64_t s_kp[BLK], s_vp[BLK];
     __shared__ uint32_t s_len[BLK];
@@ -753,7 +754,10 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
 }
 
 cudaError_t prefill_attn_init() {
-    return cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(prefill_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)pf::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(prefill_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)pf::SMEM_BYTES);
 }
 
@@ -771,9 +775,13 @@ cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* 
     if (e != cudaSuccess) return e;
     const uint32_t grid = nitems < (uint32_t)num_sms ? nitems : (uint32_t)num_sms;
     // programmatic dependent of the plan kernel: TMEM allocation and barrier set-up overlap it
-    return launch_pdl(prefill_attn_kernel, dim3(grid), dim3(pf::THREADS), pf::SMEM_BYTES, stream,
+    if (pm)
+        return launch_pdl(prefill_attn_kernel<true>, dim3(grid), dim3(pf::THREADS), pf::SMEM_BYTES, stream,
+                          (uint16_t*)ctx_out, (const uint16_t*)q, (const uint16_t*)gate, k_ptrs, v_ptrs, seq_lens, rows,
+                          window, status, (const uint32_t*)order, counter, *pm, row_seq);
+    return launch_pdl(prefill_attn_kernel<false>, dim3(grid), dim3(pf::THREADS), pf::SMEM_BYTES, stream,
                       (uint16_t*)ctx_out, (const uint16_t*)q, (const uint16_t*)gate, k_ptrs, v_ptrs, seq_lens, rows,
-                      window, status, (const uint32_t*)order, counter, pm ? *pm : PagedMap{}, row_seq);
+                      window, status, (const uint32_t*)order, counter, PagedMap{}, row_seq);
 }
 
 }  // namespace oxi
