@@ -66,8 +66,11 @@ const char* oxi_status_string(int32_t status);
 const char* oxi_last_error_string(void);
 
 /* Creates the per-device workspace (split-KV partials, conv staging,
- * host-entry staging).  Replaces the scratch half of BatchEngine::new
- * (batch_engine.rs:320-364).  max_batch <= 1024. */
+ * host-entry staging, argmax candidates).  Replaces the scratch half of
+ * BatchEngine::new (batch_engine.rs:320-364).  max_batch <= 1024.
+ * Calls on one handle use that workspace: they must be ordered on the device
+ * (one stream, or events between streams), as the engine's single decode stream
+ * orders them; independent streams take one handle each. */
 int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_t max_seq_len,
                    uint32_t max_prefill_rows);
 int32_t oxi_destroy(oxi_handle* h);
