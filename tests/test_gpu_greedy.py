@@ -97,6 +97,39 @@ def test_greedy_64_steps_identical_tokens():
     assert kv.device_status() == 0
     assert len({tuple(r) for r in t_ours.T}) > 1          # the loop is not degenerate
 
+    # the same loop over a paged layout: blocks of 16 tokens scattered over one pool per layer
+    from oxide_infer_b200 import PagedLayout
+    bs = 16
+    need = [(int(n) + STEPS + 1 + bs - 1) // bs for n in lens]
+    total = sum(need) + 1
+    perm = np.random.default_rng(7).permutation(total).astype(np.int32)
+    tables = np.zeros((NSEQ, max(need)), np.int32)
+    o = 0
+    for i in range(NSEQ):
+        tables[i, :need[i]] = perm[o:o + need[i]]
+        o += need[i]
+    dt = torch.from_numpy(tables).cuda()
+    pools, lays = [], []
+    for l in range(LAYERS):
+        kpool = torch.zeros(total, bs, NKV, HD, dtype=torch.float16, device="cuda")
+        vpool = torch.zeros_like(kpool)
+        for i, n in enumerate(lens):
+            for jb in range((int(n) + bs - 1) // bs):
+                lo, hi = jb * bs, min((jb + 1) * bs, int(n))
+                kpool[tables[i, jb], :hi - lo] = caches[l][i][0][lo:hi]
+                vpool[tables[i, jb], :hi - lo] = caches[l][i][1][lo:hi]
+        pools.append((kpool, vpool))
+        lays.append(PagedLayout.of(kpool, vpool, dt, bs))
+
+    def ours_paged(l, q, k, v, gate, pos, sl, kp, vp, cache):
+        ctx = torch.empty(NSEQ, NQ, HD, dtype=torch.float16, device="cuda")
+        kv.append_decode_paged(ctx, q, k, v, gate, w[f"qn{l}"], w[f"kn{l}"], cos, sin, sl, lays[l])
+        return ctx
+
+    t_paged, _ = _run(ours_paged, w, lens, caches, cos, sin, tok0, our_embed, our_argmax)
+    assert kv.device_status() == 0
+    assert np.array_equal(t_paged, t_ours)
+
     if refptx.available():
         ref = refptx.RefPtx()
 
