@@ -510,6 +510,32 @@ def run_conv(args, torch):
         ref = refptx.RefPtx()
         ms_ref = _time_loop(torch, lambda: [ref.conv_decode(y[l], ptrs[l], bcx[l], w[l], b) for l in range(nl)],
                             args.steps, args.warmup)
+    # prefill side of the same layers: configuration 4's wave (32 requests x 128 new rows) through one
+    # conv layer - gather of the carried state, conv on every row, commit of each chunk's final state
+    import numpy as np
+    nseq, new = 32, 128
+    rows = nseq * new
+    kvp = KvPath(0, max_batch=b, max_seq_len=4096, max_prefill_rows=rows)
+    carry = rn(nseq, hid, 6)
+    pbcx = rn(rows, 3 * hid)
+    py = torch.zeros(rows, hid, dtype=torch.float16, device="cuda")
+    origin_np = np.repeat(np.arange(nseq) * new, new).astype(np.int32)
+    origin = torch.from_numpy(origin_np).cuda()
+    lpos = torch.from_numpy(np.tile(np.arange(new), nseq).astype(np.int32)).cuda()
+    cptr = torch.tensor([carry[i // new].data_ptr() for i in range(rows)], dtype=torch.int64, device="cuda")
+    ms_pf = _time_loop(torch, lambda: kvp.conv_prefill(py, cptr, origin, lpos, pbcx, w[0]), args.steps, args.warmup)
+    ms_pf_ref = None
+    if refptx.available():
+        pool = torch.zeros(rows, hid, 6, dtype=torch.float16, device="cuda")
+        pool_ptrs = torch.tensor([pool.data_ptr() + r * hid * 12 for r in range(rows)], dtype=torch.int64, device="cuda")
+
+        def ref_pf():  # BE:847-899 on the device; the per-chunk copy-back (server.rs:1192-1224) as 32 device copies
+            ref.conv_state_prefill(pool, cptr, origin, lpos, pbcx, rows)
+            ref.conv_decode(py, pool_ptrs, pbcx, w[0], rows)
+            for i in range(nseq):
+                carry[i].copy_(pool[(i + 1) * new - 1])
+        ms_pf_ref = _time_loop(torch, ref_pf, max(3, args.steps // 2), 3)
+    pf_bytes = nseq * (16384 * new + 49152)
     sampler.stop()
     step_bytes = nl * (b * 65536 + 28672)
     peak, kind = measured_peak_gbs()
@@ -522,6 +548,9 @@ def run_conv(args, torch):
                          "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": round(step_bytes / (ms_graph * 1e-3) / 1e9 / peak, 4),
                          "note": "8.4 MB per launch: launch-latency bound, not bandwidth bound"},
             "reference_kernels_us_per_layer": None if ms_ref is None else round(ms_ref / nl * 1e3, 2),
+            "prefill_wave_one_layer": {"rows": rows, "us": round(ms_pf * 1e3, 2), "gbs": round(pf_bytes / (ms_pf * 1e-3) / 1e9, 1),
+                                       "algorithmic_bytes": pf_bytes,
+                                       "reference_kernels_us": None if ms_pf_ref is None else round(ms_pf_ref * 1e3, 2)},
             "gpu_launches": nl * args.steps, "clocks": clocks, "device_status": kv.device_status()}
 
 
