@@ -11,18 +11,27 @@
 
 namespace oxi {
 
-// grid = B, block = 20 warps: warps 0..15 own the query heads, 16..19 the K
-// heads; threads 0..63 also copy the 1 KB V row with 16-byte vectors.
-__global__ void __launch_bounds__(640)
+// A CTA takes APPEND_ROWS rows; five warps per row: warps 0..3 of a row own four query heads each,
+// the fifth the four K heads, so that the row's cos / sin vectors are fetched once per warp and the
+// loads of four heads are in flight together (a prefill wave appends thousands of rows).  The
+// first 64 threads of a row's warps also copy the 1 KB V row with 16-byte vectors.
+constexpr int APPEND_ROWS = 4;
+__global__ void __launch_bounds__(APPEND_ROWS * 160)
 append_kernel(uint16_t* __restrict__ q_io, const uint16_t* __restrict__ k_in,
               const uint16_t* __restrict__ v_in, const uint16_t* __restrict__ q_norm_w,
               const uint16_t* __restrict__ k_norm_w, const uint16_t* __restrict__ cos_t,
               const uint16_t* __restrict__ sin_t, const uint32_t* __restrict__ pos_ids,
               const uint64_t* __restrict__ k_ptrs, const uint64_t* __restrict__ v_ptrs, float eps,
-              uint32_t* __restrict__ status, const PagedMap pm) {
-    const uint32_t b = blockIdx.x;
+              uint32_t* __restrict__ status, const PagedMap pm, uint32_t batch) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t b = blockIdx.x * APPEND_ROWS + (uint32_t)(warp / 5);
+    const int wq = warp % 5;  // 0..3: query heads 4*wq .. 4*wq+3; 4: the K heads
+    const int tid_row = threadIdx.x - (warp / 5) * 160;
     pdl_launch_dependents();
+    if (b >= batch) {
+        pdl_wait();
+        return;
+    }
     // the step's tables, norm weights and RoPE rows are not written by any kernel: fetch them
     // while the preceding kernel is still draining
     const uint32_t pos = pos_ids[b];
@@ -34,12 +43,12 @@ append_kernel(uint16_t* __restrict__ q_io, const uint16_t* __restrict__ k_in,
         uint32_t id = 0;
         if (pg >= pm.max_blocks) {
             page_ok = false;
-            if (threadIdx.x == 0) atomicOr(status, DEV_BAD_SEQ_LEN);
+            if (tid_row == 0) atomicOr(status, DEV_BAD_SEQ_LEN);
         } else {
             id = pm.block_tables[(size_t)b * pm.max_blocks + pg];
             if (id >= pm.num_blocks) {
                 page_ok = false;
-                if (threadIdx.x == 0) atomicOr(status, DEV_BAD_BLOCK);
+                if (tid_row == 0) atomicOr(status, DEV_BAD_BLOCK);
             }
         }
         const uint64_t off = (uint64_t)id * pm.block_stride + (uint64_t)(pos & ((1u << pm.lbs) - 1u)) * KV_ROW_BYTES -
@@ -51,32 +60,39 @@ append_kernel(uint16_t* __restrict__ q_io, const uint16_t* __restrict__ k_in,
         vp = v_ptrs[b];
     }
     float wv[4], cv[4], sv[4];
-    load4(warp < NQ ? q_norm_w : k_norm_w, lane, wv);
+    load4(wq < 4 ? q_norm_w : k_norm_w, lane, wv);
     load4(cos_t + (size_t)pos * HD, lane, cv);
     load4(sin_t + (size_t)pos * HD, lane, sv);
     pdl_wait();  // q/k/v come from the preceding kernel; the caches may still be read by it
     const bool aligned = page_ok && ((kp | vp) & 15ull) == 0ull;
-    if (!aligned && page_ok && threadIdx.x == 0) atomicOr(status, DEV_MISALIGNED_PTR);
-    uint16_t out[4];
-    if (warp < NQ) {
-        uint16_t* xh = q_io + ((size_t)b * NQ + warp) * HD;
-        head_norm_rope<true, true>(xh, wv, eps, cv, sv, lane, out);
+    if (!aligned && page_ok && tid_row == 0) atomicOr(status, DEV_MISALIGNED_PTR);
+    // four heads: all loads first (q is normalised in place, so later loads must not wait for earlier stores)
+    const uint16_t* xin = wq < 4 ? q_io + ((size_t)b * NQ + wq * 4) * HD : k_in + (size_t)b * NKV * HD;
+    float x[4][4];
+    uint16_t x16[4][4];
 #pragma unroll
-        for (int i = 0; i < 4; i++) xh[lane + 32 * i] = out[i];
-    } else {
-        const int kh = warp - NQ;
-        const uint16_t* xh = k_in + ((size_t)b * NKV + kh) * HD;
-        head_norm_rope<true, true>(xh, wv, eps, cv, sv, lane, out);
-        if (aligned) {
-            uint16_t* dst = reinterpret_cast<uint16_t*>(kp) + (size_t)pos * (NKV * HD) + kh * HD;
+    for (int hh = 0; hh < 4; hh++)
 #pragma unroll
-            for (int i = 0; i < 4; i++) dst[lane + 32 * i] = out[i];
+        for (int i = 0; i < 4; i++) {
+            x16[hh][i] = xin[hh * HD + lane + 32 * i];
+            x[hh][i] = h2f(x16[hh][i]);
+        }
+    uint16_t* xout = wq < 4 ? q_io + ((size_t)b * NQ + wq * 4) * HD
+                            : reinterpret_cast<uint16_t*>(kp) + (size_t)pos * (NKV * HD);
+    const bool store = wq < 4 || aligned;
+#pragma unroll
+    for (int hh = 0; hh < 4; hh++) {
+        uint16_t out[4];
+        head_norm_rope_vals<true, true>(x[hh], x16[hh], wv, eps, cv, sv, out);
+        if (store) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) xout[hh * HD + lane + 32 * i] = out[i];
         }
     }
-    if (threadIdx.x < 64 && aligned) {
+    if (tid_row < 64 && aligned) {
         const uint4* src = reinterpret_cast<const uint4*>(v_in + (size_t)b * (NKV * HD));
         uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(vp) + (size_t)pos * KV_ROW_BYTES);
-        dst[threadIdx.x] = src[threadIdx.x];
+        dst[tid_row] = src[tid_row];
     }
 }
 
@@ -160,20 +176,20 @@ cudaError_t launch_append(cudaStream_t stream, void* q_io, const void* k_in, con
                           const void* q_norm_w, const void* k_norm_w, const void* cos_t,
                           const void* sin_t, const uint32_t* pos_ids, const uint64_t* k_ptrs,
                           const uint64_t* v_ptrs, uint32_t batch, float eps, uint32_t* status) {
-    return launch_pdl(append_kernel, dim3(batch), dim3(640), 0, stream, (uint16_t*)q_io,
-                      (const uint16_t*)k_in, (const uint16_t*)v_in, (const uint16_t*)q_norm_w,
+    return launch_pdl(append_kernel, dim3((batch + APPEND_ROWS - 1) / APPEND_ROWS), dim3(APPEND_ROWS * 160), 0, stream,
+                      (uint16_t*)q_io, (const uint16_t*)k_in, (const uint16_t*)v_in, (const uint16_t*)q_norm_w,
                       (const uint16_t*)k_norm_w, (const uint16_t*)cos_t, (const uint16_t*)sin_t, pos_ids,
-                      k_ptrs, v_ptrs, eps, status, PagedMap{});
+                      k_ptrs, v_ptrs, eps, status, PagedMap{}, batch);
 }
 
 cudaError_t launch_append_paged(cudaStream_t stream, void* q_io, const void* k_in, const void* v_in,
                                 const void* q_norm_w, const void* k_norm_w, const void* cos_t,
                                 const void* sin_t, const uint32_t* pos_ids, const PagedMap& pm,
                                 uint32_t batch, float eps, uint32_t* status) {
-    return launch_pdl(append_kernel, dim3(batch), dim3(640), 0, stream, (uint16_t*)q_io,
-                      (const uint16_t*)k_in, (const uint16_t*)v_in, (const uint16_t*)q_norm_w,
+    return launch_pdl(append_kernel, dim3((batch + APPEND_ROWS - 1) / APPEND_ROWS), dim3(APPEND_ROWS * 160), 0, stream,
+                      (uint16_t*)q_io, (const uint16_t*)k_in, (const uint16_t*)v_in, (const uint16_t*)q_norm_w,
                       (const uint16_t*)k_norm_w, (const uint16_t*)cos_t, (const uint16_t*)sin_t, pos_ids,
-                      (const uint64_t*)nullptr, (const uint64_t*)nullptr, eps, status, pm);
+                      (const uint64_t*)nullptr, (const uint64_t*)nullptr, eps, status, pm, batch);
 }
 
 cudaError_t launch_qk_rmsnorm(cudaStream_t stream, void* x_io, const void* w, float eps,

@@ -10,13 +10,11 @@ namespace oxi {
 // x[i] is dim lane + 32*i; wv / cv / sv are the norm weight, cos and sin of the same dims
 // (already converted to f32 by the caller, which can fetch them early).  Returns the f16 bit
 // patterns in out[i].
+// Core on values already in registers: x[i] is dim lane + 32*i as f32, x16[i] its f16 bit pattern.
 template <bool kNorm, bool kRope>
-__device__ __forceinline__ void head_norm_rope(const uint16_t* __restrict__ x_head, const float (&wv)[4],
-                                               float eps, const float (&cv)[4], const float (&sv)[4],
-                                               int lane, uint16_t (&out)[4]) {
-    float x[4];
-#pragma unroll
-    for (int i = 0; i < 4; i++) x[i] = h2f(x_head[lane + 32 * i]);
+__device__ __forceinline__ void head_norm_rope_vals(const float (&x)[4], const uint16_t (&x16)[4], const float (&wv)[4],
+                                                    float eps, const float (&cv)[4], const float (&sv)[4],
+                                                    uint16_t (&out)[4]) {
     uint16_t y16[4];
     if (kNorm) {
         float sum = 0.0f;
@@ -33,7 +31,7 @@ __device__ __forceinline__ void head_norm_rope(const uint16_t* __restrict__ x_he
         for (int i = 0; i < 4; i++) y16[i] = f2h(__fmul_rn(__fmul_rn(x[i], r), wv[i]));
     } else {
 #pragma unroll
-        for (int i = 0; i < 4; i++) y16[i] = x_head[lane + 32 * i];
+        for (int i = 0; i < 4; i++) y16[i] = x16[i];
     }
     if (kRope) {
         float y[4];
@@ -51,6 +49,20 @@ __device__ __forceinline__ void head_norm_rope(const uint16_t* __restrict__ x_he
 #pragma unroll
         for (int i = 0; i < 4; i++) out[i] = y16[i];
     }
+}
+
+template <bool kNorm, bool kRope>
+__device__ __forceinline__ void head_norm_rope(const uint16_t* __restrict__ x_head, const float (&wv)[4],
+                                               float eps, const float (&cv)[4], const float (&sv)[4],
+                                               int lane, uint16_t (&out)[4]) {
+    float x[4];
+    uint16_t x16[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        x16[i] = x_head[lane + 32 * i];
+        x[i] = h2f(x16[i]);
+    }
+    head_norm_rope_vals<kNorm, kRope>(x, x16, wv, eps, cv, sv, out);
 }
 
 __device__ __forceinline__ void load4(const uint16_t* __restrict__ p, int lane, float (&v)[4]) {
