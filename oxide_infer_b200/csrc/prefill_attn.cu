@@ -231,7 +231,6 @@ prefill_plan_small_kernel(const uint32_t* __restrict__ seq_lens, uint32_t rows, 
     pdl_launch_dependents();
     s_lo[tid] = 0xffffffffu;
     s_hi[tid] = 0u;
-    if (tid == 0) *counter = 0u;
     __syncthreads();
     for (uint32_t r = tid; r < rows; r += 1024) {
         const uint32_t sl = seq_lens[r];
@@ -248,14 +247,19 @@ prefill_plan_small_kernel(const uint32_t* __restrict__ seq_lens, uint32_t rows, 
         s_key[tid] = key;
     }
     __syncthreads();
+    uint32_t rank = 0;
     if (tid < nblocks) {
-        uint32_t rank = 0;
         for (uint32_t j = 0; j < nblocks; j++) {
             const uint32_t kj = s_key[j];
             rank += (kj > key || (kj == key && j < tid)) ? 1u : 0u;
         }
-        order[rank] = tid;
     }
+    // Launched as a programmatic dependent itself: everything above only read seq_lens (a step input)
+    // and overlapped the kernel before (the wave's append, or the previous layer's attention, which may
+    // still be claiming items through `order` and `counter`); the outputs are written after it finished.
+    pdl_wait();
+    if (tid == 0) *counter = 0u;
+    if (tid < nblocks) order[rank] = tid;
 }
 
 // A run of consecutive block rows that share one cache, with the union of their key intervals.
@@ -768,7 +772,7 @@ cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* 
                                 const PagedMap* pm, const uint32_t* row_seq) {
     const uint32_t nitems = ((rows + pf::BLK - 1) / pf::BLK) * NKV;
     if ((rows + pf::BLK - 1) / pf::BLK <= 1024u)
-        prefill_plan_small_kernel<<<1, 1024, 0, stream>>>(seq_lens, rows, window, order, counter);
+        (void)launch_pdl(prefill_plan_small_kernel, dim3(1), dim3(1024), 0, stream, seq_lens, rows, window, order, counter);
     else
         prefill_plan_kernel<<<1, 1024, 0, stream>>>(seq_lens, rows, window, order, counter);
     cudaError_t e = cudaGetLastError();
