@@ -196,3 +196,20 @@ def test_paged_prefill_equals_contiguous_prefill(block_size, window):
     torch.cuda.synchronize()
     assert kvp.device_status() == 0
     assert torch.equal(ctx.view(torch.int16), ctx2.view(torch.int16))
+
+
+@pytest.mark.parametrize("block_size,window", [(32, 77), (16, 1024)])
+def test_paged_fused_step_with_window(kv, block_size, window):
+    """Sliding windows start in the middle of a block and of a 4-token copy group."""
+    import torch
+    case = DecodeCase([5, 76, 77, 78, 300, 1023, 1024, 1025, 3000], seed=49)
+    d = case.device()
+    kv.append_decode(d.ctx, d.q, d.k, d.v, d.gate, d.q_norm_w, d.k_norm_w, d.cos, d.sin, d.pos_ids, d.seq_lens,
+                     d.k_ptrs, d.v_ptrs, window)
+    d2 = case.device()
+    lay, pool, k_view, v_view, tables = _paged(case, d2, block_size, seed=50)
+    kv.append_decode_paged(d2.ctx, d2.q, d2.k, d2.v, d2.gate, d2.q_norm_w, d2.k_norm_w, d2.cos, d2.sin, d2.seq_lens, lay,
+                           window)
+    torch.cuda.synchronize()
+    assert kv.device_status() == 0
+    assert torch.equal(d.ctx.view(torch.int16), d2.ctx.view(torch.int16))

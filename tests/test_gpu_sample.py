@@ -100,3 +100,31 @@ def test_embed_lookup_odd_hidden_and_bad_id(kv):
     assert np.array_equal(got[[0, 1, 3]], table[[39, 0, 12]])
     assert not got[2].any()
     assert kv.device_status() & 8  # OXI_DEV_BAD_TOKEN (reading the status clears it)
+
+
+def test_argmax_unaligned_rows_and_tiny_vocabularies(kv):
+    """Logits that do not start on a 16-byte boundary (scalar path) and vocabularies of 1 ... 9."""
+    import torch
+    rng = np.random.default_rng(34)
+    for batch, vocab in [(3, 1), (2, 2), (4, 7), (2, 9), (5, 1003), (2, 128000)]:
+        host = (np.round(rng.standard_normal(batch * vocab + 1, dtype=np.float32) * 2) / 2).astype(np.float16)
+        flat = torch.from_numpy(host).cuda()
+        logits = flat[1:].view(batch, vocab)  # data pointer is 2 bytes past a 16-byte boundary
+        assert logits.data_ptr() % 16 == 2 and logits.is_contiguous()
+        tok = torch.full((batch,), -1, dtype=torch.int32, device="cuda")
+        kv.argmax(tok, logits)
+        torch.cuda.synchronize()
+        want = O.argmax(host[1:].reshape(batch, vocab))
+        assert np.array_equal(tok.cpu().numpy().astype(np.uint32), want), (batch, vocab)
+
+
+def test_advance_step_moves_only_what_it_is_given(kv):
+    import torch
+    pos = torch.arange(10, dtype=torch.int32, device="cuda")
+    sl = pos + 1
+    kv.advance_step(pos, sl, 3)
+    kv.advance_step(None, sl, 2)
+    kv.advance_step(pos, None, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(pos.cpu(), torch.arange(10, dtype=torch.int32) + 3)
+    assert torch.equal(sl.cpu(), torch.arange(10, dtype=torch.int32) + 6)
