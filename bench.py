@@ -675,6 +675,35 @@ def run_decode_paged(args, torch):
             "gpu_launches": 2 * LAYERS * args.steps, "clocks": clocks, "device_status": kv.device_status()}
 
 
+def _prefill_long_prompt_leg(args, torch, rn):
+    """A small wave of long prompts (2 requests, 128 new rows each, 32,768 keys of prefix): 16 work
+    items for 148 SMs unless the key-range split cuts the blocks into parts."""
+    import numpy as np
+    from oxide_infer_b200 import KvPath
+    nseq, new, prefix = 2, 128, 32768
+    rows = nseq * new
+    kc = [rn(prefix + new, NKV, HD) for _ in range(nseq)]
+    vc = [rn(prefix + new, NKV, HD) for _ in range(nseq)]
+    q, gate = rn(rows, NQ, HD), rn(rows, NQ)
+    owner = np.repeat(np.arange(nseq), new)
+    lens = (prefix + 1 + np.tile(np.arange(new), nseq)).astype(np.int32)
+    kp = torch.tensor([kc[i].data_ptr() for i in owner], dtype=torch.int64, device="cuda")
+    vp = torch.tensor([vc[i].data_ptr() for i in owner], dtype=torch.int64, device="cuda")
+    dlen = torch.from_numpy(lens).cuda()
+    ctx = torch.zeros(rows, NQ, HD, dtype=torch.float16, device="cuda")
+    out = {"rows": rows, "prefix": prefix}
+    for name, part_keys in (("unsplit", 0), ("split", 512)):
+        kv = KvPath(0, max_batch=8, max_seq_len=prefix + new, max_prefill_rows=rows)
+        kv.prefill_split_configure(part_keys, 256 if part_keys else 0)
+        ms = _time_loop(torch, lambda: kv.prefill_attn(ctx, q, gate, kp, vp, dlen, 0), args.steps, args.warmup)
+        out["us_" + name] = round(ms * 1e3, 1)
+        out["status_" + name] = kv.device_status()
+        del kv
+    flops = 4.0 * rows * NQ * HD * (prefix + (new + 1) / 2.0)
+    out["tflops_best"] = round(flops / (min(v for k, v in out.items() if k.startswith("us_")) * 1e-6) / 1e12, 1)
+    return out
+
+
 def run_prefill(args, torch):
     """Config 4: one wave of 128 new tokens for each of 32 sequences, prefixes uniform 0..8192
     (seeded), one attention layer: append of the 4096 wave rows, then causal gated GQA attention."""
@@ -725,6 +754,7 @@ def run_prefill(args, torch):
             ref.attn_online(rctx, q, kp, vp, dlen, rows, 0)
             ref.sigmoid_gate(rctx, gate, rows)
         ms_ref = _time_loop(torch, ref_attn, max(3, args.steps // 4), 3)
+    long_wave = _prefill_long_prompt_leg(args, torch, rn)
     sampler.stop()
     flops = float(sum(8192 * (128 * int(p) + 8256) for p in prefix))
     kv_bytes = float(sum(2048 * (int(p) + new) for p in prefix)) + rows * (4096 + 4096 + 32)
@@ -745,6 +775,7 @@ def run_prefill(args, torch):
             "roofline": {"kernel": "prefill_attn_kernel", "bound": "tensor", "achieved": round(tf, 2), "peak": peak_tf,
                          "peak_kind": kind, "unit": "TFLOP/s", "frac": round(tf / peak_tf, 4)},
             "reference_online_plus_gate_ms": None if ms_ref is None else round(ms_ref, 4),
+            "long_prompt_wave": long_wave,
             "gpu_launches": 3 * args.steps, "clocks": clocks, "device_status": kv.device_status()}
 
 

@@ -30,6 +30,8 @@ SIGNATURES = {
     "oxi_decode_attn_paged": [_vp] * 7 + [_u32, _u32],
     "oxi_append_decode_paged": [_vp] * 13 + [_u32, _u32, _f32],
     "oxi_prefill_attn_paged": [_vp] * 8 + [_u32, _u32],
+    "oxi_prefill_split_configure": [_vp, _u32, _u32],
+    "oxi_prefill_split_slot_bytes": [],
     "oxi_embed_lookup": [_vp] * 5 + [_u32, _u32, _u32],
     "oxi_argmax": [_vp] * 4 + [_u32, _u32],
     "oxi_qk_rmsnorm": [_vp, _vp, _vp, _vp, _f32, _u32, _u32],
@@ -40,7 +42,7 @@ SIGNATURES = {
     "oxi_decode_attn_static": [_vp] * 7 + [_u32, _u32, _u32],
 }
 _RESTYPE = {"oxi_status_string": C.c_char_p, "oxi_last_error_string": C.c_char_p,
-            "oxi_workspace_bytes": C.c_size_t}
+            "oxi_workspace_bytes": C.c_size_t, "oxi_prefill_split_slot_bytes": C.c_uint64}
 
 _lib = None
 

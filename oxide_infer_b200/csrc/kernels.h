@@ -47,6 +47,12 @@ cudaError_t launch_append_decode(cudaStream_t stream, const DecodeWorkspace& ws,
 uint32_t decode_chunk_keys();    // keys per split-KV work item
 uint32_t decode_max_rows();      // rows one launch can take
 
+// Workspace of the key-range split of prefill attention (small waves of long prompts).
+struct PrefillSplitWs {
+    uint32_t* units;     // prefill_split_table_bytes(): unit, slot and block tables
+    float* part;         // max_slots * prefill_split_slot_bytes(): partial O rows, then (max, sum) pairs
+    uint32_t max_slots;  // 0: not reserved
+};
 cudaError_t prefill_attn_init();
 cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* q,
                                 const void* gate, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
@@ -55,7 +61,11 @@ cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* 
                                 uint32_t* order /* [ceil(rows/32)] block order scratch */,
                                 uint32_t* counter /* item claim counter */,
                                 const PagedMap* pm = nullptr /* paged K/V: k_ptrs / v_ptrs unused */,
-                                const uint32_t* row_seq = nullptr /* paged: table row of each wave row */);
+                                const uint32_t* row_seq = nullptr /* paged: table row of each wave row */,
+                                const PrefillSplitWs* split = nullptr /* key-range split of small waves */,
+                                uint32_t part_keys = 0 /* keys per part; 0: no split */);
+size_t prefill_split_slot_bytes();   // partial-result bytes per slot of PrefillSplitWs::part
+size_t prefill_split_table_bytes();  // bytes of PrefillSplitWs::units
 
 cudaError_t launch_conv_decode(cudaStream_t stream, void* y_out, const uint64_t* conv_ptrs,
                                const void* bcx, const void* conv_w, uint32_t batch,

@@ -20,6 +20,8 @@ struct oxi_handle {
     uint32_t* pf_order;   // [ceil(max_prefill_rows/32)] prefill block order
     void* am_cand;        // [max_batch][argmax_max_splits()][256] argmax candidates of the row splits
     uint32_t* am_count;   // [max_batch] arrival counters, zero between launches
+    PrefillSplitWs pf_split;  // reserved by oxi_prefill_split_configure
+    uint32_t pf_part_keys;    // keys per part of a split block; 0: off
     // staging for the host-buffer entry, one layer at a time, double buffered
     void* stg_q[2];       // [max_batch][16][128]
     void* stg_k[2];       // [max_batch][4][128]
@@ -179,6 +181,8 @@ int32_t oxi_destroy(oxi_handle* h) {
     cudaFree(h->pf_order);
     cudaFree(h->am_cand);
     cudaFree(h->am_count);
+    cudaFree(h->pf_split.units);
+    cudaFree(h->pf_split.part);
     for (int i = 0; i < 2; i++) {
         cudaFree(h->stg_q[i]); cudaFree(h->stg_k[i]); cudaFree(h->stg_v[i]);
         cudaFree(h->stg_gate[i]); cudaFree(h->stg_ctx[i]);
@@ -341,6 +345,33 @@ int32_t oxi_append_decode_paged(oxi_handle* h, void* stream, void* ctx_out, void
     return OXI_OK;
 }
 
+uint64_t oxi_prefill_split_slot_bytes(void) { return (uint64_t)prefill_split_slot_bytes(); }
+
+int32_t oxi_prefill_split_configure(oxi_handle* h, uint32_t part_keys, uint32_t slots) {
+    REQ_HANDLE("oxi_prefill_split_configure");
+    if (part_keys != 0u && part_keys < 256u)
+        return fail(OXI_ERR_ARG, "oxi_prefill_split_configure: part_keys must be 0 or at least 256");
+    if (slots > 4096u) return fail(OXI_ERR_ARG, "oxi_prefill_split_configure: at most 4096 slots");
+    OXI_CUDA(cudaSetDevice(h->device), "cudaSetDevice");
+    OXI_CUDA(cudaDeviceSynchronize(), "oxi_prefill_split_configure sync");
+    if (h->pf_split.max_slots) h->bytes -= prefill_split_table_bytes() + (size_t)h->pf_split.max_slots * prefill_split_slot_bytes();
+    cudaFree(h->pf_split.units);
+    cudaFree(h->pf_split.part);
+    h->pf_split = PrefillSplitWs{};
+    h->pf_part_keys = 0;
+    if (part_keys == 0u || slots == 0u) return OXI_OK;
+    if (int32_t rc = dev_alloc(h, (void**)&h->pf_split.units, prefill_split_table_bytes())) return rc;
+    if (int32_t rc = dev_alloc(h, (void**)&h->pf_split.part, (size_t)slots * prefill_split_slot_bytes())) {
+        cudaFree(h->pf_split.units);
+        h->bytes -= prefill_split_table_bytes();
+        h->pf_split = PrefillSplitWs{};
+        return rc;
+    }
+    h->pf_split.max_slots = slots;
+    h->pf_part_keys = part_keys;
+    return OXI_OK;
+}
+
 int32_t oxi_prefill_attn_paged(oxi_handle* h, void* stream, void* ctx_out, const void* q, const void* gate,
                                const oxi_paged_layout* layout, const uint32_t* row_seq, const uint32_t* seq_lens,
                                uint32_t rows, uint32_t window) {
@@ -350,7 +381,8 @@ int32_t oxi_prefill_attn_paged(oxi_handle* h, void* stream, void* ctx_out, const
     PagedMap pm;
     if (int32_t rc = paged_map(layout, "oxi_prefill_attn_paged", &pm)) return rc;
     OXI_CUDA(launch_prefill_attn((cudaStream_t)stream, ctx_out, q, gate, nullptr, nullptr, seq_lens, rows, window,
-                                 h->dws.status, h->num_sms, h->pf_order, h->dws.status + 48, &pm, row_seq),
+                                 h->dws.status, h->num_sms, h->pf_order, h->dws.status + 48, &pm, row_seq,
+                                 &h->pf_split, h->pf_part_keys),
              "prefill_attn_paged launch");
     return OXI_OK;
 }
@@ -362,7 +394,8 @@ int32_t oxi_prefill_attn(oxi_handle* h, void* stream, void* ctx_out, const void*
     REQ_PTR(ctx_out && q && k_ptrs && v_ptrs && seq_lens, "oxi_prefill_attn");
     REQ_BATCH(rows, h->max_prefill_rows, "oxi_prefill_attn");
     OXI_CUDA(launch_prefill_attn((cudaStream_t)stream, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens,
-                                 rows, window, h->dws.status, h->num_sms, h->pf_order, h->dws.status + 48),
+                                 rows, window, h->dws.status, h->num_sms, h->pf_order, h->dws.status + 48, nullptr,
+                                 nullptr, &h->pf_split, h->pf_part_keys),
              "prefill_attn launch");
     return OXI_OK;
 }

@@ -151,6 +151,25 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// Key-range split of long blocks (off when part_tiles == 0), for waves with fewer (block, KV head)
+// items than the GPU has SMs.  The plan kernel picks the smallest part size P >= part_tiles (in
+// 64-key tiles) for which the wave has at most target_items items: a block that scans more than P
+// tiles becomes ns = ceil(tiles / P) <= 32 work units, each with its own partial result
+// (unnormalised O, reference maximum, row sum per accumulator row) in a slot of the partial
+// workspace, merged by prefill_merge_kernel.  One round of near-equal items keeps the partial
+// traffic low.  A wave whose split blocks need more slots than the workspace has runs unsplit.
+constexpr int PF_MAX_SPLIT = 32;
+struct PfSplit {
+    uint32_t* units;      // [units] block | part << 16 | ns << 24, longest unit first
+    uint32_t* slots;      // [units] partial slot of the unit (blocks with ns > 1 only)
+    uint32_t* blkmeta;    // [blocks] ns | first slot << 8
+    float* part_o;        // [slot][kv head][query tile][128 rows][128] f32
+    float* part_ml;       // [slot][kv head][query tile][128 rows][2] f32
+    uint32_t part_tiles;    // smallest part, in tiles; 0: no split
+    uint32_t max_slots;     // slots of part_o / part_ml
+    uint32_t target_items;  // items the wave should not exceed (the SM count)
+};
+
 // Orders the 64-row blocks of the wave by decreasing work (key tiles to scan) with a counting
 // sort, so that the persistent CTAs of the main kernel claim the longest items first, and
 // resets the claim counter.  One CTA.
@@ -223,14 +242,16 @@ prefill_plan_kernel(const uint32_t* __restrict__ seq_lens, uint32_t rows, uint32
 // attention kernel, launched as a programmatic dependent, run its prologue meanwhile.
 __global__ void __launch_bounds__(1024)
 prefill_plan_small_kernel(const uint32_t* __restrict__ seq_lens, uint32_t rows, uint32_t window,
-                          uint32_t* __restrict__ order, uint32_t* __restrict__ counter) {
+                          uint32_t* __restrict__ order, uint32_t* __restrict__ counter, const PfSplit sp) {
     using namespace pf;
-    __shared__ uint32_t s_lo[1024], s_hi[1024], s_key[1024];
+    __shared__ uint32_t s_lo[1024], s_hi[1024], s_key[1024], s_ns[1024];
+    __shared__ uint32_t s_slots, s_part;
     const uint32_t nblocks = (rows + BLK - 1) / BLK;
     const uint32_t tid = threadIdx.x;
     pdl_launch_dependents();
     s_lo[tid] = 0xffffffffu;
     s_hi[tid] = 0u;
+    if (tid == 0) s_slots = 0u;
     __syncthreads();
     for (uint32_t r = tid; r < rows; r += 1024) {
         const uint32_t sl = seq_lens[r];
@@ -240,26 +261,80 @@ prefill_plan_small_kernel(const uint32_t* __restrict__ seq_lens, uint32_t rows, 
         }
     }
     __syncthreads();
-    uint32_t key = 0;  // key tiles to scan (the union of the block's rows, as in the general kernel)
+    // key = key tiles one work unit scans (the union of the block's rows, as in the general kernel)
+    uint32_t key = 0, ns = 1;
     if (tid < nblocks) {
         const uint32_t lo = s_lo[tid], hi = s_hi[tid];
         key = hi > lo ? (hi - lo + TK - 1) / TK : 0u;
-        s_key[tid] = key;
+    }
+    if (sp.part_tiles != 0u) {
+        // Part size: the smallest P >= part_tiles with sum_b ceil(tiles_b / P) * 4 <= target_items and
+        // at most 32 parts per block, by bisection in warp 0 (a split wave has at most 64 blocks).
+        if (tid < 32) {
+            const uint32_t t0 = key;  // tiles of block tid and of block tid + 32
+            uint32_t tb = 0u;
+            if (tid + 32 < nblocks) {
+                const uint32_t lo2 = s_lo[tid + 32], hi2 = s_hi[tid + 32];
+                tb = hi2 > lo2 ? (hi2 - lo2 + TK - 1) / TK : 0u;
+            }
+            uint32_t tmax = max(t0, tb);
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) tmax = max(tmax, __shfl_xor_sync(0xffffffffu, tmax, off));
+            auto items_at = [&](uint32_t P) {
+                uint32_t n = (t0 + P - 1) / P + (tb + P - 1) / P;
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) n += __shfl_xor_sync(0xffffffffu, n, off);
+                return n * NKV;
+            };
+            uint32_t lo = max(sp.part_tiles, (tmax + PF_MAX_SPLIT - 1) / PF_MAX_SPLIT), hi = max(lo, tmax);
+            while (lo < hi) {  // items_at is non-increasing in P; items_at(hi) <= blocks * 4 <= target_items
+                const uint32_t mid = (lo + hi) / 2;
+                if (items_at(mid) <= sp.target_items) hi = mid; else lo = mid + 1;
+            }
+            if (tid == 0) s_part = max(lo, 1u);
+        }
+        __syncthreads();
+        if (tid < nblocks && key > s_part) {
+            ns = (key + s_part - 1) / s_part;
+            atomicAdd(&s_slots, ns);
+        }
     }
     __syncthreads();
-    uint32_t rank = 0;
+    if (tid < nblocks) {
+        if (s_slots > sp.max_slots) ns = 1;  // not enough partial slots: the wave runs unsplit
+        key = (key + ns - 1) / ns;
+        s_key[tid] = key;
+        s_ns[tid] = ns;
+    }
+    __syncthreads();
+    uint32_t rank = 0, slot = 0, total = 0;
     if (tid < nblocks) {
         for (uint32_t j = 0; j < nblocks; j++) {
-            const uint32_t kj = s_key[j];
-            rank += (kj > key || (kj == key && j < tid)) ? 1u : 0u;
+            const uint32_t kj = s_key[j], nj = s_ns[j];
+            rank += (kj > key || (kj == key && j < tid)) ? nj : 0u;
+            slot += (j < tid && nj > 1u) ? nj : 0u;
+            total += nj;
         }
     }
     // Launched as a programmatic dependent itself: everything above only read seq_lens (a step input)
     // and overlapped the kernel before (the wave's append, or the previous layer's attention, which may
     // still be claiming items through `order` and `counter`); the outputs are written after it finished.
     pdl_wait();
-    if (tid == 0) *counter = 0u;
-    if (tid < nblocks) order[rank] = tid;
+    if (tid == 0) {
+        counter[0] = 0u;
+        counter[1] = total;  // work units (x 4 KV heads = items)
+    }
+    if (tid < nblocks) {
+        if (sp.part_tiles == 0u) {
+            order[rank] = tid;
+        } else {
+            for (uint32_t i = 0; i < ns; i++) {
+                sp.units[rank + i] = tid | (i << 16) | (ns << 24);
+                sp.slots[rank + i] = slot + i;
+            }
+            sp.blkmeta[tid] = ns | (slot << 8);
+        }
+    }
 }
 
 // A run of consecutive block rows that share one cache, with the union of their key intervals.
@@ -295,14 +370,14 @@ __device__ __forceinline__ bool pf_next_run(uint32_t& next, uint32_t nrows, cons
     return false;
 }
 
-template <bool kPaged>
+template <bool kPaged, bool kSplit>
 __global__ void __launch_bounds__(pf::THREADS, 1)
 prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__ q,
                     const uint16_t* __restrict__ gate, const uint64_t* __restrict__ k_ptrs,
                     const uint64_t* __restrict__ v_ptrs, const uint32_t* __restrict__ seq_lens,
                     uint32_t rows, uint32_t window, uint32_t* __restrict__ status,
                     const uint32_t* __restrict__ order, uint32_t* __restrict__ counter,
-                    const PagedMap pm, const uint32_t* __restrict__ row_seq) {
+                    const PagedMap pm, const uint32_t* __restrict__ row_seq, const PfSplit sp) {
     using namespace pf;
     // paged K/V: k_ptrs / v_ptrs are unused, wave row r reads row row_seq[r] of pm.block_tables
     constexpr bool paged = kPaged;
@@ -322,7 +397,6 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     const int tid = threadIdx.x, lane = tid & 31;
     // warp index the compiler can prove uniform: role branches and MMA issue stay in uniform control flow
     const int warp_u = __shfl_sync(0xffffffffu, tid >> 5, 0);
-    const uint32_t nitems = ((rows + BLK - 1) / BLK) * NKV;
 
     // ---- once per CTA: TMEM allocation (all 512 columns; one CTA per SM), barriers
     if (warp_u == W_MMA0) {
@@ -353,6 +427,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     tc_fence_after();
     const uint32_t tmem = __shfl_sync(0xffffffffu, s_tmem, 0);
     pdl_wait();  // the plan kernel's order and counter (and everything before it in the stream) are visible from here on
+    const uint32_t nitems = (kSplit ? counter[1] : (rows + BLK - 1) / BLK) * NKV;
 
     // Every role counts the same sequence of K/V tiles: tile gk uses ring stage gk % NS in its
     // (gk / NS)-th use and phase gk & 1 of the per-tile barriers.
@@ -368,7 +443,10 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     __syncthreads();
     const uint32_t item = s_item;
     if (item >= nitems) break;
-    const uint32_t row0 = order[item >> 2] * BLK;
+    // work unit: a 64-row block, or (with a key-range split) one of its ns parts
+    const uint32_t ud = kSplit ? sp.units[item >> 2] : order[item >> 2];
+    const uint32_t row0 = (kSplit ? (ud & 0xffffu) : ud) * BLK;
+    const uint32_t part = kSplit ? (ud >> 16) & 0xffu : 0u, nparts = kSplit ? ud >> 24 : 1u;
     const int kvh = item & 3u;
     const uint32_t nrows = min((uint32_t)BLK, rows - row0);
 
@@ -402,6 +480,15 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         s_len[tid] = sl;  // 0 marks a row that is skipped
     }
     __syncthreads();
+    // with a key-range split this unit takes tiles [t_lo, t_hi) of the block's tile sequence
+    uint32_t t_lo = 0, t_hi = 0xffffffffu;
+    if (kSplit) {
+        uint32_t gt = 0, next = 0;
+        PfRun run;
+        while (pf_next_run(next, nrows, s_kp, s_vp, s_len, window, run)) gt += (run.hi - run.lo + TK - 1) / TK;
+        t_lo = (uint32_t)((uint64_t)gt * part / nparts);
+        t_hi = (uint32_t)((uint64_t)gt * (part + 1u) / nparts);
+    }
 
     if (warp_u < 8) {
         // ================= softmax warps: query tile j, accumulator row (head hw, token lane) =================
@@ -449,6 +536,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
 
         float m_ref = -1.0e30f, l_run = 0.0f;  // maximum used for the exponentials (may be stale), row sum
         bool o_valid = false;                  // O in TMEM holds a sum (false until the item's first PV)
+        uint32_t tflat = 0;                    // tiles of the block's runs before this one (key-range split)
         uint32_t next = 0;
         PfRun run;
         while (pf_next_run(next, nrows, s_kp, s_vp, s_len, window, run)) {
@@ -468,7 +556,13 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                 }
             }
             const uint32_t ntiles = (run.hi - run.lo + TK - 1) / TK;
-            for (uint32_t tile = 0; tile < ntiles; tile++) {
+            uint32_t tile0 = 0, tile1 = ntiles;  // this unit's tiles of the run
+            if (kSplit) {
+                tile0 = min(ntiles, max(t_lo, tflat) - tflat);
+                tile1 = min(ntiles, max(t_hi, tflat) - tflat);
+                tflat += ntiles;
+            }
+            for (uint32_t tile = tile0; tile < tile1; tile++) {
                 ok &= mbar_wait_bounded(&bar_sfull[j], gk & 1u, &s_abort);  // S_j(tile) complete
                 __syncwarp();
                 tc_fence_after();
@@ -538,6 +632,31 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
             }
         }
 
+        // ---- a part of a split block leaves its unnormalised O row, reference maximum and row sum for
+        // prefill_merge_kernel (a part without tiles leaves an empty sum)
+        if (kSplit && nparts > 1u) {
+            const uint32_t row = (uint32_t)(hw * 32 + lane);
+            const size_t pidx = ((size_t)sp.slots[item >> 2] * NKV + kvh) * 2 + j;
+            const bool live = tok < nrows && s_len[tok] != 0;
+            if (o_valid) {
+                ok &= mbar_wait_bounded(&bar_ofull[j], n_o & 1u, &s_abort);
+                ++n_o;
+                __syncwarp();
+                tc_fence_after();
+                uint4* po = reinterpret_cast<uint4*>(sp.part_o + (pidx * M + row) * HD);
+#pragma unroll
+                for (int ch = 0; ch < 4; ch++) {
+                    uint32_t orow[32];
+                    tmem_ld32(o_t + ch * 32, orow);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int v4 = 0; v4 < 8; v4++)
+                        po[ch * 8 + v4] = make_uint4(orow[4 * v4], orow[4 * v4 + 1], orow[4 * v4 + 2], orow[4 * v4 + 3]);
+                }
+            }
+            *reinterpret_cast<float2*>(sp.part_ml + (pidx * M + row) * 2) =
+                make_float2(m_ref, (o_valid && live && ok) ? l_run : 0.0f);
+        } else
         // ---- epilogue: O row from TMEM, 1/sum, f16, gate on the f16 value (as online kernel + gate kernel)
         if (o_valid) {
             ok &= mbar_wait_bounded(&bar_ofull[j], n_o & 1u, &s_abort);
@@ -648,14 +767,22 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
             ++n_burst;
         };
         uint32_t nt = 0;  // tiles of this item whose score MMAs have been issued
-        uint32_t next = 0;
-        PfRun run;
-        while (pf_next_run(next, nrows, s_kp, s_vp, s_len, window, run)) {
-            const uint32_t ntiles = (run.hi - run.lo + TK - 1) / TK;
-            for (uint32_t tile = 0; tile < ntiles; tile++) {
+        if (kSplit) {
+            for (uint32_t t = t_lo; t < t_hi; t++) {
                 step(nt, nt >= 2, true, false);
                 ++nt;
                 ++gk;
+            }
+        } else {
+            uint32_t next = 0;
+            PfRun run;
+            while (pf_next_run(next, nrows, s_kp, s_vp, s_len, window, run)) {
+                const uint32_t ntiles = (run.hi - run.lo + TK - 1) / TK;
+                for (uint32_t tile = 0; tile < ntiles; tile++) {
+                    step(nt, nt >= 2, true, false);
+                    ++nt;
+                    ++gk;
+                }
             }
         }
         if (nt > 0) {
@@ -673,6 +800,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         // row r, chunk position (c%8) ^ (r%8)
         const uint32_t c = lane & 15u, r0 = lane >> 4;
         uint32_t pending = 0;  // tiles requested whose full barrier has not been signalled yet
+        uint32_t tflat = 0;    // tiles of the block's runs before this one (key-range split)
         uint32_t next = 0;
         PfRun run;
         while (pf_next_run(next, nrows, s_kp, s_vp, s_len, window, run)) {
@@ -695,8 +823,14 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                 }
                 return id;
             };
-            uint32_t pg_next = paged ? fetch_pages(run.lo) : 0u;
-            for (uint32_t tile = 0; tile < ntiles; tile++) {
+            uint32_t tile0 = 0, tile1 = ntiles;  // this unit's tiles of the run
+            if (kSplit) {
+                tile0 = min(ntiles, max(t_lo, tflat) - tflat);
+                tile1 = min(ntiles, max(t_hi, tflat) - tflat);
+                tflat += ntiles;
+            }
+            uint32_t pg_next = (paged && tile0 < tile1) ? fetch_pages(run.lo + tile0 * TK) : 0u;
+            for (uint32_t tile = tile0; tile < tile1; tile++) {
                 const uint32_t st = gk % NS;
                 // the MMAs that read this stage's previous tile have completed (first use: passes at once)
                 ok &= mbar_wait_bounded(&empty[st], ((gk / NS) & 1u) ^ 1u, &s_abort);
@@ -705,7 +839,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                 const char* src = base + (size_t)(kbeg + r0) * KV_ROW_BYTES + c * 16;
                 if (paged) {
                     const uint32_t pg_cur = pg_next;
-                    if (tile + 1 < ntiles) pg_next = fetch_pages(kbeg + TK);
+                    if (tile + 1 < tile1) pg_next = fetch_pages(kbeg + TK);
                     const uint32_t p0 = kbeg >> pm.lbs, mask = (1u << pm.lbs) - 1u;
 #pragma unroll 8
                     for (int k = 0; k < TK / 2; k++) {
@@ -757,35 +891,145 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     }
 }
 
+// Combines the partial results of split blocks: one warp per accumulator row (grid = blocks x
+// 4 KV heads x 2 query tiles x 32 groups of 4 rows), a lane holds 4 of the 128 dimensions.  Part s
+// of a row holds O_s = sum_k 2^(x_k - m_s) v_k and l_s = sum_k 2^(x_k - m_s); the row's result is
+// sum_s 2^(m_s - m) O_s / sum_s 2^(m_s - m) l_s with m = max_s m_s, rounded to f16 and gated like
+// the unsplit epilogue.
+__global__ void __launch_bounds__(128)
+prefill_merge_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__ gate,
+                     uint32_t rows, const PfSplit sp) {
+    using namespace pf;
+    const uint32_t tile = blockIdx.x >> 5;  // (block, KV head, query tile)
+    const uint32_t blk = tile >> 3, kvh = (tile >> 1) & 3u, j = tile & 1u;
+    const uint32_t meta = sp.blkmeta[blk];
+    const uint32_t ns = meta & 0xffu, slot0 = meta >> 8;
+    if (ns <= 1u) return;  // written by the attention kernel
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t row = (blockIdx.x & 31u) * 4 + (threadIdx.x >> 5);
+    const uint32_t row0 = blk * BLK, nrows = min((uint32_t)BLK, rows - row0);
+    const uint32_t tok = j * TOK + (row & 31u), head = kvh * 4 + (row >> 5);
+    if (tok >= nrows) return;
+    // lane s holds (m, l) of part s; a part without keys for this row has l = 0
+    float m_s = -1.0e30f, l_s = 0.0f;
+    if (lane < ns) {
+        const size_t pidx = ((size_t)(slot0 + lane) * NKV + kvh) * 2 + j;
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(sp.part_ml + (pidx * M + row) * 2));
+        if (ml.y > 0.0f) {
+            m_s = ml.x;
+            l_s = ml.y;
+        }
+    }
+    float m = m_s;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    const float w_s = l_s > 0.0f ? ex2_approx_ftz(m_s - m) : 0.0f;
+    float lsum = w_s * l_s;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, off);
+    if (!(lsum > 0.0f)) return;  // row without keys: not written, as in the unsplit kernel
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (uint32_t s0 = 0; s0 < ns; s0 += 8) {  // eight loads in flight
+        float4 o[8];
+        float w[8];
+#pragma unroll
+        for (uint32_t u = 0; u < 8; u++) {
+            const uint32_t s = s0 + u;
+            w[u] = __shfl_sync(0xffffffffu, w_s, s & 31u);
+            if (s >= ns) w[u] = 0.0f;
+            const size_t pidx = ((size_t)(slot0 + s) * NKV + kvh) * 2 + j;
+            // a part with weight 0 may never have been written
+            o[u] = w[u] != 0.0f ? __ldcg(reinterpret_cast<const float4*>(sp.part_o + (pidx * M + row) * HD) + lane)
+                                : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+#pragma unroll
+        for (uint32_t u = 0; u < 8; u++) {
+            acc.x = fmaf(w[u], o[u].x, acc.x);
+            acc.y = fmaf(w[u], o[u].y, acc.y);
+            acc.z = fmaf(w[u], o[u].z, acc.z);
+            acc.w = fmaf(w[u], o[u].w, acc.w);
+        }
+    }
+    const float inv = rcp_approx_ftz(lsum);
+    const size_t rh = (size_t)(row0 + tok) * NQ + head;
+    uint16_t h[4] = {f2h(__fmul_rn(acc.x, inv)), f2h(__fmul_rn(acc.y, inv)), f2h(__fmul_rn(acc.z, inv)),
+                     f2h(__fmul_rn(acc.w, inv))};
+    if (gate) {
+        const float sig = sigmoid_ref(h2f(gate[rh]));
+#pragma unroll
+        for (int e = 0; e < 4; e++) h[e] = f2h(__fmul_rn(h2f(h[e]), sig));
+    }
+    reinterpret_cast<uint2*>(ctx_out + rh * HD)[lane] =
+        make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16), (uint32_t)h[2] | ((uint32_t)h[3] << 16));
+}
+
+size_t prefill_split_table_bytes() { return (size_t)3 * 1024 * PF_MAX_SPLIT * sizeof(uint32_t); }
+size_t prefill_split_slot_bytes() { return (size_t)NKV * 2 * pf::M * (HD + 2) * sizeof(float); }
+
 cudaError_t prefill_attn_init() {
-    cudaError_t e = cudaFuncSetAttribute(prefill_attn_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)pf::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    return cudaFuncSetAttribute(prefill_attn_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                (int)pf::SMEM_BYTES);
+    cudaError_t e = cudaSuccess;
+    const int smem = (int)pf::SMEM_BYTES;
+    if ((e = cudaFuncSetAttribute(prefill_attn_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return e;
+    if ((e = cudaFuncSetAttribute(prefill_attn_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return e;
+    if ((e = cudaFuncSetAttribute(prefill_attn_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return e;
+    return cudaFuncSetAttribute(prefill_attn_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+}
+
+template <bool kPaged, bool kSplit>
+static cudaError_t launch_pf(cudaStream_t stream, uint32_t grid, void* ctx_out, const void* q, const void* gate,
+                             const uint64_t* k_ptrs, const uint64_t* v_ptrs, const uint32_t* seq_lens, uint32_t rows,
+                             uint32_t window, uint32_t* status, uint32_t* order, uint32_t* counter, const PagedMap& pm,
+                             const uint32_t* row_seq, const PfSplit& sp) {
+    // programmatic dependent of the plan kernel: TMEM allocation and barrier set-up overlap it
+    return launch_pdl(prefill_attn_kernel<kPaged, kSplit>, dim3(grid), dim3(pf::THREADS), pf::SMEM_BYTES, stream,
+                      (uint16_t*)ctx_out, (const uint16_t*)q, (const uint16_t*)gate, k_ptrs, v_ptrs, seq_lens, rows,
+                      window, status, (const uint32_t*)order, counter, pm, row_seq, sp);
 }
 
 cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* q,
                                 const void* gate, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
                                 const uint32_t* seq_lens, uint32_t rows, uint32_t window,
                                 uint32_t* status, int num_sms, uint32_t* order, uint32_t* counter,
-                                const PagedMap* pm, const uint32_t* row_seq) {
-    const uint32_t nitems = ((rows + pf::BLK - 1) / pf::BLK) * NKV;
-    if ((rows + pf::BLK - 1) / pf::BLK <= 1024u)
-        (void)launch_pdl(prefill_plan_small_kernel, dim3(1), dim3(1024), 0, stream, seq_lens, rows, window, order, counter);
+                                const PagedMap* pm, const uint32_t* row_seq, const PrefillSplitWs* ws,
+                                uint32_t part_keys) {
+    const uint32_t nblocks = (rows + pf::BLK - 1) / pf::BLK;
+    // the split is for waves that leave SMs idle; larger waves balance by claiming longest first
+    const bool split = ws && ws->max_slots != 0u && part_keys != 0u && nblocks * NKV < (uint32_t)num_sms;
+    PfSplit sp{};
+    if (split) {
+        sp.units = ws->units;
+        sp.slots = ws->units + 1024 * PF_MAX_SPLIT;
+        sp.blkmeta = ws->units + 2 * 1024 * PF_MAX_SPLIT;
+        sp.part_o = ws->part;
+        sp.part_ml = ws->part + (size_t)ws->max_slots * NKV * 2 * pf::M * HD;
+        sp.part_tiles = (part_keys + pf::TK - 1) / pf::TK;
+        sp.max_slots = ws->max_slots;
+        sp.target_items = (uint32_t)num_sms;
+    }
+    if (nblocks <= 1024u)
+        (void)launch_pdl(prefill_plan_small_kernel, dim3(1), dim3(1024), 0, stream, seq_lens, rows, window, order, counter, sp);
     else
         prefill_plan_kernel<<<1, 1024, 0, stream>>>(seq_lens, rows, window, order, counter);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
-    const uint32_t grid = nitems < (uint32_t)num_sms ? nitems : (uint32_t)num_sms;
-    // programmatic dependent of the plan kernel: TMEM allocation and barrier set-up overlap it
-    if (pm)
-        return launch_pdl(prefill_attn_kernel<true>, dim3(grid), dim3(pf::THREADS), pf::SMEM_BYTES, stream,
-                          (uint16_t*)ctx_out, (const uint16_t*)q, (const uint16_t*)gate, k_ptrs, v_ptrs, seq_lens, rows,
-                          window, status, (const uint32_t*)order, counter, *pm, row_seq);
-    return launch_pdl(prefill_attn_kernel<false>, dim3(grid), dim3(pf::THREADS), pf::SMEM_BYTES, stream,
-                      (uint16_t*)ctx_out, (const uint16_t*)q, (const uint16_t*)gate, k_ptrs, v_ptrs, seq_lens, rows,
-                      window, status, (const uint32_t*)order, counter, PagedMap{}, row_seq);
+    const PagedMap map = pm ? *pm : PagedMap{};
+    if (!split) {
+        const uint32_t nitems = nblocks * NKV;
+        const uint32_t grid = nitems < (uint32_t)num_sms ? nitems : (uint32_t)num_sms;
+        return pm ? launch_pf<true, false>(stream, grid, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, rows, window, status,
+                                           order, counter, map, row_seq, sp)
+                  : launch_pf<false, false>(stream, grid, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, rows, window, status,
+                                            order, counter, map, row_seq, sp);
+    }
+    // the unit count is only known on the device: one CTA per SM, those without a unit leave at once
+    e = pm ? launch_pf<true, true>(stream, (uint32_t)num_sms, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, rows, window,
+                                   status, order, counter, map, row_seq, sp)
+           : launch_pf<false, true>(stream, (uint32_t)num_sms, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, rows, window,
+                                    status, order, counter, map, row_seq, sp);
+    if (e != cudaSuccess) return e;
+    // a plain launch: as a programmatic dependent it measured no faster
+    prefill_merge_kernel<<<nblocks * 8 * 32, 128, 0, stream>>>((uint16_t*)ctx_out, (const uint16_t*)gate, rows, sp);
+    return cudaGetLastError();
 }
 
 }  // namespace oxi

@@ -157,6 +157,16 @@ class KvPath:
                                          _p(k_ptrs), _p(v_ptrs), _p(seq_lens), n, window),
                "oxi_prefill_attn")
 
+    def prefill_split_configure(self, min_part_keys: int, slots: int):
+        """Key-range split of small prefill waves: waves with fewer (block, KV head) items than SMs cut
+        their long blocks into equal key ranges (enough to fill the SMs once, at most 32 per block, none
+        shorter than min_part_keys), with `slots` partial results reserved on the handle
+        (prefill_split_slot_bytes() each).  min_part_keys = 0 or slots = 0 turns it off.  Synchronises."""
+        _check(self.lib.oxi_prefill_split_configure(self.h, min_part_keys, slots), "oxi_prefill_split_configure")
+
+    def prefill_split_slot_bytes(self) -> int:
+        return int(self.lib.oxi_prefill_split_slot_bytes())
+
     def conv_decode(self, y_out, conv_ptrs, bcx, conv_w, batch: int | None = None):
         b = bcx.shape[0] if batch is None else batch
         _check(self.lib.oxi_conv_decode(self.h, _stream(), _p(y_out), _p(conv_ptrs), _p(bcx),
