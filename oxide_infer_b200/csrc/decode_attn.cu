@@ -117,6 +117,8 @@ struct DecodeParams {
     float* partial_stats;
     uint32_t* work_counter;
     uint32_t* status;
+    float* merge_acc;      // [batch][16][ceil(max_chunks / 16)][132]: slice sums of rows with more than 16 key ranges
+    uint32_t* merge_count; // [batch][4] arrival counters of those rows, zero between launches
     uint32_t batch;
     uint32_t window;
     uint32_t max_chunks;
@@ -586,10 +588,22 @@ decode_attn_kernel(const DecodeParams p) {
 
 // Merges the partials of every row that was covered by more than one item, and
 // resets the work counter for the next launch.
-// grid = B*4 CTAs of 4 warps: warp = one query head of one row; lane owns dims
+// grid = (B*4, E) CTAs of 4 warps: warp = one query head of one row; lane owns dims
 // 4*lane .. 4*lane+3.  Loads are issued in blocks of 16 key ranges, all
 // independent of the arithmetic, which runs in key-range order, so the result
-// does not depend on scheduling and the kernel costs two memory round trips.
+// does not depend on scheduling.  A row of up to 16 key ranges (4096 keys) is one
+// such block: two memory round trips, done by the CTA with blockIdx.y = 0.
+// A longer row is cut into slices of 16 key ranges; slice s is summed (weights
+// relative to the row's maximum) by CTA y = s mod E into a scratch slot, and the
+// CTA of the row that arrives last adds the slices in slice order.  The slices
+// and the order of every sum depend on the row's own length only, never on E or
+// on the other rows of the batch; E only spreads a long row's loads over more
+// CTAs (a 32,768-key row: 4 round trips instead of 9).
+constexpr int MERGE_BLK = 16;            // key ranges per block of loads = per slice
+constexpr int MERGE_SLOT = HD + 4;       // floats per slice slot: 128 sums, the weight sum, padding to 16 bytes
+constexpr int MERGE_MAX_Y = 8;
+
+template <bool kSliced>  // false: the workspace holds rows of at most 16 key ranges (no slice scratch)
 __global__ void __launch_bounds__(128)
 decode_merge_kernel(const DecodeParams p) {
     pdl_launch_dependents();
@@ -601,20 +615,32 @@ decode_merge_kernel(const DecodeParams p) {
     const uint64_t kvp = p.paged.block_tables ? 0ull : (p.k_ptrs[b] | p.v_ptrs[b]);
     const float gate_f = p.gate ? h2f(p.gate[(size_t)b * NQ + hd]) : 0.0f;
     pdl_wait();
-    if (blockIdx.x == 0 && threadIdx.x == 0) *p.work_counter = 0u;
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) *p.work_counter = 0u;
     if (slen == 0u || slen > p.max_seq_len || (kvp & 15ull) != 0ull) return;
     if (p.paged.block_tables && ((slen - 1u) >> p.paged.lbs) >= p.paged.max_blocks) return;
     const uint32_t nchunks = row_chunks(slen, p.window);
     if (nchunks <= 1) return;
+    const uint32_t nslices = kSliced ? (nchunks + MERGE_BLK - 1) / MERGE_BLK : 1u;
+    // CTAs that work on this row and head group: several only where that saves memory round trips
+    // (one CTA: 1 + nslices, several: 3 + nslices / ny); the sums are the same either way
+    const uint32_t ny = (kSliced && nslices >= 4u) ? min(gridDim.y, nslices) : 1u;
+    if (blockIdx.y >= ny) return;
     const float* stats = p.partial_stats + (((size_t)b * p.max_chunks) * NQ + hd) * 2;
     const float* accs = p.partial_acc + (((size_t)b * p.max_chunks) * NQ + hd) * HD;
     float m = -1.0e30f;
     for (uint32_t cc = lane; cc < nchunks; cc += 32) m = fmaxf(m, __ldcg(stats + (size_t)cc * NQ * 2));
-    constexpr int BLK = 16;
+    constexpr int BLK = MERGE_BLK;
     float l = 0.0f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     bool have_max = false;
-    for (uint32_t c0 = 0; c0 < nchunks; c0 += BLK) {
+    const uint32_t slots_per_head = (p.max_chunks + MERGE_BLK - 1) / MERGE_BLK;
+    float* slot0 = kSliced ? p.merge_acc + ((size_t)b * NQ + hd) * slots_per_head * MERGE_SLOT : nullptr;
+    float l_tot = 0.0f;  // ny == 1: the slice sums are added here, in slice order, as the last CTA would
+    float4 acc_tot = make_float4(0.f, 0.f, 0.f, 0.f);
+    // without slices: one pass over all key ranges, block after block, sums carried across the blocks
+    const uint32_t nloop = kSliced ? nslices : (nchunks + BLK - 1) / BLK;
+    for (uint32_t sl = blockIdx.y; sl < nloop; sl += ny) {
+        const uint32_t c0 = sl * BLK;
         float2 st[BLK];
         float4 pv[BLK];
 #pragma unroll
@@ -628,6 +654,10 @@ decode_merge_kernel(const DecodeParams p) {
             for (int off = 16; off >= 1; off >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
             have_max = true;
         }
+        if (kSliced) {
+            l = 0.0f;
+            acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
 #pragma unroll
         for (int i = 0; i < BLK; i++) {
             const float wgt = (c0 + i < nchunks) ? ex2_approx_ftz(st[i].x - m) : 0.0f;
@@ -636,6 +666,58 @@ decode_merge_kernel(const DecodeParams p) {
             acc.y = fmaf(wgt, pv[i].y, acc.y);
             acc.z = fmaf(wgt, pv[i].z, acc.z);
             acc.w = fmaf(wgt, pv[i].w, acc.w);
+        }
+        if (ny > 1u) {
+            float* slot = slot0 + (size_t)sl * MERGE_SLOT;
+            __stcg(reinterpret_cast<float4*>(slot) + lane, acc);
+            if (lane == 0) __stcg(slot + HD, l);
+        } else if (nslices > 1u) {
+            l_tot += l;
+            acc_tot.x += acc.x;
+            acc_tot.y += acc.y;
+            acc_tot.z += acc.z;
+            acc_tot.w += acc.w;
+        }
+    }
+    if (ny == 1u && nslices > 1u) {
+        l = l_tot;
+        acc = acc_tot;
+    }
+    if (ny > 1u) {
+        // the CTA of this (row, head group) that arrives last adds the slices in slice order
+        __shared__ uint32_t s_last;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t* cnt = p.merge_count + blockIdx.x;
+            const bool last = atomicAdd(cnt, 1u) == ny - 1u;
+            if (last) *cnt = 0u;  // ready for the next launch
+            s_last = last ? 1u : 0u;
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        l = 0.0f;
+        acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t s0 = 0; s0 < nslices; s0 += 8) {
+            float4 sv[8];
+            float sw[8];
+#pragma unroll
+            for (uint32_t u = 0; u < 8; u++) {
+                const float* slot = slot0 + (size_t)min(s0 + u, nslices - 1u) * MERGE_SLOT;
+                sv[u] = __ldcg(reinterpret_cast<const float4*>(slot) + lane);
+                sw[u] = __ldcg(slot + HD);
+            }
+#pragma unroll
+            for (uint32_t u = 0; u < 8; u++) {
+                if (s0 + u < nslices) {
+                    l += sw[u];
+                    acc.x += sv[u].x;
+                    acc.y += sv[u].y;
+                    acc.z += sv[u].z;
+                    acc.w += sv[u].w;
+                }
+            }
         }
     }
     const float inv = rcp_approx_ftz(l);
@@ -649,6 +731,28 @@ decode_merge_kernel(const DecodeParams p) {
     uint2 packed = make_uint2((uint32_t)h[0] | ((uint32_t)h[1] << 16),
                               (uint32_t)h[2] | ((uint32_t)h[3] << 16));
     *reinterpret_cast<uint2*>(p.ctx_out + ((size_t)b * NQ + hd) * HD + 4 * lane) = packed;
+}
+
+// CTAs per (row, head group) of the merge: enough to spread the slices of long rows, few enough
+// that the CTAs without work (short rows) do not cost a second wave.
+static dim3 merge_grid(const DecodeWorkspace& ws, uint32_t batch) {
+    const uint32_t slices = (ws.max_chunks + MERGE_BLK - 1) / MERGE_BLK;
+    uint32_t y = slices >= 4u ? slices : 1u;  // rows of fewer than 4 slices stay with one CTA
+    const uint32_t cap = (uint32_t)(16 * ws.num_sms) / (batch * NKV);  // about one resident wave of 128-thread CTAs
+    if (y > cap) y = cap;
+    if (y > (uint32_t)MERGE_MAX_Y) y = MERGE_MAX_Y;
+    if (y < 1u) y = 1u;
+    return dim3(batch * NKV, y);
+}
+
+static cudaError_t launch_merge(cudaStream_t stream, const DecodeWorkspace& ws, uint32_t batch, const DecodeParams& p) {
+    if (ws.merge_acc) return launch_pdl(decode_merge_kernel<true>, merge_grid(ws, batch), dim3(128), 0, stream, p);
+    return launch_pdl(decode_merge_kernel<false>, dim3(batch * NKV), dim3(128), 0, stream, p);
+}
+
+size_t decode_merge_scratch_bytes(uint32_t max_batch, uint32_t max_chunks) {
+    const size_t slices = (max_chunks + MERGE_BLK - 1) / MERGE_BLK;
+    return slices > 1 ? (size_t)max_batch * NQ * slices * MERGE_SLOT * sizeof(float) : 0;
 }
 
 uint32_t decode_chunk_keys() { return dec::CHUNK; }
@@ -680,6 +784,8 @@ static DecodeParams make_params(const DecodeWorkspace& ws, void* ctx_out, const 
     p.partial_stats = ws.partial_stats;
     p.work_counter = ws.work_counter;
     p.status = ws.status;
+    p.merge_acc = ws.merge_acc;
+    p.merge_count = ws.merge_count;
     p.batch = batch;
     p.window = window;
     p.max_chunks = ws.max_chunks;
@@ -695,7 +801,7 @@ cudaError_t launch_decode_attn(cudaStream_t stream, const DecodeWorkspace& ws, v
     cudaError_t e = launch_pdl(decode_attn_kernel<false, false>, dim3(ws.num_sms), dim3(dec::THREADS), dec::SMEM_BYTES,
                                stream, p);
     if (e != cudaSuccess) return e;
-    return launch_pdl(decode_merge_kernel, dim3(batch * NKV), dim3(128), 0, stream, p);
+    return launch_merge(stream, ws, batch, p);
 }
 
 cudaError_t launch_append_decode(cudaStream_t stream, const DecodeWorkspace& ws, void* ctx_out, const void* q_io,
@@ -714,7 +820,7 @@ cudaError_t launch_append_decode(cudaStream_t stream, const DecodeWorkspace& ws,
     cudaError_t e = launch_pdl(decode_attn_kernel<true, false>, dim3(ws.num_sms), dim3(dec::THREADS), dec::SMEM_BYTES,
                                stream, p);
     if (e != cudaSuccess) return e;
-    return launch_pdl(decode_merge_kernel, dim3(batch * NKV), dim3(128), 0, stream, p);
+    return launch_merge(stream, ws, batch, p);
 }
 
 cudaError_t launch_decode_attn_paged(cudaStream_t stream, const DecodeWorkspace& ws, void* ctx_out, const void* q,
@@ -725,7 +831,7 @@ cudaError_t launch_decode_attn_paged(cudaStream_t stream, const DecodeWorkspace&
     cudaError_t e = launch_pdl(decode_attn_kernel<false, true>, dim3(ws.num_sms), dim3(dec::THREADS), dec::SMEM_BYTES,
                                stream, p);
     if (e != cudaSuccess) return e;
-    return launch_pdl(decode_merge_kernel, dim3(batch * NKV), dim3(128), 0, stream, p);
+    return launch_merge(stream, ws, batch, p);
 }
 
 cudaError_t launch_append_decode_paged(cudaStream_t stream, const DecodeWorkspace& ws, void* ctx_out, const void* q_io,
@@ -745,7 +851,7 @@ cudaError_t launch_append_decode_paged(cudaStream_t stream, const DecodeWorkspac
     cudaError_t e = launch_pdl(decode_attn_kernel<true, true>, dim3(ws.num_sms), dim3(dec::THREADS), dec::SMEM_BYTES,
                                stream, p);
     if (e != cudaSuccess) return e;
-    return launch_pdl(decode_merge_kernel, dim3(batch * NKV), dim3(128), 0, stream, p);
+    return launch_merge(stream, ws, batch, p);
 }
 
 }  // namespace oxi
@@ -823,7 +929,7 @@ extern "C" int32_t oxi_decode_attn_static(void* stream, void* ctx_out, const voi
     // The array keeps whatever the previous call left: the control block must start at zero.
     e = cudaMemsetAsync(pd.base, 0, nalloc::CTRL_BYTES, s);
     if (e != cudaSuccess) return (int32_t)e;
-    DecodeWorkspace ws;
+    DecodeWorkspace ws{};  // no slice scratch: rows are at most 16 key ranges long here
     ws.status = reinterpret_cast<uint32_t*>(pd.base);
     ws.work_counter = reinterpret_cast<uint32_t*>(pd.base + 128);
     ws.partial_acc = reinterpret_cast<float*>(pd.base + nalloc::CTRL_BYTES);

@@ -13,6 +13,8 @@ struct DecodeWorkspace {
     float* partial_stats;   // [max_batch][max_chunks][16][2]  (running max in log2 units, sum)
     uint32_t* status;       // device status word (OR of DEV_* bits)
     uint32_t* work_counter; // items claimed beyond the first per CTA; zero between launches
+    float* merge_acc;       // decode_merge_scratch_bytes(): slice sums of rows longer than 16 key ranges (null: none)
+    uint32_t* merge_count;  // [max_batch][4] arrival counters of the merge, zero between launches
     uint32_t max_chunks;    // partial slots per row
     uint32_t max_seq_len;
     int num_sms;
@@ -46,6 +48,7 @@ cudaError_t launch_append_decode(cudaStream_t stream, const DecodeWorkspace& ws,
                                  uint32_t batch, uint32_t window, float eps);
 uint32_t decode_chunk_keys();    // keys per split-KV work item
 uint32_t decode_max_rows();      // rows one launch can take
+size_t decode_merge_scratch_bytes(uint32_t max_batch, uint32_t max_chunks);
 
 // Workspace of the key-range split of prefill attention (small waves of long prompts).
 struct PrefillSplitWs {

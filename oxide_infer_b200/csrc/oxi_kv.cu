@@ -118,6 +118,14 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
     if ((rc = dev_alloc(h, (void**)&h->dws.partial_stats, slots * 2 * sizeof(float)))) goto bad;
     if ((rc = dev_alloc(h, (void**)&h->dws.status, 256))) goto bad;
     h->dws.work_counter = h->dws.status + 32;  // same zero-initialised 256-byte block, own 128-byte line
+    if (const size_t mb = decode_merge_scratch_bytes(max_batch, max_chunks)) {
+        if ((rc = dev_alloc(h, (void**)&h->dws.merge_acc, mb))) goto bad;
+    }
+    if ((rc = dev_alloc(h, (void**)&h->dws.merge_count, (size_t)max_batch * NKV * 4))) goto bad;
+    if (cudaMemset(h->dws.merge_count, 0, (size_t)max_batch * NKV * 4) != cudaSuccess) {
+        rc = cuda_fail(cudaGetLastError(), "cudaMemset");
+        goto bad;
+    }
     if ((rc = dev_alloc(h, &h->am_cand, (size_t)max_batch * argmax_max_splits() * 256 * 8))) goto bad;
     if ((rc = dev_alloc(h, (void**)&h->am_count, (size_t)max_batch * 4))) goto bad;
     if (cudaMemset(h->am_count, 0, (size_t)max_batch * 4) != cudaSuccess) {
@@ -177,6 +185,8 @@ int32_t oxi_destroy(oxi_handle* h) {
     cudaFree(h->dws.partial_acc);
     cudaFree(h->dws.partial_stats);
     cudaFree(h->dws.status);
+    cudaFree(h->dws.merge_acc);
+    cudaFree(h->dws.merge_count);
     cudaFree(h->conv_stage);
     cudaFree(h->pf_order);
     cudaFree(h->am_cand);

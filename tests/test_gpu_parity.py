@@ -232,6 +232,37 @@ def test_decode_batch_composition_invariance(kv):
     assert torch.equal(again.view(torch.int16), full.view(torch.int16))
 
 
+def test_decode_long_rows_merge_by_slices_independent_of_launch_shape(kv):
+    """Rows of more than 16 key ranges are merged in slices by several CTAs; how many CTAs share a
+    row depends on the batch and on the handle, the bytes must not: a long row alone, among many
+    short rows (fewer CTAs per row) and through a handle with another maximum length."""
+    from oxide_infer_b200 import KvPath
+    lens = np.concatenate([[20000, 4097, 33000, 8191], np.random.default_rng(5).integers(10, 600, 250)])  # 254 rows: 2 CTAs per row here, 8 below
+    case = DecodeCase(lens, seed=5)
+    d = _run_append(kv, case)
+    kv.decode_attn(d.ctx, d.q, d.gate, d.k_ptrs, d.v_ptrs, d.seq_lens, 0)
+    full = d.ctx.clone()
+    sub = lambda t, i, n: t[i:i + n].contiguous()
+    other = KvPath(0, max_batch=4, max_seq_len=131072, max_prefill_rows=0)
+    for h in (kv, other):
+        for i, n in ((0, 1), (2, 1), (0, 4), (1, 3)):
+            out = torch.zeros(n, NQ, HD, dtype=torch.float16, device="cuda")
+            h.decode_attn(out, sub(d.q, i, n), sub(d.gate, i, n), sub(d.k_ptrs, i, n), sub(d.v_ptrs, i, n),
+                          sub(d.seq_lens, i, n), 0)
+            torch.cuda.synchronize()
+            assert torch.equal(out.view(torch.int16), full[i:i + n].view(torch.int16))
+    # windows cut a long row back to one slice or to a few
+    for window in (4096, 5000):
+        a = torch.zeros_like(full)
+        kv.decode_attn(a, d.q, d.gate, d.k_ptrs, d.v_ptrs, d.seq_lens, window)
+        one = torch.zeros(1, NQ, HD, dtype=torch.float16, device="cuda")
+        kv.decode_attn(one, sub(d.q, 2, 1), sub(d.gate, 2, 1), sub(d.k_ptrs, 2, 1), sub(d.v_ptrs, 2, 1),
+                       sub(d.seq_lens, 2, 1), window)
+        torch.cuda.synchronize()
+        assert torch.equal(one[0].view(torch.int16), a[2].view(torch.int16))
+    assert kv.device_status() == 0 and other.device_status() == 0
+
+
 def test_reference_known_answer_cases_on_gpu(kv, O):
     """The reference's own test shapes through the library: uniform-softmax mean position
     (debug_online_attn.rs), pat()-seeded rows 300/180/64/300 vs f64 < 3e-3
