@@ -15,7 +15,11 @@ namespace oxi {
 // the fifth the four K heads, so that the row's cos / sin vectors are fetched once per warp and the
 // loads of four heads are in flight together (a prefill wave appends thousands of rows).  The
 // first 64 threads of a row's warps also copy the 1 KB V row with 16-byte vectors.
-constexpr int APPEND_ROWS = 4;
+// Two rows per CTA measured best on a 4,096-row wave (one: the same; four: 9 us slower; six: 7 us slower).
+#ifndef OXI_APPEND_ROWS
+#define OXI_APPEND_ROWS 2
+#endif
+constexpr int APPEND_ROWS = OXI_APPEND_ROWS;
 __global__ void __launch_bounds__(APPEND_ROWS * 160)
 append_kernel(uint16_t* __restrict__ q_io, const uint16_t* __restrict__ k_in,
               const uint16_t* __restrict__ v_in, const uint16_t* __restrict__ q_norm_w,
