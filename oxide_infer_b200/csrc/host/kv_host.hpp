@@ -7,6 +7,9 @@
 //                       (crates/oxide-infer-server/src/batch_engine.rs:78-87)
 //   StepTables          layer-major k/v/conv pointer tables + positions, uploaded once per
 //                       step (batch_engine.rs:681-751)
+//   PrefillPlanner      prompts -> chunks -> waves (bin/server.rs:1076-1112)
+//   WaveTables          a wave's per-row tables: positions, chunk origins, carry-state and K/V
+//                       pointers (PrefillMeta, batch_engine.rs:156-160; bin/server.rs:1113-1141)
 //   KvPathEngine        the per-layer launch sites of the hot path
 //                       (batch_engine.rs:840-899, 941-1239) on top of liboxi_kv
 //
@@ -14,6 +17,7 @@
 // uploads and KvPathEngine.  Define OXI_HOST_NO_CUDA to use the allocator logic alone
 // (externally owned slabs), e.g. in host-only unit tests.
 #pragma once
+#include <algorithm>
 #include <cstddef>
 #include <cstdint>
 #include <map>
@@ -241,6 +245,100 @@ struct StepTablesHost {
     }
 };
 
+// ---- prefill waves (bin/server.rs:1076-1131) --------------------------------------------------
+
+// Rows [start, start + len) of request `req`'s prompt, consecutive rows of one wave.
+struct WaveChunk {
+    size_t req, start, len;
+    bool operator==(const WaveChunk& o) const { return req == o.req && start == o.start && len == o.len; }
+};
+
+// Cuts prompts into chunks of at most max_rows tokens and packs whole chunks into waves of at most
+// max_rows rows, as the reference's worker does: requests in order of increasing prompt length
+// (stable), a request's chunks in order, a wave takes the next chunks for as long as they fit.
+// The chunk rows of a request stay contiguous inside a wave; the request's persistent conv state
+// carries the 6-token history across its chunks, which therefore never share a wave.
+class PrefillPlanner {
+  public:
+    PrefillPlanner(const std::vector<size_t>& prompt_lens, size_t max_rows) : max_rows_(max_rows) {
+        if (max_rows == 0) throw std::invalid_argument("a wave needs at least one row");
+        std::vector<size_t> order(prompt_lens.size());
+        for (size_t i = 0; i < order.size(); i++) order[i] = i;
+        std::stable_sort(order.begin(), order.end(), [&](size_t a, size_t b) { return prompt_lens[a] < prompt_lens[b]; });
+        for (size_t r : order)
+            for (size_t start = 0; start < prompt_lens[r]; start += max_rows)
+                chunks_.push_back({r, start, std::min(max_rows, prompt_lens[r] - start)});
+    }
+    // The next wave, or an empty vector when every chunk has been handed out.
+    std::vector<WaveChunk> next() {
+        std::vector<WaveChunk> wave;
+        size_t used = 0;
+        while (next_ < chunks_.size()) {
+            const WaveChunk& c = chunks_[next_];
+            if (used + c.len > max_rows_) break;
+            // two chunks of one request depend on each other through the carried conv state (with the
+            // sizes above they never fit one wave anyway: all but a request's last chunk fill a wave)
+            if (!wave.empty() && wave.back().req == c.req) break;
+            wave.push_back(c);
+            used += c.len;
+            ++next_;
+        }
+        return wave;
+    }
+    size_t chunks_left() const { return chunks_.size() - next_; }
+
+  private:
+    size_t max_rows_, next_ = 0;
+    std::vector<WaveChunk> chunks_;
+};
+
+// Host image of one wave's per-row tables (PrefillMeta, batch_engine.rs:156-160, and the rows of
+// bin/server.rs:1113-1131): row r of the wave is token start + j of its request, at cache
+// position first_pos[req] + start + j.  Pointer tables are layer-major, tbl[layer * rows + r].
+struct WaveTablesHost {
+    size_t rows = 0, layers = 0;
+    std::vector<uint64_t> k_ptrs, v_ptrs, carry_ptrs;
+    std::vector<uint32_t> pos_ids, seq_lens, origins, local_pos, row_req;
+
+    // seqs[req] is the request's sequence; first_pos[req] the cache position of its prompt's first
+    // token (0 unless a prefix is already cached).
+    void build(const std::vector<WaveChunk>& wave, const std::vector<const BatchSequence*>& seqs,
+               const std::vector<uint32_t>& first_pos, const KvLayout& layout) {
+        if (seqs.size() != first_pos.size()) throw std::invalid_argument("one first position per request");
+        rows = 0;
+        for (const WaveChunk& c : wave) {
+            if (c.req >= seqs.size() || c.len == 0) throw std::invalid_argument("bad wave chunk");
+            rows += c.len;
+        }
+        layers = layout.num_layers();
+        pos_ids.clear(); seq_lens.clear(); origins.clear(); local_pos.clear(); row_req.clear();
+        for (const WaveChunk& c : wave) {
+            const uint32_t origin = (uint32_t)pos_ids.size();
+            for (size_t j = 0; j < c.len; j++) {
+                const uint32_t pos = first_pos[c.req] + (uint32_t)(c.start + j);
+                pos_ids.push_back(pos);
+                seq_lens.push_back(pos + 1u);  // causal: the row sees the keys up to itself
+                origins.push_back(origin);
+                local_pos.push_back((uint32_t)j);
+                row_req.push_back((uint32_t)c.req);
+            }
+        }
+        k_ptrs.assign(layers * rows, 0);
+        v_ptrs.assign(layers * rows, 0);
+        carry_ptrs.assign(layers * rows, 0);
+        for (size_t l = 0; l < layers; l++)
+            for (size_t r = 0; r < rows; r++) {
+                const BatchSequence* sq = seqs[row_req[r]];
+                if (layout.is_conv(l)) {
+                    carry_ptrs[l * rows + r] = sq->conv_state_ptr(l);
+                } else {
+                    k_ptrs[l * rows + r] = sq->k_cache_ptr(l);
+                    v_ptrs[l * rows + r] = sq->v_cache_ptr(l);
+                }
+            }
+    }
+};
+
 #ifndef OXI_HOST_NO_CUDA
 // Device copy of the tables; uploads are asynchronous on the caller's stream from pinned
 // memory (batch_engine.rs:732-740), so nothing synchronises on the decode path.
@@ -301,6 +399,64 @@ class StepTables {
     void* h_ = nullptr;
 };
 
+// Device copy of a wave's tables (one pinned staging block, asynchronous uploads).
+class WaveTables {
+  public:
+    WaveTables(size_t max_rows, size_t layers) : max_rows_(max_rows), layers_(layers) {
+        const size_t n = max_rows * layers;
+        check(cudaMalloc((void**)&d_k_, n * 8), "wave tables");
+        check(cudaMalloc((void**)&d_v_, n * 8), "wave tables");
+        check(cudaMalloc((void**)&d_carry_, n * 8), "wave tables");
+        check(cudaMalloc((void**)&d_u32_, 4 * max_rows * 4), "wave tables");
+        check(cudaMallocHost((void**)&h_, 3 * n * 8 + 4 * max_rows * 4), "pinned wave tables");
+    }
+    ~WaveTables() {
+        cudaFree(d_k_); cudaFree(d_v_); cudaFree(d_carry_); cudaFree(d_u32_);
+        if (h_) cudaFreeHost(h_);
+    }
+    WaveTables(const WaveTables&) = delete;
+    WaveTables& operator=(const WaveTables&) = delete;
+
+    // The staging block is reused: the previous upload must have completed on its stream.
+    void upload(const WaveTablesHost& t, cudaStream_t s) {
+        if (t.rows == 0 || t.rows > max_rows_ || t.layers != layers_) throw std::invalid_argument("wave exceeds the allocated size");
+        rows_ = t.rows;
+        const size_t n = t.rows * t.layers;
+        uint64_t* hk = (uint64_t*)h_;
+        uint64_t* hv = hk + max_rows_ * layers_;
+        uint64_t* hc = hv + max_rows_ * layers_;
+        uint32_t* hu = (uint32_t*)(hc + max_rows_ * layers_);
+        std::copy(t.k_ptrs.begin(), t.k_ptrs.end(), hk);
+        std::copy(t.v_ptrs.begin(), t.v_ptrs.end(), hv);
+        std::copy(t.carry_ptrs.begin(), t.carry_ptrs.end(), hc);
+        std::copy(t.pos_ids.begin(), t.pos_ids.end(), hu);
+        std::copy(t.seq_lens.begin(), t.seq_lens.end(), hu + max_rows_);
+        std::copy(t.origins.begin(), t.origins.end(), hu + 2 * max_rows_);
+        std::copy(t.local_pos.begin(), t.local_pos.end(), hu + 3 * max_rows_);
+        check(cudaMemcpyAsync(d_k_, hk, n * 8, cudaMemcpyHostToDevice, s), "upload");
+        check(cudaMemcpyAsync(d_v_, hv, n * 8, cudaMemcpyHostToDevice, s), "upload");
+        check(cudaMemcpyAsync(d_carry_, hc, n * 8, cudaMemcpyHostToDevice, s), "upload");
+        check(cudaMemcpyAsync(d_u32_, hu, 4 * max_rows_ * 4, cudaMemcpyHostToDevice, s), "upload");
+    }
+    size_t rows() const { return rows_; }
+    const uint64_t* k_ptrs(size_t layer) const { return d_k_ + layer * rows_; }
+    const uint64_t* v_ptrs(size_t layer) const { return d_v_ + layer * rows_; }
+    const uint64_t* carry_ptrs(size_t layer) const { return d_carry_ + layer * rows_; }
+    const uint32_t* pos_ids() const { return d_u32_; }
+    const uint32_t* seq_lens() const { return d_u32_ + max_rows_; }
+    const uint32_t* origins() const { return d_u32_ + 2 * max_rows_; }
+    const uint32_t* local_pos() const { return d_u32_ + 3 * max_rows_; }
+
+  private:
+    static void check(cudaError_t e, const char* what) {
+        if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+    }
+    size_t max_rows_, layers_, rows_ = 0;
+    uint64_t *d_k_ = nullptr, *d_v_ = nullptr, *d_carry_ = nullptr;
+    uint32_t* d_u32_ = nullptr;
+    void* h_ = nullptr;
+};
+
 // The hot-path launch sites of one layer, on the caller's stream.  Throws std::runtime_error
 // with the library's message on a non-zero status (the engine's anyhow style).
 class KvPathEngine {
@@ -324,6 +480,28 @@ class KvPathEngine {
     // batch_engine.rs:840-899 for conv layer `layer` (decode rows).
     void conv_decode(cudaStream_t s, const StepTables& t, size_t layer, void* y, const void* bcx, const void* conv_w) {
         ok(oxi_conv_decode(h_, s, y, t.conv_ptrs(layer), bcx, conv_w, (uint32_t)t.batch()), "oxi_conv_decode");
+    }
+    // A prefill wave through attention layer `layer` (batch_engine.rs:941-1014 on the wave's rows, then
+    // :1045-1077): every row's K/V is appended at its position, then the rows attend causally.
+    void attention_prefill(cudaStream_t s, const WaveTables& t, size_t layer, void* ctx, void* q_io, const void* k,
+                           const void* v, const void* gate, const void* q_norm_w, const void* k_norm_w,
+                           const void* cos_table, const void* sin_table, uint32_t window, float eps = 1e-5f) {
+        ok(oxi_append(h_, s, q_io, k, v, q_norm_w, k_norm_w, cos_table, sin_table, t.pos_ids(), t.k_ptrs(layer),
+                      t.v_ptrs(layer), (uint32_t)t.rows(), eps),
+           "oxi_append");
+        ok(oxi_prefill_attn(h_, s, ctx, q_io, gate, t.k_ptrs(layer), t.v_ptrs(layer), t.seq_lens(), (uint32_t)t.rows(),
+                            window),
+           "oxi_prefill_attn");
+    }
+    // A prefill wave through conv layer `layer` (batch_engine.rs:847-899 and the copy-back of
+    // bin/server.rs:1192-1224): the requests' persistent states are updated by the call.
+    void conv_prefill(cudaStream_t s, const WaveTables& t, size_t layer, void* y, const void* bcx, const void* conv_w) {
+        ok(oxi_conv_prefill(h_, s, y, t.carry_ptrs(layer), t.origins(), t.local_pos(), bcx, conv_w, (uint32_t)t.rows()),
+           "oxi_conv_prefill");
+    }
+    // Lets small waves of long prompts use idle SMs (see oxi_prefill_split_configure).
+    void configure_prefill_split(uint32_t min_part_keys, uint32_t slots) {
+        ok(oxi_prefill_split_configure(h_, min_part_keys, slots), "oxi_prefill_split_configure");
     }
     // Moves every row of the tables one token ahead on the device.  While the batch membership is
     // unchanged, a captured graph of (all layers + this call) replays step after step with no upload

@@ -1,6 +1,7 @@
 // Host-only checks of the C++ host layer: layout addressing (kv_pool.rs:46-61), first-fit
 // leases with coalescing release (kv_pool.rs:175-251), layer-major table building
-// (batch_engine.rs:709-731).  No CUDA: slabs are plain numbers.
+// (batch_engine.rs:709-731), prefill wave planning and per-row wave tables
+// (bin/server.rs:1076-1141).  No CUDA: slabs are plain numbers.
 #define OXI_HOST_NO_CUDA
 #include "../../oxide_infer_b200/csrc/host/kv_host.hpp"
 
@@ -58,6 +59,44 @@ int main() {
     CHECK(t.v_ptrs[4 * 2 + 0] == layout->v_cache_ptr(4, l0->tok_off));
     CHECK(t.conv_ptrs[1 * 2 + 1] == layout->conv_state_ptr(1, l1->slot));
     CHECK(t.k_ptrs[0] == 0 && t.conv_ptrs[2 * 2] == 0);  // a layer has entries of its own kind only
+    // prefill waves: requests by increasing prompt length, chunks of at most 128 rows, whole chunks
+    // packed while they fit (bin/server.rs:1076-1112)
+    {
+        PrefillPlanner pl({300, 5, 130, 0, 128}, 128);
+        const std::vector<std::vector<WaveChunk>> want = {
+            {{1, 0, 5}},                  // the 128-row chunk of request 4 does not fit beside it
+            {{4, 0, 128}},
+            {{2, 0, 128}},
+            {{2, 128, 2}},                // 2 + 128 > 128
+            {{0, 0, 128}}, {{0, 128, 128}}, {{0, 256, 44}}};
+        for (const auto& w : want) CHECK(pl.next() == w);
+        CHECK(pl.next().empty() && pl.chunks_left() == 0);
+        PrefillPlanner small({3, 4, 200, 6}, 16);  // short prompts share a wave; equal keys keep their order
+        CHECK((small.next() == std::vector<WaveChunk>{{0, 0, 3}, {1, 0, 4}, {3, 0, 6}}));
+        CHECK((small.next() == std::vector<WaveChunk>{{2, 0, 16}}));
+        bool bad = false;
+        try { PrefillPlanner none({1}, 0); } catch (const std::invalid_argument&) { bad = true; }
+        CHECK(bad);
+    }
+    {
+        // per-row tables of a wave: positions, chunk origins, positions inside the chunk, pointers
+        WaveTablesHost w;
+        const std::vector<WaveChunk> wave = {{1, 0, 3}, {0, 64, 2}};
+        w.build(wave, {&s0, &s1}, {100, 0}, *layout);
+        CHECK(w.rows == 5 && w.layers == 5);
+        const uint32_t pos[5] = {0, 1, 2, 164, 165}, org[5] = {0, 0, 0, 3, 3}, lp[5] = {0, 1, 2, 0, 1};
+        for (int r = 0; r < 5; r++) {
+            CHECK(w.pos_ids[r] == pos[r] && w.seq_lens[r] == pos[r] + 1 && w.origins[r] == org[r] && w.local_pos[r] == lp[r]);
+            CHECK(w.row_req[r] == (r < 3 ? 1u : 0u));
+        }
+        CHECK(w.k_ptrs[2 * 5 + 0] == s1.k_cache_ptr(2) && w.k_ptrs[2 * 5 + 4] == s0.k_cache_ptr(2));
+        CHECK(w.v_ptrs[4 * 5 + 3] == s0.v_cache_ptr(4));
+        CHECK(w.carry_ptrs[3 * 5 + 1] == s1.conv_state_ptr(3) && w.carry_ptrs[0 * 5 + 4] == s0.conv_state_ptr(0));
+        CHECK(w.k_ptrs[0] == 0 && w.carry_ptrs[2 * 5] == 0);
+        bool bad = false;
+        try { w.build({{2, 0, 1}}, {&s0, &s1}, {0, 0}, *layout); } catch (const std::invalid_argument&) { bad = true; }
+        CHECK(bad);
+    }
     std::printf("kv_host cpu checks passed\n");
     return 0;
 }

@@ -34,3 +34,19 @@ def test_host_layer_decode_step_gpu():
     r = subprocess.run([exe], capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "passed" in r.stdout
+
+
+@pytest.mark.gpu
+def test_host_layer_prefill_waves_equal_token_by_token_decode_gpu():
+    """Prompts prefilled in waves planned by the host layer leave the same K/V rows, conv outputs and
+    conv states as the same tokens fed one at a time through the decode path."""
+    from oxide_infer_b200 import build
+    so = build.build()
+    os.makedirs(BUILD, exist_ok=True)
+    exe = os.path.join(BUILD, "test_kv_host_prefill_gpu")
+    subprocess.run(["nvcc", "-std=c++17", "-O1", "-gencode", "arch=compute_100a,code=sm_100a", "-o", exe,
+                    os.path.join(CPP, "test_kv_host_prefill_gpu.cpp"), so, "-Xlinker", "-rpath", "-Xlinker",
+                    os.path.dirname(so)], check=True)
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "passed" in r.stdout
