@@ -7,6 +7,10 @@
 //                       (crates/oxide-infer-server/src/batch_engine.rs:78-87)
 //   StepTables          layer-major k/v/conv pointer tables + positions, uploaded once per
 //                       step (batch_engine.rs:681-751)
+//   PagedKvPool / PagedBlockManager / PagedStepTables
+//                       block pool, per-sequence block lists with shared-prefix reference counts
+//                       and the step's block tables (crates/oxide-infer-core/src/paged_pool.rs,
+//                       crates/oxide-infer-scheduler/src/block_manager.rs)
 //   PrefillPlanner      prompts -> chunks -> waves (bin/server.rs:1076-1112)
 //   WaveTables          a wave's per-row tables: positions, chunk origins, carry-state and K/V
 //                       pointers (PrefillMeta, batch_engine.rs:156-160; bin/server.rs:1113-1141)
@@ -20,11 +24,13 @@
 #include <algorithm>
 #include <cstddef>
 #include <cstdint>
+#include <deque>
 #include <map>
 #include <memory>
 #include <optional>
 #include <stdexcept>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #ifndef OXI_HOST_NO_CUDA
@@ -245,6 +251,166 @@ struct StepTablesHost {
     }
 };
 
+// ---- paged K/V (core/src/paged_pool.rs, scheduler/src/block_manager.rs) -----------------------
+
+// Geometry of the paged pool: every block holds K and V rows of all attention layers,
+// [layer][K | V][block_size tokens][4 KV heads][128] f16 (paged_pool.rs:11-24 with the path's
+// 4 heads x 128 dims).
+struct PagedPoolConfig {
+    size_t num_blocks = 0, block_size = 0, num_layers = 0;
+    size_t rows_per_block() const { return 2 * num_layers * block_size; }
+    size_t block_bytes() const { return rows_per_block() * KV_DIM * ELEM; }
+};
+
+// Physical blocks and their free list (paged_pool.rs:27-75): blocks are handed out in the order
+// 0, 1, 2, ...; a freed block goes to the back of the queue.
+class PagedKvPool {
+  public:
+    // Memory owned by the caller (or none: pure bookkeeping with base 0).
+    PagedKvPool(uint64_t base, const PagedPoolConfig& cfg) : base_(base), cfg_(cfg) {
+        const size_t bs = cfg.block_size;
+        if (!cfg.num_blocks || !cfg.num_layers || bs < 16 || bs > 256 || (bs & (bs - 1)))
+            throw std::invalid_argument("paged pool: block_size must be 16, 32, 64, 128 or 256; blocks and layers > 0");
+        for (size_t i = 0; i < cfg.num_blocks; i++) free_.push_back(i);
+    }
+#ifndef OXI_HOST_NO_CUDA
+    static std::shared_ptr<PagedKvPool> create(const PagedPoolConfig& cfg) {
+        void* p = nullptr;
+        if (cudaMalloc(&p, cfg.num_blocks * cfg.block_bytes()) != cudaSuccess) throw std::runtime_error("paged pool allocation failed");
+        cudaMemset(p, 0, cfg.num_blocks * cfg.block_bytes());
+        std::shared_ptr<PagedKvPool> pool;
+        try {
+            pool.reset(new PagedKvPool((uint64_t)p, cfg));
+        } catch (...) {
+            cudaFree(p);
+            throw;
+        }
+        pool->owned_ = p;
+        return pool;
+    }
+    ~PagedKvPool() {
+        if (owned_) cudaFree(owned_);
+    }
+#endif
+    PagedKvPool(const PagedKvPool&) = delete;
+    PagedKvPool& operator=(const PagedKvPool&) = delete;
+
+    std::optional<size_t> allocate_block() {
+        if (free_.empty()) return std::nullopt;
+        const size_t b = free_.front();
+        free_.pop_front();
+        return b;
+    }
+    void free_block(size_t block) { free_.push_back(block); }
+    size_t free_block_count() const { return free_.size(); }
+    const PagedPoolConfig& config() const { return cfg_; }
+    // First K (V) row of attention layer `layer` inside block 0; block i is block_bytes() further.
+    uint64_t k_rows(size_t layer) const { return base_ + (2 * layer) * cfg_.block_size * KV_DIM * ELEM; }
+    uint64_t v_rows(size_t layer) const { return base_ + (2 * layer + 1) * cfg_.block_size * KV_DIM * ELEM; }
+
+  private:
+    uint64_t base_;
+    PagedPoolConfig cfg_;
+    std::deque<size_t> free_;
+    void* owned_ = nullptr;
+};
+
+// Logical-to-physical block lists of the live sequences with reference counts for shared prefix
+// blocks (block_manager.rs:17-131).  Not thread-safe: one scheduler thread owns it.
+class PagedBlockManager {
+  public:
+    explicit PagedBlockManager(std::shared_ptr<PagedKvPool> pool) : pool_(std::move(pool)) {
+        if (!pool_) throw std::invalid_argument("paged block manager needs a pool");
+    }
+    size_t block_size() const { return pool_->config().block_size; }
+
+    // Blocks for the first num_tokens tokens of a new sequence: the shared prefix blocks are
+    // adopted (one more reference each), the rest come from the pool.  If the pool runs dry the
+    // blocks taken so far are given back and std::runtime_error is thrown.
+    void allocate_for_seq(uint64_t seq_id, size_t num_tokens, const std::vector<size_t>& shared_blocks = {}) {
+        if (tables_.count(seq_id)) throw std::invalid_argument("sequence already has a block table");
+        const size_t needed = (num_tokens + block_size() - 1) / block_size();
+        std::vector<size_t> blocks;
+        for (size_t b : shared_blocks) {
+            ++refs_[b];
+            blocks.push_back(b);
+        }
+        while (blocks.size() < needed) {
+            const auto b = pool_->allocate_block();
+            if (!b) {
+                for (size_t x : blocks) drop(x);
+                throw std::runtime_error("paged KV pool exhausted");
+            }
+            refs_[*b] = 1;
+            blocks.push_back(*b);
+        }
+        tables_[seq_id] = std::move(blocks);
+    }
+    // Called before the token at position current_token_len is appended: a new block is taken
+    // only when that position opens a block.  Returns the new block, if any.
+    std::optional<size_t> append_token(uint64_t seq_id, size_t current_token_len) {
+        auto it = tables_.find(seq_id);
+        if (it == tables_.end()) throw std::invalid_argument("unknown sequence");
+        if (current_token_len % block_size() != 0) return std::nullopt;
+        const auto b = pool_->allocate_block();
+        if (!b) throw std::runtime_error("paged KV pool exhausted");
+        refs_[*b] = 1;
+        it->second.push_back(*b);
+        return b;
+    }
+    const std::vector<size_t>* get_block_table(uint64_t seq_id) const {
+        auto it = tables_.find(seq_id);
+        return it == tables_.end() ? nullptr : &it->second;
+    }
+    // Drops the sequence; a block returns to the pool when its last reference goes.
+    void free_seq(uint64_t seq_id) {
+        auto it = tables_.find(seq_id);
+        if (it == tables_.end()) return;
+        for (size_t b : it->second) drop(b);
+        tables_.erase(it);
+    }
+    const PagedKvPool& pool() const { return *pool_; }
+
+  private:
+    void drop(size_t b) {
+        auto r = refs_.find(b);
+        if (r == refs_.end()) return;
+        if (r->second > 0) --r->second;
+        if (r->second == 0) {
+            refs_.erase(r);
+            pool_->free_block(b);
+        }
+    }
+    std::shared_ptr<PagedKvPool> pool_;
+    std::unordered_map<uint64_t, std::vector<size_t>> tables_;
+    std::unordered_map<size_t, size_t> refs_;
+};
+
+// Host image of one decode step over the paged layout: block_tables[b][i] = block of tokens
+// [i * block_size, (i + 1) * block_size) of row b, padded with 0.
+struct PagedStepTablesHost {
+    size_t batch = 0, max_blocks = 0;
+    std::vector<uint32_t> block_tables, pos_ids, seq_lens;
+
+    void build(const PagedBlockManager& mgr, const std::vector<uint64_t>& seq_ids, const std::vector<uint32_t>& positions,
+               size_t max_blocks_per_row) {
+        if (seq_ids.size() != positions.size()) throw std::invalid_argument("one position per sequence");
+        batch = seq_ids.size();
+        max_blocks = max_blocks_per_row;
+        block_tables.assign(batch * max_blocks, 0u);
+        pos_ids = positions;
+        seq_lens.resize(batch);
+        for (size_t i = 0; i < batch; i++) {
+            seq_lens[i] = positions[i] + 1u;
+            const std::vector<size_t>* t = mgr.get_block_table(seq_ids[i]);
+            if (!t) throw std::invalid_argument("unknown sequence");
+            if (t->size() > max_blocks || (size_t)positions[i] / mgr.block_size() >= t->size())
+                throw std::invalid_argument("block table does not cover the step's position");
+            for (size_t j = 0; j < t->size(); j++) block_tables[i * max_blocks + j] = (uint32_t)(*t)[j];
+        }
+    }
+};
+
 // ---- prefill waves (bin/server.rs:1076-1131) --------------------------------------------------
 
 // Rows [start, start + len) of request `req`'s prompt, consecutive rows of one wave.
@@ -457,6 +623,54 @@ class WaveTables {
     void* h_ = nullptr;
 };
 
+// Device copy of a paged decode step's tables.
+class PagedStepTables {
+  public:
+    PagedStepTables(size_t max_batch, size_t max_blocks) : max_batch_(max_batch), max_blocks_(max_blocks) {
+        check(cudaMalloc((void**)&d_, words() * 4), "paged tables");
+        check(cudaMallocHost((void**)&h_, words() * 4), "pinned paged tables");
+    }
+    ~PagedStepTables() {
+        cudaFree(d_);
+        if (h_) cudaFreeHost(h_);
+    }
+    PagedStepTables(const PagedStepTables&) = delete;
+    PagedStepTables& operator=(const PagedStepTables&) = delete;
+
+    // The staging block is reused: the previous upload must have completed on its stream.
+    void upload(const PagedStepTablesHost& t, cudaStream_t s) {
+        if (t.batch == 0 || t.batch > max_batch_ || t.max_blocks != max_blocks_) throw std::invalid_argument("paged tables exceed the allocated size");
+        batch_ = t.batch;
+        std::copy(t.block_tables.begin(), t.block_tables.end(), h_);
+        std::copy(t.pos_ids.begin(), t.pos_ids.end(), h_ + max_batch_ * max_blocks_);
+        std::copy(t.seq_lens.begin(), t.seq_lens.end(), h_ + max_batch_ * max_blocks_ + max_batch_);
+        check(cudaMemcpyAsync(d_, h_, words() * 4, cudaMemcpyHostToDevice, s), "upload");
+    }
+    size_t batch() const { return batch_; }
+    const uint32_t* pos_ids() const { return d_ + max_batch_ * max_blocks_; }
+    const uint32_t* seq_lens() const { return d_ + max_batch_ * max_blocks_ + max_batch_; }
+    // The layout argument of the paged entry points for attention layer `layer` of `pool`.
+    oxi_paged_layout layout(const PagedKvPool& pool, size_t layer) const {
+        oxi_paged_layout l{};
+        l.k_pool = (const void*)pool.k_rows(layer);
+        l.v_pool = (const void*)pool.v_rows(layer);
+        l.block_tables = d_;
+        l.block_stride_bytes = pool.config().block_bytes();
+        l.max_blocks = (uint32_t)max_blocks_;
+        l.block_size = (uint32_t)pool.config().block_size;
+        l.num_blocks = (uint32_t)pool.config().num_blocks;
+        return l;
+    }
+
+  private:
+    size_t words() const { return max_batch_ * max_blocks_ + 2 * max_batch_; }
+    static void check(cudaError_t e, const char* what) {
+        if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+    }
+    size_t max_batch_, max_blocks_, batch_ = 0;
+    uint32_t *d_ = nullptr, *h_ = nullptr;
+};
+
 // The hot-path launch sites of one layer, on the caller's stream.  Throws std::runtime_error
 // with the library's message on a non-zero status (the engine's anyhow style).
 class KvPathEngine {
@@ -476,6 +690,17 @@ class KvPathEngine {
         ok(oxi_append_decode(h_, s, ctx, q_io, k, v, gate, q_norm_w, k_norm_w, cos_table, sin_table, t.pos_ids(),
                              t.seq_lens(), t.k_ptrs(layer), t.v_ptrs(layer), (uint32_t)t.batch(), window, eps),
            "oxi_append_decode");
+    }
+    // The same step over the paged layout (the K/V row is written into its block, then attention
+    // over the block table); `layer` counts attention layers, as the pool does.
+    void attention_decode_paged(cudaStream_t s, const PagedStepTables& t, const PagedKvPool& pool, size_t layer, void* ctx,
+                                void* q_io, const void* k, const void* v, const void* gate, const void* q_norm_w,
+                                const void* k_norm_w, const void* cos_table, const void* sin_table, uint32_t window,
+                                float eps = 1e-5f) {
+        const oxi_paged_layout l = t.layout(pool, layer);
+        ok(oxi_append_decode_paged(h_, s, ctx, q_io, k, v, gate, q_norm_w, k_norm_w, cos_table, sin_table, t.seq_lens(), &l,
+                                   (uint32_t)t.batch(), window, eps),
+           "oxi_append_decode_paged");
     }
     // batch_engine.rs:840-899 for conv layer `layer` (decode rows).
     void conv_decode(cudaStream_t s, const StepTables& t, size_t layer, void* y, const void* bcx, const void* conv_w) {

@@ -97,6 +97,61 @@ int main() {
         try { w.build({{2, 0, 1}}, {&s0, &s1}, {0, 0}, *layout); } catch (const std::invalid_argument&) { bad = true; }
         CHECK(bad);
     }
+    {
+        // paged blocks: the scenario of the reference's own unit test (block_manager.rs:139-178): 10 blocks
+        // of 16 tokens; 32 tokens take 2 blocks; a second sequence adopts the first block as a shared
+        // prefix and takes one new block; a shared block returns to the pool with its last owner
+        PagedPoolConfig cfg;
+        cfg.num_blocks = 10; cfg.block_size = 16; cfg.num_layers = 1;
+        auto pp = std::make_shared<PagedKvPool>(0x40000000ull, cfg);
+        PagedBlockManager mgr(pp);
+        mgr.allocate_for_seq(1001, 32);
+        const auto* b1 = mgr.get_block_table(1001);
+        CHECK(b1 && b1->size() == 2 && pp->free_block_count() == 8);
+        mgr.allocate_for_seq(1002, 32, {(*b1)[0]});
+        const auto* b2 = mgr.get_block_table(1002);
+        CHECK(b2 && b2->size() == 2 && (*b2)[0] == (*b1)[0] && pp->free_block_count() == 7);
+        mgr.free_seq(1001);
+        CHECK(pp->free_block_count() == 8 && !mgr.get_block_table(1001));
+        mgr.free_seq(1002);
+        CHECK(pp->free_block_count() == 10);
+        // growth: a block is taken only when the position opens one
+        mgr.allocate_for_seq(7, 16);
+        CHECK(mgr.get_block_table(7)->size() == 1);
+        CHECK(!mgr.append_token(7, 15));
+        CHECK(mgr.append_token(7, 16).has_value() && mgr.get_block_table(7)->size() == 2);
+        CHECK(!mgr.append_token(7, 17));
+        // exhaustion gives everything back, also the extra reference on an adopted block
+        const size_t shared = (*mgr.get_block_table(7))[0], before = pp->free_block_count();
+        bool oom = false;
+        try { mgr.allocate_for_seq(8, 16 * 11, {shared}); } catch (const std::runtime_error&) { oom = true; }
+        CHECK(oom && pp->free_block_count() == before && !mgr.get_block_table(8));
+        mgr.free_seq(7);
+        CHECK(pp->free_block_count() == 10);
+        bool unknown = false;
+        try { mgr.append_token(99, 16); } catch (const std::invalid_argument&) { unknown = true; }
+        CHECK(unknown && pp->free_block_count() == 10);
+        // addressing: [layer][K | V][block_size][512] inside a block
+        PagedPoolConfig c3;
+        c3.num_blocks = 4; c3.block_size = 32; c3.num_layers = 3;
+        PagedKvPool p3(0x1000, c3);
+        CHECK(c3.block_bytes() == 2 * 3 * 32 * 1024);
+        CHECK(p3.k_rows(0) == 0x1000 && p3.v_rows(0) == 0x1000 + 32 * 1024 && p3.k_rows(2) == 0x1000 + 4 * 32 * 1024);
+        bool badbs = false;
+        try { PagedPoolConfig c4 = c3; c4.block_size = 24; PagedKvPool p4(0, c4); } catch (const std::invalid_argument&) { badbs = true; }
+        CHECK(badbs);
+        // the step's block tables
+        mgr.allocate_for_seq(1, 40);   // 3 blocks
+        mgr.allocate_for_seq(2, 5);    // 1 block
+        PagedStepTablesHost pt;
+        pt.build(mgr, {2, 1}, {4, 39}, 4);
+        CHECK(pt.batch == 2 && pt.seq_lens[0] == 5 && pt.seq_lens[1] == 40);
+        CHECK(pt.block_tables[0] == (*mgr.get_block_table(2))[0] && pt.block_tables[1] == 0);
+        for (int j = 0; j < 3; j++) CHECK(pt.block_tables[4 + j] == (*mgr.get_block_table(1))[j]);
+        bool uncovered = false;
+        try { pt.build(mgr, {2}, {16}, 4); } catch (const std::invalid_argument&) { uncovered = true; }  // position 16 needs a 2nd block
+        CHECK(uncovered);
+    }
     std::printf("kv_host cpu checks passed\n");
     return 0;
 }

@@ -50,3 +50,19 @@ def test_host_layer_prefill_waves_equal_token_by_token_decode_gpu():
     r = subprocess.run([exe], capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
     assert "passed" in r.stdout
+
+
+@pytest.mark.gpu
+def test_host_layer_paged_decode_equals_contiguous_decode_gpu():
+    """Decode steps over blocks handed out by the host layer's block manager give the same context bytes
+    as the same steps over contiguous leases."""
+    from oxide_infer_b200 import build
+    so = build.build()
+    os.makedirs(BUILD, exist_ok=True)
+    exe = os.path.join(BUILD, "test_kv_host_paged_gpu")
+    subprocess.run(["nvcc", "-std=c++17", "-O1", "-gencode", "arch=compute_100a,code=sm_100a", "-o", exe,
+                    os.path.join(CPP, "test_kv_host_paged_gpu.cpp"), so, "-Xlinker", "-rpath", "-Xlinker",
+                    os.path.dirname(so)], check=True)
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "passed" in r.stdout
