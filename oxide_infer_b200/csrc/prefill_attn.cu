@@ -342,28 +342,17 @@ struct PfRun {
     uint32_t r0, r1, lo, hi;
 };
 
-// Finds the next run at or after row `next` that has keys to scan.  Every thread of the CTA walks
-// the same tables, so all warp roles see the same sequence of runs and tiles.
-__device__ __forceinline__ bool pf_next_run(uint32_t& next, uint32_t nrows, const uint64_t* s_kp,
-                                            const uint64_t* s_vp, const uint32_t* s_len,
-                                            uint32_t window, PfRun& run) {
-    while (next < nrows) {
-        const uint32_t r0 = next;
-        uint32_t r1 = r0 + 1;
-        while (r1 < nrows && s_kp[r1] == s_kp[r0] && s_vp[r1] == s_vp[r0]) r1++;
-        next = r1;
-        uint32_t lo = 0xffffffffu, hi = 0;
-        for (uint32_t i = r0; i < r1; i++) {
-            const uint32_t sl = s_len[i];
-            if (sl == 0) continue;  // skipped row
-            lo = min(lo, window_start(sl, window));
-            hi = max(hi, sl);
-        }
-        if (hi > lo) {
-            run.r0 = r0;
-            run.r1 = r1;
-            run.lo = lo;
-            run.hi = hi;
+// Takes the next run of the block's run list (built once per item by warp 0, see the kernel)
+// that has keys to scan.  Every warp role walks the same list, so all see the same sequence
+// of runs and tiles.
+__device__ __forceinline__ bool pf_next_run(uint32_t& next, uint32_t nruns, const uint32_t (*s_runs)[4], PfRun& run) {
+    while (next < nruns) {
+        const uint4 r = *reinterpret_cast<const uint4*>(s_runs[next++]);
+        if (r.w > r.z) {
+            run.r0 = r.x;
+            run.r1 = r.y;
+            run.lo = r.z;
+            run.hi = r.w;
             return true;
         }
     }
@@ -384,6 +373,9 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     extern __shared__ unsigned char smem_raw[];
     __shared__ uint64_t s_kp[BLK], s_vp[BLK];
     __shared__ uint32_t s_len[BLK];
+    __shared__ __align__(16) uint32_t s_runs[BLK][4];  // runs of equal pointers: first row, end row, first key, end key
+    __shared__ uint32_t s_nruns;
+    __shared__ uint32_t s_tile[2][3];  // per query tile: largest window start, smallest length, all 32 rows valid
     // loaders -> MMA warps (32 arrivals) and back (one tcgen05.commit from each MMA warp)
     __shared__ __align__(8) uint64_t bar_kfull[NS], bar_kempty[NS], bar_vfull[NS], bar_vempty[NS];
     // per query tile: S ready (commit), S read into registers (128 arrivals), P stored (128 arrivals),
@@ -450,42 +442,98 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     const int kvh = item & 3u;
     const uint32_t nrows = min((uint32_t)BLK, rows - row0);
 
-    // ---- tables of the block's rows
-    if (tid < BLK) {
-        uint64_t kp = 0, vp = 0;
-        uint32_t sl = 0;
-        if ((uint32_t)tid < nrows) {
-            const uint32_t r = row0 + tid;
-            sl = seq_lens[r];
-            bool too_long = false;
-            if (paged) {
-                // the run logic below only compares these two words: (table row + 1) * 16 keeps rows of one
-                // sequence equal, non-zero and "aligned"
-                kp = vp = ((uint64_t)row_seq[r] + 1ull) << 4;
-                too_long = sl != 0u && ((sl - 1u) >> pm.lbs) >= pm.max_blocks;  // more blocks than the table has columns
-            } else {
-                kp = k_ptrs[r];
-                vp = v_ptrs[r];
+    // ---- tables of the block's rows and the list of runs, by warp 0 (lane l: rows l and l + 32).
+    // A run is a maximal range of consecutive rows that share one cache (equal pointers); its key
+    // interval is the union of its rows' intervals.
+    if (warp_u == 0) {
+        uint64_t kp[2], vp[2];
+        uint32_t sl[2], ws[2];
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+            const uint32_t rr = (uint32_t)lane + 32u * hf;
+            kp[hf] = vp[hf] = 0;
+            sl[hf] = 0;
+            if (rr < nrows) {
+                const uint32_t r = row0 + rr;
+                sl[hf] = seq_lens[r];
+                bool too_long = false;
+                if (paged) {
+                    // the run logic below only compares these two words: (table row + 1) * 16 keeps rows of one
+                    // sequence equal, non-zero and "aligned"
+                    kp[hf] = vp[hf] = ((uint64_t)row_seq[r] + 1ull) << 4;
+                    too_long = sl[hf] != 0u && ((sl[hf] - 1u) >> pm.lbs) >= pm.max_blocks;  // more blocks than the table has columns
+                } else {
+                    kp[hf] = k_ptrs[r];
+                    vp[hf] = v_ptrs[r];
+                }
+                if (((kp[hf] | vp[hf]) & 15ull) != 0ull) {
+                    if (kvh == 0) atomicOr(status, DEV_MISALIGNED_PTR);
+                    sl[hf] = 0;
+                } else if (sl[hf] == 0u || too_long) {
+                    if (kvh == 0) atomicOr(status, DEV_BAD_SEQ_LEN);
+                    sl[hf] = 0;
+                }
             }
-            if (((kp | vp) & 15ull) != 0ull) {
-                if (kvh == 0) atomicOr(status, DEV_MISALIGNED_PTR);
-                sl = 0;
-            } else if (sl == 0u || too_long) {
-                if (kvh == 0) atomicOr(status, DEV_BAD_SEQ_LEN);
-                sl = 0;
+            ws[hf] = sl[hf] ? window_start(sl[hf], window) : 0u;
+            s_kp[rr] = kp[hf];
+            s_vp[rr] = vp[hf];
+            s_len[rr] = sl[hf];  // 0 marks a row that is skipped
+            s_runs[rr][0] = 0u;
+            s_runs[rr][1] = 0u;
+            s_runs[rr][2] = 0xffffffffu;
+            s_runs[rr][3] = 0u;
+        }
+        // a row starts a run when its pointers differ from the row before
+        uint32_t mask[2];
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+            uint64_t pk = __shfl_up_sync(0xffffffffu, kp[hf], 1), pv = __shfl_up_sync(0xffffffffu, vp[hf], 1);
+            const uint64_t k31 = __shfl_sync(0xffffffffu, kp[0], 31), v31 = __shfl_sync(0xffffffffu, vp[0], 31);
+            if (lane == 0) {
+                pk = k31;
+                pv = v31;
+            }
+            const uint32_t rr = (uint32_t)lane + 32u * hf;
+            const bool start = rr < nrows && (rr == 0u || kp[hf] != pk || vp[hf] != pv);
+            mask[hf] = __ballot_sync(0xffffffffu, start);
+        }
+        __syncwarp();
+        const uint64_t starts = (uint64_t)mask[0] | ((uint64_t)mask[1] << 32);
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+            const uint32_t rr = (uint32_t)lane + 32u * hf;
+            if (rr < nrows) {
+                const uint32_t id = (uint32_t)__popcll(starts & (~0ull >> (63u - rr))) - 1u;  // runs that start at or before rr
+                if (sl[hf] != 0u) {
+                    atomicMin(&s_runs[id][2], ws[hf]);
+                    atomicMax(&s_runs[id][3], sl[hf]);
+                }
+                if ((starts >> rr) & 1ull) {
+                    const uint64_t later = rr < 63u ? starts >> (rr + 1u) : 0ull;
+                    s_runs[id][0] = rr;
+                    s_runs[id][1] = later ? rr + (uint32_t)__ffsll((long long)later) : nrows;
+                }
+            }
+            // mask-free tiles of query tile hf need every one of its 32 rows: their common key range
+            const bool all = __all_sync(0xffffffffu, sl[hf] != 0u);
+            const uint32_t lo_max = __reduce_max_sync(0xffffffffu, ws[hf]);
+            const uint32_t hi_min = __reduce_min_sync(0xffffffffu, sl[hf]);
+            if (lane == 0) {
+                s_tile[hf][0] = lo_max;
+                s_tile[hf][1] = hi_min;
+                s_tile[hf][2] = all ? 1u : 0u;
             }
         }
-        s_kp[tid] = kp;
-        s_vp[tid] = vp;
-        s_len[tid] = sl;  // 0 marks a row that is skipped
+        if (lane == 0) s_nruns = (uint32_t)__popcll(starts);
     }
     __syncthreads();
+    const uint32_t nruns = s_nruns;
     // with a key-range split this unit takes tiles [t_lo, t_hi) of the block's tile sequence
     uint32_t t_lo = 0, t_hi = 0xffffffffu;
     if (kSplit) {
         uint32_t gt = 0, next = 0;
         PfRun run;
-        while (pf_next_run(next, nrows, s_kp, s_vp, s_len, window, run)) gt += (run.hi - run.lo + TK - 1) / TK;
+        while (pf_next_run(next, nruns, s_runs, run)) gt += (run.hi - run.lo + TK - 1) / TK;
         t_lo = (uint32_t)((uint64_t)gt * part / nparts);
         t_hi = (uint32_t)((uint64_t)gt * (part + 1u) / nparts);
     }
@@ -539,22 +587,14 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         uint32_t tflat = 0;                    // tiles of the block's runs before this one (key-range split)
         uint32_t next = 0;
         PfRun run;
-        while (pf_next_run(next, nrows, s_kp, s_vp, s_len, window, run)) {
+        while (pf_next_run(next, nruns, s_runs, run)) {
             // this thread's row: valid key interval inside the run, empty if not in the run
             const bool in = tok >= run.r0 && tok < run.r1 && s_len[tok] != 0;
             const uint32_t rhi = in ? s_len[tok] : 0u;
             const uint32_t rlo = in ? window_start(s_len[tok], window) : 0u;
             // key range that is valid for every row of this query tile (mask-free tiles)
-            uint32_t lo_max = 0, hi_min = 0xffffffffu;
-            bool full = run.r0 <= (uint32_t)(j * TOK) && run.r1 >= (uint32_t)(j * TOK + TOK);
-            if (full) {
-                for (int i = j * TOK; i < j * TOK + TOK; i++) {
-                    const uint32_t sl = s_len[i];
-                    if (sl == 0) full = false;
-                    lo_max = max(lo_max, window_start(sl, window));
-                    hi_min = min(hi_min, sl);
-                }
-            }
+            const uint32_t lo_max = s_tile[j][0], hi_min = s_tile[j][1];
+            const bool full = run.r0 <= (uint32_t)(j * TOK) && run.r1 >= (uint32_t)(j * TOK + TOK) && s_tile[j][2] != 0u;
             const uint32_t ntiles = (run.hi - run.lo + TK - 1) / TK;
             uint32_t tile0 = 0, tile1 = ntiles;  // this unit's tiles of the run
             if (kSplit) {
@@ -776,7 +816,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         } else {
             uint32_t next = 0;
             PfRun run;
-            while (pf_next_run(next, nrows, s_kp, s_vp, s_len, window, run)) {
+            while (pf_next_run(next, nruns, s_runs, run)) {
                 const uint32_t ntiles = (run.hi - run.lo + TK - 1) / TK;
                 for (uint32_t tile = 0; tile < ntiles; tile++) {
                     step(nt, nt >= 2, true, false);
@@ -803,7 +843,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         uint32_t tflat = 0;    // tiles of the block's runs before this one (key-range split)
         uint32_t next = 0;
         PfRun run;
-        while (pf_next_run(next, nrows, s_kp, s_vp, s_len, window, run)) {
+        while (pf_next_run(next, nruns, s_runs, run)) {
             const char* base = paged ? reinterpret_cast<const char*>(is_k ? pm.k_pool : pm.v_pool) + kvh * (HD * 2)
                                      : reinterpret_cast<const char*>(is_k ? s_kp[run.r0] : s_vp[run.r0]) + kvh * (HD * 2);
             const uint32_t ntiles = (run.hi - run.lo + TK - 1) / TK;
