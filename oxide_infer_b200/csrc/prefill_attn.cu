@@ -371,18 +371,19 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     // paged K/V: k_ptrs / v_ptrs are unused, wave row r reads row row_seq[r] of pm.block_tables
     constexpr bool paged = kPaged;
     extern __shared__ unsigned char smem_raw[];
-    __shared__ uint64_t s_kp[BLK], s_vp[BLK];
-    __shared__ uint32_t s_len[BLK];
-    __shared__ __align__(16) uint32_t s_runs[BLK][4];  // runs of equal pointers: first row, end row, first key, end key
-    __shared__ uint32_t s_nruns;
-    __shared__ uint32_t s_tile[2][3];  // per query tile: largest window start, smallest length, all 32 rows valid
+    // per-item tables, double buffered: the K loader prepares the next item's while the current one finishes
+    __shared__ uint64_t s_kp[2][BLK], s_vp[2][BLK];
+    __shared__ uint32_t s_len[2][BLK];
+    __shared__ __align__(16) uint32_t s_runs[2][BLK][4];  // runs of equal pointers: first row, end row, first key, end key
+    __shared__ uint32_t s_nruns[2];
+    __shared__ uint32_t s_tile[2][2][3];  // per query tile: largest window start, smallest length, all 32 rows valid
     // loaders -> MMA warps (32 arrivals) and back (one tcgen05.commit from each MMA warp)
     __shared__ __align__(8) uint64_t bar_kfull[NS], bar_kempty[NS], bar_vfull[NS], bar_vempty[NS];
     // per query tile: S ready (commit), S read into registers (128 arrivals), P stored (128 arrivals),
     // PV of a tile complete (commit), Q stored (128 arrivals), O final (commit)
     __shared__ __align__(8) uint64_t bar_sfull[2], bar_sfree[2], bar_pfull[2], bar_pvdone[2], bar_qfull[2], bar_ofull[2];
     __shared__ __align__(8) uint64_t bar_tok[2];  // issue token of MMA warp j
-    __shared__ uint32_t s_tmem, s_abort, s_item;
+    __shared__ uint32_t s_tmem, s_abort, s_item[2], s_unit[2];
 
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;  // 1024-byte aligned tiles
     const uint32_t q1_s = sbase, k_s = sbase + Q_BYTES, v_s = k_s + NS * KV_TILE;
@@ -428,24 +429,22 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     uint32_t n_burst = 0;  // MMA warps: bursts issued so far (phase of bar_tok)
     bool ok = true;
 
-  // ======== persistent loop over (64-row block, KV head) items, longest first ========
-  for (uint32_t it = 0;; ++it) {
-    __syncthreads();  // the previous item's tables are no longer in use
-    if (tid == 0) s_item = atomicAdd(counter, 1u);
-    __syncthreads();
-    const uint32_t item = s_item;
-    if (item >= nitems) break;
-    // work unit: a 64-row block, or (with a key-range split) one of its ns parts
-    const uint32_t ud = kSplit ? sp.units[item >> 2] : order[item >> 2];
-    const uint32_t row0 = (kSplit ? (ud & 0xffffu) : ud) * BLK;
-    const uint32_t part = kSplit ? (ud >> 16) & 0xffu : 0u, nparts = kSplit ? ud >> 24 : 1u;
-    const int kvh = item & 3u;
-    const uint32_t nrows = min((uint32_t)BLK, rows - row0);
-
-    // ---- tables of the block's rows and the list of runs, by warp 0 (lane l: rows l and l + 32).
+    // Claims the next item and prepares its tables in buffer `buf`; run by all lanes of the K loader warp
+    // while the other roles finish the current item (before the loop for the first item).
+    auto prepare_item = [&](uint32_t buf) {
+        uint32_t item = 0;
+        if (lane == 0) item = atomicAdd(counter, 1u);
+        item = __shfl_sync(0xffffffffu, item, 0);
+        if (lane == 0) s_item[buf] = item;
+        if (item >= nitems) return;
+        const uint32_t ud = kSplit ? sp.units[item >> 2] : order[item >> 2];
+        if (lane == 0) s_unit[buf] = ud;
+        const uint32_t row0 = (kSplit ? (ud & 0xffffu) : ud) * BLK;
+        const int kvh = item & 3u;
+        const uint32_t nrows = min((uint32_t)BLK, rows - row0);
+    // ---- tables of the block's rows and the list of runs, by one warp (lane l: rows l and l + 32).
     // A run is a maximal range of consecutive rows that share one cache (equal pointers); its key
     // interval is the union of its rows' intervals.
-    if (warp_u == 0) {
         uint64_t kp[2], vp[2];
         uint32_t sl[2], ws[2];
 #pragma unroll
@@ -475,13 +474,13 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                 }
             }
             ws[hf] = sl[hf] ? window_start(sl[hf], window) : 0u;
-            s_kp[rr] = kp[hf];
-            s_vp[rr] = vp[hf];
-            s_len[rr] = sl[hf];  // 0 marks a row that is skipped
-            s_runs[rr][0] = 0u;
-            s_runs[rr][1] = 0u;
-            s_runs[rr][2] = 0xffffffffu;
-            s_runs[rr][3] = 0u;
+            s_kp[buf][rr] = kp[hf];
+            s_vp[buf][rr] = vp[hf];
+            s_len[buf][rr] = sl[hf];  // 0 marks a row that is skipped
+            s_runs[buf][rr][0] = 0u;
+            s_runs[buf][rr][1] = 0u;
+            s_runs[buf][rr][2] = 0xffffffffu;
+            s_runs[buf][rr][3] = 0u;
         }
         // a row starts a run when its pointers differ from the row before
         uint32_t mask[2];
@@ -505,13 +504,13 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
             if (rr < nrows) {
                 const uint32_t id = (uint32_t)__popcll(starts & (~0ull >> (63u - rr))) - 1u;  // runs that start at or before rr
                 if (sl[hf] != 0u) {
-                    atomicMin(&s_runs[id][2], ws[hf]);
-                    atomicMax(&s_runs[id][3], sl[hf]);
+                    atomicMin(&s_runs[buf][id][2], ws[hf]);
+                    atomicMax(&s_runs[buf][id][3], sl[hf]);
                 }
                 if ((starts >> rr) & 1ull) {
                     const uint64_t later = rr < 63u ? starts >> (rr + 1u) : 0ull;
-                    s_runs[id][0] = rr;
-                    s_runs[id][1] = later ? rr + (uint32_t)__ffsll((long long)later) : nrows;
+                    s_runs[buf][id][0] = rr;
+                    s_runs[buf][id][1] = later ? rr + (uint32_t)__ffsll((long long)later) : nrows;
                 }
             }
             // mask-free tiles of query tile hf need every one of its 32 rows: their common key range
@@ -519,21 +518,41 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
             const uint32_t lo_max = __reduce_max_sync(0xffffffffu, ws[hf]);
             const uint32_t hi_min = __reduce_min_sync(0xffffffffu, sl[hf]);
             if (lane == 0) {
-                s_tile[hf][0] = lo_max;
-                s_tile[hf][1] = hi_min;
-                s_tile[hf][2] = all ? 1u : 0u;
+                s_tile[buf][hf][0] = lo_max;
+                s_tile[buf][hf][1] = hi_min;
+                s_tile[buf][hf][2] = all ? 1u : 0u;
             }
         }
-        if (lane == 0) s_nruns = (uint32_t)__popcll(starts);
-    }
+        if (lane == 0) s_nruns[buf] = (uint32_t)__popcll(starts);
+    };
+    if (warp_u == W_KLOAD) prepare_item(0u);
+
+  // ======== persistent loop over (64-row block, KV head) items, longest first ========
+  for (uint32_t it = 0;; ++it) {
+    // every role is done with the previous item; this item's tables (written by the K loader) are visible
     __syncthreads();
-    const uint32_t nruns = s_nruns;
+    const uint32_t buf = it & 1u;
+    const uint32_t item = s_item[buf];
+    if (item >= nitems) break;
+    const uint64_t* const c_kp = s_kp[buf];
+    const uint64_t* const c_vp = s_vp[buf];
+    const uint32_t* const c_len = s_len[buf];
+    const uint32_t (*const c_runs)[4] = s_runs[buf];
+    const uint32_t (*const c_tile)[3] = s_tile[buf];
+    const uint32_t nruns = s_nruns[buf];
+    // work unit: a 64-row block, or (with a key-range split) one of its ns parts
+    const uint32_t ud = s_unit[buf];
+    const uint32_t row0 = (kSplit ? (ud & 0xffffu) : ud) * BLK;
+    const uint32_t part = kSplit ? (ud >> 16) & 0xffu : 0u, nparts = kSplit ? ud >> 24 : 1u;
+    const int kvh = item & 3u;
+    const uint32_t nrows = min((uint32_t)BLK, rows - row0);
+
     // with a key-range split this unit takes tiles [t_lo, t_hi) of the block's tile sequence
     uint32_t t_lo = 0, t_hi = 0xffffffffu;
     if (kSplit) {
         uint32_t gt = 0, next = 0;
         PfRun run;
-        while (pf_next_run(next, nruns, s_runs, run)) gt += (run.hi - run.lo + TK - 1) / TK;
+        while (pf_next_run(next, nruns, c_runs, run)) gt += (run.hi - run.lo + TK - 1) / TK;
         t_lo = (uint32_t)((uint64_t)gt * part / nparts);
         t_hi = (uint32_t)((uint64_t)gt * (part + 1u) / nparts);
     }
@@ -587,14 +606,14 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         uint32_t tflat = 0;                    // tiles of the block's runs before this one (key-range split)
         uint32_t next = 0;
         PfRun run;
-        while (pf_next_run(next, nruns, s_runs, run)) {
+        while (pf_next_run(next, nruns, c_runs, run)) {
             // this thread's row: valid key interval inside the run, empty if not in the run
-            const bool in = tok >= run.r0 && tok < run.r1 && s_len[tok] != 0;
-            const uint32_t rhi = in ? s_len[tok] : 0u;
-            const uint32_t rlo = in ? window_start(s_len[tok], window) : 0u;
+            const bool in = tok >= run.r0 && tok < run.r1 && c_len[tok] != 0;
+            const uint32_t rhi = in ? c_len[tok] : 0u;
+            const uint32_t rlo = in ? window_start(c_len[tok], window) : 0u;
             // key range that is valid for every row of this query tile (mask-free tiles)
-            const uint32_t lo_max = s_tile[j][0], hi_min = s_tile[j][1];
-            const bool full = run.r0 <= (uint32_t)(j * TOK) && run.r1 >= (uint32_t)(j * TOK + TOK) && s_tile[j][2] != 0u;
+            const uint32_t lo_max = c_tile[j][0], hi_min = c_tile[j][1];
+            const bool full = run.r0 <= (uint32_t)(j * TOK) && run.r1 >= (uint32_t)(j * TOK + TOK) && c_tile[j][2] != 0u;
             const uint32_t ntiles = (run.hi - run.lo + TK - 1) / TK;
             uint32_t tile0 = 0, tile1 = ntiles;  // this unit's tiles of the run
             if (kSplit) {
@@ -677,7 +696,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         if (kSplit && nparts > 1u) {
             const uint32_t row = (uint32_t)(hw * 32 + lane);
             const size_t pidx = ((size_t)sp.slots[item >> 2] * NKV + kvh) * 2 + j;
-            const bool live = tok < nrows && s_len[tok] != 0;
+            const bool live = tok < nrows && c_len[tok] != 0;
             if (o_valid) {
                 ok &= mbar_wait_bounded(&bar_ofull[j], n_o & 1u, &s_abort);
                 ++n_o;
@@ -703,7 +722,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
             ++n_o;
             __syncwarp();
             tc_fence_after();
-            const bool write = tok < nrows && s_len[tok] != 0 && ok;
+            const bool write = tok < nrows && c_len[tok] != 0 && ok;
             const float inv = rcp_approx_ftz(l_run);
             const size_t rh = (size_t)(row0 + (write ? tok : 0u)) * NQ + head;
             const float sig = (gate && write) ? sigmoid_ref(h2f(gate[rh])) : 1.0f;
@@ -816,7 +835,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         } else {
             uint32_t next = 0;
             PfRun run;
-            while (pf_next_run(next, nruns, s_runs, run)) {
+            while (pf_next_run(next, nruns, c_runs, run)) {
                 const uint32_t ntiles = (run.hi - run.lo + TK - 1) / TK;
                 for (uint32_t tile = 0; tile < ntiles; tile++) {
                     step(nt, nt >= 2, true, false);
@@ -843,13 +862,13 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         uint32_t tflat = 0;    // tiles of the block's runs before this one (key-range split)
         uint32_t next = 0;
         PfRun run;
-        while (pf_next_run(next, nruns, s_runs, run)) {
+        while (pf_next_run(next, nruns, c_runs, run)) {
             const char* base = paged ? reinterpret_cast<const char*>(is_k ? pm.k_pool : pm.v_pool) + kvh * (HD * 2)
-                                     : reinterpret_cast<const char*>(is_k ? s_kp[run.r0] : s_vp[run.r0]) + kvh * (HD * 2);
+                                     : reinterpret_cast<const char*>(is_k ? c_kp[run.r0] : c_vp[run.r0]) + kvh * (HD * 2);
             const uint32_t ntiles = (run.hi - run.lo + TK - 1) / TK;
             // paged: lane l holds the block of page (tile's first page + l); a 64-key tile spans at most 5
             // blocks of >= 16 tokens; the next tile's entries are fetched while this tile is copied
-            const uint32_t* trow = paged ? pm.block_tables + (size_t)((s_kp[run.r0] >> 4) - 1ull) * pm.max_blocks : nullptr;
+            const uint32_t* trow = paged ? pm.block_tables + (size_t)((c_kp[run.r0] >> 4) - 1ull) * pm.max_blocks : nullptr;
             const uint32_t last_page = paged ? (run.hi - 1u) >> pm.lbs : 0u;
             auto fetch_pages = [&](uint32_t kb) -> uint32_t {
                 const uint32_t pg = (kb >> pm.lbs) + (uint32_t)lane;
@@ -919,6 +938,9 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         cp_async_wait<0>();
         fence_proxy_async_smem();
         for (; pending > 0; --pending) mbar_arrive(&full[(gk - pending) % NS]);
+        // all tiles of this item are on their way to the tensor core: claim the next item and prepare its
+        // tables while the other roles work through the last tiles
+        if (is_k) prepare_item(buf ^ 1u);
     }
   }  // item loop
 
