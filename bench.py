@@ -170,6 +170,7 @@ def cpu_baseline(seq_len: int, batch: int, budget_s: float = 12.0):
     import numpy as np
     from oracle import cpu as O
     O.build()
+    O.use_all_cores()
     rng = np.random.default_rng(0)
     f16 = lambda *s: rng.standard_normal(s, dtype=np.float32).astype(np.float16)
     b = batch

@@ -44,6 +44,8 @@ def lib() -> C.CDLL:
         L.orc_f2h.restype = C.c_uint16
         L.orc_f2h.argtypes = [C.c_float]
         L.orc_num_threads.restype = C.c_int
+        L.orc_set_num_threads.restype = None
+        L.orc_set_num_threads.argtypes = [C.c_int]
         _lib = L
     return _lib
 
@@ -61,6 +63,15 @@ def _u32(v):
 
 def num_threads() -> int:
     return int(lib().orc_num_threads())
+
+
+def use_all_cores() -> int:
+    """Lets the OpenMP loops use every core this process may run on, whatever OMP_NUM_THREADS says
+    (torch.distributed.run exports OMP_NUM_THREADS=1 to its workers).  Returns the thread count."""
+    import os
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_num_threads(n)
+    return num_threads()
 
 
 # --------------------------------------------------------------- helpers --

@@ -609,6 +609,17 @@ void orc_argmax(uint32_t* tokens_out, const uint16_t* logits, uint32_t vocab, ui
     }
 }
 
+/* Sets the number of OpenMP threads of the following calls (a launcher may have exported
+ * OMP_NUM_THREADS=1 for its worker processes); n <= 0 leaves it alone. */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+    extern void omp_set_num_threads(int);
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
     extern int omp_get_max_threads(void);
