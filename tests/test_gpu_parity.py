@@ -459,6 +459,39 @@ def test_prefill_attn(kv, ref, O, chunks, window):
         assert np.abs(mine - _np(rctx).astype(np.float32)).max() <= ATTN_TOL
 
 
+def test_prefill_attn_many_runs_per_block(kv, O):
+    """Run boundaries at every row: 70 single-row chunks of 70 requests (64 runs in the first block), then
+    two caches alternating row by row (equal pointers that are not neighbours must not merge), with
+    skipped rows (length 0) at the block's and the warp's edges."""
+    rng = np.random.default_rng(77)
+    chunks = [(1, int(p)) for p in rng.integers(0, 200, 70)]
+    q, gate, ks, vs, owner, slen = _prefill_case(chunks, 1, seed=77)
+    for case in range(2):
+        if case == 1:  # rows alternate between cache 0 and cache 1, lengths grow row by row
+            owner = [r & 1 for r in range(70)]
+            ks = [rng.standard_normal((300, NKV, HD), dtype=np.float32).astype(np.float16) for _ in (0, 1)]
+            vs = [rng.standard_normal((300, NKV, HD), dtype=np.float32).astype(np.float16) for _ in (0, 1)]
+            slen = np.array([100 + 2 * r for r in range(70)], np.uint32)
+            slen[[0, 31, 32, 63, 64]] = 0
+        rows = len(owner)
+        dk = [torch.from_numpy(a).cuda() for a in ks]
+        dv = [torch.from_numpy(a).cuda() for a in vs]
+        dq, dg = torch.from_numpy(q).cuda(), torch.from_numpy(gate).cuda()
+        kp, vp = dev_ptr_table([dk[i] for i in owner]), dev_ptr_table([dv[i] for i in owner])
+        ctx = torch.full((rows, NQ, HD), 5.0, dtype=torch.float16, device="cuda")
+        kv.prefill_attn(ctx, dq, dg, kp, vp, u32(slen), 0)
+        torch.cuda.synchronize()
+        status = kv.device_status()
+        mine = _np(ctx).astype(np.float32)
+        live = slen != 0
+        assert status == (0 if live.all() else 2)  # OXI_DEV_BAD_SEQ_LEN for the skipped rows
+        hk, hv = O.ptr_table([ks[i] for i in owner]), O.ptr_table([vs[i] for i in owner])
+        want = O.attn_online(q, hk, hv, np.where(live, slen, 1).astype(np.uint32), 0)
+        O.sigmoid_gate(want, gate)
+        assert np.abs(mine[live] - want.astype(np.float32)[live]).max() <= ATTN_TOL
+        assert (mine[~live] == 5.0).all()  # skipped rows are not written
+
+
 # ------------------------------------------------- fused append + decode --
 
 @pytest.mark.parametrize("lens,window", [([64, 100, 511, 300, 77, 256, 255, 129], 0),
