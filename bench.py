@@ -100,6 +100,12 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_min_mhz": sm[0] if sm else None,
                 "sm_max_mhz": self.max_mhz, "samples": len(sm), "reasons": reasons}
 
+    def wait_ready(self, timeout: float = 3.0):
+        """Blocks until the first sample is in (NVML start-up takes longer than a short timed region)."""
+        t0 = time.perf_counter()
+        while not self.sm and time.perf_counter() - t0 < timeout:
+            time.sleep(0.005)
+
     def stop(self):
         self.stop_flag = True
         self.join(timeout=6)
@@ -220,6 +226,7 @@ def run_ours(args, torch, rank, world, local_rank):
 
     sampler = ClockSampler(gpu_index(local_rank))
     sampler.start()
+    sampler.wait_ready()
     for _ in range(args.warmup):
         step()
     barrier()
@@ -395,6 +402,7 @@ def run_reference(args, torch, rank, world, local_rank):
 
     sampler = ClockSampler(gpu_index(local_rank))
     sampler.start()
+    sampler.wait_ready()
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
@@ -495,6 +503,7 @@ def run_conv(args, torch):
     ptrs = torch.tensor([[state[l, i].data_ptr() for i in range(b)] for l in range(nl)], dtype=torch.int64, device="cuda")
     sampler = ClockSampler(0)
     sampler.start()
+    sampler.wait_ready()
 
     def ours():
         for l in range(nl):
@@ -571,6 +580,7 @@ def run_sample(args, torch):
     hidden = torch.zeros(b, hid, dtype=torch.float16, device="cuda")
     sampler = ClockSampler(0)
     sampler.start()
+    sampler.wait_ready()
 
     def ours():
         for i in range(nbuf):
@@ -631,6 +641,7 @@ def run_decode_paged(args, torch):
     kv = KvPath(0, max_batch=BATCH, max_seq_len=CTX, max_prefill_rows=0)
     sampler = ClockSampler(0)
     sampler.start()
+    sampler.wait_ready()
     w0 = time.perf_counter()
 
     def timed(step):
@@ -735,6 +746,7 @@ def run_prefill(args, torch):
     ctx = torch.zeros(rows, NQ, HD, dtype=torch.float16, device="cuda")
     sampler = ClockSampler(0)
     sampler.start()
+    sampler.wait_ready()
 
     def attn():
         kv.prefill_attn(ctx, q, gate, kp, vp, dlen, 0)
@@ -831,6 +843,7 @@ def run_serving_mix(args, torch, rank, world, local_rank):
 
     sampler = ClockSampler(gpu_index(local_rank))
     sampler.start()
+    sampler.wait_ready()
     run64()  # warm-up pass (also the W >= 3 warm-up steps: 64 of them)
     barrier()
     reps = max(1, args.steps // steps)
