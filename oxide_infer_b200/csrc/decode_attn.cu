@@ -738,7 +738,10 @@ decode_merge_kernel(const DecodeParams p) {
 static dim3 merge_grid(const DecodeWorkspace& ws, uint32_t batch) {
     const uint32_t slices = (ws.max_chunks + MERGE_BLK - 1) / MERGE_BLK;
     uint32_t y = slices >= 4u ? slices : 1u;  // rows of fewer than 4 slices stay with one CTA
-    const uint32_t cap = (uint32_t)(16 * ws.num_sms) / (batch * NKV);  // about one resident wave of 128-thread CTAs
+#ifndef OXI_MERGE_CTAS_PER_SM
+#define OXI_MERGE_CTAS_PER_SM 16
+#endif
+    const uint32_t cap = (uint32_t)(OXI_MERGE_CTAS_PER_SM * ws.num_sms) / (batch * NKV);  // about one resident wave of 128-thread CTAs
     if (y > cap) y = cap;
     if (y > (uint32_t)MERGE_MAX_Y) y = MERGE_MAX_Y;
     if (y < 1u) y = 1u;
