@@ -689,7 +689,7 @@ def run_decode_paged(args, torch):
 
 def _prefill_long_prompt_leg(args, torch, rn):
     """A small wave of long prompts (2 requests, 128 new rows each, 32,768 keys of prefix): 16 work
-    items for 148 SMs unless the key-range split cuts the blocks into parts."""
+    items for 148 SMs unless the key-range split (the handle's default) cuts the blocks into parts."""
     import numpy as np
     from oxide_infer_b200 import KvPath
     nseq, new, prefix = 2, 128, 32768
@@ -706,7 +706,8 @@ def _prefill_long_prompt_leg(args, torch, rn):
     out = {"rows": rows, "prefix": prefix}
     for name, part_keys in (("unsplit", 0), ("split", 512)):
         kv = KvPath(0, max_batch=8, max_seq_len=prefix + new, max_prefill_rows=rows)
-        kv.prefill_split_configure(part_keys, 256 if part_keys else 0)
+        if not part_keys:
+            kv.prefill_split_configure(0, 0)  # a new handle splits small waves by default
         ms = _time_loop(torch, lambda: kv.prefill_attn(ctx, q, gate, kp, vp, dlen, 0), args.steps, args.warmup)
         out["us_" + name] = round(ms * 1e3, 1)
         out["status_" + name] = kv.device_status()

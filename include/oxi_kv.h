@@ -138,23 +138,27 @@ int32_t oxi_prefill_attn(oxi_handle* h, void* stream, void* ctx_out, const void*
                          const void* gate, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
                          const uint32_t* seq_lens, uint32_t rows, uint32_t window);
 
-/* Optional key-range split for small prefill waves (a few long prompts; the
- * reference's PREFILL_MAX_CONCURRENT = 32 admission limit, batch_engine.rs:93,
- * keeps waves small).  One work item of oxi_prefill_attn is a 64-row block on
- * one KV head; a wave with fewer items than the GPU has SMs leaves SMs idle for
- * as long as its longest block scans its keys.  After this call such waves cut
- * their long blocks into parts of equal key ranges - as many as fill the SMs
- * once, at most 32 per block, none shorter than min_part_keys - and merge the
- * parts' partial results (unnormalised sums, row maximum, row sum, f32) in a
- * second kernel.  `slots` partial results of oxi_prefill_split_slot_bytes()
- * each are reserved on the handle, one per part of a split block; a wave that
- * would need more runs unsplit, and so does every wave with at least as many
- * items as SMs.  Results stay within the attention tolerance of the unsplit
- * path (not bit-identical to it: the order of the sums changes) and are
- * reproducible from launch to launch.  min_part_keys = 0 or slots = 0 turns the
- * split off and frees the reservation; otherwise min_part_keys >= 256 and
- * slots <= 4096.  Synchronises the device; call it with no work of this handle
- * in flight.  Applies to oxi_prefill_attn and oxi_prefill_attn_paged. */
+/* Key-range split for small prefill waves (a few long prompts; the reference's
+ * PREFILL_MAX_CONCURRENT = 32 admission limit, batch_engine.rs:93, keeps waves
+ * small).  One work item of oxi_prefill_attn is a 64-row block on one KV head;
+ * a wave with fewer items than the GPU has SMs would leave SMs idle for as long
+ * as its longest block scans its keys.  Such waves cut their long blocks into
+ * parts of equal key ranges - as many as fill the SMs once, at most 32 per
+ * block, none shorter than min_part_keys - and merge the parts' partial results
+ * (unnormalised sums, row maximum, row sum, f32) in a second kernel.  `slots`
+ * partial results of oxi_prefill_split_slot_bytes() each are reserved on the
+ * handle, one per part of a split block; a wave that would need more runs
+ * unsplit, and so does every wave with at least as many items as SMs.
+ * oxi_create turns the split on for handles with max_prefill_rows > 0, with
+ * min_part_keys = OXI_PREFILL_SPLIT_DEFAULT_MIN_PART_KEYS and SMs / 4 + 3 slots
+ * (a split wave never has more parts than that); this call changes the setting.
+ * Results stay within the attention tolerance of the unsplit path (not
+ * bit-identical to it: the order of the sums changes) and are reproducible from
+ * launch to launch.  min_part_keys = 0 or slots = 0 turns the split off and
+ * frees the reservation; otherwise min_part_keys >= 256 and slots <= 4096.
+ * Synchronises the device; call it with no work of this handle in flight.
+ * Applies to oxi_prefill_attn and oxi_prefill_attn_paged. */
+#define OXI_PREFILL_SPLIT_DEFAULT_MIN_PART_KEYS 512u
 int32_t oxi_prefill_split_configure(oxi_handle* h, uint32_t min_part_keys, uint32_t slots);
 uint64_t oxi_prefill_split_slot_bytes(void);
 

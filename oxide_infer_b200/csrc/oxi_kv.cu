@@ -171,7 +171,15 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
         if (e == cudaSuccess) e = prefill_attn_init();
         if (e != cudaSuccess) { rc = cuda_fail(e, "cudaFuncSetAttribute"); goto bad; }
     }
-    OXI_CUDA(cudaDeviceSynchronize(), "oxi_create sync");
+    if (cudaDeviceSynchronize() != cudaSuccess) {
+        rc = cuda_fail(cudaGetLastError(), "oxi_create sync");
+        goto bad;
+    }
+    // Small prefill waves spread their long blocks over idle SMs by default: a split wave has at most
+    // one (block part, KV head) item per SM, hence at most num_sms / 4 parts in flight.
+    if (max_prefill_rows && (rc = oxi_prefill_split_configure(h, OXI_PREFILL_SPLIT_DEFAULT_MIN_PART_KEYS,
+                                                              (uint32_t)h->num_sms / NKV + 3u)))
+        goto bad;
     *out = h;
     return OXI_OK;
 bad:

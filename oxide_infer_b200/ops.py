@@ -161,7 +161,8 @@ class KvPath:
         """Key-range split of small prefill waves: waves with fewer (block, KV head) items than SMs cut
         their long blocks into equal key ranges (enough to fill the SMs once, at most 32 per block, none
         shorter than min_part_keys), with `slots` partial results reserved on the handle
-        (prefill_split_slot_bytes() each).  min_part_keys = 0 or slots = 0 turns it off.  Synchronises."""
+        (prefill_split_slot_bytes() each).  On by default (512 keys, SMs / 4 + 3 slots) for handles with
+        max_prefill_rows > 0; min_part_keys = 0 or slots = 0 turns it off.  Synchronises."""
         _check(self.lib.oxi_prefill_split_configure(self.h, min_part_keys, slots), "oxi_prefill_split_configure")
 
     def prefill_split_slot_bytes(self) -> int:

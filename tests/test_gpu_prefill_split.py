@@ -57,6 +57,7 @@ def kvs():
     a = KvPath(0, max_batch=8, max_seq_len=40960, max_prefill_rows=4096)
     a.prefill_split_configure(256, 256)
     b = KvPath(0, max_batch=8, max_seq_len=40960, max_prefill_rows=4096)
+    b.prefill_split_configure(0, 0)  # the split is on by default
     return a, b
 
 
@@ -117,6 +118,10 @@ def test_waves_that_do_not_qualify_are_bit_identical(kvs):
     assert torch.equal(w.run(split, 0).view(torch.int16), w.run(plain, 0).view(torch.int16))
     # more parts than reserved slots: runs unsplit
     few = KvPath(0, max_batch=8, max_seq_len=40960, max_prefill_rows=4096)
+    # a new handle splits by default, with a reservation no split wave can exceed
+    w = Wave([(4000, 128)], seed=14)
+    assert not torch.equal(w.run(few, 0).view(torch.int16), w.run(plain, 0).view(torch.int16))
+    assert np.abs(w.run(few, 0).float().cpu().numpy() - w.oracle(0)).max() <= ATTN_TOL
     few.prefill_split_configure(256, 4)
     w = Wave([(4000, 128)], seed=14)
     assert torch.equal(w.run(few, 0).view(torch.int16), w.run(plain, 0).view(torch.int16))
