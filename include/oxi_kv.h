@@ -162,6 +162,17 @@ int32_t oxi_prefill_attn(oxi_handle* h, void* stream, void* ctx_out, const void*
 int32_t oxi_prefill_split_configure(oxi_handle* h, uint32_t min_part_keys, uint32_t slots);
 uint64_t oxi_prefill_split_slot_bytes(void);
 
+/* Registers the slab that holds the K/V caches (the reference keeps every
+ * sequence's K and V rows of all layers in one slab, kv_pool.rs:31-61).  Rows of
+ * oxi_prefill_attn whose k_ptrs / v_ptrs entry lies a whole number of 1024-byte
+ * rows from `base` and inside the slab are then loaded by the TMA unit (tiled
+ * tensor copies with the 128-byte swizzle) instead of by per-thread 16-byte
+ * copies; other rows, and the ragged last tile of a sequence, keep the
+ * per-thread path, so any table stays legal and the results are bit-identical
+ * either way.  One slab per handle; base = NULL or bytes = 0 unregisters.
+ * Host-side only (encodes a tensor map), nothing is enqueued. */
+int32_t oxi_register_kv_slab(oxi_handle* h, const void* base, uint64_t bytes);
+
 /* One-token causal conv1d + gating with the 6-slot carry state, one launch.
  * Replaces batched_fused_causal_conv1d_gating_ptr_fp16 (batched_attn.rs:727-881,
  * launched at batch_engine.rs:840-899).

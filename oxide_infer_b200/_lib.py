@@ -31,6 +31,7 @@ SIGNATURES = {
     "oxi_append_decode_paged": [_vp] * 13 + [_u32, _u32, _f32],
     "oxi_prefill_attn_paged": [_vp] * 8 + [_u32, _u32],
     "oxi_prefill_split_configure": [_vp, _u32, _u32],
+    "oxi_register_kv_slab": [_vp, _vp, C.c_uint64],
     "oxi_prefill_split_slot_bytes": [],
     "oxi_embed_lookup": [_vp] * 5 + [_u32, _u32, _u32],
     "oxi_argmax": [_vp] * 4 + [_u32, _u32],

@@ -50,6 +50,17 @@ uint32_t decode_chunk_keys();    // keys per split-KV work item
 uint32_t decode_max_rows();      // rows one launch can take
 size_t decode_merge_scratch_bytes(uint32_t max_batch, uint32_t max_chunks);
 
+// A K/V slab registered for TMA loads in prefill attention: a tiled tensor map (128 bytes, opaque to
+// everything but the driver and the TMA unit) over rows of 1024 bytes starting at `base`.
+struct alignas(64) TmaDesc {
+    uint64_t opaque[16];
+};
+struct PrefillSlab {
+    TmaDesc map;     // 2-D f16 tensor {512 elements, rows}, box {64, 64}, 128-byte swizzle
+    uint64_t base;   // device address of row 0
+    uint32_t rows;   // 0: no slab registered
+};
+
 // Workspace of the key-range split of prefill attention (small waves of long prompts).
 struct PrefillSplitWs {
     uint32_t* units;     // prefill_split_table_bytes(): unit, slot and block tables
@@ -66,7 +77,8 @@ cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* 
                                 const PagedMap* pm = nullptr /* paged K/V: k_ptrs / v_ptrs unused */,
                                 const uint32_t* row_seq = nullptr /* paged: table row of each wave row */,
                                 const PrefillSplitWs* split = nullptr /* key-range split of small waves */,
-                                uint32_t part_keys = 0 /* keys per part; 0: no split */);
+                                uint32_t part_keys = 0 /* keys per part; 0: no split */,
+                                const PrefillSlab* slab = nullptr /* K/V rows inside it are loaded by TMA */);
 size_t prefill_split_slot_bytes();   // partial-result bytes per slot of PrefillSplitWs::part
 size_t prefill_split_table_bytes();  // bytes of PrefillSplitWs::units
 

@@ -2,6 +2,8 @@
 // validation, and the launch sequences behind each exported operator.
 #include "../../include/oxi_kv.h"
 
+#include <cuda.h>  // CUtensorMap and its enums only; the encoder is fetched through the runtime
+
 #include <cstdio>
 #include <cstring>
 #include <new>
@@ -22,6 +24,7 @@ struct oxi_handle {
     uint32_t* am_count;   // [max_batch] arrival counters, zero between launches
     PrefillSplitWs pf_split;  // reserved by oxi_prefill_split_configure
     uint32_t pf_part_keys;    // keys per part of a split block; 0: off
+    PrefillSlab pf_slab;      // registered by oxi_register_kv_slab; rows == 0: none
     // staging for the host-buffer entry, one layer at a time, double buffered
     void* stg_q[2];       // [max_batch][16][128]
     void* stg_k[2];       // [max_batch][4][128]
@@ -390,6 +393,38 @@ int32_t oxi_prefill_split_configure(oxi_handle* h, uint32_t part_keys, uint32_t 
     return OXI_OK;
 }
 
+int32_t oxi_register_kv_slab(oxi_handle* h, const void* base, uint64_t bytes) {
+    REQ_HANDLE("oxi_register_kv_slab");
+    h->pf_slab = PrefillSlab{};
+    if (!base || bytes == 0) return OXI_OK;  // unregistered
+    if (((uintptr_t)base & 15u) != 0u) return fail(OXI_ERR_ARG, "oxi_register_kv_slab: base must be 16-byte aligned");
+    const uint64_t rows = bytes / KV_ROW_BYTES;
+    if (rows == 0 || rows > 0x7fffffffull) return fail(OXI_ERR_ARG, "oxi_register_kv_slab: 1 .. 2^31-1 rows of 1024 bytes");
+    typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    OXI_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres), "cudaGetDriverEntryPoint");
+    if (!fn || qres != cudaDriverEntryPointSuccess) return fail(OXI_ERR_NO_DEVICE, "oxi_register_kv_slab: driver has no cuTensorMapEncodeTiled");
+    static_assert(sizeof(CUtensorMap) == sizeof(TmaDesc), "tensor map size");
+    // rows of [4 KV heads][128] f16; a box is 64 rows x 64 elements (128 bytes, one swizzle span)
+    const cuuint64_t dims[2] = {(cuuint64_t)(NKV * HD), (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)KV_ROW_BYTES};
+    const cuuint32_t box[2] = {64u, 64u};
+    const cuuint32_t estr[2] = {1u, 1u};
+    PrefillSlab s{};
+    const CUresult r = ((encode_fn)fn)(reinterpret_cast<CUtensorMap*>(&s.map), CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                                       const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(OXI_ERR_ARG, "oxi_register_kv_slab: cuTensorMapEncodeTiled rejected the slab");
+    s.base = (uint64_t)(uintptr_t)base;
+    s.rows = (uint32_t)rows;
+    h->pf_slab = s;
+    return OXI_OK;
+}
+
 int32_t oxi_prefill_attn_paged(oxi_handle* h, void* stream, void* ctx_out, const void* q, const void* gate,
                                const oxi_paged_layout* layout, const uint32_t* row_seq, const uint32_t* seq_lens,
                                uint32_t rows, uint32_t window) {
@@ -400,7 +435,7 @@ int32_t oxi_prefill_attn_paged(oxi_handle* h, void* stream, void* ctx_out, const
     if (int32_t rc = paged_map(layout, "oxi_prefill_attn_paged", &pm)) return rc;
     OXI_CUDA(launch_prefill_attn((cudaStream_t)stream, ctx_out, q, gate, nullptr, nullptr, seq_lens, rows, window,
                                  h->dws.status, h->num_sms, h->pf_order, h->dws.status + 48, &pm, row_seq,
-                                 &h->pf_split, h->pf_part_keys),
+                                 &h->pf_split, h->pf_part_keys, nullptr),
              "prefill_attn_paged launch");
     return OXI_OK;
 }
@@ -413,7 +448,7 @@ int32_t oxi_prefill_attn(oxi_handle* h, void* stream, void* ctx_out, const void*
     REQ_BATCH(rows, h->max_prefill_rows, "oxi_prefill_attn");
     OXI_CUDA(launch_prefill_attn((cudaStream_t)stream, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens,
                                  rows, window, h->dws.status, h->num_sms, h->pf_order, h->dws.status + 48, nullptr,
-                                 nullptr, &h->pf_split, h->pf_part_keys),
+                                 nullptr, &h->pf_split, h->pf_part_keys, &h->pf_slab),
              "prefill_attn launch");
     return OXI_OK;
 }

@@ -359,14 +359,24 @@ __device__ __forceinline__ bool pf_next_run(uint32_t& next, uint32_t nruns, cons
     return false;
 }
 
-template <bool kPaged, bool kSplit>
+// One 64-row x 64-element box of a registered K/V slab into a 128-byte-swizzled sub-tile; completion
+// is counted in bytes on `bar`.  x is a multiple of 64 elements (128 bytes), so the 16-byte rule holds.
+__device__ __forceinline__ void tma_load_box(uint32_t dst, const TmaDesc* map, uint32_t x, uint32_t y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+template <bool kPaged, bool kSplit, bool kTma>
 __global__ void __launch_bounds__(pf::THREADS, 1)
 prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__ q,
                     const uint16_t* __restrict__ gate, const uint64_t* __restrict__ k_ptrs,
                     const uint64_t* __restrict__ v_ptrs, const uint32_t* __restrict__ seq_lens,
                     uint32_t rows, uint32_t window, uint32_t* __restrict__ status,
                     const uint32_t* __restrict__ order, uint32_t* __restrict__ counter,
-                    const PagedMap pm, const uint32_t* __restrict__ row_seq, const PfSplit sp) {
+                    const PagedMap pm, const uint32_t* __restrict__ row_seq, const PfSplit sp,
+                    const __grid_constant__ TmaDesc tmap, const uint64_t slab_base, const uint32_t slab_rows) {
     using namespace pf;
     // paged K/V: k_ptrs / v_ptrs are unused, wave row r reads row row_seq[r] of pm.block_tables
     constexpr bool paged = kPaged;
@@ -889,11 +899,38 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                 tflat += ntiles;
             }
             uint32_t pg_next = (paged && tile0 < tile1) ? fetch_pages(run.lo + tile0 * TK) : 0u;
+            // Rows of a registered slab (at a whole number of 1024-byte rows from its base) come through the
+            // TMA unit: two boxes per full tile, written in the same swizzled layout, completion counted on
+            // the stage's barrier.  The run's ragged last tile keeps the zero-filling copies below.
+            bool tma_run = false;
+            uint32_t tma_y0 = 0;
+            if (kTma) {
+                const uint64_t ptr = is_k ? c_kp[run.r0] : c_vp[run.r0];
+                const uint64_t off = ptr - slab_base;
+                tma_run = ptr >= slab_base && (off & 1023ull) == 0ull && (off >> 10) + run.hi <= (uint64_t)slab_rows;
+                tma_y0 = (uint32_t)(off >> 10);
+                if (tma_run && pending) {  // tiles of an earlier run still in flight as plain copies
+                    cp_async_wait<0>();
+                    fence_proxy_async_smem();
+                    for (; pending > 0; --pending) mbar_arrive(&full[(gk - pending) % NS]);
+                }
+            }
             for (uint32_t tile = tile0; tile < tile1; tile++) {
                 const uint32_t st = gk % NS;
                 // the MMAs that read this stage's previous tile have completed (first use: passes at once)
                 ok &= mbar_wait_bounded(&empty[st], ((gk / NS) & 1u) ^ 1u, &s_abort);
                 const uint32_t kbeg = run.lo + tile * TK;
+                if (kTma && tma_run && kbeg + TK <= run.hi) {
+                    if (lane == 0 && ok) {  // after a wait gave up nothing more is copied
+                        mbar_arrive_expect_tx(&full[st], (uint32_t)KV_TILE);
+                        tma_load_box(ring + st * KV_TILE, &tmap, (uint32_t)kvh * HD, tma_y0 + kbeg, &full[st]);
+                        tma_load_box(ring + st * KV_TILE + KV_SUB, &tmap, (uint32_t)kvh * HD + 64u, tma_y0 + kbeg, &full[st]);
+                    } else {
+                        mbar_arrive(&full[st]);
+                    }
+                    ++gk;
+                    continue;
+                }
                 const uint32_t dst = ring + st * KV_TILE + (c >> 3) * KV_SUB;
                 const char* src = base + (size_t)(kbeg + r0) * KV_ROW_BYTES + c * 16;
                 if (paged) {
@@ -927,7 +964,12 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                 cp_async_commit();
                 ++pending;
                 ++gk;
-                if (pending == DEPTH) {  // the oldest tile in flight has landed: publish it to the tensor core
+                if (kTma && tma_run) {  // the one ragged tile of a run loaded by TMA: publish it at once
+                    cp_async_wait<0>();
+                    fence_proxy_async_smem();
+                    mbar_arrive(&full[(gk - 1u) % NS]);
+                    --pending;
+                } else if (pending == DEPTH) {  // the oldest tile in flight has landed: publish it to the tensor core
                     cp_async_wait<DEPTH - 1>();
                     fence_proxy_async_smem();
                     mbar_arrive(&full[(gk - DEPTH) % NS]);
@@ -1028,24 +1070,31 @@ prefill_merge_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict_
 size_t prefill_split_table_bytes() { return (size_t)3 * 1024 * PF_MAX_SPLIT * sizeof(uint32_t); }
 size_t prefill_split_slot_bytes() { return (size_t)NKV * 2 * pf::M * (HD + 2) * sizeof(float); }
 
-cudaError_t prefill_attn_init() {
-    cudaError_t e = cudaSuccess;
-    const int smem = (int)pf::SMEM_BYTES;
-    if ((e = cudaFuncSetAttribute(prefill_attn_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return e;
-    if ((e = cudaFuncSetAttribute(prefill_attn_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return e;
-    if ((e = cudaFuncSetAttribute(prefill_attn_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem))) return e;
-    return cudaFuncSetAttribute(prefill_attn_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+template <bool kPaged, bool kSplit, bool kTma>
+static cudaError_t pf_set_smem() {
+    return cudaFuncSetAttribute(prefill_attn_kernel<kPaged, kSplit, kTma>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)pf::SMEM_BYTES);
 }
 
-template <bool kPaged, bool kSplit>
+cudaError_t prefill_attn_init() {
+    cudaError_t e = cudaSuccess;
+    if ((e = pf_set_smem<false, false, false>())) return e;
+    if ((e = pf_set_smem<true, false, false>())) return e;
+    if ((e = pf_set_smem<false, true, false>())) return e;
+    if ((e = pf_set_smem<true, true, false>())) return e;
+    if ((e = pf_set_smem<false, false, true>())) return e;
+    return pf_set_smem<false, true, true>();
+}
+
+template <bool kPaged, bool kSplit, bool kTma>
 static cudaError_t launch_pf(cudaStream_t stream, uint32_t grid, void* ctx_out, const void* q, const void* gate,
                              const uint64_t* k_ptrs, const uint64_t* v_ptrs, const uint32_t* seq_lens, uint32_t rows,
                              uint32_t window, uint32_t* status, uint32_t* order, uint32_t* counter, const PagedMap& pm,
-                             const uint32_t* row_seq, const PfSplit& sp) {
+                             const uint32_t* row_seq, const PfSplit& sp, const PrefillSlab& slab) {
     // programmatic dependent of the plan kernel: TMEM allocation and barrier set-up overlap it
-    return launch_pdl(prefill_attn_kernel<kPaged, kSplit>, dim3(grid), dim3(pf::THREADS), pf::SMEM_BYTES, stream,
+    return launch_pdl(prefill_attn_kernel<kPaged, kSplit, kTma>, dim3(grid), dim3(pf::THREADS), pf::SMEM_BYTES, stream,
                       (uint16_t*)ctx_out, (const uint16_t*)q, (const uint16_t*)gate, k_ptrs, v_ptrs, seq_lens, rows,
-                      window, status, (const uint32_t*)order, counter, pm, row_seq, sp);
+                      window, status, (const uint32_t*)order, counter, pm, row_seq, sp, slab.map, slab.base, slab.rows);
 }
 
 cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* q,
@@ -1053,7 +1102,7 @@ cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* 
                                 const uint32_t* seq_lens, uint32_t rows, uint32_t window,
                                 uint32_t* status, int num_sms, uint32_t* order, uint32_t* counter,
                                 const PagedMap* pm, const uint32_t* row_seq, const PrefillSplitWs* ws,
-                                uint32_t part_keys) {
+                                uint32_t part_keys, const PrefillSlab* slab) {
     const uint32_t nblocks = (rows + pf::BLK - 1) / pf::BLK;
     // the split is for waves that leave SMs idle; larger waves balance by claiming longest first
     const bool split = ws && ws->max_slots != 0u && part_keys != 0u && nblocks * NKV < (uint32_t)num_sms;
@@ -1075,19 +1124,22 @@ cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* 
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     const PagedMap map = pm ? *pm : PagedMap{};
+    const PrefillSlab none{};
+    const bool tma = !pm && slab && slab->rows != 0u;
+    const PrefillSlab& sl = tma ? *slab : none;
+#define OXI_PF_ARGS ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, rows, window, status, order, counter, map, row_seq, sp, sl
     if (!split) {
         const uint32_t nitems = nblocks * NKV;
         const uint32_t grid = nitems < (uint32_t)num_sms ? nitems : (uint32_t)num_sms;
-        return pm ? launch_pf<true, false>(stream, grid, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, rows, window, status,
-                                           order, counter, map, row_seq, sp)
-                  : launch_pf<false, false>(stream, grid, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, rows, window, status,
-                                            order, counter, map, row_seq, sp);
+        if (pm) return launch_pf<true, false, false>(stream, grid, OXI_PF_ARGS);
+        return tma ? launch_pf<false, false, true>(stream, grid, OXI_PF_ARGS)
+                   : launch_pf<false, false, false>(stream, grid, OXI_PF_ARGS);
     }
     // the unit count is only known on the device: one CTA per SM, those without a unit leave at once
-    e = pm ? launch_pf<true, true>(stream, (uint32_t)num_sms, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, rows, window,
-                                   status, order, counter, map, row_seq, sp)
-           : launch_pf<false, true>(stream, (uint32_t)num_sms, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, rows, window,
-                                    status, order, counter, map, row_seq, sp);
+    const uint32_t grid = (uint32_t)num_sms;
+    if (pm) e = launch_pf<true, true, false>(stream, grid, OXI_PF_ARGS);
+    else e = tma ? launch_pf<false, true, true>(stream, grid, OXI_PF_ARGS) : launch_pf<false, true, false>(stream, grid, OXI_PF_ARGS);
+#undef OXI_PF_ARGS
     if (e != cudaSuccess) return e;
     // a plain launch: as a programmatic dependent it measured no faster
     prefill_merge_kernel<<<nblocks * 8 * 32, 128, 0, stream>>>((uint16_t*)ctx_out, (const uint16_t*)gate, rows, sp);

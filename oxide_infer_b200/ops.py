@@ -165,6 +165,15 @@ class KvPath:
         max_prefill_rows > 0; min_part_keys = 0 or slots = 0 turns it off.  Synchronises."""
         _check(self.lib.oxi_prefill_split_configure(self.h, min_part_keys, slots), "oxi_prefill_split_configure")
 
+    def register_kv_slab(self, slab):
+        """K/V rows of prefill attention that lie inside `slab` (a torch tensor, or None to unregister) at a whole
+        number of 1024-byte rows from its start are loaded by the TMA unit."""
+        if slab is None:
+            _check(self.lib.oxi_register_kv_slab(self.h, None, 0), "oxi_register_kv_slab")
+        else:
+            _check(self.lib.oxi_register_kv_slab(self.h, _p(slab), slab.numel() * slab.element_size()),
+                   "oxi_register_kv_slab")
+
     def prefill_split_slot_bytes(self) -> int:
         return int(self.lib.oxi_prefill_split_slot_bytes())
 

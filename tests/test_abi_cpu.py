@@ -62,6 +62,7 @@ def test_create_without_gpu_fails_cleanly(lib):
     assert lib.oxi_append_decode_paged(None, *([None] * 12), 1, 0, 1e-5) == -1
     assert lib.oxi_prefill_attn_paged(None, *([None] * 7), 1, 0) == -1
     assert lib.oxi_prefill_split_configure(None, 256, 16) == -1
+    assert lib.oxi_register_kv_slab(None, None, 0) == -1
     assert lib.oxi_prefill_split_slot_bytes() == 4 * 2 * 128 * 130 * 4
 
 
