@@ -763,6 +763,8 @@ def run_prefill(args, torch):
     ms_wave = _time_loop(torch, wave, args.steps, args.warmup)
     ms_attn = _time_loop(torch, attn, args.steps, args.warmup)
     clocks = sampler.window(w0, time.perf_counter())
+    # the same wave through a sliding-window layer (the reference's model has 5 of them, window 256)
+    ms_attn_w256 = _time_loop(torch, lambda: kv.prefill_attn(ctx, q, gate, kp, vp, dlen, 256), args.steps, args.warmup)
     kv.register_kv_slab(slab)  # the same wave with TMA tile copies instead of per-thread 16-byte copies
     ms_attn_tma = _time_loop(torch, attn, args.steps, args.warmup)
     kv.register_kv_slab(None)
@@ -791,6 +793,7 @@ def run_prefill(args, torch):
     return {"metric": "prefill_attention_tflops", "value": round(tf, 2), "unit": "TFLOP/s", "n_gpus": 1,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_wave, 4),
             "ms_attention_only": round(ms_attn, 4), "ms_attention_only_registered_slab_tma": round(ms_attn_tma, 4),
+            "ms_attention_only_window_256": round(ms_attn_w256, 4),
             "higher_is_better": True, "dtype": "f16", "data": "synthetic",
             "config": {"workload": "prefill_wave_32seq_x128tok_prefix_U0_8192_one_layer", "rows": rows,
                        "prefix_sum": int(prefix.sum()), "causal_exact_flops": flops, "algorithmic_bytes": kv_bytes},
