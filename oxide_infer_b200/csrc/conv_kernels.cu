@@ -62,114 +62,159 @@ conv_decode_kernel(uint16_t* __restrict__ y_out, const uint64_t* __restrict__ co
 // (j = local_pos-6+k >= 0) or carry[c][6+j] (j < 0).  The chunk's last row also writes the state
 // the request must carry forward into `stage[row]` (committed by pass 2, because other rows of the
 // chunk may still be reading the carry state).
-// A thread walks PF_ROWS consecutive wave rows for its 4 channels and keeps the 6 history products
-// in registers: while the next row continues the same chunk the window just slides (one f16 product
-// in, one out), otherwise it is rebuilt from the chunk's earlier rows of `bcx` and / or the carried
-// state.  Every row of bcx is thus read (PF_ROWS + 6) / PF_ROWS times instead of 7; PF_ROWS is kept small
-// because a wave has few rows (4096 x 512 thread columns) and rows of a thread are sequential.
-#ifndef OXI_PF_ROWS
-#define OXI_PF_ROWS 8
+// A CTA takes CT_ROWS wave rows x CT_CH channels.  All its global loads are
+// issued at once (B and x of the tile's rows and of the 6 rows before it, C and the tables of its own
+// rows), the f32 products B*x go to shared memory, and after one barrier every thread forms the
+// outputs of its rows from shared memory: history taps are the f16-rounded products of the six rows
+// before (or carried state for the first six rows of a chunk), the newest tap the unrounded product.
+// One memory round trip per CTA instead of one per row (a thread that walked 8 consecutive rows with the
+// window in registers: 26.6 us for a 4096-row wave, this kernel 25.6 us; tiles of 32 rows or 128 channels
+// measured 1-2 us slower); every row of bcx is fetched (CT_ROWS + 6) / CT_ROWS times, from L2.
+#ifndef OXI_CT_ROWS
+#define OXI_CT_ROWS 16
 #endif
-constexpr int PF_ROWS = OXI_PF_ROWS;  // consecutive wave rows per thread
+#ifndef OXI_CT_CH
+#define OXI_CT_CH 256
+#endif
+#ifndef OXI_CT_PASS
+#define OXI_CT_PASS 4
+#endif
+#ifndef OXI_CT_MINB
+#define OXI_CT_MINB 4
+#endif
+constexpr int CT_ROWS = OXI_CT_ROWS, CT_CH = OXI_CT_CH, CT_PASS = OXI_CT_PASS;  // rows covered by the CTA at once
+constexpr int CT_THREADS = CT_PASS * (CT_CH / 4), CT_HALO = CONV_S;
+constexpr int CT_LOADS = (CT_ROWS + CT_HALO + CT_PASS - 1) / CT_PASS;  // row slots per thread in the load phase: 10
+constexpr int CT_OUT = CT_ROWS / CT_PASS;                           // output rows per thread: 8
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(CT_THREADS, OXI_CT_MINB)
 conv_prefill_kernel(uint16_t* __restrict__ y_out, const uint64_t* __restrict__ carry_ptrs,
-                    const uint32_t* __restrict__ origin, const uint32_t* __restrict__ local_pos,
-                    const uint16_t* __restrict__ bcx, const uint16_t* __restrict__ conv_w,
-                    uint32_t rows, uint16_t* __restrict__ stage, uint32_t* __restrict__ status) {
-    const uint32_t r_begin = blockIdx.y * PF_ROWS;
-    const uint32_t r_end = min(rows, r_begin + (uint32_t)PF_ROWS);
-    const uint32_t c0 = (blockIdx.x * 128 + threadIdx.x) * 4;
+                         const uint32_t* __restrict__ origin, const uint32_t* __restrict__ local_pos,
+                         const uint16_t* __restrict__ bcx, const uint16_t* __restrict__ conv_w,
+                         uint32_t rows, uint16_t* __restrict__ stage, uint32_t* __restrict__ status) {
+    __shared__ __align__(16) float prod[CT_ROWS + CT_HALO][CT_CH];  // B*x, row i = wave row r_tile - 6 + i
+    __shared__ uint64_t s_cp[CT_ROWS];
+    __shared__ int32_t s_lpos[CT_ROWS];
+    __shared__ uint32_t s_last[CT_ROWS];
+    pdl_launch_dependents();
+    const uint32_t r_tile = blockIdx.y * CT_ROWS;
+    const uint32_t tx = threadIdx.x % (CT_CH / 4), ty = threadIdx.x / (CT_CH / 4);
+    const uint32_t c0 = blockIdx.x * CT_CH + tx * 4;
 
+    // ---- all loads
+    union U2 { uint2 v; uint16_t h[4]; };
+    U2 vb[CT_LOADS], vx[CT_LOADS], vc[CT_OUT];
+#pragma unroll
+    for (int it = 0; it < CT_LOADS; it++) {
+        const int32_t i = (int32_t)ty + CT_PASS * it;
+        const int64_t g = (int64_t)r_tile + i - CT_HALO;
+        const bool valid = i < CT_ROWS + CT_HALO && g >= 0 && g < (int64_t)rows;
+        const uint16_t* row = bcx + (size_t)(valid ? g : 0) * 3 * HIDDEN;
+        vb[it].v = valid ? *reinterpret_cast<const uint2*>(row + c0) : make_uint2(0u, 0u);
+        vx[it].v = valid ? *reinterpret_cast<const uint2*>(row + 2 * HIDDEN + c0) : make_uint2(0u, 0u);
+    }
+#pragma unroll
+    for (int m = 0; m < CT_OUT; m++) {
+        const uint32_t r = r_tile + ty + CT_PASS * m;
+        vc[m].v = r < rows ? *reinterpret_cast<const uint2*>(bcx + (size_t)r * 3 * HIDDEN + HIDDEN + c0) : make_uint2(0u, 0u);
+    }
     union { uint2 v[7]; uint16_t h[28]; } w;
 #pragma unroll
     for (int i = 0; i < 7; i++) w.v[i] = __ldg(reinterpret_cast<const uint2*>(conv_w + (size_t)c0 * CONV_K) + i);
+    if (threadIdx.x < CT_ROWS) {
+        const uint32_t r = r_tile + threadIdx.x;
+        if (r < rows) {
+            s_cp[threadIdx.x] = carry_ptrs[r];
+            s_lpos[threadIdx.x] = (int32_t)local_pos[r];
+            s_last[threadIdx.x] = (r + 1 == rows) || (origin[r + 1] != origin[r]);
+        }
+    }
+    // ---- products to shared memory
+#pragma unroll
+    for (int it = 0; it < CT_LOADS; it++) {
+        const int32_t i = (int32_t)ty + CT_PASS * it;
+        if (i < CT_ROWS + CT_HALO) {
+            float4 f;
+            f.x = __fmul_rn(h2f(vb[it].h[0]), h2f(vx[it].h[0]));
+            f.y = __fmul_rn(h2f(vb[it].h[1]), h2f(vx[it].h[1]));
+            f.z = __fmul_rn(h2f(vb[it].h[2]), h2f(vx[it].h[2]));
+            f.w = __fmul_rn(h2f(vb[it].h[3]), h2f(vx[it].h[3]));
+            *reinterpret_cast<float4*>(&prod[i][tx * 4]) = f;
+        }
+    }
+    __syncthreads();
 
-    // taps[k][ch]: history products as f16 bit patterns, k = 0 oldest
-    uint16_t taps[CONV_S][4];
-    int32_t prev_org = -1, prev_lpos = -2;  // the row whose new state `taps` holds
-    for (uint32_t r = r_begin; r < r_end; r++) {
-        const uint16_t* row = bcx + (size_t)r * 3 * HIDDEN;
-        union { uint2 v; uint16_t h[4]; } vb, vc, vx, vy;
-        vb.v = *reinterpret_cast<const uint2*>(row + c0);
-        vc.v = *reinterpret_cast<const uint2*>(row + HIDDEN + c0);
-        vx.v = *reinterpret_cast<const uint2*>(row + 2 * HIDDEN + c0);
-        const uint64_t cp = carry_ptrs[r];
+    // ---- outputs
+#pragma unroll
+    for (int m = 0; m < CT_OUT; m++) {
+        const uint32_t lr = ty + CT_PASS * m, r = r_tile + lr;
+        if (r >= rows) continue;
+        const uint64_t cp = s_cp[lr];
         if (cp & 15ull) {
-            if (threadIdx.x == 0 && blockIdx.x == 0) atomicOr(status, DEV_MISALIGNED_PTR);
-            prev_org = -1;
+            if (tx == 0 && blockIdx.x == 0) atomicOr(status, DEV_MISALIGNED_PTR);
             continue;
         }
-        const int32_t org = (int32_t)origin[r];
-        const int32_t lpos = (int32_t)local_pos[r];
-        const bool last = (r + 1 == rows) || (origin[r + 1] != origin[r]);
-        if (!(org == prev_org && lpos == prev_lpos + 1)) {
-            // not the continuation of the row before: build the window from scratch
-            if (lpos < CONV_S) {
-                union { uint4 v[3]; uint16_t h[24]; } cs;
-                const uint16_t* carry = reinterpret_cast<const uint16_t*>(cp) + (size_t)c0 * CONV_S;
+        const int32_t lpos = s_lpos[lr];
+        // slot k of the row's window: the product of chunk position lpos + k - 6, or carried state
+        uint16_t win[CONV_S + 1][4];  // [k][channel]; k = 6 is the row's own product (its f16 form, for the state)
+        if (lpos < CONV_S) {
+            union { uint4 v[3]; uint16_t h[24]; } cs;
+            const uint16_t* carry = reinterpret_cast<const uint16_t*>(cp) + (size_t)c0 * CONV_S;
 #pragma unroll
-                for (int i = 0; i < 3; i++) cs.v[i] = reinterpret_cast<const uint4*>(carry)[i];
-#pragma unroll
-                for (int k = 0; k < CONV_S; k++) {
-                    const int32_t j = lpos + k - CONV_S;
-                    if (j < 0) {
-#pragma unroll
-                        for (int ch = 0; ch < 4; ch++) taps[k][ch] = cs.h[ch * CONV_S + (j + CONV_S)];
-                    }
-                }
-            }
+            for (int i = 0; i < 3; i++) cs.v[i] = reinterpret_cast<const uint4*>(carry)[i];
 #pragma unroll
             for (int k = 0; k < CONV_S; k++) {
                 const int32_t j = lpos + k - CONV_S;
-                if (j >= 0) {
-                    const uint16_t* src = bcx + (size_t)(org + j) * 3 * HIDDEN;
-                    union { uint2 v; uint16_t h[4]; } pb, px;
-                    pb.v = *reinterpret_cast<const uint2*>(src + c0);
-                    px.v = *reinterpret_cast<const uint2*>(src + 2 * HIDDEN + c0);
+                if (j < 0) {
 #pragma unroll
-                    for (int ch = 0; ch < 4; ch++) taps[k][ch] = f2h(__fmul_rn(h2f(pb.h[ch]), h2f(px.h[ch])));
+                    for (int ch = 0; ch < 4; ch++) win[k][ch] = cs.h[ch * CONV_S + (j + CONV_S)];
                 }
             }
         }
 #pragma unroll
+        for (int k = 0; k <= CONV_S; k++) {
+            if (k == CONV_S || lpos + k - CONV_S >= 0) {
+                const float4 f = *reinterpret_cast<const float4*>(&prod[lr + k][tx * 4]);  // wave row r - 6 + k
+                win[k][0] = f2h(f.x);
+                win[k][1] = f2h(f.y);
+                win[k][2] = f2h(f.z);
+                win[k][3] = f2h(f.w);
+            }
+        }
+        const float4 own = *reinterpret_cast<const float4*>(&prod[lr + CONV_S][tx * 4]);
+        const float fin[4] = {own.x, own.y, own.z, own.w};
+        U2 vy;
+#pragma unroll
         for (int ch = 0; ch < 4; ch++) {
-            const float fin = __fmul_rn(h2f(vb.h[ch]), h2f(vx.h[ch]));
             float acc = 0.0f;
 #pragma unroll
-            for (int k = 0; k < CONV_S; k++)
-                acc = __fmaf_rn(h2f(taps[k][ch]), h2f(w.h[ch * CONV_K + k]), acc);
-            acc = __fmaf_rn(fin, h2f(w.h[ch * CONV_K + CONV_S]), acc);
-            vy.h[ch] = f2h(__fmul_rn(acc, h2f(vc.h[ch])));
-            // the row's new state, which is the next row's window if that row continues the chunk
-#pragma unroll
-            for (int k = 0; k < CONV_S - 1; k++) taps[k][ch] = taps[k + 1][ch];
-            taps[CONV_S - 1][ch] = f2h(fin);
+            for (int k = 0; k < CONV_S; k++) acc = __fmaf_rn(h2f(win[k][ch]), h2f(w.h[ch * CONV_K + k]), acc);
+            acc = __fmaf_rn(fin[ch], h2f(w.h[ch * CONV_K + CONV_S]), acc);
+            vy.h[ch] = f2h(__fmul_rn(acc, h2f(vc[m].h[ch])));
         }
         *reinterpret_cast<uint2*>(y_out + (size_t)r * HIDDEN + c0) = vy.v;
-        if (last) {  // state layout [channel][slot]: half i of the 24 is channel i / 6, slot i % 6
+        if (s_last[lr]) {  // the chunk's new state: window slots 1 .. 6; layout [channel][slot]
             uint4* dst = reinterpret_cast<uint4*>(stage + ((size_t)r * HIDDEN + c0) * CONV_S);
             uint32_t pw[12];
 #pragma unroll
             for (int i = 0; i < 12; i++)
-                pw[i] = (uint32_t)taps[(2 * i) % CONV_S][(2 * i) / CONV_S] |
-                        ((uint32_t)taps[(2 * i + 1) % CONV_S][(2 * i + 1) / CONV_S] << 16);
+                pw[i] = (uint32_t)win[(2 * i) % CONV_S + 1][(2 * i) / CONV_S] |
+                        ((uint32_t)win[(2 * i + 1) % CONV_S + 1][(2 * i + 1) / CONV_S] << 16);
 #pragma unroll
             for (int i = 0; i < 3; i++) dst[i] = make_uint4(pw[4 * i], pw[4 * i + 1], pw[4 * i + 2], pw[4 * i + 3]);
         }
-        prev_org = org;
-        prev_lpos = lpos;
     }
 }
 
 // Prefill, pass 2: the staged final state of every chunk replaces the
 // request's persistent state.
-constexpr int COMMIT_ROWS = PF_ROWS;  // wave rows scanned per CTA (64 measured slower: the scan is serial)
+constexpr int COMMIT_ROWS = 8;  // wave rows scanned per CTA (64 measured slower: the scan is serial)
 __global__ void __launch_bounds__(128)
 conv_commit_kernel(const uint64_t* __restrict__ carry_ptrs, const uint32_t* __restrict__ origin,
                    uint32_t rows, const uint16_t* __restrict__ stage) {
     const uint32_t c0 = (blockIdx.x * 128 + threadIdx.x) * 4;
     const uint32_t r_end = min(rows, (blockIdx.y + 1) * (uint32_t)COMMIT_ROWS);
+    pdl_wait();  // launched as a programmatic dependent of pass 1: resident early, reads `stage` only after it finished
     for (uint32_t r = blockIdx.y * COMMIT_ROWS; r < r_end; r++) {  // chunk ends are rare: most rows only read origin
         const bool last = (r + 1 == rows) || (origin[r + 1] != origin[r]);
         if (!last) continue;
@@ -195,15 +240,14 @@ cudaError_t launch_conv_prefill(cudaStream_t stream, void* y_out, const uint64_t
                                 const uint32_t* origin, const uint32_t* local_pos,
                                 const void* bcx, const void* conv_w, uint32_t rows, void* stage,
                                 uint32_t* status) {
-    dim3 grid_pf(HIDDEN / 512, (rows + PF_ROWS - 1) / PF_ROWS);
-    conv_prefill_kernel<<<grid_pf, 128, 0, stream>>>((uint16_t*)y_out, carry_ptrs, origin, local_pos,
-                                                  (const uint16_t*)bcx, (const uint16_t*)conv_w,
-                                                  rows, (uint16_t*)stage, status);
+    dim3 grid_t(HIDDEN / CT_CH, (rows + CT_ROWS - 1) / CT_ROWS);
+    conv_prefill_kernel<<<grid_t, CT_THREADS, 0, stream>>>((uint16_t*)y_out, carry_ptrs, origin, local_pos,
+                                                                (const uint16_t*)bcx, (const uint16_t*)conv_w, rows,
+                                                                (uint16_t*)stage, status);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     dim3 grid_c(HIDDEN / 512, (rows + COMMIT_ROWS - 1) / COMMIT_ROWS);
-    conv_commit_kernel<<<grid_c, 128, 0, stream>>>(carry_ptrs, origin, rows, (const uint16_t*)stage);
-    return cudaGetLastError();
+    return launch_pdl(conv_commit_kernel, grid_c, dim3(128), 0, stream, carry_ptrs, origin, rows, (const uint16_t*)stage);
 }
 
 }  // namespace oxi
