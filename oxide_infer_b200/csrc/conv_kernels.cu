@@ -207,23 +207,38 @@ conv_prefill_kernel(uint16_t* __restrict__ y_out, const uint64_t* __restrict__ c
 }
 
 // Prefill, pass 2: the staged final state of every chunk replaces the
-// request's persistent state.
-constexpr int COMMIT_ROWS = 8;  // wave rows scanned per CTA (64 measured slower: the scan is serial)
+// request's persistent state.  A CTA looks at COMMIT_ROWS wave rows (one per thread) for chunk ends,
+// then all its threads copy the state of each end it found (usually one), 4 channels per thread.
+constexpr int COMMIT_ROWS = 128;
 __global__ void __launch_bounds__(128)
 conv_commit_kernel(const uint64_t* __restrict__ carry_ptrs, const uint32_t* __restrict__ origin,
                    uint32_t rows, const uint16_t* __restrict__ stage) {
+    __shared__ uint32_t s_cnt[4];
+    __shared__ uint32_t s_rows[COMMIT_ROWS];
     const uint32_t c0 = (blockIdx.x * 128 + threadIdx.x) * 4;
-    const uint32_t r_end = min(rows, (blockIdx.y + 1) * (uint32_t)COMMIT_ROWS);
+    const uint32_t r = blockIdx.y * COMMIT_ROWS + threadIdx.x;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    // step inputs, not written by pass 1: read while it is still running
+    const bool last = r < rows && ((r + 1 == rows) || (origin[r + 1] != origin[r]));
+    const uint32_t mask = __ballot_sync(0xffffffffu, last);
+    if (lane == 0) s_cnt[warp] = (uint32_t)__popc(mask);
+    __syncthreads();
+    uint32_t before = 0, n = 0;  // chunk ends are listed in row order
+    for (uint32_t wv = 0; wv < 4; wv++) {
+        before += wv < warp ? s_cnt[wv] : 0u;
+        n += s_cnt[wv];
+    }
+    if (last) s_rows[before + (uint32_t)__popc(mask & ((1u << lane) - 1u))] = r;
+    __syncthreads();
     pdl_wait();  // launched as a programmatic dependent of pass 1: resident early, reads `stage` only after it finished
-    for (uint32_t r = blockIdx.y * COMMIT_ROWS; r < r_end; r++) {  // chunk ends are rare: most rows only read origin
-        const bool last = (r + 1 == rows) || (origin[r + 1] != origin[r]);
-        if (!last) continue;
-        const uint64_t cp = carry_ptrs[r];
+    for (uint32_t i = 0; i < n; i++) {
+        const uint32_t lr = s_rows[i];
+        const uint64_t cp = carry_ptrs[lr];
         if (cp & 15ull) continue;
-        const uint4* src = reinterpret_cast<const uint4*>(stage + ((size_t)r * HIDDEN + c0) * CONV_S);
+        const uint4* src = reinterpret_cast<const uint4*>(stage + ((size_t)lr * HIDDEN + c0) * CONV_S);
         uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(cp) + (size_t)c0 * CONV_S);
 #pragma unroll
-        for (int i = 0; i < 3; i++) dst[i] = src[i];
+        for (int k = 0; k < 3; k++) dst[k] = src[k];
     }
 }
 
