@@ -100,6 +100,9 @@ conv_prefill_kernel(uint16_t* __restrict__ y_out, const uint64_t* __restrict__ c
     const uint32_t r_tile = blockIdx.y * CT_ROWS;
     const uint32_t tx = threadIdx.x % (CT_CH / 4), ty = threadIdx.x / (CT_CH / 4);
     const uint32_t c0 = blockIdx.x * CT_CH + tx * 4;
+    // launched as a programmatic dependent: bcx comes from the kernel before, and the carried states may
+    // still be written by it (the previous layer's or wave's commit)
+    pdl_wait();
 
     // ---- all loads
     union U2 { uint2 v; uint16_t h[4]; };
@@ -256,10 +259,8 @@ cudaError_t launch_conv_prefill(cudaStream_t stream, void* y_out, const uint64_t
                                 const void* bcx, const void* conv_w, uint32_t rows, void* stage,
                                 uint32_t* status) {
     dim3 grid_t(HIDDEN / CT_CH, (rows + CT_ROWS - 1) / CT_ROWS);
-    conv_prefill_kernel<<<grid_t, CT_THREADS, 0, stream>>>((uint16_t*)y_out, carry_ptrs, origin, local_pos,
-                                                                (const uint16_t*)bcx, (const uint16_t*)conv_w, rows,
-                                                                (uint16_t*)stage, status);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_pdl(conv_prefill_kernel, grid_t, dim3(CT_THREADS), 0, stream, (uint16_t*)y_out, carry_ptrs, origin,
+                               local_pos, (const uint16_t*)bcx, (const uint16_t*)conv_w, rows, (uint16_t*)stage, status);
     if (e != cudaSuccess) return e;
     dim3 grid_c(HIDDEN / 512, (rows + COMMIT_ROWS - 1) / COMMIT_ROWS);
     return launch_pdl(conv_commit_kernel, grid_c, dim3(128), 0, stream, carry_ptrs, origin, rows, (const uint16_t*)stage);
