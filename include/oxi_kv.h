@@ -66,7 +66,9 @@ const char* oxi_status_string(int32_t status);
 const char* oxi_last_error_string(void);
 
 /* Creates the per-device workspace (split-KV partials, conv staging,
- * host-entry staging, argmax candidates).  Replaces the scratch half of
+ * host-entry staging, argmax candidates and, when max_prefill_rows > 0, the
+ * partial results of the prefill key-range split, see
+ * oxi_prefill_split_configure).  Replaces the scratch half of
  * BatchEngine::new (batch_engine.rs:320-364).  max_batch <= 1024.
  * Calls on one handle use that workspace: they must be ordered on the device
  * (one stream, or events between streams), as the engine's single decode stream
