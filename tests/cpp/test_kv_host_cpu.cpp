@@ -79,6 +79,36 @@ int main() {
         CHECK(bad);
     }
     {
+        // properties on random prompt sets: every token is handed out exactly once and in order, a wave
+        // holds at most max_rows rows, chunks of one request never share a wave, short requests go first
+        uint32_t st = 99u;
+        auto rnd = [&](uint32_t n) { st = st * 1664525u + 1013904223u; return (st >> 8) % n; };
+        for (int trial = 0; trial < 200; trial++) {
+            const size_t nreq = 1 + rnd(12), max_rows = 1 + rnd(200);
+            std::vector<size_t> lens(nreq);
+            for (auto& l : lens) l = rnd(4) == 0 ? 0 : rnd(700);
+            PrefillPlanner pl(lens, max_rows);
+            std::vector<size_t> next_tok(nreq, 0);
+            size_t last_len = 0;
+            for (auto wave = pl.next(); !wave.empty(); wave = pl.next()) {
+                size_t used = 0;
+                for (size_t i = 0; i < wave.size(); i++) {
+                    const WaveChunk& c = wave[i];
+                    CHECK(c.req < nreq && c.len >= 1 && c.len <= max_rows);
+                    CHECK(c.start == next_tok[c.req]);  // a request's chunks come in order, without gaps
+                    next_tok[c.req] += c.len;
+                    CHECK(next_tok[c.req] <= lens[c.req]);
+                    CHECK(lens[c.req] >= last_len);     // requests by increasing prompt length
+                    last_len = lens[c.req];
+                    for (size_t k = 0; k < i; k++) CHECK(wave[k].req != c.req);
+                    used += c.len;
+                }
+                CHECK(used <= max_rows);
+            }
+            for (size_t r = 0; r < nreq; r++) CHECK(next_tok[r] == lens[r]);
+        }
+    }
+    {
         // per-row tables of a wave: positions, chunk origins, positions inside the chunk, pointers
         WaveTablesHost w;
         const std::vector<WaveChunk> wave = {{1, 0, 3}, {0, 64, 2}};
