@@ -79,6 +79,62 @@ int main() {
         CHECK(bad);
     }
     {
+        // random allocate / grow / free with shared prefix blocks: no block is lost or handed out twice
+        PagedPoolConfig cfg;
+        cfg.num_blocks = 64; cfg.block_size = 16; cfg.num_layers = 2;
+        auto pp = std::make_shared<PagedKvPool>(0, cfg);
+        PagedBlockManager mgr(pp);
+        uint32_t st = 7u;
+        auto rnd = [&](uint32_t n) { st = st * 1664525u + 1013904223u; return (st >> 8) % n; };
+        std::map<uint64_t, size_t> live;  // sequence -> tokens
+        uint64_t next_id = 1;
+        for (int step = 0; step < 3000; step++) {
+            const uint32_t op = rnd(4);
+            if (op == 0 || live.empty()) {
+                const size_t tokens = 1 + rnd(100);
+                std::vector<size_t> shared;
+                if (!live.empty() && rnd(2)) {  // adopt a prefix of full blocks of a live sequence
+                    auto it = live.begin();
+                    std::advance(it, rnd((uint32_t)live.size()));
+                    const auto* t = mgr.get_block_table(it->first);
+                    const size_t full = std::min(it->second, tokens) / 16;
+                    for (size_t i = 0; i < full && i < t->size(); i++) shared.push_back((*t)[i]);
+                }
+                try {
+                    mgr.allocate_for_seq(next_id, tokens, shared);
+                    live[next_id++] = tokens;
+                } catch (const std::runtime_error&) {
+                }
+            } else if (op == 1) {
+                auto it = live.begin();
+                std::advance(it, rnd((uint32_t)live.size()));
+                try {
+                    mgr.append_token(it->first, it->second);
+                    it->second += 1;
+                } catch (const std::runtime_error&) {
+                }
+            } else if (op == 2) {
+                auto it = live.begin();
+                std::advance(it, rnd((uint32_t)live.size()));
+                mgr.free_seq(it->first);
+                live.erase(it);
+            }
+            // invariants: tables cover the tokens; distinct blocks in use + free blocks = all blocks
+            std::map<size_t, int> used;
+            for (auto& kv : live) {
+                const auto* t = mgr.get_block_table(kv.first);
+                CHECK(t && t->size() >= (kv.second + 15) / 16);
+                for (size_t b : *t) {
+                    CHECK(b < cfg.num_blocks);
+                    used[b]++;
+                }
+            }
+            CHECK(used.size() + pp->free_block_count() == cfg.num_blocks);
+        }
+        for (auto& kv : live) mgr.free_seq(kv.first);
+        CHECK(pp->free_block_count() == cfg.num_blocks);
+    }
+    {
         // properties on random prompt sets: every token is handed out exactly once and in order, a wave
         // holds at most max_rows rows, chunks of one request never share a wave, short requests go first
         uint32_t st = 99u;
