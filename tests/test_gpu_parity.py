@@ -459,6 +459,49 @@ def test_prefill_attn(kv, ref, O, chunks, window):
         assert np.abs(mine - _np(rctx).astype(np.float32)).max() <= ATTN_TOL
 
 
+def test_prefill_full_size_wave_against_reference_and_request_order(ref):
+    """Configuration 4 at full size (32 requests x 128 new rows, prefixes U[0, 8192], 4096 wave rows): every
+    row against the reference's own online kernel + gate kernel, and a size-independent property: the order
+    of the requests inside the wave must not change any request's output bytes."""
+    from oxide_infer_b200 import KvPath
+    nseq, new = 32, 128
+    rows = nseq * new
+    rng = np.random.default_rng(4)
+    prefix = rng.integers(0, 8193, nseq)
+    kvp = KvPath(0, max_batch=8, max_seq_len=8192 + new, max_prefill_rows=rows)
+    g = torch.Generator(device="cuda").manual_seed(44)
+    rn = lambda *s: torch.empty(*s, dtype=torch.float16, device="cuda").normal_(generator=g)
+    kc = [rn(int(p) + new, NKV, HD) for p in prefix]
+    vc = [rn(int(p) + new, NKV, HD) for p in prefix]
+    q, gate = rn(rows, NQ, HD), rn(rows, NQ)
+
+    def run(order):
+        owner = np.repeat(order, new)
+        lens = (prefix[owner] + np.tile(np.arange(new), nseq) + 1).astype(np.int32)
+        kp = torch.tensor([kc[i].data_ptr() for i in owner], dtype=torch.int64, device="cuda")
+        vp = torch.tensor([vc[i].data_ptr() for i in owner], dtype=torch.int64, device="cuda")
+        src = torch.from_numpy(np.concatenate([np.arange(i * new, (i + 1) * new) for i in order])).cuda()
+        qq, gg = q[src].contiguous(), gate[src].contiguous()  # request i keeps its q and gate rows
+        ctx = torch.zeros(rows, NQ, HD, dtype=torch.float16, device="cuda")
+        dl = torch.from_numpy(lens).cuda()
+        kvp.prefill_attn(ctx, qq, gg, kp, vp, dl, 0)
+        torch.cuda.synchronize()
+        return ctx, (qq, gg, kp, vp, dl), src
+
+    base, args, _ = run(np.arange(nseq))
+    assert kvp.device_status() == 0 and torch.isfinite(base.float()).all()
+    perm = np.random.default_rng(9).permutation(nseq)
+    other, _, src = run(perm)
+    assert torch.equal(other.view(torch.int16), base[src].view(torch.int16))
+    if ref is not None:
+        qq, gg, kp, vp, dl = args
+        rctx = torch.zeros_like(base)
+        ref.attn_online(rctx, qq, kp, vp, dl, rows, 0)
+        ref.sigmoid_gate(rctx, gg, rows)
+        torch.cuda.synchronize()
+        assert (base.float() - rctx.float()).abs().max().item() <= ATTN_TOL
+
+
 def test_prefill_attn_many_runs_per_block(kv, O):
     """Run boundaries at every row: 70 single-row chunks of 70 requests (64 runs in the first block), then
     two caches alternating row by row (equal pointers that are not neighbours must not merge), with
