@@ -502,6 +502,48 @@ def test_prefill_full_size_wave_against_reference_and_request_order(ref):
         assert (base.float() - rctx.float()).abs().max().item() <= ATTN_TOL
 
 
+def test_prefill_wave_of_more_than_1024_blocks(O):
+    """Waves beyond 65,536 rows (1024 blocks of 64) are ordered by the general counting-sort plan kernel: the
+    bytes must equal those of the same requests sent as two smaller waves (ranked by the small plan kernel),
+    and sampled requests must match the oracle."""
+    from oxide_infer_b200 import KvPath
+    nseq, new = 1040, 64  # 1040 blocks
+    rows = nseq * new
+    rng = np.random.default_rng(12)
+    prefix = rng.integers(0, 300, nseq)
+    kvp = KvPath(0, max_batch=8, max_seq_len=512, max_prefill_rows=rows)
+    g = torch.Generator(device="cuda").manual_seed(12)
+    rn = lambda *s: torch.empty(*s, dtype=torch.float16, device="cuda").normal_(generator=g)
+    cap = prefix + new
+    offs = np.concatenate([[0], np.cumsum(cap)])
+    kslab, vslab = rn(int(offs[-1]), NKV, HD), rn(int(offs[-1]), NKV, HD)
+    q, gate = rn(rows, NQ, HD), rn(rows, NQ)
+    owner = np.repeat(np.arange(nseq), new)
+    lens = (prefix[owner] + np.tile(np.arange(new), nseq) + 1).astype(np.int32)
+    kp = torch.from_numpy(kslab.data_ptr() + offs[owner] * 1024).cuda()
+    vp = torch.from_numpy(vslab.data_ptr() + offs[owner] * 1024).cuda()
+    dl = torch.from_numpy(lens).cuda()
+    ctx = torch.zeros(rows, NQ, HD, dtype=torch.float16, device="cuda")
+    kvp.prefill_attn(ctx, q, gate, kp, vp, dl, 0)
+    torch.cuda.synchronize()
+    assert kvp.device_status() == 0
+    two = torch.zeros_like(ctx)
+    half = (nseq // 2) * new
+    for lo, hi in ((0, half), (half, rows)):
+        kvp.prefill_attn(two[lo:hi], q[lo:hi], gate[lo:hi], kp[lo:hi].contiguous(), vp[lo:hi].contiguous(),
+                         dl[lo:hi].contiguous(), 0)
+    torch.cuda.synchronize()
+    assert torch.equal(ctx.view(torch.int16), two.view(torch.int16))
+    hk, hv = kslab.cpu().numpy(), vslab.cpu().numpy()
+    for i in (0, 517, nseq - 1):
+        sl = slice(i * new, (i + 1) * new)
+        kc, vc = hk[offs[i]:offs[i + 1]], hv[offs[i]:offs[i + 1]]
+        want = O.attn_online(q[sl].cpu().numpy(), O.ptr_table([kc] * new), O.ptr_table([vc] * new),
+                             lens[sl].astype(np.uint32), 0)
+        O.sigmoid_gate(want, gate[sl].cpu().numpy())
+        assert np.abs(ctx[sl].float().cpu().numpy() - want.astype(np.float32)).max() <= ATTN_TOL
+
+
 def test_prefill_attn_many_runs_per_block(kv, O):
     """Run boundaries at every row: 70 single-row chunks of 70 requests (64 runs in the first block), then
     two caches alternating row by row (equal pointers that are not neighbours must not merge), with
