@@ -651,6 +651,38 @@ def test_decode_long_context_and_wide_batch(kv, ref):
         assert np.abs(_np(d.ctx).astype(np.float32) - _np(r.ctx).astype(np.float32)).max() <= ATTN_TOL
 
 
+def test_decode_maximum_batch_of_1024_rows(ref):
+    """The largest batch one launch takes (1024 rows; the row tables live in shared memory): fused step against
+    the reference's kernels, bytes of a row equal to the same row in a batch of 8, one row more is refused."""
+    from oxide_infer_b200 import KvPath
+    big = KvPath(0, max_batch=1024, max_seq_len=1024, max_prefill_rows=0)
+    lens = np.random.default_rng(51).integers(1, 900, 1024)
+    case = DecodeCase(lens, seed=51)
+    d = case.device()
+    big.append_decode(d.ctx, d.q, d.k, d.v, d.gate, d.q_norm_w, d.k_norm_w, d.cos, d.sin, d.pos_ids, d.seq_lens,
+                      d.k_ptrs, d.v_ptrs, 0)
+    torch.cuda.synchronize()
+    assert big.device_status() == 0
+    if ref is not None:
+        r = case.device()
+        ref.append(r.q, r.k, r.v, r.q_norm_w, r.k_norm_w, r.cos, r.sin, r.pos_ids, r.k_ptrs, r.v_ptrs, 1024)
+        ref.decode_attention(r.ctx, r.q, r.gate, r.k_ptrs, r.v_ptrs, r.seq_lens, 1024, 0, int(case.seq_lens.max()))
+        torch.cuda.synchronize()
+        assert np.abs(_np(d.ctx).astype(np.float32) - _np(r.ctx).astype(np.float32)).max() <= ATTN_TOL
+        for i in (0, 511, 1023):
+            assert torch.equal(d.k_cache[i].view(torch.int16), r.k_cache[i].view(torch.int16))
+    # rows 1000..1007 alone through the unfused pair: the same bytes as inside the batch of 1024
+    a = case.device()
+    big.append(a.q, a.k, a.v, a.q_norm_w, a.k_norm_w, a.cos, a.sin, a.pos_ids, a.k_ptrs, a.v_ptrs)
+    sub = lambda t: t[1000:1008].contiguous()
+    one = torch.zeros(8, NQ, HD, dtype=torch.float16, device="cuda")
+    big.decode_attn(one, sub(a.q), sub(a.gate), sub(a.k_ptrs), sub(a.v_ptrs), sub(a.seq_lens), 0)
+    torch.cuda.synchronize()
+    assert torch.equal(one.view(torch.int16), d.ctx[1000:1008].view(torch.int16))
+    with pytest.raises(Exception):
+        KvPath(0, max_batch=1025, max_seq_len=64, max_prefill_rows=0)
+
+
 def test_decode_step_replays_from_a_cuda_graph(kv):
     """The fused step (programmatic dependent launches included) can be captured once and replayed:
     a replay on fresh inputs equals the eager result byte for byte."""
