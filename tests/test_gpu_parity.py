@@ -376,7 +376,8 @@ def test_conv_unit_weights_zero_state_gpu(kv):
     assert (y == 2.0).all() and (st[0][:, 5] == 2.0).all() and (st[0][:, :5] == 0).all()
 
 
-@pytest.mark.parametrize("lens", [[1, 5, 6, 7, 19], [128, 128], [3]])
+@pytest.mark.parametrize("lens", [[1, 5, 6, 7, 19], [128, 128], [3], [16, 16, 1, 15, 17, 33], [13, 40, 2, 9], [250, 1, 5],
+                                  [10, 6, 16, 31, 1, 1, 1, 64]])
 def test_conv_prefill_bit_exact(kv, ref, O, lens):
     rng = np.random.default_rng(sum(lens))
     rows = sum(lens)
