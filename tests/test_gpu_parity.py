@@ -414,6 +414,43 @@ def test_conv_prefill_bit_exact(kv, ref, O, lens):
             assert torch.equal(a.view(torch.int16), r.view(torch.int16))
 
 
+def test_conv_prefill_chunking_invariance_and_decode_equivalence(kv):
+    """A prompt's conv outputs and final state do not depend on how it is cut into chunks: 300 rows as one
+    chunk, as waves of 128 + 128 + 44 rows carried through the persistent state, as 7 + 293, and token by
+    token through the decode kernel - all bit-identical."""
+    rng = np.random.default_rng(300)
+    n = 300
+    bcx = torch.from_numpy(rng.standard_normal((n, 3 * HIDDEN), dtype=np.float32).astype(np.float16)).cuda()
+    w = torch.from_numpy((rng.standard_normal((HIDDEN, 7), dtype=np.float32) * 0.1).astype(np.float16)).cuda()
+    state0 = torch.from_numpy(rng.standard_normal((HIDDEN, 6), dtype=np.float32).astype(np.float16)).cuda()
+
+    def run(cuts):
+        st = state0.clone()
+        y = torch.zeros(n, HIDDEN, dtype=torch.float16, device="cuda")
+        lo = 0
+        for m in cuts:
+            kv.conv_prefill(y[lo:lo + m], dev_ptr_table([st] * m), u32(np.zeros(m, np.uint32)),
+                            u32(np.arange(m, dtype=np.uint32)), bcx[lo:lo + m].contiguous(), w)
+            lo += m
+        torch.cuda.synchronize()
+        assert lo == n
+        return y, st
+
+    y1, s1 = run([300])
+    for cuts in ([128, 128, 44], [7, 293], [1] * 5 + [295]):
+        y2, s2 = run(cuts)
+        assert torch.equal(y1.view(torch.int16), y2.view(torch.int16))
+        assert torch.equal(s1.view(torch.int16), s2.view(torch.int16))
+    st = state0.clone()
+    yd = torch.zeros(n, HIDDEN, dtype=torch.float16, device="cuda")
+    ptr = dev_ptr_table([st])
+    for t in range(n):
+        kv.conv_decode(yd[t:t + 1], ptr, bcx[t:t + 1].contiguous(), w)
+    torch.cuda.synchronize()
+    assert torch.equal(y1.view(torch.int16), yd.view(torch.int16))
+    assert torch.equal(s1.view(torch.int16), st.view(torch.int16))
+
+
 # ----------------------------------------------------------------- prefill --
 
 def _prefill_case(chunks, cache_len, seed, kscale=1.0):
