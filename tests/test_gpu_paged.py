@@ -213,3 +213,38 @@ def test_paged_fused_step_with_window(kv, block_size, window):
     torch.cuda.synchronize()
     assert kv.device_status() == 0
     assert torch.equal(d.ctx.view(torch.int16), d2.ctx.view(torch.int16))
+
+
+def test_paged_decode_with_shared_prefix_blocks(kv):
+    """Two sequences whose tables point at the same physical blocks for a common 64-token prefix (what the
+    block manager's reference counts are for): each gets the result of its own contiguous copy."""
+    import torch
+    from oxide_infer_b200 import PagedLayout
+    bs, shared_tokens = 16, 64
+    case = DecodeCase([200, 333], seed=77)
+    d = case.device()
+    # make the prefix common in the contiguous caches too
+    d.k_cache[1][:shared_tokens] = d.k_cache[0][:shared_tokens]
+    d.v_cache[1][:shared_tokens] = d.v_cache[0][:shared_tokens]
+    kv.append(d.q, d.k, d.v, d.q_norm_w, d.k_norm_w, d.cos, d.sin, d.pos_ids, d.k_ptrs, d.v_ptrs)
+    kv.decode_attn(d.ctx, d.q, d.gate, d.k_ptrs, d.v_ptrs, d.seq_lens, 0)
+    need = [(int(n) + 1 + bs - 1) // bs for n in case.lens]
+    nshared = shared_tokens // bs
+    total = need[0] + need[1] - nshared + 1
+    kpool = torch.zeros(total, bs, NKV, HD, dtype=torch.float16, device="cuda")
+    vpool = torch.zeros_like(kpool)
+    tables = np.zeros((2, max(need)), np.int32)
+    tables[0, :need[0]] = np.arange(1, need[0] + 1)
+    tables[1, :nshared] = tables[0, :nshared]  # the shared blocks
+    tables[1, nshared:need[1]] = np.arange(need[0] + 1, need[0] + 1 + need[1] - nshared)
+    for i in range(2):
+        for j in range(need[i]):
+            lo, hi = j * bs, min((j + 1) * bs, int(case.lens[i]) + 1)
+            kpool[tables[i, j], :hi - lo] = d.k_cache[i][lo:hi]
+            vpool[tables[i, j], :hi - lo] = d.v_cache[i][lo:hi]
+    lay = PagedLayout.of(kpool, vpool, torch.from_numpy(tables).cuda(), bs)
+    ctx = torch.zeros_like(d.ctx)
+    kv.decode_attn_paged(ctx, d.q, d.gate, lay, d.seq_lens, 0)
+    torch.cuda.synchronize()
+    assert kv.device_status() == 0
+    assert torch.equal(ctx.view(torch.int16), d.ctx.view(torch.int16))
