@@ -721,6 +721,42 @@ def test_decode_maximum_batch_of_1024_rows(ref):
         KvPath(0, max_batch=1025, max_seq_len=64, max_prefill_rows=0)
 
 
+@pytest.mark.parametrize("pinned", [True, False])
+def test_host_buffer_step_equals_device_path(kv, pinned):
+    """oxi_decode_step_host (q/k/v/gate, tables and positions in host memory, context back to the host, copies
+    overlapped with the kernels on the library's own streams) gives the bytes of the per-layer device calls and
+    leaves the same K/V rows - for three layers with their own caches and norm weights, twice in a row."""
+    lens = [300, 1, 4095, 64, 777, 255]
+    layers, b = 3, len(lens)
+    cases = [DecodeCase(lens, seed=60 + l, max_pos=4100) for l in range(layers)]
+    dev = [c.device() for c in cases]   # device path
+    hst = [c.device() for c in cases]   # caches used by the host-buffer path
+    for d in dev:
+        kv.append_decode(d.ctx, d.q, d.k, d.v, d.gate, d.q_norm_w, d.k_norm_w, d.cos, d.sin, d.pos_ids, d.seq_lens,
+                         d.k_ptrs, d.v_ptrs, 0)
+    torch.cuda.synchronize()
+    place = (lambda t: t.cpu().pin_memory()) if pinned else (lambda t: t.cpu())
+    stack = lambda name: place(torch.stack([getattr(d, name) for d in hst]))
+    hq, hk, hv, hg = stack("q"), stack("k"), stack("v"), stack("gate")
+    hkp, hvp = stack("k_ptrs"), stack("v_ptrs")
+    hpos = place(hst[0].pos_ids)
+    qw = torch.stack([d.q_norm_w for d in hst]).contiguous()
+    kw = torch.stack([d.k_norm_w for d in hst]).contiguous()
+    hctx = torch.zeros(layers, b, NQ, HD, dtype=torch.float16)
+    if pinned:
+        hctx = hctx.pin_memory()
+    for rep in range(2):  # the second call appends the same rows again: idempotent on the caches
+        hctx.zero_()
+        kv.decode_step_host(hctx, hq, hk, hv, hg, qw, kw, hst[0].cos, hst[0].sin, hpos, hkp, hvp, b, layers)
+        torch.cuda.synchronize()
+        for l in range(layers):
+            assert torch.equal(hctx[l].view(torch.int16), dev[l].ctx.cpu().view(torch.int16))
+            for i in (0, 2, 5):
+                assert torch.equal(hst[l].k_cache[i].view(torch.int16), dev[l].k_cache[i].view(torch.int16))
+                assert torch.equal(hst[l].v_cache[i].view(torch.int16), dev[l].v_cache[i].view(torch.int16))
+    assert kv.device_status() == 0
+
+
 def test_decode_step_replays_from_a_cuda_graph(kv):
     """The fused step (programmatic dependent launches included) can be captured once and replayed:
     a replay on fresh inputs equals the eager result byte for byte."""
