@@ -8,7 +8,7 @@
  *  crates/oxide-infer-server/src/batch_engine.rs:387-404).  Every function
  * below therefore cites the PTX entry point(s) and the engine launch site it
  * replaces; a Rust `extern "C"` block binding these symbols is the only change
- * the engine needs (see INTEGRATION.md).
+ * the engine needs.
  *
  * Conventions (same as the reference's launch sites):
  *   - every tensor argument is a DEVICE pointer owned by the caller; fp16
@@ -55,7 +55,9 @@ enum {
     OXI_DEV_BAD_SEQ_LEN = 2u,    /* seq_len 0 or beyond the handle's max_seq_len; row skipped */
     OXI_DEV_WAIT_TIMEOUT = 4u,   /* an in-kernel pipeline wait gave up (internal error)       */
     OXI_DEV_BAD_TOKEN = 8u,      /* a token id was beyond the embedding table; row zero-filled */
-    OXI_DEV_BAD_BLOCK = 16u      /* a block id in a paged layout's table was >= num_blocks      */
+    OXI_DEV_BAD_BLOCK = 16u,     /* a block id in a paged layout's table was >= num_blocks      */
+    OXI_DEV_OUT_OF_BOUNDS = 32u  /* raised only by libraries built with -DOXI_BOUNDS: a table-driven
+                                    index was out of range; the access was not performed         */
 };
 
 typedef struct oxi_handle oxi_handle;
@@ -301,6 +303,22 @@ int32_t oxi_decode_step_host(oxi_handle* h, void* stream, void* ctx_host, const 
                              const uint64_t* v_ptrs_host, uint32_t batch, uint32_t layers,
                              uint32_t window, float eps);
 
+/* ---- test support ------------------------------------------------------- */
+
+/* Every in-kernel pipeline wait (a consumer waiting for a stage of K/V rows, the
+ * tensor-core warps waiting for a tile) is bounded: after about one second it
+ * gives up, the CTA finishes without writing output and OXI_DEV_WAIT_TIMEOUT is
+ * raised.  Nothing in normal operation makes a wait run out, so this call exists
+ * to exercise that path without faulting or hanging the GPU: it arms the NEXT
+ * launch of this handle's decode-attention kernel (which = 0) or prefill-attention
+ * kernel (which = 1) so that CTA 0 withholds its stage-th pipeline stage (decode:
+ * no copy is issued for it; prefill: the K tile is copied but never published) and
+ * all waits of that launch last limit_us microseconds instead of a second.  The
+ * armed launch returns normally with OXI_DEV_WAIT_TIMEOUT set and with the rows of
+ * CTA 0's work items unwritten; later launches are unaffected.  No counterpart in
+ * the reference. */
+int32_t oxi_debug_arm_wait_fault(oxi_handle* h, uint32_t which, uint32_t stage, uint32_t limit_us);
+
 /* ---- entry point that allocates nothing -------------------------------- */
 
 #define OXI_STATIC_MAX_BATCH 16u      /* rows per call                         */
@@ -330,6 +348,12 @@ int32_t oxi_decode_attn_static(void* stream, void* ctx_out, const void* q, const
                                const uint64_t* k_ptrs, const uint64_t* v_ptrs,
                                const uint32_t* seq_lens, uint32_t batch, uint32_t max_seq_len,
                                uint32_t window);
+/* oxi_device_status for the path above: synchronises `stream`, returns and clears
+ * the OXI_DEV_* bits raised by oxi_decode_attn_static calls on the current device
+ * since the last read (a skipped row - bad seq_len, misaligned pointer - is
+ * otherwise invisible to a caller without a handle).  The word lives in the same
+ * array; oxi_decode_attn_static never clears it.  Allocates nothing. */
+int32_t oxi_static_device_status(void* stream, uint32_t* bits_out);
 
 #ifdef __cplusplus
 }

@@ -6,7 +6,9 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SO_PATH = os.path.join(HERE, "liboxi_kv.so")
+# OXI_KV_LIB selects another build of the same library (the bounds-checking build of
+# oxide_infer_b200.build, for the tests); there is still no fallback if it is missing.
+SO_PATH = os.environ.get("OXI_KV_LIB") or os.path.join(HERE, "liboxi_kv.so")
 
 _vp, _u32, _i32, _f32 = C.c_void_p, C.c_uint32, C.c_int32, C.c_float
 
@@ -41,6 +43,8 @@ SIGNATURES = {
     "oxi_sigmoid_gate": [_vp] * 4 + [_u32],
     "oxi_decode_step_host": [_vp] * 14 + [_u32, _u32, _u32, _f32],
     "oxi_decode_attn_static": [_vp] * 7 + [_u32, _u32, _u32],
+    "oxi_debug_arm_wait_fault": [_vp, _u32, _u32, _u32],
+    "oxi_static_device_status": [_vp, C.POINTER(_u32)],
 }
 _RESTYPE = {"oxi_status_string": C.c_char_p, "oxi_last_error_string": C.c_char_p,
             "oxi_workspace_bytes": C.c_size_t, "oxi_prefill_split_slot_bytes": C.c_uint64}

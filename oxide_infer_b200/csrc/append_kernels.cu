@@ -159,21 +159,43 @@ sigmoid_gate_kernel(uint16_t* __restrict__ ctx_io, const uint16_t* __restrict__ 
 
 // pos_ids[b] += delta, seq_lens[b] += delta: the step tables advance on the device, so a captured
 // graph of a decode step can be replayed for consecutive tokens without any upload.
+// Kernels of this library read the step tables in their prologue, BEFORE their own
+// griddepcontrol.wait (the tables are normally complete before the preceding kernel starts).  A
+// kernel that WRITES the tables must therefore release its dependents only after its writes are
+// visible device-wide: wait for the predecessors (they still read the old tables), write, fence,
+// and only then trigger.  A dependent launched behind this kernel cannot start before every CTA
+// has passed the fence, so its prologue sees the advanced tables.
 __global__ void __launch_bounds__(256)
 advance_step_kernel(uint32_t* __restrict__ pos_ids, uint32_t* __restrict__ seq_lens, uint32_t batch, uint32_t delta) {
     const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
-    pdl_launch_dependents();
     pdl_wait();  // the preceding step's kernels still read the tables
     if (b < batch) {
         if (pos_ids) pos_ids[b] += delta;
         if (seq_lens) seq_lens[b] += delta;
     }
+    __threadfence();
+    __syncthreads();
+    pdl_launch_dependents();
+}
+
+// seq_lens[b] = pos_ids[b] + 1 (batch_engine.rs:689-691): the host-buffer entry uploads positions
+// only and derives the lengths here, so nothing is computed on the CPU at enqueue time.  Launched
+// as a plain kernel on the upload stream; consumers are ordered behind it by an event.
+__global__ void __launch_bounds__(256)
+len_from_pos_kernel(const uint32_t* __restrict__ pos_ids, uint32_t* __restrict__ seq_lens, uint32_t batch) {
+    const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b < batch) seq_lens[b] = pos_ids[b] + 1u;
 }
 
 cudaError_t launch_advance_step(cudaStream_t stream, uint32_t* pos_ids, uint32_t* seq_lens, uint32_t batch,
                                 uint32_t delta) {
     return launch_pdl(advance_step_kernel, dim3((batch + 255) / 256), dim3(256), 0, stream, pos_ids, seq_lens, batch,
                       delta);
+}
+
+cudaError_t launch_len_from_pos(cudaStream_t stream, const uint32_t* pos_ids, uint32_t* seq_lens, uint32_t batch) {
+    len_from_pos_kernel<<<(batch + 255) / 256, 256, 0, stream>>>(pos_ids, seq_lens, batch);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_append(cudaStream_t stream, void* q_io, const void* k_in, const void* v_in,

@@ -22,6 +22,23 @@ constexpr uint32_t DEV_BAD_SEQ_LEN = 2u;
 constexpr uint32_t DEV_WAIT_TIMEOUT = 4u;
 constexpr uint32_t DEV_BAD_TOKEN = 8u;
 constexpr uint32_t DEV_BAD_BLOCK = 16u;
+constexpr uint32_t DEV_OUT_OF_BOUNDS = 32u;  // only raised by builds with -DOXI_BOUNDS
+
+// Builds with -DOXI_BOUNDS check the indices of every table-driven access (cache rows, partial
+// slots, shared-memory stages, wave rows) and, instead of performing an access that is out of
+// range, record DEV_OUT_OF_BOUNDS in the status word.  In normal builds the checks compile away.
+#ifdef OXI_BOUNDS
+#define OXI_IN_BOUNDS(cond, status_ptr) ((cond) ? true : (atomicOr((status_ptr), ::oxi::DEV_OUT_OF_BOUNDS), false))
+#else
+#define OXI_IN_BOUNDS(cond, status_ptr) true
+#endif
+
+// Test support: makes one pipeline stage of one CTA go missing so that the bounded waits run out.
+// skip_plus1 == 0 (every normal launch): nothing is skipped and waits last WAIT_LIMIT_US.
+struct WaitFault {
+    uint32_t skip_plus1;  // CTA 0 withholds its (skip_plus1 - 1)-th stage / tile
+    uint32_t limit_us;    // wait limit of this launch when armed
+};
 
 // Paged K/V layout of one layer: token t of row b lives in block block_tables[b][t >> lbs] at slot
 // t & (2^lbs - 1); block i's K rows start at k_pool + i * block_stride (V: v_pool), one row =
@@ -107,19 +124,25 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-// Bounded wait: gives up after about one second, or at once when another wait
-// of this CTA already gave up (*abort_flag != 0).  Returns false on give-up.
+constexpr uint32_t WAIT_LIMIT_US = 1000000u;  // in-kernel pipeline waits give up after about one second
+
+// Bounded wait: gives up after limit_us microseconds, or at once when another wait of this CTA
+// already gave up (*abort_flag != 0).  Returns false on give-up.  The limit is a kernel
+// parameter only so that a test can make a wait run out in a millisecond.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
-                                                  volatile uint32_t* abort_flag) {
+                                                  volatile uint32_t* abort_flag,
+                                                  uint32_t limit_us = WAIT_LIMIT_US) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    const uint64_t limit_ns = (uint64_t)limit_us * 1000ull;
     uint64_t t0 = 0;
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 255u) == 0u) {
+        if ((it & 63u) == 0u) {
             if (*abort_flag) return false;
             uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > 1000000000ull) {
+            else if (now - t0 > limit_ns) {
                 *abort_flag = 1u;
                 return false;
             }
@@ -127,11 +150,16 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     }
 }
 
-// Plain iteration-limited wait (used on the give-up path to drain copies in flight).
-__device__ __forceinline__ bool mbar_wait_iters(uint64_t* bar, uint32_t parity, uint32_t iters) {
-    for (uint32_t it = 0; it < iters; ++it)
+// Time-limited wait without the abort flag (used on the give-up path to let copies that were
+// already issued land before the CTA's shared memory is released).
+__device__ __forceinline__ bool mbar_wait_drain(uint64_t* bar, uint32_t parity, uint32_t limit_us) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t limit_ns = (uint64_t)limit_us * 1000ull;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
         if (mbar_try_wait(bar, parity)) return true;
-    return false;
+        if (global_timer_ns() - t0 > limit_ns) return false;
+    }
 }
 
 // ---- 1-D bulk copy global -> shared (TMA engine), completion on an mbarrier.

@@ -26,6 +26,7 @@ conv_decode_kernel(uint16_t* __restrict__ y_out, const uint64_t* __restrict__ co
         if (threadIdx.x == 0 && blockIdx.x == 0) atomicOr(status, DEV_MISALIGNED_PTR);
         return;
     }
+    if (!OXI_IN_BOUNDS(c0 + 4u <= (uint32_t)HIDDEN, status)) return;  // bounds build: the thread's channels exist
     uint16_t* state = reinterpret_cast<uint16_t*>(sp) + (size_t)c0 * CONV_S;
     const uint16_t* row = bcx + (size_t)b * 3 * HIDDEN;
 
@@ -158,6 +159,8 @@ conv_prefill_kernel(uint16_t* __restrict__ y_out, const uint64_t* __restrict__ c
             continue;
         }
         const int32_t lpos = s_lpos[lr];
+        // bounds build: a chunk position cannot lie before the wave's first row, and the staged state has a row per wave row
+        if (!OXI_IN_BOUNDS(lpos >= 0 && (uint32_t)lpos <= r && c0 + 4u <= (uint32_t)HIDDEN, status)) continue;
         // slot k of the row's window: the product of chunk position lpos + k - 6, or carried state
         uint16_t win[CONV_S + 1][4];  // [k][channel]; k = 6 is the row's own product (its f16 form, for the state)
         if (lpos < CONV_S) {

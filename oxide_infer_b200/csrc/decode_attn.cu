@@ -134,6 +134,7 @@ struct DecodeParams {
     const uint16_t* cos_t;
     const uint16_t* sin_t;
     float eps;
+    WaitFault fault;  // test support; zero on every normal launch
 };
 
 __device__ __forceinline__ uint32_t row_chunks(uint32_t slen, uint32_t window) {
@@ -165,6 +166,7 @@ decode_attn_kernel(const DecodeParams p) {
     uint32_t* s_len = prefix + MAX_ROWS + 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t wait_us = p.fault.skip_plus1 ? p.fault.limit_us : WAIT_LIMIT_US;
     pdl_launch_dependents();  // the merge kernel may be scheduled now; it waits for this grid to finish
 
     // ---- prologue: barriers, per-row range counts, prefix sum, lengths into shared memory
@@ -298,10 +300,13 @@ decode_attn_kernel(const DecodeParams p) {
             for (uint32_t t = t0; t < t1; t += KS, ++fill) {
                 const uint32_t slot = fill % NSTAGE;
                 if (fill >= NSTAGE &&
-                    !mbar_wait_bounded(&empty_bar[slot], ((fill / NSTAGE) & 1u) ^ 1u, abort_flag)) {
+                    !mbar_wait_bounded(&empty_bar[slot], ((fill / NSTAGE) & 1u) ^ 1u, abort_flag, wait_us)) {
                     ok = false;
                     break;
                 }
+                // test support: this CTA's stage goes missing (no descriptor, no arrival, no copy), so the
+                // consumers' wait for it runs out
+                if (p.fault.skip_plus1 && blockIdx.x == 0 && fill + 1u == p.fault.skip_plus1) continue;
                 const uint32_t nvalid = min((uint32_t)KS, t1 - t);
                 const bool first = (t == t0), last = (t + KS >= t1);
                 // fused: the owner's last stage ends with the key being appended; it is not in the
@@ -337,7 +342,13 @@ decode_attn_kernel(const DecodeParams p) {
                     if (grp * GK < ncopy) {
                         const uint32_t nk = min((uint32_t)GK, ncopy - grp * GK);
                         const uint32_t dst = sbase + (is_v ? HALF_BYTES : 0) + grp * GPITCH;
-                        if (kPaged) {
+                        // bounds build: the copied rows lie inside the row's keys and inside the stage
+                        if (!OXI_IN_BOUNDS(cb < p.batch && t + grp * GK + nk <= cslen &&
+                                               grp * GPITCH + nk * KV_ROW_BYTES <= (uint32_t)HALF_BYTES, p.status)) {
+                            // nothing is copied; the stage's expected byte count must still be met
+                            asm volatile("mbarrier.complete_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&full_bar[slot])),
+                                         "r"(nk * KV_ROW_BYTES) : "memory");
+                        } else if (kPaged) {
                             const unsigned char* pool = is_v ? p.paged.v_pool : p.paged.k_pool;
                             const uint32_t off = (t + grp * GK) & bs_mask;
                             const uint32_t n1 = min(nk, bs_mask + 1u - off);
@@ -366,7 +377,7 @@ decode_attn_kernel(const DecodeParams p) {
         if (ok) {
             // end-of-work descriptor so the consumers leave their loop
             const uint32_t slot = fill % NSTAGE;
-            if (fill < NSTAGE || mbar_wait_bounded(&empty_bar[slot], ((fill / NSTAGE) & 1u) ^ 1u, abort_flag)) {
+            if (fill < NSTAGE || mbar_wait_bounded(&empty_bar[slot], ((fill / NSTAGE) & 1u) ^ 1u, abort_flag, wait_us)) {
                 if (lane == 0) {
                     *reinterpret_cast<uint4*>(stages + (size_t)slot * STAGE_BYTES + DESC_OFF) =
                         make_uint4(0u, 0u, F_END, 0u);
@@ -382,7 +393,7 @@ decode_attn_kernel(const DecodeParams p) {
             // time to land before this CTA's shared memory is released.
             if (lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
             for (uint32_t k = fill > NSTAGE ? fill - NSTAGE : 0; k < fill; ++k)
-                mbar_wait_iters(&full_bar[k % NSTAGE], (k / NSTAGE) & 1u, 1u << 16);
+                mbar_wait_drain(&full_bar[k % NSTAGE], (k / NSTAGE) & 1u, wait_us);
         }
         return;
     }
@@ -404,7 +415,7 @@ decode_attn_kernel(const DecodeParams p) {
 
     for (uint32_t take = 0;; ++take) {
         const uint32_t slot = take % NSTAGE;
-        if (!mbar_wait_bounded(&full_bar[slot], (take / NSTAGE) & 1u, abort_flag)) {
+        if (!mbar_wait_bounded(&full_bar[slot], (take / NSTAGE) & 1u, abort_flag, wait_us)) {
             if (lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
             break;
         }
@@ -467,14 +478,16 @@ decode_attn_kernel(const DecodeParams p) {
             const uint64_t kp64 = *reinterpret_cast<const uint64_t*>(sb + DESC_OFF + 16);
             const uint64_t vp64 = *reinterpret_cast<const uint64_t*>(sb + DESC_OFF + 24);
             uint16_t* krow_g = reinterpret_cast<uint16_t*>(kp64 + (size_t)desc.w * KV_ROW_BYTES) + kvh * HD;
+            // bounds build: the appended row is the row's last key and lies inside the stage
+            const bool row_ok = OXI_IN_BOUNDS(desc.w < p.max_seq_len && kidx < (uint32_t)KS, p.status);
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 krow_s[lane + 32 * i] = out[i];
-                krow_g[lane + 32 * i] = out[i];
+                if (row_ok) krow_g[lane + 32 * i] = out[i];
             }
             const uint2 vv = *reinterpret_cast<const uint2*>(sb + X_OFF + X_V + kvh * (HD * 2) + lane * 8);
             *reinterpret_cast<uint2*>(vst + roff + lane * 8) = vv;
-            *reinterpret_cast<uint2*>(vp64 + (size_t)desc.w * KV_ROW_BYTES + kvh * (HD * 2) + lane * 8) = vv;
+            if (row_ok) *reinterpret_cast<uint2*>(vp64 + (size_t)desc.w * KV_ROW_BYTES + kvh * (HD * 2) + lane * 8) = vv;
             __syncwarp();
         }
         if (nvalid < KS) {
@@ -574,7 +587,7 @@ decode_attn_kernel(const DecodeParams p) {
                 }
                 *reinterpret_cast<uint32_t*>(out + 8 * j + 2 * t4) = (uint32_t)h0 | ((uint32_t)h1 << 16);
             }
-        } else {
+        } else if (OXI_IN_BOUNDS(b < p.batch && c < p.max_chunks && nchunks <= p.max_chunks, p.status)) {
             const size_t pslot = ((size_t)b * p.max_chunks + c) * NQ + head;
             float* pacc = p.partial_acc + pslot * HD;
 #pragma unroll
@@ -793,6 +806,7 @@ static DecodeParams make_params(const DecodeWorkspace& ws, void* ctx_out, const 
     p.window = window;
     p.max_chunks = ws.max_chunks;
     p.max_seq_len = ws.max_seq_len;
+    p.fault = ws.fault;
     return p;
 }
 
@@ -929,8 +943,10 @@ extern "C" int32_t oxi_decode_attn_static(void* stream, void* ctx_out, const voi
         }
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    // The array keeps whatever the previous call left: the control block must start at zero.
-    e = cudaMemsetAsync(pd.base, 0, nalloc::CTRL_BYTES, s);
+    // The array keeps whatever the previous call left.  The work counter must start at zero; the
+    // status word is left alone, so bits raised by earlier calls stay until
+    // oxi_static_device_status reads and clears them.
+    e = cudaMemsetAsync(pd.base + 128, 0, 128, s);
     if (e != cudaSuccess) return (int32_t)e;
     DecodeWorkspace ws{};  // no slice scratch: rows are at most 16 key ranges long here
     ws.status = reinterpret_cast<uint32_t*>(pd.base);
@@ -944,3 +960,29 @@ extern "C" int32_t oxi_decode_attn_static(void* stream, void* ctx_out, const voi
     return (int32_t)e;
 }
 
+// Reads and clears the status word of the allocation-free path on the current device
+// (synchronises `stream`; allocates nothing).  Before the first oxi_decode_attn_static call on a
+// device nothing can have been raised: the word reads as zero.
+extern "C" int32_t oxi_static_device_status(void* stream, uint32_t* bits_out) {
+    using namespace oxi;
+    if (!bits_out) return OXI_ERR_NULL;
+    *bits_out = 0u;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int32_t)e;
+    if (dev < 0 || dev >= nalloc::MAX_DEVICES) return OXI_ERR_NO_DEVICE;
+    unsigned char* base = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_nalloc_mutex);
+        if (!g_nalloc_dev[dev].ready) return OXI_OK;
+        base = g_nalloc_dev[dev].base;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    uint32_t bits = 0;
+    e = cudaMemcpyAsync(&bits, base, 4, cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaMemsetAsync(base, 0, 4, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return (int32_t)e;
+    *bits_out = bits;
+    return OXI_OK;
+}

@@ -18,6 +18,7 @@ struct DecodeWorkspace {
     uint32_t max_chunks;    // partial slots per row
     uint32_t max_seq_len;
     int num_sms;
+    WaitFault fault;        // test support (a stage of CTA 0 goes missing); zero on every normal launch
 };
 
 cudaError_t launch_append(cudaStream_t stream, void* q_io, const void* k_in, const void* v_in,
@@ -26,6 +27,7 @@ cudaError_t launch_append(cudaStream_t stream, void* q_io, const void* k_in, con
                           const uint64_t* v_ptrs, uint32_t batch, float eps, uint32_t* status);
 cudaError_t launch_advance_step(cudaStream_t stream, uint32_t* pos_ids, uint32_t* seq_lens, uint32_t batch,
                                 uint32_t delta);
+cudaError_t launch_len_from_pos(cudaStream_t stream, const uint32_t* pos_ids, uint32_t* seq_lens, uint32_t batch);
 cudaError_t launch_qk_rmsnorm(cudaStream_t stream, void* x_io, const void* w, float eps,
                               uint32_t heads, uint32_t batch);
 cudaError_t launch_rope(cudaStream_t stream, void* x_io, const void* cos_t, const void* sin_t,
@@ -78,7 +80,8 @@ cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* 
                                 const uint32_t* row_seq = nullptr /* paged: table row of each wave row */,
                                 const PrefillSplitWs* split = nullptr /* key-range split of small waves */,
                                 uint32_t part_keys = 0 /* keys per part; 0: no split */,
-                                const PrefillSlab* slab = nullptr /* K/V rows inside it are loaded by TMA */);
+                                const PrefillSlab* slab = nullptr /* K/V rows inside it are loaded by TMA */,
+                                const WaitFault* fault = nullptr /* test support: a K tile of CTA 0 goes missing */);
 size_t prefill_split_slot_bytes();   // partial-result bytes per slot of PrefillSplitWs::part
 size_t prefill_split_table_bytes();  // bytes of PrefillSplitWs::units
 

@@ -25,6 +25,7 @@ struct oxi_handle {
     PrefillSplitWs pf_split;  // reserved by oxi_prefill_split_configure
     uint32_t pf_part_keys;    // keys per part of a split block; 0: off
     PrefillSlab pf_slab;      // registered by oxi_register_kv_slab; rows == 0: none
+    WaitFault dbg_decode, dbg_prefill;  // armed by oxi_debug_arm_wait_fault for the next launch only
     // staging for the host-buffer entry, one layer at a time, double buffered
     void* stg_q[2];       // [max_batch][16][128]
     void* stg_k[2];       // [max_batch][4][128]
@@ -35,7 +36,6 @@ struct oxi_handle {
     uint64_t* stg_vp[2];
     uint32_t* stg_pos;    // [max_batch]
     uint32_t* stg_len;    // [max_batch]
-    uint32_t* host_len;   // pinned [max_batch]
     // copy streams and events of the host-buffer entry: uploads of layer l+1 and the
     // download of layer l-1 overlap the kernels of layer l
     cudaStream_t h2d, d2h;
@@ -150,10 +150,6 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
     }
     if ((rc = dev_alloc(h, (void**)&h->stg_pos, (size_t)max_batch * 4))) goto bad;
     if ((rc = dev_alloc(h, (void**)&h->stg_len, (size_t)max_batch * 4))) goto bad;
-    if (cudaMallocHost((void**)&h->host_len, (size_t)max_batch * 4) != cudaSuccess) {
-        rc = cuda_fail(cudaGetLastError(), "cudaMallocHost");
-        goto bad;
-    }
     {
         cudaError_t e = cudaStreamCreateWithFlags(&h->h2d, cudaStreamNonBlocking);
         if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->d2h, cudaStreamNonBlocking);
@@ -211,7 +207,6 @@ int32_t oxi_destroy(oxi_handle* h) {
     }
     cudaFree(h->stg_pos);
     cudaFree(h->stg_len);
-    if (h->host_len) cudaFreeHost(h->host_len);
     if (h->h2d) cudaStreamDestroy(h->h2d);
     if (h->d2h) cudaStreamDestroy(h->d2h);
     if (h->ev_start) cudaEventDestroy(h->ev_start);
@@ -235,6 +230,30 @@ int32_t oxi_device_status(oxi_handle* h, void* stream, uint32_t* bits_out) {
     OXI_CUDA(cudaMemsetAsync(h->dws.status, 0, 4, s), "status clear");
     OXI_CUDA(cudaStreamSynchronize(s), "status sync");
     *bits_out = bits;
+    return OXI_OK;
+}
+
+// The decode workspace for one launch; an armed test fault applies to this launch only.
+static DecodeWorkspace take_dws(oxi_handle* h) {
+    DecodeWorkspace ws = h->dws;
+    ws.fault = h->dbg_decode;
+    h->dbg_decode = WaitFault{};
+    return ws;
+}
+static WaitFault take_prefill_fault(oxi_handle* h) {
+    const WaitFault f = h->dbg_prefill;
+    h->dbg_prefill = WaitFault{};
+    return f;
+}
+
+int32_t oxi_debug_arm_wait_fault(oxi_handle* h, uint32_t which, uint32_t stage, uint32_t limit_us) {
+    if (!h) return fail(OXI_ERR_NULL, "oxi_debug_arm_wait_fault: handle is null");
+    if (which > 1u || limit_us == 0u || limit_us > 1000000u || stage >= 0x7fffffffu)
+        return fail(OXI_ERR_ARG, "oxi_debug_arm_wait_fault: which is 0 or 1, limit_us 1..1000000");
+    WaitFault f;
+    f.skip_plus1 = stage + 1u;
+    f.limit_us = limit_us;
+    (which == 0u ? h->dbg_decode : h->dbg_prefill) = f;
     return OXI_OK;
 }
 
@@ -266,7 +285,7 @@ int32_t oxi_decode_attn(oxi_handle* h, void* stream, void* ctx_out, const void* 
     REQ_HANDLE("oxi_decode_attn");
     REQ_PTR(ctx_out && q && k_ptrs && v_ptrs && seq_lens, "oxi_decode_attn");
     REQ_BATCH(batch, h->max_batch, "oxi_decode_attn");
-    OXI_CUDA(launch_decode_attn((cudaStream_t)stream, h->dws, ctx_out, q, gate, k_ptrs, v_ptrs,
+    OXI_CUDA(launch_decode_attn((cudaStream_t)stream, take_dws(h), ctx_out, q, gate, k_ptrs, v_ptrs,
                                 seq_lens, batch, window),
              "decode_attn launch");
     return OXI_OK;
@@ -283,7 +302,7 @@ int32_t oxi_append_decode(oxi_handle* h, void* stream, void* ctx_out, void* q_io
                 seq_lens && k_ptrs && v_ptrs, "oxi_append_decode");
     REQ_BATCH(batch, h->max_batch, "oxi_append_decode");
     if (!(eps >= 0.0f)) return fail(OXI_ERR_ARG, "oxi_append_decode: eps must be >= 0");
-    OXI_CUDA(launch_append_decode((cudaStream_t)stream, h->dws, ctx_out, q_io, k_in, v_in, gate, q_norm_w,
+    OXI_CUDA(launch_append_decode((cudaStream_t)stream, take_dws(h), ctx_out, q_io, k_in, v_in, gate, q_norm_w,
                                   k_norm_w, cos_table, sin_table, seq_lens, k_ptrs, v_ptrs, batch, window, eps),
              "append_decode launch");
     return OXI_OK;
@@ -343,7 +362,7 @@ int32_t oxi_decode_attn_paged(oxi_handle* h, void* stream, void* ctx_out, const 
     REQ_BATCH(batch, h->max_batch, "oxi_decode_attn_paged");
     PagedMap pm;
     if (int32_t rc = paged_map(layout, "oxi_decode_attn_paged", &pm)) return rc;
-    OXI_CUDA(launch_decode_attn_paged((cudaStream_t)stream, h->dws, ctx_out, q, gate, pm, seq_lens, batch, window),
+    OXI_CUDA(launch_decode_attn_paged((cudaStream_t)stream, take_dws(h), ctx_out, q, gate, pm, seq_lens, batch, window),
              "decode_attn_paged launch");
     return OXI_OK;
 }
@@ -360,7 +379,7 @@ int32_t oxi_append_decode_paged(oxi_handle* h, void* stream, void* ctx_out, void
     if (!(eps >= 0.0f)) return fail(OXI_ERR_ARG, "oxi_append_decode_paged: eps must be >= 0");
     PagedMap pm;
     if (int32_t rc = paged_map(layout, "oxi_append_decode_paged", &pm)) return rc;
-    OXI_CUDA(launch_append_decode_paged((cudaStream_t)stream, h->dws, ctx_out, q_io, k_in, v_in, gate, q_norm_w,
+    OXI_CUDA(launch_append_decode_paged((cudaStream_t)stream, take_dws(h), ctx_out, q_io, k_in, v_in, gate, q_norm_w,
                                         k_norm_w, cos_table, sin_table, seq_lens, pm, batch, window, eps),
              "append_decode_paged launch");
     return OXI_OK;
@@ -433,9 +452,10 @@ int32_t oxi_prefill_attn_paged(oxi_handle* h, void* stream, void* ctx_out, const
     REQ_BATCH(rows, h->max_prefill_rows, "oxi_prefill_attn_paged");
     PagedMap pm;
     if (int32_t rc = paged_map(layout, "oxi_prefill_attn_paged", &pm)) return rc;
+    const WaitFault flt = take_prefill_fault(h);
     OXI_CUDA(launch_prefill_attn((cudaStream_t)stream, ctx_out, q, gate, nullptr, nullptr, seq_lens, rows, window,
                                  h->dws.status, h->num_sms, h->pf_order, h->dws.status + 48, &pm, row_seq,
-                                 &h->pf_split, h->pf_part_keys, nullptr),
+                                 &h->pf_split, h->pf_part_keys, nullptr, &flt),
              "prefill_attn_paged launch");
     return OXI_OK;
 }
@@ -446,9 +466,10 @@ int32_t oxi_prefill_attn(oxi_handle* h, void* stream, void* ctx_out, const void*
     REQ_HANDLE("oxi_prefill_attn");
     REQ_PTR(ctx_out && q && k_ptrs && v_ptrs && seq_lens, "oxi_prefill_attn");
     REQ_BATCH(rows, h->max_prefill_rows, "oxi_prefill_attn");
+    const WaitFault flt = take_prefill_fault(h);
     OXI_CUDA(launch_prefill_attn((cudaStream_t)stream, ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens,
                                  rows, window, h->dws.status, h->num_sms, h->pf_order, h->dws.status + 48, nullptr,
-                                 nullptr, &h->pf_split, h->pf_part_keys, &h->pf_slab),
+                                 nullptr, &h->pf_split, h->pf_part_keys, &h->pf_slab, &flt),
              "prefill_attn launch");
     return OXI_OK;
 }
@@ -559,10 +580,12 @@ int32_t oxi_decode_step_host(oxi_handle* h, void* stream, void* ctx_host, const 
     OXI_CUDA(cudaEventRecord(h->ev_start, s), "event record");
     OXI_CUDA(cudaStreamWaitEvent(h->h2d, h->ev_start, 0), "stream wait");
     OXI_CUDA(cudaStreamWaitEvent(h->d2h, h->ev_start, 0), "stream wait");
-    // step metadata: positions and lengths (seq_len counts the appended token)
-    for (uint32_t i = 0; i < batch; i++) h->host_len[i] = pos_ids_host[i] + 1u;
+    // step metadata: only the positions cross the bus; the lengths (seq_len counts the appended
+    // token) are derived on the device.  Nothing is read from pos_ids_host at enqueue time, so
+    // steps may be enqueued back to back without a sync, and a captured graph of this call
+    // re-reads pos_ids_host (pinned) at every replay.
     OXI_CUDA(cudaMemcpyAsync(h->stg_pos, pos_ids_host, (size_t)batch * 4, H2D, h->h2d), "pos upload");
-    OXI_CUDA(cudaMemcpyAsync(h->stg_len, h->host_len, (size_t)batch * 4, H2D, h->h2d), "len upload");
+    OXI_CUDA(launch_len_from_pos(h->h2d, h->stg_pos, h->stg_len, batch), "len_from_pos launch");
     for (uint32_t l = 0; l < layers; l++) {
         const int sb = l & 1;
         // uploads of layer l reuse the staging set of layer l-2: wait until its kernels are done
@@ -578,7 +601,7 @@ int32_t oxi_decode_step_host(oxi_handle* h, void* stream, void* ctx_host, const 
         OXI_CUDA(cudaStreamWaitEvent(s, h->ev_up[sb], 0), "stream wait");
         // the ctx staging buffer of layer l-2 must have been downloaded
         if (l >= 2) OXI_CUDA(cudaStreamWaitEvent(s, h->ev_down[sb], 0), "stream wait");
-        OXI_CUDA(launch_append_decode(s, h->dws, h->stg_ctx[sb], h->stg_q[sb], h->stg_k[sb], h->stg_v[sb],
+        OXI_CUDA(launch_append_decode(s, take_dws(h), h->stg_ctx[sb], h->stg_q[sb], h->stg_k[sb], h->stg_v[sb],
                                       gate_host ? h->stg_gate[sb] : nullptr,
                                       (const char*)q_norm_w_dev + (size_t)l * HD * 2,
                                       (const char*)k_norm_w_dev + (size_t)l * HD * 2, cos_table_dev,

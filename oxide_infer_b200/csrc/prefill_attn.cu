@@ -376,8 +376,10 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                     uint32_t rows, uint32_t window, uint32_t* __restrict__ status,
                     const uint32_t* __restrict__ order, uint32_t* __restrict__ counter,
                     const PagedMap pm, const uint32_t* __restrict__ row_seq, const PfSplit sp,
-                    const __grid_constant__ TmaDesc tmap, const uint64_t slab_base, const uint32_t slab_rows) {
+                    const __grid_constant__ TmaDesc tmap, const uint64_t slab_base, const uint32_t slab_rows,
+                    const WaitFault fault) {
     using namespace pf;
+    const uint32_t wait_us = fault.skip_plus1 ? fault.limit_us : WAIT_LIMIT_US;
     // paged K/V: k_ptrs / v_ptrs are unused, wave row r reads row row_seq[r] of pm.block_tables
     constexpr bool paged = kPaged;
     extern __shared__ unsigned char smem_raw[];
@@ -442,8 +444,8 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     // Claims the next item and prepares its tables in buffer `buf`; run by all lanes of the K loader warp
     // while the other roles finish the current item (before the loop for the first item).
     auto prepare_item = [&](uint32_t buf) {
-        uint32_t item = 0;
-        if (lane == 0) item = atomicAdd(counter, 1u);
+        uint32_t item = 0xffffffffu;  // a CTA one of whose waits gave up claims nothing more: the others take its share
+        if (lane == 0 && *const_cast<volatile uint32_t*>(&s_abort) == 0u) item = atomicAdd(counter, 1u);
         item = __shfl_sync(0xffffffffu, item, 0);
         if (lane == 0) s_item[buf] = item;
         if (item >= nitems) return;
@@ -632,7 +634,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                 tflat += ntiles;
             }
             for (uint32_t tile = tile0; tile < tile1; tile++) {
-                ok &= mbar_wait_bounded(&bar_sfull[j], gk & 1u, &s_abort);  // S_j(tile) complete
+                ok &= mbar_wait_bounded(&bar_sfull[j], gk & 1u, &s_abort, wait_us);  // S_j(tile) complete
                 __syncwarp();
                 tc_fence_after();
                 const uint32_t kbeg = run.lo + tile * TK;
@@ -676,7 +678,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                 }
                 l_run = l_run * corr + ((psa[0] + psa[1]) + (psa[2] + psa[3]));
                 // P_j and O_j are free once PV_j of the tile before is complete (first tile of the CTA: passes)
-                if (!pv_prev_done) ok &= mbar_wait_bounded(&bar_pvdone[j], (gk - 1u) & 1u, &s_abort);
+                if (!pv_prev_done) ok &= mbar_wait_bounded(&bar_pvdone[j], (gk - 1u) & 1u, &s_abort, wait_us);
                 __syncwarp();
                 tc_fence_after();
                 if (o_valid && __any_sync(0xffffffffu, raise)) {
@@ -707,8 +709,13 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
             const uint32_t row = (uint32_t)(hw * 32 + lane);
             const size_t pidx = ((size_t)sp.slots[item >> 2] * NKV + kvh) * 2 + j;
             const bool live = tok < nrows && c_len[tok] != 0;
-            if (o_valid) {
-                ok &= mbar_wait_bounded(&bar_ofull[j], n_o & 1u, &s_abort);
+            // bounds build: the part's slot lies inside the reserved workspace
+            const bool slot_ok = OXI_IN_BOUNDS(sp.slots[item >> 2] < sp.max_slots, status);
+            if (o_valid && !slot_ok) {
+                ok &= mbar_wait_bounded(&bar_ofull[j], n_o & 1u, &s_abort, wait_us);
+                ++n_o;
+            } else if (o_valid) {
+                ok &= mbar_wait_bounded(&bar_ofull[j], n_o & 1u, &s_abort, wait_us);
                 ++n_o;
                 __syncwarp();
                 tc_fence_after();
@@ -723,16 +730,18 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                         po[ch * 8 + v4] = make_uint4(orow[4 * v4], orow[4 * v4 + 1], orow[4 * v4 + 2], orow[4 * v4 + 3]);
                 }
             }
-            *reinterpret_cast<float2*>(sp.part_ml + (pidx * M + row) * 2) =
-                make_float2(m_ref, (o_valid && live && ok) ? l_run : 0.0f);
+            if (slot_ok) *reinterpret_cast<float2*>(sp.part_ml + (pidx * M + row) * 2) =
+                make_float2(m_ref, (o_valid && live && ok && *const_cast<volatile uint32_t*>(&s_abort) == 0u) ? l_run : 0.0f);
         } else
         // ---- epilogue: O row from TMEM, 1/sum, f16, gate on the f16 value (as online kernel + gate kernel)
         if (o_valid) {
-            ok &= mbar_wait_bounded(&bar_ofull[j], n_o & 1u, &s_abort);
+            ok &= mbar_wait_bounded(&bar_ofull[j], n_o & 1u, &s_abort, wait_us);
             ++n_o;
             __syncwarp();
             tc_fence_after();
-            const bool write = tok < nrows && c_len[tok] != 0 && ok;
+            // no output once any wait of this CTA gave up (this thread's own waits may all have passed)
+            const bool write = OXI_IN_BOUNDS(row0 + tok < rows || tok >= nrows, status) && tok < nrows && c_len[tok] != 0 && ok &&
+                               *const_cast<volatile uint32_t*>(&s_abort) == 0u;
             const float inv = rcp_approx_ftz(l_run);
             const size_t rh = (size_t)(row0 + (write ? tok : 0u)) * NQ + head;
             const float sig = (gate && write) ? sigmoid_ref(h2f(gate[rh])) : 1.0f;
@@ -770,7 +779,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         // issues its burst, the other one waits for the data of its next burst.  Bursts are never
         // interleaved: MMAs that accumulate into the same tile stay back to back on the pipe.
         const uint32_t j = warp_u == W_MMA0 ? 0u : 1u;
-        ok &= mbar_wait_bounded(&bar_qfull[j], it & 1u, &s_abort);
+        ok &= mbar_wait_bounded(&bar_qfull[j], it & 1u, &s_abort, wait_us);
         __syncwarp();
         tc_fence_after();
         // descriptors of ring stage 0; a stage / sub-tile / k-step is an offset added to the
@@ -811,17 +820,17 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
             if (has_pv) {
                 const uint32_t g = g0 + t - 2;
                 sv = g % NS;
-                ok &= mbar_wait_bounded(&bar_vfull[sv], (g / NS) & 1u, &s_abort);
-                ok &= mbar_wait_bounded(&bar_pfull[j], g & 1u, &s_abort);
+                ok &= mbar_wait_bounded(&bar_vfull[sv], (g / NS) & 1u, &s_abort, wait_us);
+                ok &= mbar_wait_bounded(&bar_pfull[j], g & 1u, &s_abort, wait_us);
             }
             if (has_qk) {
                 const uint32_t g = g0 + t;
                 sk = g % NS;
-                ok &= mbar_wait_bounded(&bar_kfull[sk], (g / NS) & 1u, &s_abort);
-                if (t >= 1) ok &= mbar_wait_bounded(&bar_sfree[j], (g - 1u) & 1u, &s_abort);
+                ok &= mbar_wait_bounded(&bar_kfull[sk], (g / NS) & 1u, &s_abort, wait_us);
+                if (t >= 1) ok &= mbar_wait_bounded(&bar_sfree[j], (g - 1u) & 1u, &s_abort, wait_us);
             }
             // the token: warp 0's n-th burst follows warp 1's (n-1)-th, warp 1's n-th follows warp 0's n-th
-            ok &= mbar_wait_bounded(&bar_tok[j], (j == 0 ? n_burst + 1u : n_burst) & 1u, &s_abort);
+            ok &= mbar_wait_bounded(&bar_tok[j], (j == 0 ? n_burst + 1u : n_burst) & 1u, &s_abort, wait_us);
             __syncwarp();
             tc_fence_after();
             if (elect_one()) {
@@ -869,6 +878,12 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         // row r, chunk position (c%8) ^ (r%8)
         const uint32_t c = lane & 15u, r0 = lane >> 4;
         uint32_t pending = 0;  // tiles requested whose full barrier has not been signalled yet
+        // publishes K (or V) tile number g to the tensor core; test support: CTA 0's K loader withholds one
+        // tile (its copies have landed, the arrival never comes), so the MMA warps' wait for it runs out
+        auto publish = [&](uint32_t g) {
+            if (is_k && fault.skip_plus1 && blockIdx.x == 0 && g + 1u == fault.skip_plus1) return;
+            mbar_arrive(&full[g % NS]);
+        };
         uint32_t tflat = 0;    // tiles of the block's runs before this one (key-range split)
         uint32_t next = 0;
         PfRun run;
@@ -912,13 +927,13 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                 if (tma_run && pending) {  // tiles of an earlier run still in flight as plain copies
                     cp_async_wait<0>();
                     fence_proxy_async_smem();
-                    for (; pending > 0; --pending) mbar_arrive(&full[(gk - pending) % NS]);
+                    for (; pending > 0; --pending) publish(gk - pending);
                 }
             }
             for (uint32_t tile = tile0; tile < tile1; tile++) {
                 const uint32_t st = gk % NS;
                 // the MMAs that read this stage's previous tile have completed (first use: passes at once)
-                ok &= mbar_wait_bounded(&empty[st], ((gk / NS) & 1u) ^ 1u, &s_abort);
+                ok &= mbar_wait_bounded(&empty[st], ((gk / NS) & 1u) ^ 1u, &s_abort, wait_us);
                 const uint32_t kbeg = run.lo + tile * TK;
                 if (kTma && tma_run && kbeg + TK <= run.hi) {
                     if (lane == 0 && ok) {  // after a wait gave up nothing more is copied
@@ -967,19 +982,19 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                 if (kTma && tma_run) {  // the one ragged tile of a run loaded by TMA: publish it at once
                     cp_async_wait<0>();
                     fence_proxy_async_smem();
-                    mbar_arrive(&full[(gk - 1u) % NS]);
+                    publish(gk - 1u);
                     --pending;
                 } else if (pending == DEPTH) {  // the oldest tile in flight has landed: publish it to the tensor core
                     cp_async_wait<DEPTH - 1>();
                     fence_proxy_async_smem();
-                    mbar_arrive(&full[(gk - DEPTH) % NS]);
+                    publish(gk - DEPTH);
                     --pending;
                 }
             }
         }
         cp_async_wait<0>();
         fence_proxy_async_smem();
-        for (; pending > 0; --pending) mbar_arrive(&full[(gk - pending) % NS]);
+        for (; pending > 0; --pending) publish(gk - pending);
         // all tiles of this item are on their way to the tensor core: claim the next item and prepare its
         // tables while the other roles work through the last tiles
         if (is_k) prepare_item(buf ^ 1u);
@@ -1090,11 +1105,11 @@ template <bool kPaged, bool kSplit, bool kTma>
 static cudaError_t launch_pf(cudaStream_t stream, uint32_t grid, void* ctx_out, const void* q, const void* gate,
                              const uint64_t* k_ptrs, const uint64_t* v_ptrs, const uint32_t* seq_lens, uint32_t rows,
                              uint32_t window, uint32_t* status, uint32_t* order, uint32_t* counter, const PagedMap& pm,
-                             const uint32_t* row_seq, const PfSplit& sp, const PrefillSlab& slab) {
+                             const uint32_t* row_seq, const PfSplit& sp, const PrefillSlab& slab, const WaitFault& fault) {
     // programmatic dependent of the plan kernel: TMEM allocation and barrier set-up overlap it
     return launch_pdl(prefill_attn_kernel<kPaged, kSplit, kTma>, dim3(grid), dim3(pf::THREADS), pf::SMEM_BYTES, stream,
                       (uint16_t*)ctx_out, (const uint16_t*)q, (const uint16_t*)gate, k_ptrs, v_ptrs, seq_lens, rows,
-                      window, status, (const uint32_t*)order, counter, pm, row_seq, sp, slab.map, slab.base, slab.rows);
+                      window, status, (const uint32_t*)order, counter, pm, row_seq, sp, slab.map, slab.base, slab.rows, fault);
 }
 
 cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* q,
@@ -1102,7 +1117,8 @@ cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* 
                                 const uint32_t* seq_lens, uint32_t rows, uint32_t window,
                                 uint32_t* status, int num_sms, uint32_t* order, uint32_t* counter,
                                 const PagedMap* pm, const uint32_t* row_seq, const PrefillSplitWs* ws,
-                                uint32_t part_keys, const PrefillSlab* slab) {
+                                uint32_t part_keys, const PrefillSlab* slab, const WaitFault* fault) {
+    const WaitFault flt = fault ? *fault : WaitFault{};
     const uint32_t nblocks = (rows + pf::BLK - 1) / pf::BLK;
     // the split is for waves that leave SMs idle; larger waves balance by claiming longest first
     const bool split = ws && ws->max_slots != 0u && part_keys != 0u && nblocks * NKV < (uint32_t)num_sms;
@@ -1127,7 +1143,7 @@ cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* 
     const PrefillSlab none{};
     const bool tma = !pm && slab && slab->rows != 0u;
     const PrefillSlab& sl = tma ? *slab : none;
-#define OXI_PF_ARGS ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, rows, window, status, order, counter, map, row_seq, sp, sl
+#define OXI_PF_ARGS ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, rows, window, status, order, counter, map, row_seq, sp, sl, flt
     if (!split) {
         const uint32_t nitems = nblocks * NKV;
         const uint32_t grid = nitems < (uint32_t)num_sms ? nitems : (uint32_t)num_sms;

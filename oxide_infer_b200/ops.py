@@ -96,6 +96,11 @@ class KvPath:
         _check(self.lib.oxi_device_status(self.h, _stream(), C.byref(bits)), "oxi_device_status")
         return bits.value
 
+    def arm_wait_fault(self, which: int, stage: int, limit_us: int = 1000):
+        """Test support (oxi_debug_arm_wait_fault): the next decode (which=0) or prefill (which=1)
+        attention launch loses one pipeline stage of CTA 0 and its waits last limit_us."""
+        _check(self.lib.oxi_debug_arm_wait_fault(self.h, which, stage, limit_us), "oxi_debug_arm_wait_fault")
+
     # ---- fused operators
     def append(self, q_io, k_in, v_in, q_norm_w, k_norm_w, cos, sin, pos_ids, k_ptrs, v_ptrs,
                eps: float = 1e-5, batch: int | None = None):

@@ -25,3 +25,84 @@ def pytest_collection_modifyitems(config, items):
     for it in items:
         if "gpu" in it.keywords:
             it.add_marker(skip)
+
+
+# ---- the reference's kernels as a live oracle ------------------------------------------------
+# oracle/_ref/*.cubin (the reference's PTX assembled for sm_100a) travel with the repository to
+# the GPU box.  Where they are missing, tests that compare against them are SKIPPED (visible in
+# the summary) instead of passing on the oracle-only assertions:
+#   OXI_REQUIRE_REF=1   missing cubins fail the test instead of skipping it
+#   OXI_ALLOW_NO_REF=1  run such tests without the reference comparison (oracle only), on request
+_REF_STATS = {"calls": 0, "tests": set()}
+
+
+class _CountingRef:
+    """Forwards to oracle.refptx.RefPtx and counts the reference kernel sequences that ran."""
+
+    def __init__(self, inner, request):
+        self._inner = inner
+        self._request = request
+
+    def __getattr__(self, name):
+        attr = getattr(self._inner, name)
+        if not callable(attr):
+            return attr
+
+        def counted(*a, **k):
+            _REF_STATS["calls"] += 1
+            return attr(*a, **k)
+        return counted
+
+
+def reference_or_policy():
+    """RefPtx instance, or None when OXI_ALLOW_NO_REF=1 asks for oracle-only runs; skips or fails otherwise."""
+    from oracle import refptx
+    if refptx.available():
+        return refptx.RefPtx()
+    if os.environ.get("OXI_REQUIRE_REF") == "1":
+        pytest.fail("oracle/_ref cubins are missing and OXI_REQUIRE_REF=1")
+    if os.environ.get("OXI_ALLOW_NO_REF") == "1":
+        return None
+    pytest.skip("reference cubins (oracle/_ref) not built: no comparison against the reference's kernels")
+
+
+@pytest.fixture(scope="session")
+def _ref_session():
+    return {"obj": None, "made": False}
+
+
+@pytest.fixture()
+def ref(request, _ref_session):
+    if not _ref_session["made"]:
+        _ref_session["obj"] = reference_or_policy()
+        _ref_session["made"] = True
+    inner = _ref_session["obj"]
+    if inner is None:
+        return None
+    _REF_STATS["tests"].add(request.node.nodeid)
+    return _CountingRef(inner, request)
+
+
+@pytest.fixture(autouse=True)
+def _guard_bands(request):
+    """After every GPU test: no kernel wrote outside a guarded buffer (tests/kvcase.py)."""
+    yield
+    if "gpu" not in request.keywords:
+        return
+    import torch
+    if not torch.cuda.is_available():
+        return
+    from tests import kvcase
+    torch.cuda.synchronize()
+    _GUARD_STATS["buffers"] += kvcase.check_guards()
+
+
+_GUARD_STATS = {"buffers": 0}
+
+
+def pytest_terminal_summary(terminalreporter):
+    if _REF_STATS["calls"]:
+        terminalreporter.write_line(
+            f"reference kernels: {_REF_STATS['calls']} launch sequences compared in {len(_REF_STATS['tests'])} tests")
+    if _GUARD_STATS["buffers"]:
+        terminalreporter.write_line(f"guard bands: {_GUARD_STATS['buffers']} guarded buffers checked, none overwritten")

@@ -11,6 +11,46 @@ import torch
 NQ, NKV, HD, HIDDEN = 16, 4, 128, 2048
 
 
+# ---- guard bands: out-of-bounds evidence without a sanitizer -------------------------------
+# Every buffer a kernel may write through a table (K/V caches, conv states, contexts) can be
+# placed between two bands of a fixed byte pattern inside one allocation.  A write that lands
+# before or behind the buffer changes a band; check_guards() (run after every GPU test by
+# tests/conftest.py) finds it.  Without the bands such a write would land in a neighbouring torch
+# allocation and pass unnoticed.
+GUARD_BYTES = 4096
+GUARD_BYTE = 0xA5
+_GUARDS = []  # (whole allocation as uint8, payload bytes, label)
+
+
+def guarded(a, label="buffer"):
+    """Copies numpy array (or CPU tensor) `a` to the GPU between two guard bands; returns the
+    payload view (same shape and dtype, 16-byte aligned)."""
+    t = torch.from_numpy(np.ascontiguousarray(a)) if isinstance(a, np.ndarray) else a.contiguous()
+    nbytes = t.numel() * t.element_size()
+    pad = (-nbytes) % 16
+    whole = torch.full((GUARD_BYTES + nbytes + pad + GUARD_BYTES,), GUARD_BYTE, dtype=torch.uint8, device="cuda")
+    payload = whole[GUARD_BYTES:GUARD_BYTES + nbytes].view(t.dtype).view(t.shape)
+    payload.copy_(t)
+    _GUARDS.append((whole, nbytes, label))
+    return payload
+
+
+def check_guards(clear=True):
+    """Asserts that no guard band registered since the last call was written to; returns how many
+    buffers were checked."""
+    n = len(_GUARDS)
+    bad = []
+    for whole, nbytes, label in _GUARDS:
+        front = whole[:GUARD_BYTES]
+        back = whole[GUARD_BYTES + nbytes:]
+        if not (bool((front == GUARD_BYTE).all()) and bool((back == GUARD_BYTE).all())):
+            bad.append(label)
+    if clear:
+        _GUARDS.clear()
+    assert not bad, f"out-of-bounds write next to: {bad[:8]} ({len(bad)} of {n} guarded buffers)"
+    return n
+
+
 def u32(t):  # numpy uint32 -> torch int32 bit pattern on the GPU
     return torch.from_numpy(np.ascontiguousarray(t).view(np.int32)).cuda()
 
@@ -53,8 +93,8 @@ class DecodeCase:
     # ---- device view
     def device(self):
         d = type("D", (), {})()
-        d.k_cache = [torch.from_numpy(a).cuda() for a in self.k_cache]
-        d.v_cache = [torch.from_numpy(a).cuda() for a in self.v_cache]
+        d.k_cache = [guarded(a, f"k_cache[{i}]") for i, a in enumerate(self.k_cache)]
+        d.v_cache = [guarded(a, f"v_cache[{i}]") for i, a in enumerate(self.v_cache)]
         d.k_ptrs, d.v_ptrs = dev_ptr_table(d.k_cache), dev_ptr_table(d.v_cache)
         d.q, d.k, d.v = (torch.from_numpy(x.copy()).cuda() for x in (self.q, self.k, self.v))
         d.gate = torch.from_numpy(self.gate).cuda()
@@ -62,7 +102,7 @@ class DecodeCase:
         d.k_norm_w = torch.from_numpy(self.k_norm_w).cuda()
         d.cos, d.sin = torch.from_numpy(self.cos).cuda(), torch.from_numpy(self.sin).cuda()
         d.pos_ids, d.seq_lens = u32(self.pos_ids), u32(self.seq_lens)
-        d.ctx = torch.zeros(self.b, NQ, HD, dtype=torch.float16, device="cuda")
+        d.ctx = guarded(np.zeros((self.b, NQ, HD), np.float16), "ctx")
         return d
 
 

@@ -130,8 +130,9 @@ def test_greedy_64_steps_identical_tokens():
     assert kv.device_status() == 0
     assert np.array_equal(t_paged, t_ours)
 
-    if refptx.available():
-        ref = refptx.RefPtx()
+    from tests.conftest import reference_or_policy
+    ref = reference_or_policy()  # skips (or fails, or goes on without it) where the cubins are missing
+    if ref is not None:
 
         def theirs(l, q, k, v, gate, pos, sl, kp, vp, cache):
             ctx = torch.empty(NSEQ, NQ, HD, dtype=torch.float16, device="cuda")

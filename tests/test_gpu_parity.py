@@ -1,5 +1,6 @@
-"""GPU parity: liboxi_kv (through the C ABI) against the CPU oracle and, when the
-prebuilt cubins are present, against the reference's own kernels on the same GPU.
+"""GPU parity: liboxi_kv (through the C ABI) against the CPU oracle and against the
+reference's own kernels on the same GPU (fixture `ref` of tests/conftest.py: tests that use it are
+skipped, not passed, where the prebuilt cubins are missing).
 
 Bars: K/V/q/conv-state bytes bit-exact vs the reference kernels (K and q within
 one f16 ulp vs the CPU oracle, whose rsqrt is correctly rounded); attention
@@ -23,14 +24,6 @@ def kv():
     yield p
     assert p.device_status() == 0
     p.close()
-
-
-@pytest.fixture(scope="module")
-def ref():
-    from oracle import refptx
-    if not refptx.available():
-        return None
-    return refptx.RefPtx()
 
 
 @pytest.fixture(scope="module")

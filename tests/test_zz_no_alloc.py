@@ -70,3 +70,9 @@ def test_static_entry_rejects_sizes_beyond_its_array():
     assert _static(lib, d, 2, 16, 0) == 0
     torch.cuda.synchronize()
     assert torch.equal(d.ctx[1], before[1]) and d.ctx[0].abs().sum().item() > 0
+    # the skipped row is reported through the path's own status word, which a later call does not clear
+    assert _static(lib, d, 1, 16, 0) == 0
+    bits = C.c_uint32(0)
+    assert lib.oxi_static_device_status(st, C.byref(bits)) == 0
+    assert bits.value == 2  # OXI_DEV_BAD_SEQ_LEN
+    assert lib.oxi_static_device_status(st, C.byref(bits)) == 0 and bits.value == 0
