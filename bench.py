@@ -200,6 +200,56 @@ def cpu_baseline(seq_len: int, batch: int, budget_s: float = 12.0):
                       f"{reps} reps in {dt:.1f} s"}
 
 
+def _graph_of(torch, fn, warm=1):
+    """Captures fn() (already warmed up by the caller) into a CUDA graph on a side stream."""
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    return graph
+
+
+def _timed_region(torch, fn, steps, barrier):
+    """K calls of fn() between two events on the current stream, a barrier + synchronize on both sides."""
+    stream = torch.cuda.current_stream()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record(stream)
+    for _ in range(steps):
+        fn()
+    t1.record(stream)
+    barrier()
+    return t0.elapsed_time(t1)
+
+
+def read_only_peak(torch, kv, bufs, reps=8):
+    """GB/s of the library's read-only stream probe (the decode kernel's bulk-copy pipeline without
+    arithmetic): one launch per buffer of `bufs` (each one layer's K or V slab, far larger than L2),
+    replayed as a CUDA graph like the headline step, with the decode kernel's 4 KB copies and with
+    32 KB copies."""
+    out = {}
+    for name, cb in (("copy_4k", 4096), ("copy_32k", 32768)):
+        def launches():
+            for b in bufs:
+                kv.stream_read(b, cb)
+        launches()
+        graph = _graph_of(torch, launches)
+        graph.replay()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(reps):
+            graph.replay()
+        t1.record()
+        torch.cuda.synchronize()
+        nbytes = reps * sum(b.numel() * b.element_size() for b in bufs)
+        out[name] = round(nbytes / (t0.elapsed_time(t1) * 1e-3) / 1e9, 1)
+    return out
+
+
 def run_ours(args, torch, rank, world, local_rank):
     from oxide_infer_b200 import KvPath
     kv = KvPath(local_rank, max_batch=BATCH, max_seq_len=CTX, max_prefill_rows=16)
@@ -229,47 +279,31 @@ def run_ours(args, torch, rank, world, local_rank):
     sampler.wait_ready()
     for _ in range(args.warmup):
         step()
-    barrier()
-    ev, t0, t1 = [], torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev = []
     w0 = time.perf_counter()
-    t0.record(stream)
-    for _ in range(args.steps):
-        step(ev)
-    t1.record(stream)
-    barrier()
+    ms = _timed_region(torch, lambda: step(ev), args.steps, barrier)
     w1 = time.perf_counter()
-    ms = t0.elapsed_time(t1)
-    attn_ms = sum(a.elapsed_time(b) for a, b in ev) / len(ev)
-    clocks = sampler.window(w0, w1)
+    pair_ms_stream = sum(a.elapsed_time(b) for a, b in ev) / len(ev)
 
     # the same K steps as replays of ONE captured 8-layer step (what an engine that captures its
     # decode step sees): identical kernels and work, no host launch gaps; timed like the stream run
-    ms_graph = None
+    ms_graph = float("inf")
+    graph = graph_h = None
     try:
-        graph = torch.cuda.CUDAGraph()
-        side = torch.cuda.Stream()
-        with torch.cuda.stream(side):
-            with torch.cuda.graph(graph, stream=side):
-                step()
+        graph = _graph_of(torch, step)
         for _ in range(3):
             graph.replay()
-        barrier()
-        t0.record(stream)
-        for _ in range(args.steps):
-            graph.replay()
-        t1.record(stream)
-        barrier()
-        ms_graph = t0.elapsed_time(t1)
+        ms_graph = _timed_region(torch, graph.replay, args.steps, barrier)
     except Exception as exc:  # every rank must take the same path below
-        ms_graph = float("inf")
         if rank == 0:
             print(f"cuda graph capture failed: {exc}", file=sys.stderr)
+    clocks = sampler.window(w0, time.perf_counter())  # both timed regions of the headline
     if args.no_e2e:
         sampler.stop()
         if rank == 0:
-            attn_gbs = alg_bytes_layer(w.seq_lens_host) / (attn_ms * 1e-3) / 1e9
+            attn_gbs = alg_bytes_layer(w.seq_lens_host) / (pair_ms_stream * 1e-3) / 1e9
             return {"profiling_case": True, "layers": LAYERS, "batch": BATCH, "ctx": CTX,
-                    "ms_per_step": round(ms / args.steps, 4), "decode_attn_us": round(attn_ms * 1e3, 2),
+                    "ms_per_step": round(ms / args.steps, 4), "decode_attn_us": round(pair_ms_stream * 1e3, 2),
                     "decode_attn_gbs": round(attn_gbs, 1), "clocks": clocks}
         return None
 
@@ -279,7 +313,7 @@ def run_ours(args, torch, rank, world, local_rank):
     hctx = torch.zeros(LAYERS, BATCH, NQ, HD, dtype=torch.float16).pin_memory()
     hpos = pin(w.pos)
     hkp, hvp = pin(torch.stack(w.k_ptrs)), pin(torch.stack(w.v_ptrs))
-    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hg, hkp, hvp)) + 2 * hpos.numel() * 4
+    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hg, hkp, hvp)) + hpos.numel() * 4
     d2h = hctx.numel() * 2
 
     def step_host():
@@ -287,56 +321,63 @@ def run_ours(args, torch, rank, world, local_rank):
 
     for _ in range(max(3, args.warmup)):
         step_host()
-    barrier()
-    t0.record(stream)
-    for _ in range(args.steps):
-        step_host()
-    t1.record(stream)
-    barrier()
-    ms_e2e = t0.elapsed_time(t1)
+    ms_e2e = _timed_region(torch, step_host, args.steps, barrier)
     e2e_mode = "stream launches"
+    ms_e2e_graph = float("inf")
     try:  # the same host-buffer step captured once (copies from the same pinned buffers included) and replayed
-        graph_h = torch.cuda.CUDAGraph()
-        side_h = torch.cuda.Stream()
-        with torch.cuda.stream(side_h):
-            with torch.cuda.graph(graph_h, stream=side_h):
-                step_host()
+        graph_h = _graph_of(torch, step_host)
         for _ in range(3):
             graph_h.replay()
-        barrier()
-        t0.record(stream)
-        for _ in range(args.steps):
-            graph_h.replay()
-        t1.record(stream)
-        barrier()
-        ms_e2e_graph = t0.elapsed_time(t1)
+        ms_e2e_graph = _timed_region(torch, graph_h.replay, args.steps, barrier)
     except Exception as exc:
-        ms_e2e_graph = float("inf")
         if rank == 0:
             print(f"cuda graph capture of the host-buffer step failed: {exc}", file=sys.stderr)
-    sampler.stop()
     step()  # untimed: same inputs as the host-buffer path, for the equality check
     status = kv.device_status()
     ctx_ok = bool(torch.isfinite(w.ctx.float()).all().item()) and bool(torch.isfinite(hctx.float()).all().item())
     same = bool((hctx.cuda() == w.ctx).all().item())
+    ro_peak = read_only_peak(torch, kv, [w.k_slab[0], w.v_slab[0], w.k_slab[1 % LAYERS], w.v_slab[1 % LAYERS]])
+    status |= kv.device_status()
+    layer_bytes = alg_bytes_layer(w.seq_lens_host)
 
-    times = torch.tensor([ms, ms_e2e, attn_ms, ms_graph, ms_e2e_graph], dtype=torch.float64, device="cuda")
+    # ---- the other configurations, every rank on its own GPU (rank 0 reports); config 5 is partitioned
+    secondary = {}
+    if not args.no_secondary:
+        secondary["decode_ragged"] = leg_decode_ragged(args, torch, "ours", w, kv)
+        if (LAYERS, BATCH, CTX) == (8, 128, 4096):
+            secondary["decode_paged"] = leg_decode_paged(args, torch, w, kv)
+        del w, graph, graph_h
+        kv.close()
+        torch.cuda.empty_cache()
+        secondary["serving_mix"] = leg_serving_mix(args, torch, "ours", rank, world, local_rank)
+        torch.cuda.empty_cache()
+        secondary["prefill"] = leg_prefill(args, torch, "ours")
+        secondary["conv"] = leg_conv(args, torch, "ours")
+        secondary["sample"] = leg_sample(args, torch)
+        torch.cuda.empty_cache()
+    sampler.stop()
+
+    times = torch.tensor([ms, ms_e2e, pair_ms_stream, ms_graph, ms_e2e_graph], dtype=torch.float64, device="cuda")
     if world > 1:
         torch.distributed.all_reduce(times, op=torch.distributed.ReduceOp.MAX)
-    ms, ms_e2e, attn_ms, ms_graph, ms_e2e_graph = (float(x) for x in times.tolist())
+    ms, ms_e2e, pair_ms_stream, ms_graph, ms_e2e_graph = (float(x) for x in times.tolist())
+    ms_e2e_stream = ms_e2e
     if ms_e2e_graph < ms_e2e:
         ms_e2e, e2e_mode = ms_e2e_graph, "cuda graph replay of the captured host-buffer step"
     if rank != 0:
         return None
 
-    step_bytes = LAYERS * alg_bytes_layer(w.seq_lens_host) * world
+    step_bytes = LAYERS * layer_bytes * world
     peak, peak_kind = measured_peak_gbs()
     ms_stream = ms  # K steps launched one call at a time on the stream
     launch_mode = "stream launches (one C-ABI call per layer)"
     if ms_graph < ms:
         ms = ms_graph
         launch_mode = "cuda graph replay of the captured 8-layer step"
-    attn_gbs = alg_bytes_layer(w.seq_lens_host) / (attn_ms * 1e-3) / 1e9
+    # the dominant kernel pair (fused decode_attn_kernel + decode_merge_kernel) is the whole timed region:
+    # its average duration in the SAME launch mode as `value` is region time / launches
+    pair_us = ms / args.steps / LAYERS * 1e3
+    attn_gbs = layer_bytes / (pair_us * 1e-6) / 1e9
     line = {
         "metric": "gqa_decode_step_hbm_gbs", "value": round(step_bytes * args.steps / (ms * 1e-3) / 1e9, 1),
         "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -345,24 +386,38 @@ def run_ours(args, torch, rank, world, local_rank):
         "data": "synthetic",
         "config": {"workload": f"decode_step_{LAYERS}_attention_layers_B{BATCH}_per_gpu_ctx{CTX}" +
                                ("_ragged_lengths_uniform_1024_4096" if RAGGED else ""),
-                   "layers": LAYERS, "batch_per_gpu": BATCH, "seq_len": CTX, "heads": "16q/4kv x128",
-                   "kv_bytes_per_gpu": int(LAYERS * w.seq_lens_host.sum() * 2 * ROW_BYTES),
-                   "l2": "inputs larger than L2 (1.07 GB of KV per layer, 8 distinct layers)",
-                   "launch": launch_mode,
-                   "parallelism": f"replicas x{world}, sequences partitioned, no collective"},
+                   "layers": LAYERS, "batch_per_gpu": BATCH, "seq_len": CTX},
+        "notes": {"heads": "16q/4kv x128", "kv_bytes_per_gpu": int(LAYERS * BATCH * CTX * 2 * ROW_BYTES),
+                  "l2": "inputs larger than L2 (1.07 GB of KV per layer, 8 distinct layers)",
+                  "launch": launch_mode,
+                  "parallelism": f"replicas x{world}, sequences partitioned, no collective"},
         "e2e": {"value": round(step_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
                 "ms_per_step": round(ms_e2e / args.steps, 4), "h2d_bytes_per_step": int(h2d),
-                "d2h_bytes_per_step": int(d2h), "launch": e2e_mode},
+                "d2h_bytes_per_step": int(d2h), "launch": e2e_mode,
+                "stream_launch_ms_per_step": round(ms_e2e_stream / args.steps, 4),
+                "cuda_graph_replay_ms_per_step": round(ms_e2e_graph / args.steps, 4) if ms_e2e_graph != float("inf") else None},
         "gpu_launches": 2 * LAYERS * args.steps,  # fused append+decode_attn, decode_merge per layer
-        "roofline": {"kernel": "decode_attn_kernel<fused append> + decode_merge_kernel", "bound": "hbm", "achieved": round(attn_gbs, 1),
-                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(attn_gbs / peak, 4),
-                     "frac_of_8TBs_nominal": round(attn_gbs / 8000.0, 4), "us_per_launch": round(attn_ms * 1e3, 2),
+        "roofline": {"kernel": "decode_attn_kernel<fused append> + decode_merge_kernel", "bound": "hbm",
+                     "achieved": round(attn_gbs, 1), "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                     "frac": round(attn_gbs / peak, 4), "frac_of_8TBs_nominal": round(attn_gbs / 8000.0, 4),
+                     "us_per_launch": round(pair_us, 2),
+                     "us_per_launch_mode": launch_mode + ": timed region / (steps x layers), one kernel pair per layer",
+                     "us_per_launch_stream_events": round(pair_ms_stream * 1e3, 2),
+                     "read_only_peak": ro_peak["copy_32k"], "read_only_peak_4k_copies": ro_peak["copy_4k"],
+                     "frac_of_read_only_peak": round(attn_gbs / ro_peak["copy_32k"], 4),
+                     "read_only_peak_kind": "measured in this run: the decode kernel's bulk-copy ring without arithmetic "
+                                            "(oxi_debug_stream_read), one launch per 1.07 GB slab, graph replay, 32 KB copies; "
+                                            "the decode kernel copies 4 KB",
                      # the ncu capture was taken at the default sizes only
-                     "traffic": TRAFFIC_PER_LAUNCH if (not RAGGED and (LAYERS, BATCH, CTX) == (8, 128, 4096)) else None},
+                     "traffic": TRAFFIC_PER_LAUNCH if (not RAGGED and (LAYERS, BATCH, CTX) == (8, 128, 4096)) else None,
+                     "traffic_source": "constant: dram bytes read + written of one launch from the ncu capture summarised in "
+                                       "profiles/decode_attn_kernel_B128_ctx4096.md, not measured in this run"},
         "clocks": clocks, "device_status": status, "finite": ctx_ok, "e2e_equals_device_path": same,
         "cuda_graph_replay_ms_per_step": round(ms_graph / args.steps, 4) if ms_graph != float("inf") else None,
         "stream_launch_ms_per_step": round(ms_stream / args.steps, 4),
     }
+    if secondary:
+        line["secondary"] = secondary
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(CTX, BATCH)
     return line
@@ -378,18 +433,18 @@ def run_reference(args, torch, rank, world, local_rank):
     if rank != 0:
         return None
     from oracle import refptx
+    cfg = {"workload": f"decode_step_{LAYERS}_attention_layers_B{BATCH}_per_gpu_ctx{CTX}", "layers": LAYERS,
+           "batch_per_gpu": BATCH, "seq_len": CTX}
     if not refptx.available():
         cb = cpu_baseline(CTX, BATCH)
         return {"impl": "reference", "metric": "gqa_decode_step_hbm_gbs", "value": cb["value"], "unit": "GB/s",
                 "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True,
-                "scaling": "weak", "dtype": "f16", "data": "synthetic",
-                "config": {"workload": "decode_step_8_attention_layers_B128_per_gpu_ctx4096",
-                           "note": "reference cubins absent: CPU oracle port timed instead"},
+                "scaling": "weak", "dtype": "f16", "data": "synthetic", "config": cfg,
+                "notes": {"what": "reference cubins absent: CPU oracle port timed instead"},
                 "cpu_baseline": cb,
                 "e2e": {"value": cb["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     ref = refptx.RefPtx()
     w = build_workload(torch, CTX, BATCH, LAYERS, seed=1234)
-    stream = torch.cuda.current_stream()
     nch = ref.nchunks_for(CTX, 0)
     acc = torch.empty(BATCH * nch * NQ * HD, dtype=torch.float32, device="cuda")
     stats = torch.empty(BATCH * nch * NQ * 2, dtype=torch.float32, device="cuda")
@@ -400,23 +455,27 @@ def run_reference(args, torch, rank, world, local_rank):
             ref.append(w.q[l], kbuf[l], w.v[l], w.qw[l], w.kw[l], w.cos, w.sin, w.pos, w.k_ptrs[l], w.v_ptrs[l], BATCH)
             ref.decode_attention(w.ctx[l], w.q[l], w.gate[l], w.k_ptrs[l], w.v_ptrs[l], w.lens, BATCH, 0, CTX, acc, stats)
 
+    barrier = torch.cuda.synchronize
     sampler = ClockSampler(gpu_index(local_rank))
     sampler.start()
     sampler.wait_ready()
     for _ in range(args.warmup):
         step()
-    torch.cuda.synchronize()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     w0 = time.perf_counter()
-    t0.record(stream)
-    for _ in range(args.steps):
-        step()
-    t1.record(stream)
-    torch.cuda.synchronize()
+    ms_stream = _timed_region(torch, step, args.steps, barrier)
     w1 = time.perf_counter()
-    ms = t0.elapsed_time(t1)
     clocks = sampler.window(w0, w1)
-    sampler.stop()
+    # the same 72-launch step captured once and replayed, like our arm's graph mode
+    ms_graph = float("inf")
+    try:
+        graph = _graph_of(torch, step)
+        for _ in range(3):
+            graph.replay()
+        ms_graph = _timed_region(torch, graph.replay, args.steps, barrier)
+    except Exception as exc:
+        print(f"cuda graph capture of the reference step failed: {exc}", file=sys.stderr)
+    ms = min(ms_stream, ms_graph)
+    launch_mode = "cuda graph replay of the captured 72-launch step" if ms_graph < ms_stream else "stream launches"
 
     # end to end with the same host traffic as our arm: upload q/k/v/gate + tables, download ctx
     pin = lambda t: t.cpu().pin_memory()
@@ -439,39 +498,400 @@ def run_reference(args, torch, rank, world, local_rank):
 
     for _ in range(3):
         step_host()
-    torch.cuda.synchronize()
-    t0.record(stream)
-    for _ in range(args.steps):
-        step_host()
-    t1.record(stream)
-    torch.cuda.synchronize()
-    ms_e2e = t0.elapsed_time(t1)
+    ms_e2e_stream = _timed_region(torch, step_host, args.steps, barrier)
+    ms_e2e_graph = float("inf")
+    try:
+        graph_h = _graph_of(torch, step_host)
+        for _ in range(3):
+            graph_h.replay()
+        ms_e2e_graph = _timed_region(torch, graph_h.replay, args.steps, barrier)
+    except Exception as exc:
+        print(f"cuda graph capture of the reference host-buffer step failed: {exc}", file=sys.stderr)
+    ms_e2e = min(ms_e2e_stream, ms_e2e_graph)
     h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hg, hkp, hvp))
     step_bytes = LAYERS * alg_bytes_layer(w.seq_lens_host)
+
+    secondary = {}
+    if not args.no_secondary:
+        secondary["decode_ragged"] = leg_decode_ragged(args, torch, "reference", w, ref)
+        del w, acc, stats, kbuf
+        torch.cuda.empty_cache()
+        secondary["serving_mix"] = leg_serving_mix(args, torch, "reference", 0, 1, local_rank)
+        torch.cuda.empty_cache()
+        secondary["prefill"] = leg_prefill(args, torch, "reference")
+        secondary["conv"] = leg_conv(args, torch, "reference")
+    sampler.stop()
     line = {
         "impl": "reference", "metric": "gqa_decode_step_hbm_gbs",
         "value": round(step_bytes * args.steps / (ms * 1e-3) / 1e9, 1), "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms / args.steps, 4),
         "us_per_layer": round(ms / args.steps / LAYERS * 1e3, 2), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "decode_step_8_attention_layers_B128_per_gpu_ctx4096", "layers": LAYERS,
-                   "batch_per_gpu": BATCH, "seq_len": CTX,
-                   "what": "reference PTX kernels (sm_80 text assembled for sm_100a) on one B200, "
-                           "engine launch sequence: 2 norm, 2 rope, 2 copy, split4, combine, gate",
-                   "parallelism": "single GPU (the reference has no multi-GPU path)"},
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": cfg,
+        "notes": {"what": "reference PTX kernels (sm_80 text assembled for sm_100a) on one B200, "
+                          "engine launch sequence: 2 norm, 2 rope, 2 copy, split4, combine, gate",
+                  "launch": launch_mode,
+                  "parallelism": "single GPU (the reference has no multi-GPU path)"},
+        "stream_launch_ms_per_step": round(ms_stream / args.steps, 4),
+        "cuda_graph_replay_ms_per_step": round(ms_graph / args.steps, 4) if ms_graph != float("inf") else None,
         "e2e": {"value": round(step_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
                 "ms_per_step": round(ms_e2e / args.steps, 4), "h2d_bytes_per_step": int(h2d),
-                "d2h_bytes_per_step": int(hctx.numel() * 2)},
+                "d2h_bytes_per_step": int(hctx.numel() * 2),
+                "stream_launch_ms_per_step": round(ms_e2e_stream / args.steps, 4),
+                "cuda_graph_replay_ms_per_step": round(ms_e2e_graph / args.steps, 4) if ms_e2e_graph != float("inf") else None},
         "gpu_launches": 9 * LAYERS * args.steps, "clocks": clocks,
     }
+    if secondary:
+        line["secondary"] = secondary
     if not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(CTX, BATCH)
     return line
 
 
 # ---------------------------------------------------------------------------
-# Secondary workloads (not the headline line): conv-state path (config 3) and the
-# chunked-prefill wave (config 4).  One GPU; both arms are timed in the same run.
+# The other configurations as short legs of the default run (key "secondary" of the line).  impl =
+# "ours" runs this library, impl = "reference" (only under --impl reference) the reference's kernels.
+
+def _tensor_peak():
+    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(pk):
+        try:
+            return float(json.load(open(pk))["bf16_tflops_sustained"]), "measured"
+        except Exception:
+            pass
+    return 1400.0, "fallback"
+
+
+def leg_decode_ragged(args, torch, impl, w, eng):
+    """Configuration 2's lengths: old context uniform 1024..4096 (seeded) on the headline's caches."""
+    import numpy as np
+    lens_np = np.minimum(np.random.default_rng(2).integers(1024, 4097, BATCH) + 1, CTX).astype(np.int64)
+    pos = torch.from_numpy((lens_np - 1).astype(np.int32)).cuda()
+    lens = torch.from_numpy(lens_np.astype(np.int32)).cuda()
+    if impl == "ours":
+        def step():
+            for l in range(LAYERS):
+                eng.append_decode(w.ctx[l], w.q0[l], w.k[l], w.v[l], w.gate[l], w.qw[l], w.kw[l], w.cos, w.sin, pos, lens,
+                                  w.k_ptrs[l], w.v_ptrs[l])
+    else:
+        nch = eng.nchunks_for(CTX, 0)
+        acc = torch.empty(BATCH * nch * NQ * HD, dtype=torch.float32, device="cuda")
+        stats = torch.empty(BATCH * nch * NQ * 2, dtype=torch.float32, device="cuda")
+        kb = w.k.clone()
+
+        def step():
+            for l in range(LAYERS):
+                eng.append(w.q[l], kb[l], w.v[l], w.qw[l], w.kw[l], w.cos, w.sin, pos, w.k_ptrs[l], w.v_ptrs[l], BATCH)
+                eng.decode_attention(w.ctx[l], w.q[l], w.gate[l], w.k_ptrs[l], w.v_ptrs[l], lens, BATCH, 0, CTX, acc, stats)
+    for _ in range(3):
+        step()
+    graph = _graph_of(torch, step)
+    ms = _time_loop(torch, graph.replay, args.steps, 3)
+    step_bytes = LAYERS * alg_bytes_layer(lens_np)
+    peak, kind = measured_peak_gbs()
+    gbs = step_bytes / (ms * 1e-3) / 1e9
+    return {"workload": f"decode_step_{LAYERS}_layers_B{BATCH}_ctx_uniform_1024_4096", "ms_per_step": round(ms, 4),
+            "us_per_layer": round(ms / LAYERS * 1e3, 2), "gbs": round(gbs, 1), "frac": round(gbs / peak, 4),
+            "peak": peak, "peak_kind": kind, "launch": "cuda graph replay", "mean_keys": float(lens_np.mean())}
+
+
+def leg_decode_paged(args, torch, w, kv):
+    """The headline step over a paged layout: the same slabs seen as pools of 16-token blocks, every
+    sequence's pages scattered over the pool by a seeded permutation (CUDA-graph replay)."""
+    import numpy as np
+    from oxide_infer_b200 import PagedLayout
+    bs = 16
+    per_seq = CTX // bs
+    nblk = BATCH * per_seq
+    table = torch.from_numpy(np.random.default_rng(7).permutation(nblk).astype(np.int32).reshape(BATCH, per_seq)).cuda()
+    lays = [PagedLayout.of(w.k_slab[l].view(nblk, bs, NKV, HD), w.v_slab[l].view(nblk, bs, NKV, HD), table, bs)
+            for l in range(LAYERS)]
+
+    def paged():
+        for l in range(LAYERS):
+            kv.append_decode_paged(w.ctx[l], w.q0[l], w.k[l], w.v[l], w.gate[l], w.qw[l], w.kw[l], w.cos, w.sin,
+                                   w.lens, lays[l])
+    for _ in range(3):
+        paged()
+    graph = _graph_of(torch, paged)
+    ms = _time_loop(torch, graph.replay, args.steps, 3)
+    step_bytes = LAYERS * alg_bytes_layer(w.seq_lens_host)
+    peak, kind = measured_peak_gbs()
+    gbs = step_bytes / (ms * 1e-3) / 1e9
+    return {"workload": "decode_step_8_layers_B128_ctx4096_paged_kv_16_token_blocks", "ms_per_step": round(ms, 4),
+            "us_per_layer": round(ms / LAYERS * 1e3, 2), "gbs": round(gbs, 1), "frac": round(gbs / peak, 4),
+            "peak": peak, "peak_kind": kind, "launch": "cuda graph replay"}
+
+
+def leg_prefill(args, torch, impl):
+    """Configuration 4: one wave of 128 new tokens for each of 32 sequences, prefixes uniform 0..8192
+    (seeded), one attention layer.  ours: append of the 4,096 rows + causal gated attention;
+    reference: its non-GEMM path, the online kernel over all rows + the gate kernel
+    (batch_engine.rs:1214-1239) - its cuBLASLt path cannot be driven without the engine."""
+    import numpy as np
+    from oxide_infer_b200 import rotary_tables
+    nseq, new = 32, 128
+    rows = nseq * new
+    prefix = np.random.default_rng(4).integers(0, 8193, nseq)
+    g = torch.Generator(device="cuda").manual_seed(4)
+    rn = lambda *s: torch.empty(*s, dtype=torch.float16, device="cuda").normal_(generator=g)
+    cap = [int(p) + new for p in prefix]
+    slab = rn(2 * sum(cap), NKV, HD)
+    offs = np.concatenate([[0], np.cumsum(cap)])
+    kc = [slab[offs[i]:offs[i + 1]] for i in range(nseq)]
+    vc = [slab[sum(cap) + offs[i]:sum(cap) + offs[i + 1]] for i in range(nseq)]
+    q, k, v, gate = rn(rows, NQ, HD), rn(rows, NKV, HD), rn(rows, NKV, HD), rn(rows, NQ)
+    qw = (1 + 0.02 * torch.randn(HD, device="cuda", generator=g)).half()
+    kw = (1 + 0.02 * torch.randn(HD, device="cuda", generator=g)).half()
+    cos, sin = rotary_tables(8192 + new, 1e6, 0.5)
+    cos, sin = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
+    owner = np.repeat(np.arange(nseq), new)
+    pos = (prefix[owner] + np.tile(np.arange(new), nseq)).astype(np.int32)
+    kp = torch.tensor([kc[i].data_ptr() for i in owner], dtype=torch.int64, device="cuda")
+    vp = torch.tensor([vc[i].data_ptr() for i in owner], dtype=torch.int64, device="cuda")
+    dpos, dlen = torch.from_numpy(pos).cuda(), torch.from_numpy(pos + 1).cuda()
+    ctx = torch.zeros(rows, NQ, HD, dtype=torch.float16, device="cuda")
+    flops = float(sum(8192 * (128 * int(p) + 8256) for p in prefix))
+    peak_tf, kind = _tensor_peak()
+    out = {"workload": "prefill_wave_32seq_x128tok_prefix_U0_8192_one_layer", "rows": rows, "causal_exact_gflop": round(flops / 1e9, 1)}
+    if impl == "ours":
+        from oxide_infer_b200 import KvPath
+        kv = KvPath(torch.cuda.current_device(), max_batch=128, max_seq_len=8192 + new, max_prefill_rows=rows)
+        ms_attn = _time_loop(torch, lambda: kv.prefill_attn(ctx, q, gate, kp, vp, dlen, 0), args.steps, 3)
+
+        def wave():
+            kv.append(q, k, v, qw, kw, cos, sin, dpos, kp, vp, batch=rows)
+            kv.prefill_attn(ctx, q, gate, kp, vp, dlen, 0)
+        ms_wave = _time_loop(torch, wave, args.steps, 3)
+        tf = flops / (ms_attn * 1e-3) / 1e12
+        out.update({"ms_attention": round(ms_attn, 4), "ms_append_plus_attention": round(ms_wave, 4), "tflops": round(tf, 1),
+                    "frac": round(tf / peak_tf, 4), "peak": peak_tf, "peak_kind": kind + " (sustained bf16 GEMM)",
+                    "bound": "tensor", "device_status": kv.device_status()})
+        kv.close()
+    else:
+        from oracle import refptx
+        ref = refptx.RefPtx()
+
+        def ref_attn():
+            ref.attn_online(ctx, q, kp, vp, dlen, rows, 0)
+            ref.sigmoid_gate(ctx, gate, rows)
+        ms = _time_loop(torch, ref_attn, 3, 3)
+        out.update({"ms_attention": round(ms, 4), "tflops": round(flops / (ms * 1e-3) / 1e12, 2),
+                    "what": "online kernel over all wave rows + gate kernel"})
+    return out
+
+
+def leg_conv(args, torch, impl):
+    """Configuration 3: 16 conv layers, batch 128, one decode update per layer (CUDA-graph replay of the
+    16 launches), and configuration 4's wave (32 x 128 rows) through one conv layer."""
+    import numpy as np
+    nl, b, hid = 16, 128, 2048
+    g = torch.Generator(device="cuda").manual_seed(3)
+    rn = lambda *s, sc=1.0: (torch.randn(*s, device="cuda", generator=g) * sc).half()
+    state, bcx, w = rn(nl, b, hid, 6), rn(nl, b, 3 * hid), rn(nl, hid, 7, sc=0.1)
+    y = torch.zeros(nl, b, hid, dtype=torch.float16, device="cuda")
+    ptrs = torch.tensor([[state[l, i].data_ptr() for i in range(b)] for l in range(nl)], dtype=torch.int64, device="cuda")
+    nseq, new = 32, 128
+    rows = nseq * new
+    carry, pbcx = rn(nseq, hid, 6), rn(rows, 3 * hid)
+    py = torch.zeros(rows, hid, dtype=torch.float16, device="cuda")
+    origin = torch.from_numpy(np.repeat(np.arange(nseq) * new, new).astype(np.int32)).cuda()
+    lpos = torch.from_numpy(np.tile(np.arange(new), nseq).astype(np.int32)).cuda()
+    cptr = torch.tensor([carry[i // new].data_ptr() for i in range(rows)], dtype=torch.int64, device="cuda")
+    step_bytes = nl * (b * 65536 + 28672)
+    pf_bytes = nseq * (16384 * new + 49152)
+    peak, kind = measured_peak_gbs()
+    out = {"workload": "conv_decode_16_layers_B128_2048ch_K7"}
+    if impl == "ours":
+        from oxide_infer_b200 import KvPath
+        kv = KvPath(torch.cuda.current_device(), max_batch=b, max_seq_len=4096, max_prefill_rows=rows)
+
+        def dec():
+            for l in range(nl):
+                kv.conv_decode(y[l], ptrs[l], bcx[l], w[l])
+        pf = lambda: kv.conv_prefill(py, cptr, origin, lpos, pbcx, w[0])
+    else:
+        from oracle import refptx
+        ref = refptx.RefPtx()
+        pool = torch.zeros(rows, hid, 6, dtype=torch.float16, device="cuda")
+        pool_ptrs = torch.tensor([pool.data_ptr() + r * hid * 12 for r in range(rows)], dtype=torch.int64, device="cuda")
+
+        def dec():
+            for l in range(nl):
+                ref.conv_decode(y[l], ptrs[l], bcx[l], w[l], b)
+
+        def pf():  # batch_engine.rs:847-899 on the device; the per-chunk copy-back (server.rs:1192-1224) as 32 device copies
+            ref.conv_state_prefill(pool, cptr, origin, lpos, pbcx, rows)
+            ref.conv_decode(py, pool_ptrs, pbcx, w[0], rows)
+            for i in range(nseq):
+                carry[i].copy_(pool[(i + 1) * new - 1])
+    for _ in range(3):
+        dec()
+    graph = _graph_of(torch, dec)
+    ms = _time_loop(torch, graph.replay, max(args.steps, 50), 3)
+    for _ in range(3):
+        pf()
+    graph_pf = _graph_of(torch, pf)
+    ms_pf = _time_loop(torch, graph_pf.replay, max(args.steps, 20), 3)
+    gbs = step_bytes / (ms * 1e-3) / 1e9
+    out.update({"us_per_layer": round(ms / nl * 1e3, 2), "gbs": round(gbs, 1), "frac": round(gbs / peak, 4), "peak": peak,
+                "peak_kind": kind, "launch": "cuda graph replay of the 16 launches",
+                "note": "8.4 MB per launch: bound by launch and memory latency, not bandwidth",
+                "prefill_wave_one_layer": {"rows": rows, "us": round(ms_pf * 1e3, 2),
+                                           "gbs": round(pf_bytes / (ms_pf * 1e-3) / 1e9, 1)}})
+    if impl == "ours":
+        out["device_status"] = kv.device_status()
+        kv.close()
+    return out
+
+
+def leg_sample(args, torch):
+    """Argmax over 128 x 128,000 f16 logits + the embedding gather of the chosen rows (hidden 2048); eight logits
+    buffers (262 MB) rotate; CUDA-graph replay of the eight pairs."""
+    from oxide_infer_b200 import KvPath
+    b, vocab, hid, nbuf = 128, 128000, 2048, 8
+    kv = KvPath(torch.cuda.current_device(), max_batch=b, max_seq_len=256, max_prefill_rows=0)
+    g = torch.Generator(device="cuda").manual_seed(6)
+    logits = [torch.empty(b, vocab, dtype=torch.float16, device="cuda").normal_(generator=g) for _ in range(nbuf)]
+    table = torch.empty(vocab, hid, dtype=torch.float16, device="cuda").normal_(generator=g)
+    tok = torch.zeros(nbuf, b, dtype=torch.int32, device="cuda")
+    hidden = torch.zeros(b, hid, dtype=torch.float16, device="cuda")
+
+    def pairs():
+        for i in range(nbuf):
+            kv.argmax(tok[i], logits[i])
+            kv.embed_lookup(hidden, table, tok[i])
+    for _ in range(3):
+        pairs()
+    graph = _graph_of(torch, pairs)
+    ms = _time_loop(torch, graph.replay, max(args.steps, 50), 3)
+    am_bytes = b * vocab * 2 + b * 4
+    peak, kind = measured_peak_gbs()
+    gbs = nbuf * am_bytes / (ms * 1e-3) / 1e9
+    out = {"workload": "argmax_B128_vocab128000_plus_embed_gather_hidden2048", "us_per_pair": round(ms / nbuf * 1e3, 2),
+           "gbs_lower_bound_of_argmax": round(gbs, 1), "frac": round(gbs / peak, 4), "peak": peak, "peak_kind": kind,
+           "device_status": kv.device_status()}
+    kv.close()
+    return out
+
+
+def _fill_normal_tiled(torch, t, g):
+    """N(0,1) values for a large tensor: one 256 MB random block tiled (far larger than L2, so the
+    timing sees fresh HBM lines; generating tens of GB of fresh normals takes longer than the bench)."""
+    flat = t.view(-1)
+    blk = min(flat.numel(), 128 * 1024 * 1024)
+    flat[:blk].normal_(generator=g)
+    off = blk
+    while off < flat.numel():
+        n = min(blk, flat.numel() - off)
+        flat[off:off + n].copy_(flat[:n])
+        off += n
+
+
+def leg_serving_mix(args, torch, impl, rank, world, local_rank):
+    """Configuration 5: 1,024 sequences with lognormal context lengths (median 2048, sigma 1.0 - the
+    spread is not given by the configuration and is chosen here -, clipped to [16, 32704]), 8 attention
+    layers, 64 consecutive decode steps with advancing positions.  The FIXED set is partitioned over
+    the ranks by oxide_infer_b200.shard.assign_sequences: strong scaling, replicas, no collective.
+    The reference arm runs all 1,024 sequences on one GPU (it has no multi-GPU path)."""
+    import numpy as np
+    from oxide_infer_b200 import rotary_tables
+    from oxide_infer_b200.shard import assign_sequences, shard_keys
+    nseq, layers, steps = 1024, 8, 64
+    rng = np.random.default_rng(5)
+    lens_all = np.clip(np.round(np.exp(rng.normal(np.log(2048), 1.0, nseq))), 16, 32768 - 64).astype(np.int64)
+    parts = assign_sequences(lens_all, world)
+    lens = lens_all[parts[rank]]
+    b = len(lens)
+    cap = lens + steps + 1
+    g = torch.Generator(device="cuda").manual_seed(50 + rank)
+    total_rows = int(cap.sum())
+    offs = np.concatenate([[0], np.cumsum(cap)[:-1]]) * ROW_BYTES
+    k_ptrs, v_ptrs, slabs = [], [], []
+    for _ in range(layers):
+        ks = torch.empty(total_rows, NKV, HD, dtype=torch.float16, device="cuda")
+        vs = torch.empty(total_rows, NKV, HD, dtype=torch.float16, device="cuda")
+        _fill_normal_tiled(torch, ks, g)
+        _fill_normal_tiled(torch, vs, g)
+        slabs.append((ks, vs))
+        k_ptrs.append(torch.from_numpy(ks.data_ptr() + offs).cuda())
+        v_ptrs.append(torch.from_numpy(vs.data_ptr() + offs).cuda())
+    rn = lambda *s: torch.empty(*s, dtype=torch.float16, device="cuda").normal_(generator=g)
+    q, k, v, gate = rn(layers, b, NQ, HD), rn(layers, b, NKV, HD), rn(layers, b, NKV, HD), rn(layers, b, NQ)
+    qw = torch.ones(HD, dtype=torch.float16, device="cuda")
+    cos, sin = rotary_tables(32768 + steps, 1e6, 0.5)
+    cos, sin = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
+    ctx = torch.zeros(layers, b, NQ, HD, dtype=torch.float16, device="cuda")
+    pos_steps = [torch.from_numpy((lens + s_).astype(np.int32)).cuda() for s_ in range(steps)]
+    len_steps = [p + 1 for p in pos_steps]
+    status = None
+    if impl == "ours":
+        from oxide_infer_b200 import KvPath
+        kv = KvPath(local_rank, max_batch=max(b, 1), max_seq_len=32768 + steps, max_prefill_rows=0)
+
+        def one(s_):
+            for l in range(layers):
+                kv.append_decode(ctx[l], q[l], k[l], v[l], gate[l], qw, qw, cos, sin, pos_steps[s_], len_steps[s_],
+                                 k_ptrs[l], v_ptrs[l])
+    else:
+        from oracle import refptx
+        ref = refptx.RefPtx()
+        max_len = int(lens.max()) + steps + 1
+        nch = ref.nchunks_for(max_len, 0)
+        acc = torch.empty(b * nch * NQ * HD, dtype=torch.float32, device="cuda")
+        stats = torch.empty(b * nch * NQ * 2, dtype=torch.float32, device="cuda")
+        qb, kb = q.clone(), k.clone()
+
+        def one(s_):
+            for l in range(layers):
+                ref.append(qb[l], kb[l], v[l], qw, qw, cos, sin, pos_steps[s_], k_ptrs[l], v_ptrs[l], b)
+                ref.decode_attention(ctx[l], qb[l], gate[l], k_ptrs[l], v_ptrs[l], len_steps[s_], b, 0,
+                                     int(lens.max()) + s_ + 1, acc, stats)
+
+    def run64():
+        for s_ in range(steps):
+            one(s_)
+
+    def barrier():
+        if world > 1 and impl == "ours":
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    for s_ in range(4):  # warm-up steps (W >= 3)
+        one(s_)
+    launch = "stream launches"
+    fn = run64
+    try:  # the 64 steps as one captured graph: no host launch gaps at 8 GPUs, where a layer takes ~70 us
+        graph = _graph_of(torch, run64)
+        graph.replay()
+        fn, launch = graph.replay, "cuda graph replay of the 64 captured steps"
+    except Exception as exc:
+        if rank == 0:
+            print(f"serving mix: cuda graph capture failed ({exc}); stream launches", file=sys.stderr)
+    ms = _timed_region(torch, fn, 1, barrier)
+    if impl == "ours":
+        status = kv.device_status()
+    finite = bool(torch.isfinite(ctx.float()).all().item())
+    tt = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    if world > 1 and impl == "ours":
+        torch.distributed.all_reduce(tt, op=torch.distributed.ReduceOp.MAX)
+    ms = float(tt.item())
+    if impl == "ours":
+        kv.close()
+    total_bytes = sum(layers * alg_bytes_layer(lens_all + s_ + 1) for s_ in range(steps))
+    keys = shard_keys(lens_all, parts)
+    peak, kind = measured_peak_gbs()
+    gbs = total_bytes / (ms * 1e-3) / 1e9
+    return {"workload": "serving_mix_1024seq_lognormal_median2048_sigma1_8layers_64steps", "scaling": "strong",
+            "n_gpus": world, "ms_per_64_steps": round(ms, 3), "tokens_per_s": round(nseq * steps / (ms * 1e-3), 1),
+            "gbs": round(gbs, 1), "gbs_per_gpu": round(gbs / world, 1), "frac_per_gpu": round(gbs / world / peak, 4),
+            "peak": peak, "peak_kind": kind, "launch": launch, "sequences": nseq,
+            "kv_bytes_total": int(lens_all.sum()) * layers * 2 * ROW_BYTES,
+            "keys_per_gpu_min_max": [int(min(keys)), int(max(keys))], "longest_row_keys": int(lens_all.max()) + steps,
+            "device_status": status, "finite": finite}
+
+
+# ---------------------------------------------------------------------------
+# Detailed single-workload lines (--workload ...), this library only.
 
 def _time_loop(torch, fn, steps, warmup):
     stream = torch.cuda.current_stream()
@@ -487,90 +907,12 @@ def _time_loop(torch, fn, steps, warmup):
     return t0.elapsed_time(t1) / steps
 
 
-def run_conv(args, torch):
-    """Config 3: 16 conv layers, batch 128, 2048 channels, 7 taps, 6-slot fp16 carry state per
-    (layer, sequence) behind conv_ptrs; one decode update per layer."""
-    from oxide_infer_b200 import KvPath
-    from oracle import refptx
-    nl, b, hid = 16, 128, 2048
-    kv = KvPath(0, max_batch=b, max_seq_len=4096, max_prefill_rows=16)
-    g = torch.Generator(device="cuda").manual_seed(3)
-    rn = lambda *s, sc=1.0: (torch.randn(*s, device="cuda", generator=g) * sc).half()
-    state = rn(nl, b, hid, 6)
-    bcx = rn(nl, b, 3 * hid)
-    w = rn(nl, hid, 7, sc=0.1)
-    y = torch.zeros(nl, b, hid, dtype=torch.float16, device="cuda")
-    ptrs = torch.tensor([[state[l, i].data_ptr() for i in range(b)] for l in range(nl)], dtype=torch.int64, device="cuda")
-    sampler = ClockSampler(0)
-    sampler.start()
-    sampler.wait_ready()
-
-    def ours():
-        for l in range(nl):
-            kv.conv_decode(y[l], ptrs[l], bcx[l], w[l])
-    w0 = time.perf_counter()
-    ms = _time_loop(torch, ours, args.steps, args.warmup)
-    clocks = sampler.window(w0, time.perf_counter())
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        ours()
-    ms_graph = _time_loop(torch, graph.replay, args.steps, args.warmup)
-    ms_ref = None
-    if refptx.available():
-        ref = refptx.RefPtx()
-        ms_ref = _time_loop(torch, lambda: [ref.conv_decode(y[l], ptrs[l], bcx[l], w[l], b) for l in range(nl)],
-                            args.steps, args.warmup)
-    # prefill side of the same layers: configuration 4's wave (32 requests x 128 new rows) through one
-    # conv layer - gather of the carried state, conv on every row, commit of each chunk's final state
-    import numpy as np
-    nseq, new = 32, 128
-    rows = nseq * new
-    kvp = KvPath(0, max_batch=b, max_seq_len=4096, max_prefill_rows=rows)
-    carry = rn(nseq, hid, 6)
-    pbcx = rn(rows, 3 * hid)
-    py = torch.zeros(rows, hid, dtype=torch.float16, device="cuda")
-    origin_np = np.repeat(np.arange(nseq) * new, new).astype(np.int32)
-    origin = torch.from_numpy(origin_np).cuda()
-    lpos = torch.from_numpy(np.tile(np.arange(new), nseq).astype(np.int32)).cuda()
-    cptr = torch.tensor([carry[i // new].data_ptr() for i in range(rows)], dtype=torch.int64, device="cuda")
-    ms_pf = _time_loop(torch, lambda: kvp.conv_prefill(py, cptr, origin, lpos, pbcx, w[0]), args.steps, args.warmup)
-    ms_pf_ref = None
-    if refptx.available():
-        pool = torch.zeros(rows, hid, 6, dtype=torch.float16, device="cuda")
-        pool_ptrs = torch.tensor([pool.data_ptr() + r * hid * 12 for r in range(rows)], dtype=torch.int64, device="cuda")
-
-        def ref_pf():  # BE:847-899 on the device; the per-chunk copy-back (server.rs:1192-1224) as 32 device copies
-            ref.conv_state_prefill(pool, cptr, origin, lpos, pbcx, rows)
-            ref.conv_decode(py, pool_ptrs, pbcx, w[0], rows)
-            for i in range(nseq):
-                carry[i].copy_(pool[(i + 1) * new - 1])
-        ms_pf_ref = _time_loop(torch, ref_pf, max(3, args.steps // 2), 3)
-    pf_bytes = nseq * (16384 * new + 49152)
-    sampler.stop()
-    step_bytes = nl * (b * 65536 + 28672)
-    peak, kind = measured_peak_gbs()
-    return {"metric": "conv_state_decode_hbm_gbs", "value": round(step_bytes / (ms_graph * 1e-3) / 1e9, 1), "unit": "GB/s",
-            "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_graph, 4),
-            "us_per_layer": round(ms_graph / nl * 1e3, 2), "us_per_layer_stream_launches": round(ms / nl * 1e3, 2),
-            "higher_is_better": True, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": "conv_decode_16_layers_B128_2048ch_K7", "note": "value is the 16-layer sequence replayed as a CUDA graph"},
-            "roofline": {"kernel": "conv_decode_kernel", "bound": "hbm", "achieved": round(step_bytes / (ms_graph * 1e-3) / 1e9, 1),
-                         "peak": peak, "peak_kind": kind, "unit": "GB/s", "frac": round(step_bytes / (ms_graph * 1e-3) / 1e9 / peak, 4),
-                         "note": "8.4 MB per launch: launch-latency bound, not bandwidth bound"},
-            "reference_kernels_us_per_layer": None if ms_ref is None else round(ms_ref / nl * 1e3, 2),
-            "prefill_wave_one_layer": {"rows": rows, "us": round(ms_pf * 1e3, 2), "gbs": round(pf_bytes / (ms_pf * 1e-3) / 1e9, 1),
-                                       "algorithmic_bytes": pf_bytes,
-                                       "reference_kernels_us": None if ms_pf_ref is None else round(ms_pf_ref * 1e3, 2)},
-            "gpu_launches": nl * args.steps, "clocks": clocks, "device_status": kv.device_status()}
-
-
 def run_sample(args, torch):
     """Sampling side of a decode step at the reference's sizes: argmax over 128,000 f16 logits for
     each of 128 rows (batch_engine.rs:75, :1367-1378) and the embedding gather of the 128 chosen
     rows of a [128000][2048] table.  Eight distinct logits buffers (262 MB) rotate so that no launch
     finds its input in L2."""
     from oxide_infer_b200 import KvPath
-    from oracle import refptx
     b, vocab, hid, nbuf = 128, 128000, 2048, 8
     kv = KvPath(0, max_batch=b, max_seq_len=256, max_prefill_rows=0)
     g = torch.Generator(device="cuda").manual_seed(6)
@@ -601,16 +943,6 @@ def run_sample(args, torch):
     clocks = sampler.window(w0, time.perf_counter())
     want = torch.stack([x.float().argmax(1) for x in logits]).int()  # random normal f16 logits: ties are possible but
     agree = float((want == tok).float().mean().item())              # rare; parity proper is in tests/test_gpu_sample.py
-    ms_ref = None
-    if refptx.available():
-        ref = refptx.RefPtx()
-        rt = torch.zeros(b, dtype=torch.int32, device="cuda")
-
-        def ref_pair():
-            for i in range(nbuf):
-                ref.argmax(rt, logits[i], vocab, b)
-                ref.embed_lookup(hidden, table, rt, hid, b)
-        ms_ref = _time_loop(torch, ref_pair, max(3, args.steps // 2), 3)
     sampler.stop()
     pair_bytes = b * vocab * 2 + b * 4 + b * (4 + 2 * hid * 2)   # logits once, ids out; ids in, row in, row out
     am_bytes = b * vocab * 2 + b * 4
@@ -625,7 +957,6 @@ def run_sample(args, torch):
                        "l2": "8 distinct logits buffers (262 MB) rotate", "note": "value is the 8 pairs replayed as a CUDA graph"},
             "roofline": {"kernel": "argmax_kernel", "bound": "hbm", "achieved": round(am_gbs, 1), "peak": peak, "peak_kind": kind,
                          "unit": "GB/s", "frac": round(am_gbs / peak, 4), "bytes_per_launch": am_bytes},
-            "reference_kernels_us_per_pair": None if ms_ref is None else round(ms_ref / nbuf * 1e3, 2),
             "agreement_with_torch_argmax": agree,
             "gpu_launches": 2 * nbuf * args.steps, "clocks": clocks, "device_status": kv.device_status()}
 
@@ -722,7 +1053,6 @@ def run_prefill(args, torch):
     (seeded), one attention layer: append of the 4096 wave rows, then causal gated GQA attention."""
     import numpy as np
     from oxide_infer_b200 import KvPath, rotary_tables
-    from oracle import refptx
     nseq, new = 32, 128
     rows = nseq * new
     rng = np.random.default_rng(4)
@@ -768,15 +1098,6 @@ def run_prefill(args, torch):
     kv.register_kv_slab(slab)  # the same wave with TMA tile copies instead of per-thread 16-byte copies
     ms_attn_tma = _time_loop(torch, attn, args.steps, args.warmup)
     kv.register_kv_slab(None)
-    ms_ref = None
-    if refptx.available():
-        ref = refptx.RefPtx()
-        rctx = torch.zeros_like(ctx)
-
-        def ref_attn():  # the reference's non-GEMM path: online kernel over all rows + gate (BE:1214-1239)
-            ref.attn_online(rctx, q, kp, vp, dlen, rows, 0)
-            ref.sigmoid_gate(rctx, gate, rows)
-        ms_ref = _time_loop(torch, ref_attn, max(3, args.steps // 4), 3)
     long_wave = _prefill_long_prompt_leg(args, torch, rn)
     sampler.stop()
     flops = float(sum(8192 * (128 * int(p) + 8256) for p in prefix))
@@ -799,98 +1120,8 @@ def run_prefill(args, torch):
                        "prefix_sum": int(prefix.sum()), "causal_exact_flops": flops, "algorithmic_bytes": kv_bytes},
             "roofline": {"kernel": "prefill_attn_kernel", "bound": "tensor", "achieved": round(tf, 2), "peak": peak_tf,
                          "peak_kind": kind, "unit": "TFLOP/s", "frac": round(tf / peak_tf, 4)},
-            "reference_online_plus_gate_ms": None if ms_ref is None else round(ms_ref, 4),
             "long_prompt_wave": long_wave,
             "gpu_launches": 3 * args.steps, "clocks": clocks, "device_status": kv.device_status()}
-
-
-def run_serving_mix(args, torch, rank, world, local_rank):
-    """Config 5: 1,024 sequences with lognormal context lengths (median 2048, sigma 1.0 - the
-    spread is not given by the configuration and is chosen here -, clipped to [16, 32704]),
-    8 attention layers, 64 consecutive decode steps (append + gated GQA attention, positions
-    advancing).  The FIXED set of sequences is partitioned over the ranks by
-    oxide_infer_b200.shard.assign_sequences (strong scaling, replicas, no collective)."""
-    import numpy as np
-    from oxide_infer_b200 import KvPath, rotary_tables
-    from oxide_infer_b200.shard import assign_sequences, shard_keys
-    nseq, layers, steps = 1024, 8, 64
-    rng = np.random.default_rng(5)
-    lens_all = np.clip(np.round(np.exp(rng.normal(np.log(2048), 1.0, nseq))), 16, 32768 - 64).astype(np.int64)
-    parts = assign_sequences(lens_all, world)
-    mine = parts[rank]
-    lens = lens_all[mine]
-    b = len(mine)
-    cap = lens + steps + 1
-    kv = KvPath(local_rank, max_batch=max(b, 1), max_seq_len=32768 + steps, max_prefill_rows=0)
-    g = torch.Generator(device="cuda").manual_seed(50 + rank)
-    total_rows = int(cap.sum())
-    k_ptrs, v_ptrs, slabs = [], [], []
-    offs = np.concatenate([[0], np.cumsum(cap)[:-1]]) * ROW_BYTES
-    for _ in range(layers):
-        ks = torch.empty(total_rows, NKV, HD, dtype=torch.float16, device="cuda").normal_(generator=g)
-        vs = torch.empty(total_rows, NKV, HD, dtype=torch.float16, device="cuda").normal_(generator=g)
-        slabs.append((ks, vs))
-        k_ptrs.append(torch.from_numpy(ks.data_ptr() + offs).cuda())
-        v_ptrs.append(torch.from_numpy(vs.data_ptr() + offs).cuda())
-    rn = lambda *s: torch.empty(*s, dtype=torch.float16, device="cuda").normal_(generator=g)
-    q, k, v, gate = rn(layers, b, NQ, HD), rn(layers, b, NKV, HD), rn(layers, b, NKV, HD), rn(layers, b, NQ)
-    qw = torch.ones(HD, dtype=torch.float16, device="cuda")
-    cos, sin = rotary_tables(32768 + steps, 1e6, 0.5)
-    cos, sin = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
-    ctx = torch.zeros(layers, b, NQ, HD, dtype=torch.float16, device="cuda")
-    pos_steps = [torch.from_numpy((lens + s_).astype(np.int32)).cuda() for s_ in range(steps)]
-    len_steps = [p + 1 for p in pos_steps]
-    stream = torch.cuda.current_stream()
-
-    def run64():
-        for s_ in range(steps):
-            for l in range(layers):
-                kv.append_decode(ctx[l], q[l], k[l], v[l], gate[l], qw, qw, cos, sin, pos_steps[s_], len_steps[s_],
-                                 k_ptrs[l], v_ptrs[l])
-
-    def barrier():
-        if world > 1:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
-
-    sampler = ClockSampler(gpu_index(local_rank))
-    sampler.start()
-    sampler.wait_ready()
-    run64()  # warm-up pass (also the W >= 3 warm-up steps: 64 of them)
-    barrier()
-    reps = max(1, args.steps // steps)
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    w0 = time.perf_counter()
-    t0.record(stream)
-    for _ in range(reps):
-        run64()
-    t1.record(stream)
-    barrier()
-    clocks = sampler.window(w0, time.perf_counter())
-    sampler.stop()
-    ms = t0.elapsed_time(t1) / reps
-    status = kv.device_status()
-    tt = torch.tensor([ms], dtype=torch.float64, device="cuda")
-    if world > 1:
-        torch.distributed.all_reduce(tt, op=torch.distributed.ReduceOp.MAX)
-    if rank != 0:
-        return None
-    ms = float(tt.item())
-    total_bytes = sum(layers * alg_bytes_layer(lens_all + s_ + 1) for s_ in range(steps))
-    keys = shard_keys(lens_all, parts)
-    peak, kind = measured_peak_gbs()
-    gbs = total_bytes / (ms * 1e-3) / 1e9
-    return {"metric": "serving_mix_64_decode_steps_hbm_gbs", "value": round(gbs, 1), "unit": "GB/s", "n_gpus": world,
-            "steps": steps * reps, "warmup": steps, "ms_per_step": round(ms / steps, 4), "ms_per_64_steps": round(ms, 3),
-            "tokens_per_s": round(nseq * steps / (ms * 1e-3), 1), "higher_is_better": True, "scaling": "strong",
-            "dtype": "f16", "data": "synthetic",
-            "config": {"workload": "serving_mix_1024seq_lognormal_median2048_sigma1_8layers_64steps",
-                       "sequences": nseq, "kv_bytes_total": int(lens_all.sum()) * layers * 2 * ROW_BYTES,
-                       "keys_per_gpu_min_max": [int(min(keys)), int(max(keys))],
-                       "parallelism": f"replicas x{world}, sequences partitioned longest-first, no collective"},
-            "roofline": {"bound": "hbm", "achieved": round(gbs / world, 1), "peak": peak, "peak_kind": kind,
-                         "unit": "GB/s per GPU", "frac": round(gbs / world / peak, 4)},
-            "gpu_launches": 2 * layers * steps * reps, "clocks": clocks, "device_status": status}
 
 
 def main():
@@ -901,6 +1132,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--no-secondary", action="store_true", help="headline workload only (skip the other configurations)")
     ap.add_argument("--layers", type=int, default=LAYERS, help="override for small profiling cases")
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--ctx", type=int, default=CTX)
@@ -911,6 +1143,8 @@ def main():
     args = ap.parse_args()
     globals().update(LAYERS=args.layers, BATCH=args.batch, CTX=args.ctx, RAGGED=args.ragged)
     args.warmup = max(args.warmup, 3)
+    if (args.layers, args.batch, args.ctx) != (8, 128, 4096) or args.ragged or args.no_e2e:
+        args.no_secondary = True  # the other configurations ride along with the default headline only
 
     import torch
     rank = int(os.environ.get("RANK", "0"))
@@ -926,15 +1160,16 @@ def main():
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
         if args.workload == "conv":
-            line = run_conv(args, torch) if rank == 0 else None
+            line = leg_conv(args, torch, args.impl) if rank == 0 else None
         elif args.workload == "prefill":
-            line = run_prefill(args, torch) if rank == 0 else None
+            line = (run_prefill(args, torch) if args.impl == "ours" else leg_prefill(args, torch, "reference")) if rank == 0 else None
         elif args.workload == "sample":
             line = run_sample(args, torch) if rank == 0 else None
         elif args.workload == "decode_paged":
             line = run_decode_paged(args, torch) if rank == 0 else None
         elif args.workload == "serving_mix":
-            line = run_serving_mix(args, torch, rank, world, local_rank)
+            line = leg_serving_mix(args, torch, args.impl, rank, world, local_rank)
+            line = line if rank == 0 else None
         else:
             line = (run_ours if args.impl == "ours" else run_reference)(args, torch, rank, world, local_rank)
         if line is not None:

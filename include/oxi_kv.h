@@ -303,6 +303,70 @@ int32_t oxi_decode_step_host(oxi_handle* h, void* stream, void* ctx_host, const 
                              const uint64_t* v_ptrs_host, uint32_t batch, uint32_t layers,
                              uint32_t window, float eps);
 
+/* ---- host side of the path as a C API: slab pool, leases, step tables ---- */
+
+/* The reference keeps every sequence's K/V rows and conv states in two slabs and
+ * hands each request a lease: a contiguous range of token rows plus a conv slot
+ * (KvPool / KvLayout / KvLease, kv_pool.rs:31-251).  K of attention layer a lives
+ * in plane 2a of the KV slab, V in plane 2a+1, each capacity_tokens rows of 1024
+ * bytes (kv_pool.rs:46-61); the conv state of (slot, conv layer c) is a
+ * [2048][6] f16 block.  These entry points restate that pool and the per-step
+ * table build + upload of the engine (batch_engine.rs:709-740) so that a host
+ * without the Rust engine can drive the operators above; a host that has its own
+ * pool ignores them.  oxi_host_last_error_string() gives the text of the last
+ * error of these functions on the calling thread. */
+typedef struct oxi_kv_pool oxi_kv_pool;
+typedef struct oxi_step_tables oxi_step_tables;
+typedef struct oxi_lease {
+    uint64_t tok_off; /* first token row of the lease inside every K / V plane */
+    uint64_t tokens;  /* rows leased: the sequence may grow to this many tokens */
+    uint64_t slot;    /* conv-state slot */
+} oxi_lease;
+const char* oxi_host_last_error_string(void);
+
+/* Allocates both slabs on the current device (KvPool::new, kv_pool.rs:82-150):
+ * layer_is_conv[l] != 0 marks conv layers; the token capacity is halved until the
+ * KV slab fits (never below 4096 tokens), as the reference does. */
+int32_t oxi_pool_create(oxi_kv_pool** out, const uint8_t* layer_is_conv, uint32_t num_layers, uint32_t max_batch,
+                        uint64_t capacity_tokens);
+int32_t oxi_pool_destroy(oxi_kv_pool* pool);
+uint64_t oxi_pool_capacity_tokens(const oxi_kv_pool* pool);
+uint64_t oxi_pool_free_tokens(const oxi_kv_pool* pool);
+uint32_t oxi_pool_free_slots(const oxi_kv_pool* pool);
+/* First-fit lease of `tokens` contiguous rows and a conv slot whose states are
+ * zeroed on `stream` (KvPool::acquire, kv_pool.rs:175-218).  OXI_ERR_WORKSPACE
+ * when no slot or no range of that size is free (the reference returns None). */
+int32_t oxi_pool_acquire(oxi_kv_pool* pool, void* stream, uint64_t tokens, oxi_lease* out);
+/* Returns the rows (coalescing with free neighbours) and the slot (kv_pool.rs:220-246). */
+int32_t oxi_pool_release(oxi_kv_pool* pool, const oxi_lease* lease);
+/* Device addresses the BatchSequence trait hands the engine (batch_engine.rs:78-87);
+ * 0 when the layer is not of that kind. */
+uint64_t oxi_pool_k_ptr(const oxi_kv_pool* pool, uint32_t layer, const oxi_lease* lease);
+uint64_t oxi_pool_v_ptr(const oxi_kv_pool* pool, uint32_t layer, const oxi_lease* lease);
+uint64_t oxi_pool_conv_ptr(const oxi_kv_pool* pool, uint32_t layer, const oxi_lease* lease);
+
+/* One decode step's tables (batch_engine.rs:709-740): layer-major pointer tables
+ * tbl[layer * batch + i] for K, V and conv state, positions and seq_lens =
+ * position + 1.  set_row fills row i of the host image from a lease and the
+ * position of the token appended in this step; upload copies rows 0..batch-1
+ * to the device on `stream` from pinned memory (a ring of staging blocks: uploads
+ * may be enqueued back to back without a sync).  The accessors return DEVICE
+ * addresses, valid after the first upload and stable for the life of the object,
+ * to be passed to oxi_append_decode, oxi_conv_decode, ...; advance moves every
+ * row delta tokens ahead on the device (oxi_advance_step) and in the host image,
+ * so that steps with unchanged membership need no upload. */
+int32_t oxi_tables_create(oxi_step_tables** out, const oxi_kv_pool* pool, uint32_t max_batch);
+int32_t oxi_tables_destroy(oxi_step_tables* tables);
+int32_t oxi_tables_set_row(oxi_step_tables* tables, uint32_t row, const oxi_lease* lease, uint32_t position);
+int32_t oxi_tables_upload(oxi_step_tables* tables, void* stream, uint32_t batch);
+int32_t oxi_tables_advance(oxi_handle* h, oxi_step_tables* tables, void* stream, uint32_t delta);
+uint32_t oxi_tables_batch(const oxi_step_tables* tables);
+const uint64_t* oxi_tables_k_ptrs(const oxi_step_tables* tables, uint32_t layer);
+const uint64_t* oxi_tables_v_ptrs(const oxi_step_tables* tables, uint32_t layer);
+const uint64_t* oxi_tables_conv_ptrs(const oxi_step_tables* tables, uint32_t layer);
+const uint32_t* oxi_tables_pos_ids(const oxi_step_tables* tables);
+const uint32_t* oxi_tables_seq_lens(const oxi_step_tables* tables);
+
 /* ---- test support ------------------------------------------------------- */
 
 /* Every in-kernel pipeline wait (a consumer waiting for a stage of K/V rows, the
@@ -318,6 +382,16 @@ int32_t oxi_decode_step_host(oxi_handle* h, void* stream, void* ctx_host, const 
  * CTA 0's work items unwritten; later launches are unaffected.  No counterpart in
  * the reference. */
 int32_t oxi_debug_arm_wait_fault(oxi_handle* h, uint32_t which, uint32_t stage, uint32_t limit_us);
+
+/* Measurement support: streams `bytes` (rounded down to whole 64 KB stages) from
+ * `src` through the decode-attention kernel's memory pipeline - one persistent CTA
+ * per SM, 1-D bulk copies of copy_bytes each into a 3-stage ring of 64 KB stages,
+ * mbarrier hand-over to four consumer warps - with no arithmetic.  Timed by the
+ * caller (events on `stream`), it gives the read-only bandwidth ceiling of that
+ * pipeline, the yardstick beside the read+write copy bandwidth.  copy_bytes is a
+ * power of two in 16 .. 65536 (the decode kernel copies 4096).  No counterpart in
+ * the reference. */
+int32_t oxi_debug_stream_read(oxi_handle* h, void* stream, const void* src, uint64_t bytes, uint32_t copy_bytes);
 
 /* ---- entry point that allocates nothing -------------------------------- */
 

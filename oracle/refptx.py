@@ -147,6 +147,53 @@ class RefPtx:
                      (C.c_uint32, 7), (C.c_uint32, rows), (C.c_uint32, HIDDEN * 6),
                      (C.c_uint32, 3 * HIDDEN * 2), (C.c_uint32, 2 * HIDDEN * 2)])
 
+    # ---- the three kernels of the GEMM prefill path (BE:439-592); the two GEMMs between them run in
+    # cuBLASLt in the engine and are supplied by the caller
+
+    def attn_pack_q(self, q_pack, q_in, rows):  # BE:477-497: [row][head][dim] -> [head][row][dim]
+        self.launch("batched_attn_pack_q_fp16", (rows, 1, 1), (256, 1, 1),
+                    [(C.c_void_p, q_in), (C.c_void_p, q_pack), (C.c_uint32, NQ), (C.c_uint32, HD),
+                     (C.c_uint32, rows)])
+
+    def attn_softmax_mask(self, scores, p_out, sums, seq_lens, rows, keys, t_lo, window,
+                          scale=0.0883883476):  # BE:530-553: one KV head's [4*rows][keys] f32 scores
+        self.launch("batched_attn_softmax_mask_fp16", (rows, 4, 1), (128, 1, 1),
+                    [(C.c_void_p, scores), (C.c_void_p, p_out), (C.c_void_p, sums), (C.c_void_p, seq_lens),
+                     (C.c_uint32, rows), (C.c_uint32, keys), (C.c_uint32, t_lo), (C.c_uint32, window),
+                     (C.c_float, scale)])
+
+    def attn_gate_scatter(self, ctx, attn_tmp, gate, sums, rows):  # BE:566-588
+        self.launch("batched_attn_gate_scatter_fp16", (NQ, rows, 1), (HD, 1, 1),
+                    [(C.c_void_p, ctx), (C.c_void_p, attn_tmp), (C.c_void_p, gate), (C.c_void_p, sums),
+                     (C.c_uint32, rows), (C.c_uint32, NQ), (C.c_uint32, HD)])
+
+    def gemm_attention_chunk(self, ctx, q, gate, k_cache, v_cache, seq_lens, rows, slen_min, slen_max, window):
+        """BatchEngine::gemm_attention_chunk (BE:439-592) with the two cuBLASLt calls (f16 in, f32
+        accumulate) replaced by torch float32 matmuls on the same f16 operands: QK^T to f32 scores,
+        PV rounded to f16.  k_cache / v_cache [tokens][4][128] of the chunk's request; seq_lens [rows]
+        device u32.  Returns (sums [16][rows] f32) beside writing ctx [rows][16][128]."""
+        prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = False
+        try:
+            t_lo = max(slen_min - window, 0) if window > 0 else 0
+            keys = slen_max - t_lo
+            n = 4 * rows
+            qpack = torch.empty(NQ, rows, HD, dtype=torch.float16, device=q.device)
+            self.attn_pack_q(qpack, q, rows)
+            sums = torch.zeros(NQ * rows, dtype=torch.float32, device=q.device)
+            tmp = torch.empty(NQ, rows, HD, dtype=torch.float16, device=q.device)
+            for kvh in range(NKV):
+                kk = k_cache[t_lo:t_lo + keys, kvh].float()          # [keys][128]
+                vv = v_cache[t_lo:t_lo + keys, kvh].float()
+                scores = (qpack[4 * kvh:4 * kvh + 4].reshape(n, HD).float() @ kk.t()).contiguous()   # [4*rows][keys]
+                p = torch.empty(n, keys, dtype=torch.float16, device=q.device)
+                self.attn_softmax_mask(scores, p, sums[kvh * n:(kvh + 1) * n], seq_lens, rows, keys, t_lo, window)
+                tmp[4 * kvh:4 * kvh + 4] = (p.float() @ vv).half().view(4, rows, HD)
+            self.attn_gate_scatter(ctx, tmp, gate, sums, rows)
+            return sums.view(NQ, rows)
+        finally:
+            torch.backends.cuda.matmul.allow_tf32 = prev
+
     # ---- the engine's sequences ----
 
     @staticmethod

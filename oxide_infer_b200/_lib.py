@@ -43,10 +43,38 @@ SIGNATURES = {
     "oxi_sigmoid_gate": [_vp] * 4 + [_u32],
     "oxi_decode_step_host": [_vp] * 14 + [_u32, _u32, _u32, _f32],
     "oxi_decode_attn_static": [_vp] * 7 + [_u32, _u32, _u32],
+    "oxi_host_last_error_string": [],
+    "oxi_pool_create": [C.POINTER(_vp), _vp, _u32, _u32, C.c_uint64],
+    "oxi_pool_destroy": [_vp],
+    "oxi_pool_capacity_tokens": [_vp],
+    "oxi_pool_free_tokens": [_vp],
+    "oxi_pool_free_slots": [_vp],
+    "oxi_pool_acquire": [_vp, _vp, C.c_uint64, _vp],
+    "oxi_pool_release": [_vp, _vp],
+    "oxi_pool_k_ptr": [_vp, _u32, _vp],
+    "oxi_pool_v_ptr": [_vp, _u32, _vp],
+    "oxi_pool_conv_ptr": [_vp, _u32, _vp],
+    "oxi_tables_create": [C.POINTER(_vp), _vp, _u32],
+    "oxi_tables_destroy": [_vp],
+    "oxi_tables_set_row": [_vp, _u32, _vp, _u32],
+    "oxi_tables_upload": [_vp, _vp, _u32],
+    "oxi_tables_advance": [_vp, _vp, _vp, _u32],
+    "oxi_tables_batch": [_vp],
+    "oxi_tables_k_ptrs": [_vp, _u32],
+    "oxi_tables_v_ptrs": [_vp, _u32],
+    "oxi_tables_conv_ptrs": [_vp, _u32],
+    "oxi_tables_pos_ids": [_vp],
+    "oxi_tables_seq_lens": [_vp],
     "oxi_debug_arm_wait_fault": [_vp, _u32, _u32, _u32],
     "oxi_static_device_status": [_vp, C.POINTER(_u32)],
+    "oxi_debug_stream_read": [_vp, _vp, _vp, C.c_uint64, _u32],
 }
 _RESTYPE = {"oxi_status_string": C.c_char_p, "oxi_last_error_string": C.c_char_p,
+            "oxi_host_last_error_string": C.c_char_p,
+            "oxi_pool_capacity_tokens": C.c_uint64, "oxi_pool_free_tokens": C.c_uint64, "oxi_pool_free_slots": _u32,
+            "oxi_pool_k_ptr": C.c_uint64, "oxi_pool_v_ptr": C.c_uint64, "oxi_pool_conv_ptr": C.c_uint64,
+            "oxi_tables_batch": _u32, "oxi_tables_k_ptrs": _vp, "oxi_tables_v_ptrs": _vp,
+            "oxi_tables_conv_ptrs": _vp, "oxi_tables_pos_ids": _vp, "oxi_tables_seq_lens": _vp,
             "oxi_workspace_bytes": C.c_size_t, "oxi_prefill_split_slot_bytes": C.c_uint64}
 
 _lib = None

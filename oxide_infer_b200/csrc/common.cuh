@@ -133,16 +133,16 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
                                                   volatile uint32_t* abort_flag,
                                                   uint32_t limit_us = WAIT_LIMIT_US) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    const uint64_t limit_ns = (uint64_t)limit_us * 1000ull;
     uint64_t t0 = 0;
+    // the flag and the clock are looked at every 256 polls only: the waiting warps share issue slots
+    // with the warps that do the arithmetic
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 63u) == 0u) {
+        if ((it & 255u) == 0u) {
             if (*abort_flag) return false;
             uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > limit_ns) {
+            else if (now - t0 > (uint64_t)limit_us * 1000ull) {
                 *abort_flag = 1u;
                 return false;
             }

@@ -518,10 +518,12 @@ class StepTables {
         check(cudaMalloc((void**)&d_pos_, max_batch * 4), "tables");
         check(cudaMalloc((void**)&d_len_, max_batch * 4), "tables");
         check(cudaMallocHost((void**)&h_, (3 * n * 8) + 2 * max_batch * 4), "pinned tables");
+        check(cudaEventCreateWithFlags(&uploaded_, cudaEventDisableTiming), "event");
     }
     ~StepTables() {
         cudaFree(d_k_); cudaFree(d_v_); cudaFree(d_conv_); cudaFree(d_pos_); cudaFree(d_len_);
         if (h_) cudaFreeHost(h_);
+        if (uploaded_) cudaEventDestroy(uploaded_);
     }
     StepTables(const StepTables&) = delete;
     StepTables& operator=(const StepTables&) = delete;
@@ -530,6 +532,8 @@ class StepTables {
         if (t.batch > max_batch_ || t.layers != layers_) throw std::invalid_argument("tables exceed the allocated size");
         batch_ = t.batch;
         const size_t n = t.batch * t.layers;
+        // the pinned image is reused: the previous upload must have executed before it is rewritten
+        check(cudaEventSynchronize(uploaded_), "upload");
         uint64_t* hk = (uint64_t*)h_;
         uint64_t* hv = hk + max_batch_ * layers_;
         uint64_t* hc = hv + max_batch_ * layers_;
@@ -545,6 +549,7 @@ class StepTables {
         check(cudaMemcpyAsync(d_conv_, hc, n * 8, cudaMemcpyHostToDevice, s), "upload");
         check(cudaMemcpyAsync(d_pos_, hp, t.batch * 4, cudaMemcpyHostToDevice, s), "upload");
         check(cudaMemcpyAsync(d_len_, hl, t.batch * 4, cudaMemcpyHostToDevice, s), "upload");
+        check(cudaEventRecord(uploaded_, s), "upload");
     }
     size_t batch() const { return batch_; }
     const uint64_t* k_ptrs(size_t layer) const { return d_k_ + layer * batch_; }
@@ -563,6 +568,7 @@ class StepTables {
     uint64_t *d_k_ = nullptr, *d_v_ = nullptr, *d_conv_ = nullptr;
     uint32_t *d_pos_ = nullptr, *d_len_ = nullptr;
     void* h_ = nullptr;
+    cudaEvent_t uploaded_ = nullptr;
 };
 
 // Device copy of a wave's tables (one pinned staging block, asynchronous uploads).

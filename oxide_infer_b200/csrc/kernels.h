@@ -107,6 +107,12 @@ cudaError_t launch_append_decode_paged(cudaStream_t stream, const DecodeWorkspac
                                        const uint32_t* seq_lens, const PagedMap& pm, uint32_t batch, uint32_t window,
                                        float eps);
 
+// Read-only streaming probe (bench and tests): the decode kernel's copy pipeline without arithmetic.
+cudaError_t stream_probe_init();
+cudaError_t launch_stream_read(cudaStream_t stream, const void* src, uint64_t bytes, uint32_t copy_bytes, int num_sms,
+                               uint32_t* sink, uint32_t* status);
+uint32_t stream_probe_stage_bytes();
+
 // Sampling-side table kernels.
 cudaError_t launch_embed_lookup(cudaStream_t stream, void* out, const void* table,
                                 const uint32_t* token_ids, uint32_t hidden, uint32_t table_rows,

@@ -168,6 +168,7 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
     {
         cudaError_t e = decode_attn_init();
         if (e == cudaSuccess) e = prefill_attn_init();
+        if (e == cudaSuccess) e = stream_probe_init();
         if (e != cudaSuccess) { rc = cuda_fail(e, "cudaFuncSetAttribute"); goto bad; }
     }
     if (cudaDeviceSynchronize() != cudaSuccess) {
@@ -254,6 +255,18 @@ int32_t oxi_debug_arm_wait_fault(oxi_handle* h, uint32_t which, uint32_t stage, 
     f.skip_plus1 = stage + 1u;
     f.limit_us = limit_us;
     (which == 0u ? h->dbg_decode : h->dbg_prefill) = f;
+    return OXI_OK;
+}
+
+int32_t oxi_debug_stream_read(oxi_handle* h, void* stream, const void* src, uint64_t bytes, uint32_t copy_bytes) {
+    if (!h || !src) return fail(OXI_ERR_NULL, "oxi_debug_stream_read: null argument");
+    const uint32_t stage = stream_probe_stage_bytes();
+    if (copy_bytes < 16u || copy_bytes > stage || (copy_bytes & (copy_bytes - 1u)) != 0u)
+        return fail(OXI_ERR_ARG, "oxi_debug_stream_read: copy_bytes must be a power of two, 16 .. 65536");
+    if (bytes < stage || ((uintptr_t)src & 15u) != 0u)
+        return fail(OXI_ERR_ARG, "oxi_debug_stream_read: at least 64 KB from a 16-byte aligned address");
+    OXI_CUDA(launch_stream_read((cudaStream_t)stream, src, bytes, copy_bytes, h->num_sms, h->dws.status + 8, h->dws.status),
+             "stream_read launch");
     return OXI_OK;
 }
 

@@ -379,7 +379,11 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                     const __grid_constant__ TmaDesc tmap, const uint64_t slab_base, const uint32_t slab_rows,
                     const WaitFault fault) {
     using namespace pf;
+#ifdef OXI_PF_CONST_WAIT
+    const uint32_t wait_us = WAIT_LIMIT_US;
+#else
     const uint32_t wait_us = fault.skip_plus1 ? fault.limit_us : WAIT_LIMIT_US;
+#endif
     // paged K/V: k_ptrs / v_ptrs are unused, wave row r reads row row_seq[r] of pm.block_tables
     constexpr bool paged = kPaged;
     extern __shared__ unsigned char smem_raw[];

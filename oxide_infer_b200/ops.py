@@ -101,6 +101,12 @@ class KvPath:
         attention launch loses one pipeline stage of CTA 0 and its waits last limit_us."""
         _check(self.lib.oxi_debug_arm_wait_fault(self.h, which, stage, limit_us), "oxi_debug_arm_wait_fault")
 
+    def stream_read(self, src, copy_bytes: int = 4096):
+        """Measurement support (oxi_debug_stream_read): reads tensor `src` once through the decode
+        kernel's bulk-copy pipeline without arithmetic."""
+        _check(self.lib.oxi_debug_stream_read(self.h, _stream(), _p(src), src.numel() * src.element_size(), copy_bytes),
+               "oxi_debug_stream_read")
+
     # ---- fused operators
     def append(self, q_io, k_in, v_in, q_norm_w, k_norm_w, cos, sin, pos_ids, k_ptrs, v_ptrs,
                eps: float = 1e-5, batch: int | None = None):
