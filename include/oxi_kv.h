@@ -198,6 +198,38 @@ int32_t oxi_conv_prefill(oxi_handle* h, void* stream, void* y_out, const uint64_
                          const uint32_t* origin, const uint32_t* local_pos, const void* bcx,
                          const void* conv_w, uint32_t rows);
 
+/* ---- the linear layers on either side of the path -------------------------- */
+
+/* Tensor maps over a layer's projection weights (host object, no device memory, nothing is copied: the
+ * weights stay where the caller keeps them and must outlive the object).  Weight layout is the
+ * engine's: [out_features][2048] f16 row-major, y = W x (lt.gemm(m = out_features, k = 2048, n = rows,
+ * W, x, y), lt_gemm.rs:828-900), 16-byte aligned. */
+typedef struct oxi_linear oxi_linear;
+/* q_proj [2048][2048], k_proj [512][2048], v_proj [512][2048], gate_proj [16][2048] of one attention layer. */
+int32_t oxi_qkvg_create(oxi_linear** out, const void* wq, const void* wk, const void* wv, const void* wg);
+int32_t oxi_linear_create(oxi_linear** out, const void* w, uint32_t out_features);
+int32_t oxi_linear_destroy(oxi_linear* w);
+
+/* The four projection GEMMs in front of the path and the append operator in ONE kernel: x [rows][2048]
+ * (the layer's normed hidden state) times q/k/v/gate weights on the tensor cores (tcgen05, f32
+ * accumulate, results rounded to f16 as the reference's GEMMs round them), and in the epilogue per
+ * token and head the Q/K RMSNorm + RoPE + KV append of oxi_append on those f16 values: K and V go
+ * straight to row pos_ids[b] of k_ptrs[b] / v_ptrs[b], q_out [rows][16][128] receives the normalised +
+ * rotated q and gate_out [rows][16] the gate for oxi_decode_attn / oxi_prefill_attn.
+ * Replaces lt.gemm x4 (batch_engine.rs:914-926) + batched_qk_rmsnorm_fp16 x2 + batched_rope_fp16 x2 +
+ * batched_kv_copy_fp16 x2 (batch_engine.rs:941-1014): ten launches and the q/k/v round trip through
+ * HBM.  raw_out (nullable) [rows][3088] receives the f16 projections [q | k | v | gate] themselves.
+ * Given those projections, q_out and the cache rows are byte-identical to oxi_append's; the projections
+ * are within one f16 step of an fp32-accumulated matmul (the summation order inside a GEMM is not
+ * specified by the reference either).  rows <= max(max_batch, max_prefill_rows). */
+int32_t oxi_project_append(oxi_handle* h, void* stream, const oxi_linear* qkvg, const void* x, void* q_out, void* gate_out,
+                           void* raw_out, const void* q_norm_w, const void* k_norm_w, const void* cos_table,
+                           const void* sin_table, const uint32_t* pos_ids, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
+                           uint32_t rows, float eps);
+/* y [rows][out_features] = x [rows][2048] W^T, the same GEMM without epilogue arithmetic: o_proj on the far
+ * side of the path (lt.gemm(2048, 2048, b, o_proj, ctx, layer), batch_engine.rs:1241-1245). */
+int32_t oxi_linear_forward(oxi_handle* h, void* stream, const oxi_linear* w, const void* x, void* y, uint32_t rows);
+
 /* ---- step tables that advance on the device ----------------------------- */
 /* pos_ids[b] += delta and seq_lens[b] += delta in place (either pointer may be
  * null).  The engine rebuilds and uploads its tables for every step
@@ -375,7 +407,8 @@ const uint32_t* oxi_tables_seq_lens(const oxi_step_tables* tables);
  * raised.  Nothing in normal operation makes a wait run out, so this call exists
  * to exercise that path without faulting or hanging the GPU: it arms the NEXT
  * launch of this handle's decode-attention kernel (which = 0) or prefill-attention
- * kernel (which = 1) so that CTA 0 withholds its stage-th pipeline stage (decode:
+ * kernel (which = 1; oxi_prefill_attn only, the armed wave runs unsplit and without
+ * a registered slab) so that CTA 0 withholds its stage-th pipeline stage (decode:
  * no copy is issued for it; prefill: the K tile is copied but never published) and
  * all waits of that launch last limit_us microseconds instead of a second.  The
  * armed launch returns normally with OXI_DEV_WAIT_TIMEOUT set and with the rows of

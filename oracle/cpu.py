@@ -190,6 +190,14 @@ def decode_layer(q_io, k_io, v_in, gate, q_norm_w, k_norm_w, cos, sin, pos_ids, 
     return ctx
 
 
+def linear(x, w):
+    """y = f16(x @ w.T) with f32 accumulation in index order (the projection GEMMs, lt.gemm)."""
+    rows, out = x.shape[0], w.shape[0]
+    y = np.empty((rows, out), np.float16)
+    lib().orc_linear_f16(_p(y), _p(x), _p(w), _u32(rows), _u32(out), _u32(x.shape[1]))
+    return y
+
+
 def prefill_gemm_chunk(q, gate, k_cache, v_cache, p0, window=0):
     rows = q.shape[0]
     ctx = np.empty((rows, NQ, HD), np.float16)

@@ -158,6 +158,25 @@ void orc_rope_table(uint16_t* cos_t, uint16_t* sin_t, uint32_t max_pos, uint32_t
     free(inv);
 }
 
+/* ------------------------------------------------- projections (lt.gemm) ---- */
+
+/* y [rows][out] = f16( x [rows][in] * w [out][in]^T ), f32 accumulation in index order with fma: the
+ * reference's projection GEMMs (lt.gemm(m = out, k = in, n = rows, W, x, y): cuBLASLt, f16 operands,
+ * f32 compute, f16 output; lt_gemm.rs:828-900, launched at batch_engine.rs:914-926 and :1241-1245).
+ * cuBLASLt does not specify its summation order, so a GPU GEMM agrees with this restatement to
+ * about one f16 step of the output, not bit for bit. */
+void orc_linear_f16(uint16_t* y, const uint16_t* x, const uint16_t* w, uint32_t rows, uint32_t out_features,
+                    uint32_t in_features) {
+#pragma omp parallel for schedule(static)
+    for (int64_t ro = 0; ro < (int64_t)rows * out_features; ro++) {
+        const uint16_t* xr = x + (size_t)(ro / out_features) * in_features;
+        const uint16_t* wr = w + (size_t)(ro % out_features) * in_features;
+        float a = 0.0f;
+        for (uint32_t k = 0; k < in_features; k++) a = fmaf(orc_h2f(xr[k]), orc_h2f(wr[k]), a);
+        y[ro] = orc_f2h(a);
+    }
+}
+
 /* ------------------------------------------------------------ a1..a3 ---- */
 
 /* batched_qk_rmsnorm_fp16, BA:13-118.  In place on x_io [B][heads][hd]. */

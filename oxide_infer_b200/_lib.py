@@ -43,6 +43,11 @@ SIGNATURES = {
     "oxi_sigmoid_gate": [_vp] * 4 + [_u32],
     "oxi_decode_step_host": [_vp] * 14 + [_u32, _u32, _u32, _f32],
     "oxi_decode_attn_static": [_vp] * 7 + [_u32, _u32, _u32],
+    "oxi_qkvg_create": [C.POINTER(_vp), _vp, _vp, _vp, _vp],
+    "oxi_linear_create": [C.POINTER(_vp), _vp, _u32],
+    "oxi_linear_destroy": [_vp],
+    "oxi_project_append": [_vp] * 14 + [_u32, _f32],
+    "oxi_linear_forward": [_vp] * 5 + [_u32],
     "oxi_host_last_error_string": [],
     "oxi_pool_create": [C.POINTER(_vp), _vp, _u32, _u32, C.c_uint64],
     "oxi_pool_destroy": [_vp],

@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO = os.path.join(HERE, "liboxi_kv.so")
-SOURCES = ["oxi_kv.cu", "append_kernels.cu", "decode_attn.cu", "conv_kernels.cu", "prefill_attn.cu", "sample_kernels.cu", "host_api.cu", "stream_probe.cu"]
+SOURCES = ["oxi_kv.cu", "append_kernels.cu", "decode_attn.cu", "conv_kernels.cu", "prefill_attn.cu", "sample_kernels.cu", "host_api.cu", "stream_probe.cu", "proj_gemm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--use_fast_math=false"]
 

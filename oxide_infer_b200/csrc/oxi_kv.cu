@@ -169,6 +169,7 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
         cudaError_t e = decode_attn_init();
         if (e == cudaSuccess) e = prefill_attn_init();
         if (e == cudaSuccess) e = stream_probe_init();
+        if (e == cudaSuccess) e = proj_gemm_init();
         if (e != cudaSuccess) { rc = cuda_fail(e, "cudaFuncSetAttribute"); goto bad; }
     }
     if (cudaDeviceSynchronize() != cudaSuccess) {
@@ -569,6 +570,93 @@ int32_t oxi_sigmoid_gate(oxi_handle* h, void* stream, void* ctx_io, const void* 
     REQ_PTR(ctx_io && gate, "oxi_sigmoid_gate");
     if (batch == 0) return fail(OXI_ERR_BATCH, "oxi_sigmoid_gate: batch is 0");
     OXI_CUDA(launch_sigmoid_gate((cudaStream_t)stream, ctx_io, gate, batch), "sigmoid_gate launch");
+    return OXI_OK;
+}
+
+// ---- linear layers on either side of the path (tensor maps over the caller's weights; host objects only)
+struct oxi_linear_s {
+    TmaDesc maps[4];        // qkvg: q, k, v, gate; plain: maps[0]
+    uint32_t out_features;  // plain: rows of the weight matrix; qkvg: 3088
+    bool qkvg;
+};
+
+static int32_t linear_map(TmaDesc* m, const void* w, uint64_t rows, const char* who) {
+    if (!w) return fail(OXI_ERR_NULL, who);
+    if (((uintptr_t)w & 15u) != 0u) return fail(OXI_ERR_ARG, "weights must be 16-byte aligned");
+    const int rc = proj_encode_map(m, w, rows);
+    if (rc == -1) return fail(OXI_ERR_NO_DEVICE, "driver has no cuTensorMapEncodeTiled");
+    if (rc != 0) return fail(OXI_ERR_ARG, "cuTensorMapEncodeTiled rejected the weight matrix");
+    return OXI_OK;
+}
+
+int32_t oxi_qkvg_create(oxi_linear** out, const void* wq, const void* wk, const void* wv, const void* wg) {
+    if (!out) return fail(OXI_ERR_NULL, "oxi_qkvg_create: out is null");
+    *out = nullptr;
+    oxi_linear_s* l = new (std::nothrow) oxi_linear_s();
+    if (!l) return fail(OXI_ERR_WORKSPACE, "oxi_qkvg_create: host allocation failed");
+    int32_t rc;
+    if ((rc = linear_map(&l->maps[0], wq, NQ * HD, "oxi_qkvg_create: q_proj is null")) ||
+        (rc = linear_map(&l->maps[1], wk, NKV * HD, "oxi_qkvg_create: k_proj is null")) ||
+        (rc = linear_map(&l->maps[2], wv, NKV * HD, "oxi_qkvg_create: v_proj is null")) ||
+        (rc = linear_map(&l->maps[3], wg, NQ, "oxi_qkvg_create: gate_proj is null"))) {
+        delete l;
+        return rc;
+    }
+    l->out_features = NQ * HD + 2 * NKV * HD + NQ;
+    l->qkvg = true;
+    *out = reinterpret_cast<oxi_linear*>(l);
+    return OXI_OK;
+}
+
+int32_t oxi_linear_create(oxi_linear** out, const void* w, uint32_t out_features) {
+    if (!out) return fail(OXI_ERR_NULL, "oxi_linear_create: out is null");
+    *out = nullptr;
+    if (out_features == 0 || out_features > (1u << 20)) return fail(OXI_ERR_ARG, "oxi_linear_create: out_features out of range");
+    oxi_linear_s* l = new (std::nothrow) oxi_linear_s();
+    if (!l) return fail(OXI_ERR_WORKSPACE, "oxi_linear_create: host allocation failed");
+    if (int32_t rc = linear_map(&l->maps[0], w, out_features, "oxi_linear_create: weights are null")) {
+        delete l;
+        return rc;
+    }
+    l->out_features = out_features;
+    l->qkvg = false;
+    *out = reinterpret_cast<oxi_linear*>(l);
+    return OXI_OK;
+}
+
+int32_t oxi_linear_destroy(oxi_linear* l) {
+    delete reinterpret_cast<oxi_linear_s*>(l);
+    return OXI_OK;
+}
+
+int32_t oxi_project_append(oxi_handle* h, void* stream, const oxi_linear* qkvg, const void* x, void* q_out, void* gate_out,
+                           void* raw_out, const void* q_norm_w, const void* k_norm_w, const void* cos_table,
+                           const void* sin_table, const uint32_t* pos_ids, const uint64_t* k_ptrs, const uint64_t* v_ptrs,
+                           uint32_t rows, float eps) {
+    REQ_HANDLE("oxi_project_append");
+    const oxi_linear_s* l = reinterpret_cast<const oxi_linear_s*>(qkvg);
+    REQ_PTR(l && x && q_out && gate_out && q_norm_w && k_norm_w && cos_table && sin_table && pos_ids && k_ptrs && v_ptrs,
+            "oxi_project_append");
+    if (!l->qkvg) return fail(OXI_ERR_ARG, "oxi_project_append: the weights object was not made by oxi_qkvg_create");
+    REQ_BATCH(rows, (h->max_batch > h->max_prefill_rows ? h->max_batch : h->max_prefill_rows), "oxi_project_append");
+    if (!(eps >= 0.0f)) return fail(OXI_ERR_ARG, "oxi_project_append: eps must be >= 0");
+    if ((((uintptr_t)x | (uintptr_t)q_out | (uintptr_t)gate_out | (uintptr_t)raw_out | (uintptr_t)cos_table |
+          (uintptr_t)sin_table) & 15u) != 0u)
+        return fail(OXI_ERR_ARG, "oxi_project_append: x, q_out, gate_out, raw_out and the rope tables must be 16-byte aligned");
+    OXI_CUDA(launch_project_append((cudaStream_t)stream, l->maps, x, rows, q_out, gate_out, raw_out, q_norm_w, k_norm_w,
+                                   cos_table, sin_table, pos_ids, k_ptrs, v_ptrs, eps, h->dws.status),
+             "project_append launch");
+    return OXI_OK;
+}
+
+int32_t oxi_linear_forward(oxi_handle* h, void* stream, const oxi_linear* w, const void* x, void* y, uint32_t rows) {
+    REQ_HANDLE("oxi_linear_forward");
+    const oxi_linear_s* l = reinterpret_cast<const oxi_linear_s*>(w);
+    REQ_PTR(l && x && y, "oxi_linear_forward");
+    if (l->qkvg) return fail(OXI_ERR_ARG, "oxi_linear_forward: the weights object was made by oxi_qkvg_create");
+    if (rows == 0 || rows > (1u << 20)) return fail(OXI_ERR_BATCH, "oxi_linear_forward: rows out of range");
+    if ((((uintptr_t)x | (uintptr_t)y) & 15u) != 0u) return fail(OXI_ERR_ARG, "oxi_linear_forward: x and y must be 16-byte aligned");
+    OXI_CUDA(launch_linear((cudaStream_t)stream, &l->maps[0], l->out_features, x, rows, y, h->dws.status), "linear launch");
     return OXI_OK;
 }
 

@@ -55,6 +55,7 @@
 // writing output and reports OXI_DEV_WAIT_TIMEOUT in the status word.
 #include "common.cuh"
 #include "kernels.h"
+#include "tc5.cuh"
 
 namespace oxi {
 
@@ -82,74 +83,6 @@ constexpr float QK_SCALE_LOG2 = ATTN_SCALE * LOG2E;
 constexpr uint32_t IDESC_QK = (1u << 4) | ((uint32_t)(TK >> 3) << 17) | ((uint32_t)(M >> 4) << 24);          // N = 64, A and B K-major
 constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(M >> 4) << 24);  // N = 128, B MN-major
 }  // namespace pf
-
-// shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
-    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-// this thread's TMEM lane, 32 consecutive 32-bit columns
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-}
-
-// true in exactly one lane of a converged warp
-__device__ __forceinline__ uint32_t elect_one() {
-    uint32_t pred;
-    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
-    return pred;
-}
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
-    const uint32_t n = valid ? 16u : 0u;  // 0 source bytes: destination is zero-filled
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // Key-range split of long blocks (off when part_tiles == 0), for waves with fewer (block, KV head)
 // items than the GPU has SMs.  The plan kernel picks the smallest part size P >= part_tiles (in
@@ -359,16 +292,13 @@ __device__ __forceinline__ bool pf_next_run(uint32_t& next, uint32_t nruns, cons
     return false;
 }
 
-// One 64-row x 64-element box of a registered K/V slab into a 128-byte-swizzled sub-tile; completion
-// is counted in bytes on `bar`.  x is a multiple of 64 elements (128 bytes), so the 16-byte rule holds.
-__device__ __forceinline__ void tma_load_box(uint32_t dst, const TmaDesc* map, uint32_t x, uint32_t y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
-        : "memory");
-}
-
-template <bool kPaged, bool kSplit, bool kTma>
+// kFault (test support only) compiles in the hooks of oxi_debug_arm_wait_fault: a wait limit taken from the
+// launch, a K tile of CTA 0 that is never published, and the propagation of a give-up to the roles whose own
+// waits passed (the MMA warps withhold "O is final", the CTA claims nothing more).  The production
+// instantiations carry none of it: the loop is sensitive to a few instructions in its waits and hand-overs
+// (measured 3-5 % on the 4,096-row wave), and there a wait only runs out after an internal error, which the
+// status word reports.
+template <bool kPaged, bool kSplit, bool kTma, bool kFault>
 __global__ void __launch_bounds__(pf::THREADS, 1)
 prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__ q,
                     const uint16_t* __restrict__ gate, const uint64_t* __restrict__ k_ptrs,
@@ -379,11 +309,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                     const __grid_constant__ TmaDesc tmap, const uint64_t slab_base, const uint32_t slab_rows,
                     const WaitFault fault) {
     using namespace pf;
-#ifdef OXI_PF_CONST_WAIT
-    const uint32_t wait_us = WAIT_LIMIT_US;
-#else
-    const uint32_t wait_us = fault.skip_plus1 ? fault.limit_us : WAIT_LIMIT_US;
-#endif
+    const uint32_t wait_us = kFault ? fault.limit_us : WAIT_LIMIT_US;
     // paged K/V: k_ptrs / v_ptrs are unused, wave row r reads row row_seq[r] of pm.block_tables
     constexpr bool paged = kPaged;
     extern __shared__ unsigned char smem_raw[];
@@ -448,8 +374,8 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
     // Claims the next item and prepares its tables in buffer `buf`; run by all lanes of the K loader warp
     // while the other roles finish the current item (before the loop for the first item).
     auto prepare_item = [&](uint32_t buf) {
-        uint32_t item = 0xffffffffu;  // a CTA one of whose waits gave up claims nothing more: the others take its share
-        if (lane == 0 && *const_cast<volatile uint32_t*>(&s_abort) == 0u) item = atomicAdd(counter, 1u);
+        uint32_t item = 0xffffffffu;  // kFault: a CTA one of whose waits gave up claims nothing more, the others take its share
+        if (lane == 0 && (!kFault || *const_cast<volatile uint32_t*>(&s_abort) == 0u)) item = atomicAdd(counter, 1u);
         item = __shfl_sync(0xffffffffu, item, 0);
         if (lane == 0) s_item[buf] = item;
         if (item >= nitems) return;
@@ -735,7 +661,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
                 }
             }
             if (slot_ok) *reinterpret_cast<float2*>(sp.part_ml + (pidx * M + row) * 2) =
-                make_float2(m_ref, (o_valid && live && ok && *const_cast<volatile uint32_t*>(&s_abort) == 0u) ? l_run : 0.0f);
+                make_float2(m_ref, (o_valid && live && ok) ? l_run : 0.0f);
         } else
         // ---- epilogue: O row from TMEM, 1/sum, f16, gate on the f16 value (as online kernel + gate kernel)
         if (o_valid) {
@@ -743,9 +669,9 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
             ++n_o;
             __syncwarp();
             tc_fence_after();
-            // no output once any wait of this CTA gave up (this thread's own waits may all have passed)
-            const bool write = OXI_IN_BOUNDS(row0 + tok < rows || tok >= nrows, status) && tok < nrows && c_len[tok] != 0 && ok &&
-                               *const_cast<volatile uint32_t*>(&s_abort) == 0u;
+            // nothing is written once a wait of this thread gave up (kFault: or any wait of the CTA - the MMA warp
+            // then withholds bar_ofull, so the wait above has failed too)
+            const bool write = OXI_IN_BOUNDS(row0 + tok < rows || tok >= nrows, status) && tok < nrows && c_len[tok] != 0 && ok;
             const float inv = rcp_approx_ftz(l_run);
             const size_t rh = (size_t)(row0 + (write ? tok : 0u)) * NQ + head;
             const float sig = (gate && write) ? sigmoid_ref(h2f(gate[rh])) : 1.0f;
@@ -840,7 +766,9 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
             if (elect_one()) {
                 if (has_pv) {
                     pv(sv, t > 2);
-                    if (last) umma_commit(&bar_ofull[j]);
+                    // "O is final" is only signalled while no wait of this CTA has given up: after a give-up the
+                    // softmax warps' wait for it fails at once (the flag is set) and they write nothing
+                    if (last && (!kFault || *const_cast<volatile uint32_t*>(&s_abort) == 0u)) umma_commit(&bar_ofull[j]);
                 }
                 if (has_qk) qk(sk);
                 mbar_arrive(&bar_tok[j ^ 1u]);
@@ -885,7 +813,7 @@ prefill_attn_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict__
         // publishes K (or V) tile number g to the tensor core; test support: CTA 0's K loader withholds one
         // tile (its copies have landed, the arrival never comes), so the MMA warps' wait for it runs out
         auto publish = [&](uint32_t g) {
-            if (is_k && fault.skip_plus1 && blockIdx.x == 0 && g + 1u == fault.skip_plus1) return;
+            if (kFault && is_k && blockIdx.x == 0 && g + 1u == fault.skip_plus1) return;
             mbar_arrive(&full[g % NS]);
         };
         uint32_t tflat = 0;    // tiles of the block's runs before this one (key-range split)
@@ -1089,9 +1017,9 @@ prefill_merge_kernel(uint16_t* __restrict__ ctx_out, const uint16_t* __restrict_
 size_t prefill_split_table_bytes() { return (size_t)3 * 1024 * PF_MAX_SPLIT * sizeof(uint32_t); }
 size_t prefill_split_slot_bytes() { return (size_t)NKV * 2 * pf::M * (HD + 2) * sizeof(float); }
 
-template <bool kPaged, bool kSplit, bool kTma>
+template <bool kPaged, bool kSplit, bool kTma, bool kFault = false>
 static cudaError_t pf_set_smem() {
-    return cudaFuncSetAttribute(prefill_attn_kernel<kPaged, kSplit, kTma>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    return cudaFuncSetAttribute(prefill_attn_kernel<kPaged, kSplit, kTma, kFault>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 (int)pf::SMEM_BYTES);
 }
 
@@ -1102,16 +1030,17 @@ cudaError_t prefill_attn_init() {
     if ((e = pf_set_smem<false, true, false>())) return e;
     if ((e = pf_set_smem<true, true, false>())) return e;
     if ((e = pf_set_smem<false, false, true>())) return e;
+    if ((e = pf_set_smem<false, false, false, true>())) return e;
     return pf_set_smem<false, true, true>();
 }
 
-template <bool kPaged, bool kSplit, bool kTma>
+template <bool kPaged, bool kSplit, bool kTma, bool kFault = false>
 static cudaError_t launch_pf(cudaStream_t stream, uint32_t grid, void* ctx_out, const void* q, const void* gate,
                              const uint64_t* k_ptrs, const uint64_t* v_ptrs, const uint32_t* seq_lens, uint32_t rows,
                              uint32_t window, uint32_t* status, uint32_t* order, uint32_t* counter, const PagedMap& pm,
                              const uint32_t* row_seq, const PfSplit& sp, const PrefillSlab& slab, const WaitFault& fault) {
     // programmatic dependent of the plan kernel: TMEM allocation and barrier set-up overlap it
-    return launch_pdl(prefill_attn_kernel<kPaged, kSplit, kTma>, dim3(grid), dim3(pf::THREADS), pf::SMEM_BYTES, stream,
+    return launch_pdl(prefill_attn_kernel<kPaged, kSplit, kTma, kFault>, dim3(grid), dim3(pf::THREADS), pf::SMEM_BYTES, stream,
                       (uint16_t*)ctx_out, (const uint16_t*)q, (const uint16_t*)gate, k_ptrs, v_ptrs, seq_lens, rows,
                       window, status, (const uint32_t*)order, counter, pm, row_seq, sp, slab.map, slab.base, slab.rows, fault);
 }
@@ -1125,7 +1054,9 @@ cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* 
     const WaitFault flt = fault ? *fault : WaitFault{};
     const uint32_t nblocks = (rows + pf::BLK - 1) / pf::BLK;
     // the split is for waves that leave SMs idle; larger waves balance by claiming longest first
-    const bool split = ws && ws->max_slots != 0u && part_keys != 0u && nblocks * NKV < (uint32_t)num_sms;
+    // an armed test fault runs the plain instantiation: pointer tables, unsplit, per-thread copies
+    const bool armed = flt.skip_plus1 != 0u && !pm;
+    const bool split = !armed && ws && ws->max_slots != 0u && part_keys != 0u && nblocks * NKV < (uint32_t)num_sms;
     PfSplit sp{};
     if (split) {
         sp.units = ws->units;
@@ -1145,13 +1076,14 @@ cudaError_t launch_prefill_attn(cudaStream_t stream, void* ctx_out, const void* 
     if (e != cudaSuccess) return e;
     const PagedMap map = pm ? *pm : PagedMap{};
     const PrefillSlab none{};
-    const bool tma = !pm && slab && slab->rows != 0u;
+    const bool tma = !armed && !pm && slab && slab->rows != 0u;
     const PrefillSlab& sl = tma ? *slab : none;
 #define OXI_PF_ARGS ctx_out, q, gate, k_ptrs, v_ptrs, seq_lens, rows, window, status, order, counter, map, row_seq, sp, sl, flt
     if (!split) {
         const uint32_t nitems = nblocks * NKV;
         const uint32_t grid = nitems < (uint32_t)num_sms ? nitems : (uint32_t)num_sms;
         if (pm) return launch_pf<true, false, false>(stream, grid, OXI_PF_ARGS);
+        if (armed) return launch_pf<false, false, false, true>(stream, grid, OXI_PF_ARGS);
         return tma ? launch_pf<false, false, true>(stream, grid, OXI_PF_ARGS)
                    : launch_pf<false, false, false>(stream, grid, OXI_PF_ARGS);
     }

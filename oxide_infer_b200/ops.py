@@ -37,6 +37,33 @@ class PagedLayout(C.Structure):
         return out
 
 
+class Linear:
+    """Tensor maps over projection weights (oxi_qkvg_create / oxi_linear_create).  The weight tensors are
+    kept alive by the object."""
+
+    def __init__(self, *weights):
+        lib = _lib.load()
+        h = C.c_void_p()
+        for w in weights:
+            if not (w.is_cuda and w.dtype == torch.float16 and w.is_contiguous() and w.shape[-1] == 2048):
+                raise ValueError("weights must be contiguous CUDA f16 [out_features][2048]")
+        if len(weights) == 4:
+            rc = lib.oxi_qkvg_create(C.byref(h), *[w.data_ptr() for w in weights])
+        elif len(weights) == 1:
+            rc = lib.oxi_linear_create(C.byref(h), weights[0].data_ptr(), weights[0].shape[0])
+        else:
+            raise ValueError("one weight matrix, or q, k, v, gate")
+        if rc != 0:
+            raise OxiError(rc, "oxi_linear_create")
+        self.h, self.lib, self._keep = h, lib, weights
+        self.out_features = sum(w.shape[0] for w in weights)
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.oxi_linear_destroy(self.h)
+            self.h = None
+
+
 class OxiError(RuntimeError):
     def __init__(self, code: int, where: str):
         lib = _lib.load()
@@ -129,6 +156,19 @@ class KvPath:
                                           _p(sin), _p(pos_ids), _p(seq_lens), _p(k_ptrs),
                                           _p(v_ptrs), q_io.shape[0], window, eps),
                "oxi_append_decode")
+
+    def project_append(self, qkvg: Linear, x, q_out, gate_out, q_norm_w, k_norm_w, cos, sin, pos_ids, k_ptrs, v_ptrs,
+                       raw_out=None, eps: float = 1e-5, rows: int | None = None):
+        """q/k/v/gate projections of x [rows][2048] + RMSNorm + RoPE + KV append in one kernel (oxi_project_append)."""
+        n = x.shape[0] if rows is None else rows
+        _check(self.lib.oxi_project_append(self.h, _stream(), qkvg.h, _p(x), _p(q_out), _p(gate_out), _p(raw_out),
+                                           _p(q_norm_w), _p(k_norm_w), _p(cos), _p(sin), _p(pos_ids), _p(k_ptrs),
+                                           _p(v_ptrs), n, eps), "oxi_project_append")
+
+    def linear(self, w: Linear, x, y, rows: int | None = None):
+        """y = x W^T (oxi_linear_forward)."""
+        n = x.shape[0] if rows is None else rows
+        _check(self.lib.oxi_linear_forward(self.h, _stream(), w.h, _p(x), _p(y), n), "oxi_linear_forward")
 
     def advance_step(self, pos_ids, seq_lens, delta: int = 1, batch: int | None = None):
         """pos_ids += delta, seq_lens += delta on the device (graph-capturable)."""

@@ -27,6 +27,15 @@ def test_header_symbols_are_exported(lib):
         assert hasattr(lib, n), n
 
 
+def test_rust_binding_in_the_integration_notes_names_every_export():
+    """The `extern "C"` block a maintainer copies declares exactly the header's functions."""
+    text = open(os.path.join(ROOT, "include", "oxi_kv.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = set(re.findall(r"\b(oxi_[a-z0-9_]+)\s*\(", text))
+    rust = set(re.findall(r"pub fn (oxi_[a-z0-9_]+)\s*\(", open(os.path.join(ROOT, "INTEGRATION.md")).read()))
+    assert rust == names, rust ^ names
+
+
 def test_version_and_status_strings(lib):
     assert lib.oxi_version() == 100
     assert lib.oxi_status_string(0) == b"ok"
