@@ -353,6 +353,7 @@ def run_ours(args, torch, rank, world, local_rank):
         torch.cuda.empty_cache()
         secondary["prefill"] = leg_prefill(args, torch, "ours")
         secondary["conv"] = leg_conv(args, torch, "ours")
+        secondary["project_append"] = leg_project_append(args, torch, "ours")
         secondary["sample"] = leg_sample(args, torch)
         torch.cuda.empty_cache()
     sampler.stop()
@@ -520,6 +521,7 @@ def run_reference(args, torch, rank, world, local_rank):
         torch.cuda.empty_cache()
         secondary["prefill"] = leg_prefill(args, torch, "reference")
         secondary["conv"] = leg_conv(args, torch, "reference")
+        secondary["project_append"] = leg_project_append(args, torch, "reference")
     sampler.stop()
     line = {
         "impl": "reference", "metric": "gqa_decode_step_hbm_gbs",
@@ -738,6 +740,74 @@ def leg_conv(args, torch, impl):
                 "note": "8.4 MB per launch: bound by launch and memory latency, not bandwidth",
                 "prefill_wave_one_layer": {"rows": rows, "us": round(ms_pf * 1e3, 2),
                                            "gbs": round(pf_bytes / (ms_pf * 1e-3) / 1e9, 1)}})
+    if impl == "ours":
+        out["device_status"] = kv.device_status()
+        kv.close()
+    return out
+
+
+def leg_project_append(args, torch, impl):
+    """The steps in front of the path fused into it: q/k/v/gate projections ([rows][2048] x [2048][3088]) with
+    RMSNorm + RoPE + KV append as the GEMM's epilogue, at the decode shape (128 rows) and at configuration 4's
+    wave (4,096 rows).  ours: oxi_project_append (one kernel).  reference: four library GEMMs (torch.matmul
+    standing in for the engine's cuBLASLt calls, batch_engine.rs:914-926) + its six append kernels."""
+    import numpy as np
+    from oxide_infer_b200 import rotary_tables
+    hid, nout = 2048, 3088
+    g = torch.Generator(device="cuda").manual_seed(8)
+    rn = lambda *s, sc=1.0: (torch.randn(*s, device="cuda", generator=g) * sc).half()
+    ws = [rn(o, hid, sc=hid ** -0.5) for o in (2048, 512, 512, 16)]
+    qw = (1 + 0.02 * torch.randn(HD, device="cuda", generator=g)).half()
+    kw = (1 + 0.02 * torch.randn(HD, device="cuda", generator=g)).half()
+    cos, sin = rotary_tables(4096 + 256, 1e6, 0.5)
+    cos, sin = torch.from_numpy(cos).cuda(), torch.from_numpy(sin).cuda()
+    peak_tf, kind = _tensor_peak()
+    peak_gbs, kind_g = measured_peak_gbs()
+    out = {"workload": "qkvg_projection_plus_append_rows128_and_rows4096"}
+    if impl == "ours":
+        from oxide_infer_b200 import KvPath, Linear
+        kv = KvPath(torch.cuda.current_device(), max_batch=128, max_seq_len=8192, max_prefill_rows=4096)
+        lin = Linear(*ws)
+    else:
+        from oracle import refptx
+        ref = refptx.RefPtx()
+    for rows, nseq in ((128, 128), (4096, 32)):
+        new = rows // nseq
+        cache_k = torch.zeros(nseq, 4096 + new, NKV, HD, dtype=torch.float16, device="cuda")
+        cache_v = torch.zeros_like(cache_k)
+        owner = np.repeat(np.arange(nseq), new)
+        pos = torch.from_numpy((4000 + np.tile(np.arange(new), nseq)).astype(np.int32)).cuda()
+        kp = torch.tensor([cache_k[i].data_ptr() for i in owner], dtype=torch.int64, device="cuda")
+        vp = torch.tensor([cache_v[i].data_ptr() for i in owner], dtype=torch.int64, device="cuda")
+        xs = [rn(rows, hid) for _ in range(4)]   # rotate inputs; the 12.6 MB of weights stay in L2, as in a real layer loop they do not
+        q_out = torch.zeros(rows, NQ, HD, dtype=torch.float16, device="cuda")
+        gate_out = torch.zeros(rows, NQ, dtype=torch.float16, device="cuda")
+        if impl == "ours":
+            def fn():
+                for x in xs:
+                    kv.project_append(lin, x, q_out, gate_out, qw, kw, cos, sin, pos, kp, vp, rows=rows)
+        else:
+            k_out = torch.zeros(rows, NKV, HD, dtype=torch.float16, device="cuda")
+            v_out = torch.zeros(rows, NKV, HD, dtype=torch.float16, device="cuda")
+
+            def fn():
+                for x in xs:
+                    torch.matmul(x, ws[0].t(), out=q_out.view(rows, 2048))
+                    torch.matmul(x, ws[1].t(), out=k_out.view(rows, 512))
+                    torch.matmul(x, ws[2].t(), out=v_out.view(rows, 512))
+                    torch.matmul(x, ws[3].t(), out=gate_out)
+                    ref.append(q_out, k_out, v_out, qw, kw, cos, sin, pos, kp, vp, rows)
+        for _ in range(3):
+            fn()
+        graph = _graph_of(torch, fn)
+        ms = _time_loop(torch, graph.replay, max(args.steps, 20), 3) / len(xs)
+        flops = 2.0 * rows * hid * nout
+        byts = nout * hid * 2 + rows * (hid * 2 + 4096 + 2048 + 32)   # weights, x, q out, K/V rows, gate
+        out[f"rows{rows}"] = {"us": round(ms * 1e3, 2), "tflops": round(flops / (ms * 1e-3) / 1e12, 1),
+                              "frac_of_tensor_peak": round(flops / (ms * 1e-3) / 1e12 / peak_tf, 4),
+                              "gbs": round(byts / (ms * 1e-3) / 1e9, 1), "launches": 1 if impl == "ours" else 10}
+    out.update({"tensor_peak": peak_tf, "tensor_peak_kind": kind + " (sustained bf16 GEMM)", "launch": "cuda graph replay",
+                "bound": "rows128: weight read (12.6 MB) and latency; rows4096: tensor"})
     if impl == "ours":
         out["device_status"] = kv.device_status()
         kv.close()
@@ -1138,7 +1208,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=CTX)
     ap.add_argument("--ragged", action="store_true",
                     help="decode workload with context lengths uniform 1024..4096 (configuration 2's ragged variant)")
-    ap.add_argument("--workload", default="decode", choices=["decode", "conv", "prefill", "serving_mix", "sample", "decode_paged"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "conv", "prefill", "serving_mix", "sample", "decode_paged", "project"],
                     help="decode = the headline line; conv / prefill / sample = secondary single-GPU lines")
     args = ap.parse_args()
     globals().update(LAYERS=args.layers, BATCH=args.batch, CTX=args.ctx, RAGGED=args.ragged)
@@ -1163,6 +1233,8 @@ def main():
             line = leg_conv(args, torch, args.impl) if rank == 0 else None
         elif args.workload == "prefill":
             line = (run_prefill(args, torch) if args.impl == "ours" else leg_prefill(args, torch, "reference")) if rank == 0 else None
+        elif args.workload == "project":
+            line = leg_project_append(args, torch, args.impl) if rank == 0 else None
         elif args.workload == "sample":
             line = run_sample(args, torch) if rank == 0 else None
         elif args.workload == "decode_paged":

@@ -575,15 +575,15 @@ int32_t oxi_sigmoid_gate(oxi_handle* h, void* stream, void* ctx_io, const void* 
 
 // ---- linear layers on either side of the path (tensor maps over the caller's weights; host objects only)
 struct oxi_linear_s {
-    TmaDesc maps[4];        // qkvg: q, k, v, gate; plain: maps[0]
+    TmaDesc maps[8];        // qkvg: q, k, v, gate with 128-row boxes, then with 256-row boxes; plain: maps[0], maps[1]
     uint32_t out_features;  // plain: rows of the weight matrix; qkvg: 3088
     bool qkvg;
 };
 
-static int32_t linear_map(TmaDesc* m, const void* w, uint64_t rows, const char* who) {
+static int32_t linear_map(TmaDesc* m, const void* w, uint64_t rows, uint32_t box_rows, const char* who) {
     if (!w) return fail(OXI_ERR_NULL, who);
     if (((uintptr_t)w & 15u) != 0u) return fail(OXI_ERR_ARG, "weights must be 16-byte aligned");
-    const int rc = proj_encode_map(m, w, rows);
+    const int rc = proj_encode_map(m, w, rows, box_rows);
     if (rc == -1) return fail(OXI_ERR_NO_DEVICE, "driver has no cuTensorMapEncodeTiled");
     if (rc != 0) return fail(OXI_ERR_ARG, "cuTensorMapEncodeTiled rejected the weight matrix");
     return OXI_OK;
@@ -594,11 +594,16 @@ int32_t oxi_qkvg_create(oxi_linear** out, const void* wq, const void* wk, const 
     *out = nullptr;
     oxi_linear_s* l = new (std::nothrow) oxi_linear_s();
     if (!l) return fail(OXI_ERR_WORKSPACE, "oxi_qkvg_create: host allocation failed");
-    int32_t rc;
-    if ((rc = linear_map(&l->maps[0], wq, NQ * HD, "oxi_qkvg_create: q_proj is null")) ||
-        (rc = linear_map(&l->maps[1], wk, NKV * HD, "oxi_qkvg_create: k_proj is null")) ||
-        (rc = linear_map(&l->maps[2], wv, NKV * HD, "oxi_qkvg_create: v_proj is null")) ||
-        (rc = linear_map(&l->maps[3], wg, NQ, "oxi_qkvg_create: gate_proj is null"))) {
+    int32_t rc = OXI_OK;
+    for (int b = 0; b < 2 && rc == OXI_OK; b++) {
+        const uint32_t box = b ? 256u : 128u;
+        if ((rc = linear_map(&l->maps[4 * b + 0], wq, NQ * HD, box, "oxi_qkvg_create: q_proj is null")) ||
+            (rc = linear_map(&l->maps[4 * b + 1], wk, NKV * HD, box, "oxi_qkvg_create: k_proj is null")) ||
+            (rc = linear_map(&l->maps[4 * b + 2], wv, NKV * HD, box, "oxi_qkvg_create: v_proj is null")) ||
+            (rc = linear_map(&l->maps[4 * b + 3], wg, NQ, box, "oxi_qkvg_create: gate_proj is null")))
+            break;
+    }
+    if (rc != OXI_OK) {
         delete l;
         return rc;
     }
@@ -614,7 +619,9 @@ int32_t oxi_linear_create(oxi_linear** out, const void* w, uint32_t out_features
     if (out_features == 0 || out_features > (1u << 20)) return fail(OXI_ERR_ARG, "oxi_linear_create: out_features out of range");
     oxi_linear_s* l = new (std::nothrow) oxi_linear_s();
     if (!l) return fail(OXI_ERR_WORKSPACE, "oxi_linear_create: host allocation failed");
-    if (int32_t rc = linear_map(&l->maps[0], w, out_features, "oxi_linear_create: weights are null")) {
+    int32_t rc = linear_map(&l->maps[0], w, out_features, 128u, "oxi_linear_create: weights are null");
+    if (rc == OXI_OK) rc = linear_map(&l->maps[1], w, out_features, 256u, "oxi_linear_create: weights are null");
+    if (rc != OXI_OK) {
         delete l;
         return rc;
     }
@@ -643,7 +650,7 @@ int32_t oxi_project_append(oxi_handle* h, void* stream, const oxi_linear* qkvg, 
     if ((((uintptr_t)x | (uintptr_t)q_out | (uintptr_t)gate_out | (uintptr_t)raw_out | (uintptr_t)cos_table |
           (uintptr_t)sin_table) & 15u) != 0u)
         return fail(OXI_ERR_ARG, "oxi_project_append: x, q_out, gate_out, raw_out and the rope tables must be 16-byte aligned");
-    OXI_CUDA(launch_project_append((cudaStream_t)stream, l->maps, x, rows, q_out, gate_out, raw_out, q_norm_w, k_norm_w,
+    OXI_CUDA(launch_project_append((cudaStream_t)stream, l->maps, h->num_sms, x, rows, q_out, gate_out, raw_out, q_norm_w, k_norm_w,
                                    cos_table, sin_table, pos_ids, k_ptrs, v_ptrs, eps, h->dws.status),
              "project_append launch");
     return OXI_OK;
@@ -656,7 +663,7 @@ int32_t oxi_linear_forward(oxi_handle* h, void* stream, const oxi_linear* w, con
     if (l->qkvg) return fail(OXI_ERR_ARG, "oxi_linear_forward: the weights object was made by oxi_qkvg_create");
     if (rows == 0 || rows > (1u << 20)) return fail(OXI_ERR_BATCH, "oxi_linear_forward: rows out of range");
     if ((((uintptr_t)x | (uintptr_t)y) & 15u) != 0u) return fail(OXI_ERR_ARG, "oxi_linear_forward: x and y must be 16-byte aligned");
-    OXI_CUDA(launch_linear((cudaStream_t)stream, &l->maps[0], l->out_features, x, rows, y, h->dws.status), "linear launch");
+    OXI_CUDA(launch_linear((cudaStream_t)stream, l->maps, h->num_sms, l->out_features, x, rows, y, h->dws.status), "linear launch");
     return OXI_OK;
 }
 

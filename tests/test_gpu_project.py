@@ -60,7 +60,9 @@ def _project(kv, case, x, ws, raw=True):
     return d, q_out, gate_out, raw_out
 
 
-@pytest.mark.parametrize("lens", [[5], [300, 1, 64, 777, 31, 2047, 512], list(range(100, 228)), list(range(10, 310))])
+# up to 256 rows run the one-tile-per-CTA kernel, more rows the persistent 128 x 256 kernel
+@pytest.mark.parametrize("lens", [[5], [300, 1, 64, 777, 31, 2047, 512], list(range(100, 228)), list(range(10, 266)),
+                                  list(range(10, 267)), list(range(10, 310))])
 def test_project_append_equals_matmul_then_append(kv, ref, lens):
     b = len(lens)
     case = DecodeCase(lens, seed=80 + b)
@@ -178,7 +180,8 @@ def test_prefill_wave_shape_and_untouched_rows(kv):
         assert torch.equal(va[i].view(torch.int16), vc[i].view(torch.int16)), i
 
 
-@pytest.mark.parametrize("rows,out", [(1, 2048), (128, 2048), (300, 2048), (7, 16), (130, 520)])
+@pytest.mark.parametrize("rows,out", [(1, 2048), (128, 2048), (300, 2048), (7, 16), (130, 520), (300, 520), (513, 16),
+                                      (1000, 3088)])
 def test_linear_forward(kv, rows, out):
     from oxide_infer_b200 import Linear
     g = torch.Generator(device="cuda").manual_seed(rows + out)
