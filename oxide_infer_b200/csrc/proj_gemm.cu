@@ -17,6 +17,10 @@
 // shared-memory stages that complete on mbarriers.  Warp 0 issues the copies, warp 1 the MMAs (one
 // elected lane), warps 2-5 run the epilogue: thread = one row of the tile (its TMEM lane), so a
 // thread holds a whole head of its token and the per-head arithmetic needs no shuffles.
+// At the decode shape (128 rows: 25 CTAs) a launch takes ~15 us, of which the tile's 128 MMAs are ~5,
+// the epilogue ~4 and launch, set-up and the first copies' latency the rest; cutting K into four parts
+// that meet in an L2 workspace (100 CTAs) measured 16-18 us (the exchange costs what the shorter main
+// loop saves) and a ring twice as deep changed nothing, so neither is here.
 //
 // Bit parity.  The projections are rounded to f16 exactly as the reference's GEMM output is, and
 // the epilogue applies the append kernel's arithmetic to those f16 values: the RMSNorm sum is formed
@@ -379,7 +383,7 @@ proj_gemm_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p) {
 namespace pgw {
 constexpr int BM = 128, BN = 256, BK = 64, NS = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;  // 16 + 32 KB
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps: two per TMEM lane quarter, one per head of the tile
 constexpr size_t SMEM_BYTES = 1024 + (size_t)NS * STAGE_BYTES;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t IDESC_N256 = (1u << 4) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -413,12 +417,12 @@ proj_gemm_wave_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p,
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&bar_acc_full[b], 1);
-            mbar_init(&bar_acc_empty[b], 4);  // one arrival per epilogue warp
+            mbar_init(&bar_acc_empty[b], 8);  // one arrival per epilogue warp
         }
         s_abort = 0u;
         mbar_fence_init();
     }
-    if (kQkvg && tid >= 64) {
+    if (kQkvg && tid >= 64 && tid < 64 + HD) {
         const int i = tid - 64;
         s_w[i] = p.q_norm_w[i];
         s_w[HD + i] = p.k_norm_w[i];
@@ -496,8 +500,9 @@ proj_gemm_wave_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p,
         }
         if (!ok && lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
     } else {
-        // ===================== epilogue warps: thread = one row of the tile =====================
-        const uint32_t quarter = (uint32_t)warp_u & 3u;
+        // ===================== epilogue warps: thread = one row of the tile, warp pair = the tile's two heads =====================
+        const uint32_t quarter = (uint32_t)warp_u & 3u;          // TMEM lanes this warp may read
+        const uint32_t group = ((uint32_t)warp_u - 2u) >> 2;     // which 128 features of the tile
         bool ok = true;
         uint32_t i = 0;
         for (uint32_t t = blockIdx.x; t < total && ok; t += gridDim.x, i++) {
@@ -520,8 +525,7 @@ proj_gemm_wave_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p,
             } else {
                 two = (ct0 + 1u) * 128u < p.out_features;
             }
-            proj_epilogue_cols<kQkvg>(t_row, ct0, row, row < p.rows, p, s_w);
-            if (two) proj_epilogue_cols<kQkvg>(t_row + 128u, ct0 + 1u, row, row < p.rows, p, s_w);
+            if (group == 0u || two) proj_epilogue_cols<kQkvg>(t_row + group * 128u, ct0 + group, row, row < p.rows, p, s_w);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_acc_empty[buf]);
