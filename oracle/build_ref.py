@@ -11,7 +11,9 @@ reference arm execute on the GPU; they are TEST INFRASTRUCTURE, never part of
 the product library.
 
 Usage: python oracle/build_ref.py [--reference /path/to/reference]
-Exits 0 and prints "reference not present" when the checkout is absent.
+The checkout is found through --reference, else the environment variable OXIDE_INFER_REFERENCE,
+else a directory named "reference" beside this repository.  Exits 0 and prints "reference not
+present" when none of them holds the file.
 """
 from __future__ import annotations
 
@@ -38,8 +40,13 @@ WANTED = [
 ]
 
 
-def build(reference: str = "/root/reference", verbose: bool = True) -> int:
-    src = os.path.join(reference, REL)
+def default_reference() -> str:
+    """OXIDE_INFER_REFERENCE, else <parent of the repository>/reference."""
+    return os.environ.get("OXIDE_INFER_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(reference: str | None = None, verbose: bool = True) -> int:
+    src = os.path.join(reference or default_reference(), REL)
     if not os.path.exists(src):
         if verbose:
             print("reference not present; oracle/_ref left as is")
@@ -65,7 +72,7 @@ def build(reference: str = "/root/reference", verbose: bool = True) -> int:
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=None)
     a = ap.parse_args()
     build(a.reference)
     sys.exit(0)
