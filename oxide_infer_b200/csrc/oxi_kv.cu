@@ -26,20 +26,23 @@ struct oxi_handle {
     uint32_t pf_part_keys;    // keys per part of a split block; 0: off
     PrefillSlab pf_slab;      // registered by oxi_register_kv_slab; rows == 0: none
     WaitFault dbg_decode, dbg_prefill;  // armed by oxi_debug_arm_wait_fault for the next launch only
-    // staging for the host-buffer entry, one layer at a time, double buffered
-    void* stg_q[2];       // [max_batch][16][128]
-    void* stg_k[2];       // [max_batch][4][128]
-    void* stg_v[2];
-    void* stg_gate[2];    // [max_batch][16]
-    void* stg_ctx[2];     // [max_batch][16][128]
-    uint64_t* stg_kp[2];  // [max_batch]
-    uint64_t* stg_vp[2];
+    // staging for the host-buffer entry: one contiguous buffer per kind holding a group of up to STG_MAX layers
+    // (layer-major, compact for the call's batch), so that a group's inputs arrive with one copy per kind
+    static constexpr int STG_MAX = 16;
+    uint32_t stg_sets;    // layers per group: 16 for handles of up to 256 rows, else 8
+    char* stg_q;          // [stg_sets][max_batch][16][128] f16
+    char* stg_k;          // [stg_sets][max_batch][4][128]
+    char* stg_v;
+    char* stg_gate;       // [stg_sets][max_batch][16]
+    char* stg_ctx;        // [stg_sets][max_batch][16][128]
+    char* stg_kp;         // [stg_sets][max_batch] u64
+    char* stg_vp;
     uint32_t* stg_pos;    // [max_batch]
     uint32_t* stg_len;    // [max_batch]
-    // copy streams and events of the host-buffer entry: uploads of layer l+1 and the
-    // download of layer l-1 overlap the kernels of layer l
+    // copy streams and events of the host-buffer entry: the uploads of a group's later layers and the
+    // downloads of its earlier layers overlap the kernels
     cudaStream_t h2d, d2h;
-    cudaEvent_t ev_start, ev_up[2], ev_comp[2], ev_down[2];
+    cudaEvent_t ev_start, ev_up_first, ev_up_rest, ev_comp[STG_MAX], ev_down_last;
     size_t bytes;
 };
 
@@ -139,14 +142,16 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
         if ((rc = dev_alloc(h, &h->conv_stage, (size_t)max_prefill_rows * HIDDEN * CONV_S * 2))) goto bad;
         if ((rc = dev_alloc(h, (void**)&h->pf_order, ((size_t)max_prefill_rows / 32 + 1) * sizeof(uint32_t)))) goto bad;
     }
-    for (int i = 0; i < 2; i++) {
-        if ((rc = dev_alloc(h, &h->stg_q[i], (size_t)max_batch * NQ * HD * 2))) goto bad;
-        if ((rc = dev_alloc(h, &h->stg_k[i], (size_t)max_batch * NKV * HD * 2))) goto bad;
-        if ((rc = dev_alloc(h, &h->stg_v[i], (size_t)max_batch * NKV * HD * 2))) goto bad;
-        if ((rc = dev_alloc(h, &h->stg_gate[i], (size_t)max_batch * NQ * 2))) goto bad;
-        if ((rc = dev_alloc(h, &h->stg_ctx[i], (size_t)max_batch * NQ * HD * 2))) goto bad;
-        if ((rc = dev_alloc(h, (void**)&h->stg_kp[i], (size_t)max_batch * 8))) goto bad;
-        if ((rc = dev_alloc(h, (void**)&h->stg_vp[i], (size_t)max_batch * 8))) goto bad;
+    h->stg_sets = max_batch <= 256u ? 16u : 8u;
+    {
+        const size_t n = (size_t)h->stg_sets * max_batch;
+        if ((rc = dev_alloc(h, (void**)&h->stg_q, n * NQ * HD * 2))) goto bad;
+        if ((rc = dev_alloc(h, (void**)&h->stg_k, n * NKV * HD * 2))) goto bad;
+        if ((rc = dev_alloc(h, (void**)&h->stg_v, n * NKV * HD * 2))) goto bad;
+        if ((rc = dev_alloc(h, (void**)&h->stg_gate, n * NQ * 2))) goto bad;
+        if ((rc = dev_alloc(h, (void**)&h->stg_ctx, n * NQ * HD * 2))) goto bad;
+        if ((rc = dev_alloc(h, (void**)&h->stg_kp, n * 8))) goto bad;
+        if ((rc = dev_alloc(h, (void**)&h->stg_vp, n * 8))) goto bad;
     }
     if ((rc = dev_alloc(h, (void**)&h->stg_pos, (size_t)max_batch * 4))) goto bad;
     if ((rc = dev_alloc(h, (void**)&h->stg_len, (size_t)max_batch * 4))) goto bad;
@@ -154,11 +159,11 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
         cudaError_t e = cudaStreamCreateWithFlags(&h->h2d, cudaStreamNonBlocking);
         if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->d2h, cudaStreamNonBlocking);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_start, cudaEventDisableTiming);
-        for (int i = 0; i < 2 && e == cudaSuccess; i++) {
-            e = cudaEventCreateWithFlags(&h->ev_up[i], cudaEventDisableTiming);
-            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_comp[i], cudaEventDisableTiming);
-            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_down[i], cudaEventDisableTiming);
-        }
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_up_first, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_up_rest, cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_down_last, cudaEventDisableTiming);
+        for (int i = 0; i < oxi_handle::STG_MAX && e == cudaSuccess; i++)
+            e = cudaEventCreateWithFlags(&h->ev_comp[i], cudaEventDisableTiming);
         if (e != cudaSuccess) { rc = cuda_fail(e, "stream/event creation"); goto bad; }
     }
     if (cudaMemset(h->dws.status, 0, 256) != cudaSuccess) {
@@ -202,21 +207,18 @@ int32_t oxi_destroy(oxi_handle* h) {
     cudaFree(h->am_count);
     cudaFree(h->pf_split.units);
     cudaFree(h->pf_split.part);
-    for (int i = 0; i < 2; i++) {
-        cudaFree(h->stg_q[i]); cudaFree(h->stg_k[i]); cudaFree(h->stg_v[i]);
-        cudaFree(h->stg_gate[i]); cudaFree(h->stg_ctx[i]);
-        cudaFree(h->stg_kp[i]); cudaFree(h->stg_vp[i]);
-    }
+    cudaFree(h->stg_q); cudaFree(h->stg_k); cudaFree(h->stg_v); cudaFree(h->stg_gate);
+    cudaFree(h->stg_ctx); cudaFree(h->stg_kp); cudaFree(h->stg_vp);
     cudaFree(h->stg_pos);
     cudaFree(h->stg_len);
     if (h->h2d) cudaStreamDestroy(h->h2d);
     if (h->d2h) cudaStreamDestroy(h->d2h);
     if (h->ev_start) cudaEventDestroy(h->ev_start);
-    for (int i = 0; i < 2; i++) {
-        if (h->ev_up[i]) cudaEventDestroy(h->ev_up[i]);
+    if (h->ev_up_first) cudaEventDestroy(h->ev_up_first);
+    if (h->ev_up_rest) cudaEventDestroy(h->ev_up_rest);
+    if (h->ev_down_last) cudaEventDestroy(h->ev_down_last);
+    for (int i = 0; i < oxi_handle::STG_MAX; i++)
         if (h->ev_comp[i]) cudaEventDestroy(h->ev_comp[i]);
-        if (h->ev_down[i]) cudaEventDestroy(h->ev_down[i]);
-    }
     cudaGetLastError();
     delete h;
     return OXI_OK;
@@ -694,36 +696,58 @@ int32_t oxi_decode_step_host(oxi_handle* h, void* stream, void* ctx_host, const 
     // re-reads pos_ids_host (pinned) at every replay.
     OXI_CUDA(cudaMemcpyAsync(h->stg_pos, pos_ids_host, (size_t)batch * 4, H2D, h->h2d), "pos upload");
     OXI_CUDA(launch_len_from_pos(h->h2d, h->stg_pos, h->stg_len, batch), "len_from_pos launch");
-    for (uint32_t l = 0; l < layers; l++) {
-        const int sb = l & 1;
-        // uploads of layer l reuse the staging set of layer l-2: wait until its kernels are done
-        if (l >= 2) OXI_CUDA(cudaStreamWaitEvent(h->h2d, h->ev_comp[sb], 0), "stream wait");
-        OXI_CUDA(cudaMemcpyAsync(h->stg_q[sb], (const char*)q_host + l * qb, qb, H2D, h->h2d), "q upload");
-        OXI_CUDA(cudaMemcpyAsync(h->stg_k[sb], (const char*)k_host + l * kb, kb, H2D, h->h2d), "k upload");
-        OXI_CUDA(cudaMemcpyAsync(h->stg_v[sb], (const char*)v_host + l * kb, kb, H2D, h->h2d), "v upload");
-        if (gate_host)
-            OXI_CUDA(cudaMemcpyAsync(h->stg_gate[sb], (const char*)gate_host + l * gb, gb, H2D, h->h2d), "gate upload");
-        OXI_CUDA(cudaMemcpyAsync(h->stg_kp[sb], k_ptrs_host + (size_t)l * batch, tb, H2D, h->h2d), "k_ptrs upload");
-        OXI_CUDA(cudaMemcpyAsync(h->stg_vp[sb], v_ptrs_host + (size_t)l * batch, tb, H2D, h->h2d), "v_ptrs upload");
-        OXI_CUDA(cudaEventRecord(h->ev_up[sb], h->h2d), "event record");
-        OXI_CUDA(cudaStreamWaitEvent(s, h->ev_up[sb], 0), "stream wait");
-        // the ctx staging buffer of layer l-2 must have been downloaded
-        if (l >= 2) OXI_CUDA(cudaStreamWaitEvent(s, h->ev_down[sb], 0), "stream wait");
-        OXI_CUDA(launch_append_decode(s, take_dws(h), h->stg_ctx[sb], h->stg_q[sb], h->stg_k[sb], h->stg_v[sb],
-                                      gate_host ? h->stg_gate[sb] : nullptr,
-                                      (const char*)q_norm_w_dev + (size_t)l * HD * 2,
-                                      (const char*)k_norm_w_dev + (size_t)l * HD * 2, cos_table_dev,
-                                      sin_table_dev, h->stg_len, h->stg_kp[sb], h->stg_vp[sb], batch, window, eps),
-                 "append_decode launch");
-        OXI_CUDA(cudaEventRecord(h->ev_comp[sb], s), "event record");
-        OXI_CUDA(cudaStreamWaitEvent(h->d2h, h->ev_comp[sb], 0), "stream wait");
-        OXI_CUDA(cudaMemcpyAsync((char*)ctx_host + l * qb, h->stg_ctx[sb], qb, cudaMemcpyDeviceToHost, h->d2h),
-                 "ctx download");
-        OXI_CUDA(cudaEventRecord(h->ev_down[sb], h->d2h), "event record");
+    // Layers are processed in groups of up to stg_sets layers staged side by side.  A group's first layer is
+    // uploaded on its own (six small copies) so that its kernels start at once; the inputs of all the other layers
+    // of the group follow as ONE copy per kind (the caller's arrays are layer-major, the staging is compact for
+    // this batch) and arrive while the first layer computes.  The caller's stream therefore waits twice per group
+    // only; between the other layers nothing sits in the stream, so each layer's kernels keep their programmatic
+    // overlap with the previous layer's (a wait between two launches takes it away).  Contexts go back layer by
+    // layer on the download stream.
+    const uint32_t G = h->stg_sets;
+    for (uint32_t g0 = 0; g0 < layers; g0 += G) {
+        const uint32_t g1 = (g0 + G < layers) ? g0 + G : layers, rest = g1 - g0 - 1u;
+        if (g0 > 0) {
+            // the staging is reused: the previous group's kernels and downloads must be done
+            OXI_CUDA(cudaStreamWaitEvent(h->h2d, h->ev_comp[G - 1u], 0), "stream wait");
+            OXI_CUDA(cudaStreamWaitEvent(s, h->ev_down_last, 0), "stream wait");
+        }
+        auto upload = [&](uint32_t l0, uint32_t n) -> cudaError_t {  // layers l0 .. l0 + n - 1 into slots l0 - g0 ...
+            const size_t slot = l0 - g0;
+            cudaError_t e = cudaMemcpyAsync(h->stg_q + slot * qb, (const char*)q_host + (size_t)l0 * qb, n * qb, H2D, h->h2d);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(h->stg_k + slot * kb, (const char*)k_host + (size_t)l0 * kb, n * kb, H2D, h->h2d);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(h->stg_v + slot * kb, (const char*)v_host + (size_t)l0 * kb, n * kb, H2D, h->h2d);
+            if (e == cudaSuccess && gate_host)
+                e = cudaMemcpyAsync(h->stg_gate + slot * gb, (const char*)gate_host + (size_t)l0 * gb, n * gb, H2D, h->h2d);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(h->stg_kp + slot * tb, k_ptrs_host + (size_t)l0 * batch, n * tb, H2D, h->h2d);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(h->stg_vp + slot * tb, v_ptrs_host + (size_t)l0 * batch, n * tb, H2D, h->h2d);
+            return e;
+        };
+        OXI_CUDA(upload(g0, 1u), "upload of a group's first layer");
+        OXI_CUDA(cudaEventRecord(h->ev_up_first, h->h2d), "event record");
+        if (rest) {
+            OXI_CUDA(upload(g0 + 1u, rest), "upload of a group's other layers");
+            OXI_CUDA(cudaEventRecord(h->ev_up_rest, h->h2d), "event record");
+        }
+        for (uint32_t l = g0; l < g1; l++) {
+            const size_t slot = l - g0;
+            if (l == g0) OXI_CUDA(cudaStreamWaitEvent(s, h->ev_up_first, 0), "stream wait");
+            else if (l == g0 + 1u) OXI_CUDA(cudaStreamWaitEvent(s, h->ev_up_rest, 0), "stream wait");
+            OXI_CUDA(launch_append_decode(s, take_dws(h), h->stg_ctx + slot * qb, h->stg_q + slot * qb, h->stg_k + slot * kb,
+                                          h->stg_v + slot * kb, gate_host ? h->stg_gate + slot * gb : nullptr,
+                                          (const char*)q_norm_w_dev + (size_t)l * HD * 2,
+                                          (const char*)k_norm_w_dev + (size_t)l * HD * 2, cos_table_dev, sin_table_dev,
+                                          h->stg_len, (const uint64_t*)(h->stg_kp + slot * tb),
+                                          (const uint64_t*)(h->stg_vp + slot * tb), batch, window, eps),
+                     "append_decode launch");
+            OXI_CUDA(cudaEventRecord(h->ev_comp[slot], s), "event record");
+            OXI_CUDA(cudaStreamWaitEvent(h->d2h, h->ev_comp[slot], 0), "stream wait");
+            OXI_CUDA(cudaMemcpyAsync((char*)ctx_host + (size_t)l * qb, h->stg_ctx + slot * qb, qb, cudaMemcpyDeviceToHost, h->d2h),
+                     "ctx download");
+        }
+        OXI_CUDA(cudaEventRecord(h->ev_down_last, h->d2h), "event record");
     }
-    // the caller's stream completes only after the last downloads
-    OXI_CUDA(cudaStreamWaitEvent(s, h->ev_down[(layers - 1) & 1], 0), "stream wait");
-    if (layers >= 2) OXI_CUDA(cudaStreamWaitEvent(s, h->ev_down[layers & 1], 0), "stream wait");
+    // the caller's stream completes only after the last download (the download stream is in order)
+    OXI_CUDA(cudaStreamWaitEvent(s, h->ev_down_last, 0), "stream wait");
     return OXI_OK;
 }
 

@@ -125,3 +125,35 @@ def test_device_tables_advance_eagerly_between_steps(kv):
     for s in range(STEPS):
         assert torch.equal(ctxs[s].cpu().view(torch.int16), want[s].view(torch.int16)), s
     _same_caches(de, dg)
+
+
+def test_host_buffer_step_with_more_layers_than_staging_sets(kv):
+    """Nineteen layers: the host-buffer entry stages a group of sixteen layers at a time (eight on handles of more than
+    256 rows), so layers 16-18 reuse the staging of layers 0-2 (their uploads wait for the first group's kernels, their
+    kernels for its downloads).  Two steps back to back."""
+    layers, b = 19, len(LENS)
+    cases = [DecodeCase(LENS, seed=200 + l, spare_rows=3, max_pos=max(LENS) + 4) for l in range(layers)]
+    dev = [c.device() for c in cases]
+    hst = [c.device() for c in cases]
+    want = []
+    for s in range(2):
+        pos, sl = u32(cases[0].lens + s), u32(cases[0].lens + s + 1)
+        for d in dev:
+            kv.append_decode(d.ctx, d.q, d.k, d.v, d.gate, d.q_norm_w, d.k_norm_w, d.cos, d.sin, pos, sl, d.k_ptrs, d.v_ptrs, 0)
+        torch.cuda.synchronize()
+        want.append(torch.stack([d.ctx for d in dev]).cpu())
+    pin = lambda t: t.cpu().pin_memory()
+    stack = lambda name: pin(torch.stack([getattr(d, name) for d in hst]))
+    hq, hk, hv, hg, hkp, hvp = stack("q"), stack("k"), stack("v"), stack("gate"), stack("k_ptrs"), stack("v_ptrs")
+    qw = torch.stack([d.q_norm_w for d in hst]).contiguous()
+    kw = torch.stack([d.k_norm_w for d in hst]).contiguous()
+    hpos = torch.from_numpy(np.stack([(cases[0].lens + s).astype(np.uint32).view(np.int32) for s in range(2)])).pin_memory()
+    hctx = torch.zeros(2, layers, b, NQ, HD, dtype=torch.float16).pin_memory()
+    for s in range(2):
+        kv.decode_step_host(hctx[s], hq, hk, hv, hg, qw, kw, hst[0].cos, hst[0].sin, hpos[s], hkp, hvp, b, layers)
+    torch.cuda.synchronize()
+    for s in range(2):
+        assert torch.equal(hctx[s].view(torch.int16), want[s].view(torch.int16)), s
+    for l in range(layers):
+        for i in range(b):
+            assert torch.equal(hst[l].k_cache[i].view(torch.int16), dev[l].k_cache[i].view(torch.int16)), (l, i)
