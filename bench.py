@@ -329,6 +329,20 @@ def run_ours(args, torch, rank, world, local_rank):
     def step_host():
         kv.decode_step_host(hctx, hq, hk, hv, hg, w.qw, w.kw, w.cos, w.sin, hpos, hkp, hvp, BATCH, LAYERS)
 
+    # host-to-device bandwidth of this box (pinned memory), for context: boxes of one pool differ by more than 2x
+    pcie_src = torch.empty(64 << 20, dtype=torch.uint8).pin_memory()
+    pcie_dst = torch.empty(64 << 20, dtype=torch.uint8, device="cuda")
+    pcie_dst.copy_(pcie_src, non_blocking=True)
+    torch.cuda.synchronize()
+    pe0, pe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    pe0.record()
+    for _ in range(4):
+        pcie_dst.copy_(pcie_src, non_blocking=True)
+    pe1.record()
+    torch.cuda.synchronize()
+    h2d_gbs = 4 * (64 << 20) / (pe0.elapsed_time(pe1) * 1e-3) / 1e9
+    del pcie_src, pcie_dst
+
     for _ in range(max(3, args.warmup)):
         step_host()
     ms_e2e = _timed_region(torch, step_host, args.steps, barrier)
@@ -363,6 +377,8 @@ def run_ours(args, torch, rank, world, local_rank):
         # measured 7 % slower (0.66 instead of 0.71 of the tensor peak)
         secondary["prefill"] = leg_prefill(args, torch, "ours")
         secondary["project_append"] = leg_project_append(args, torch, "ours")
+        secondary["layer_step"] = leg_layer_step(args, torch, "ours")
+        torch.cuda.empty_cache()
         secondary["decode_small"] = leg_decode_small(args, torch, "ours")
         secondary["conv"] = leg_conv(args, torch, "ours")
         secondary["sample"] = leg_sample(args, torch)
@@ -407,7 +423,7 @@ def run_ours(args, torch, rank, world, local_rank):
                   "parallelism": f"replicas x{world}, sequences partitioned, no collective"},
         "e2e": {"value": round(step_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
                 "ms_per_step": round(ms_e2e / args.steps, 4), "h2d_bytes_per_step": int(h2d),
-                "d2h_bytes_per_step": int(d2h), "launch": e2e_mode,
+                "d2h_bytes_per_step": int(d2h), "launch": e2e_mode, "h2d_gbs_of_this_box": round(h2d_gbs, 1),
                 "stream_launch_ms_per_step": round(ms_e2e_stream / args.steps, 4),
                 "cuda_graph_replay_ms_per_step": round(ms_e2e_graph / args.steps, 4) if ms_e2e_graph != float("inf") else None},
         "gpu_launches": 2 * LAYERS * args.steps,  # fused append+decode_attn, decode_merge per layer
@@ -532,6 +548,8 @@ def run_reference(args, torch, rank, world, local_rank):
         torch.cuda.empty_cache()
         secondary["prefill"] = leg_prefill(args, torch, "reference")
         secondary["project_append"] = leg_project_append(args, torch, "reference")
+        secondary["layer_step"] = leg_layer_step(args, torch, "reference")
+        torch.cuda.empty_cache()
         secondary["decode_small"] = leg_decode_small(args, torch, "reference")
         secondary["conv"] = leg_conv(args, torch, "reference")
         torch.cuda.empty_cache()
@@ -861,6 +879,58 @@ def leg_project_append(args, torch, impl):
                               "gbs": round(byts / (ms * 1e-3) / 1e9, 1), "launches": 1 if impl == "ours" else 10}
     out.update({"tensor_peak": peak_tf, "tensor_peak_kind": kind + " (sustained bf16 GEMM)", "launch": "cuda graph replay",
                 "bound": "rows128: weight read (12.6 MB) and latency; rows4096: tensor"})
+    if impl == "ours":
+        out["device_status"] = kv.device_status()
+        kv.close()
+    return out
+
+
+def leg_layer_step(args, torch, impl):
+    """An attention layer of a decode step from the normed hidden state to the context, 8 layers, batch 128, 4096 keys:
+    ours = oxi_project_append + oxi_decode_attn (3 launches per layer); reference = four library GEMMs (torch.matmul for the
+    engine's cuBLASLt calls) + its nine kernels (13 launches per layer).  CUDA-graph replay in both arms."""
+    layers, batch, ctx_len, hid = 8, 128, 4096, 2048
+    w = build_workload_shape(torch, ctx_len, batch, layers, seed=99)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    rn = lambda *s, sc=1.0: (torch.randn(*s, device="cuda", generator=g) * sc).half()
+    ws = [[rn(o, hid, sc=hid ** -0.5) for o in (2048, 512, 512, 16)] for _ in range(layers)]
+    x = rn(layers, batch, hid)
+    q_out = torch.zeros(batch, NQ, HD, dtype=torch.float16, device="cuda")
+    gate_out = torch.zeros(batch, NQ, dtype=torch.float16, device="cuda")
+    if impl == "ours":
+        from oxide_infer_b200 import KvPath, Linear
+        kv = KvPath(torch.cuda.current_device(), max_batch=batch, max_seq_len=ctx_len, max_prefill_rows=0)
+        lins = [Linear(*ws[l]) for l in range(layers)]
+
+        def step():
+            for l in range(layers):
+                kv.project_append(lins[l], x[l], q_out, gate_out, w.qw[l], w.kw[l], w.cos, w.sin, w.pos, w.k_ptrs[l], w.v_ptrs[l])
+                kv.decode_attn(w.ctx[l], q_out, gate_out, w.k_ptrs[l], w.v_ptrs[l], w.lens)
+        launches = 3
+    else:
+        from oracle import refptx
+        ref = refptx.RefPtx()
+        nch = ref.nchunks_for(ctx_len, 0)
+        acc = torch.empty(batch * nch * NQ * HD, dtype=torch.float32, device="cuda")
+        stats = torch.empty(batch * nch * NQ * 2, dtype=torch.float32, device="cuda")
+        k_out = torch.zeros(batch, NKV, HD, dtype=torch.float16, device="cuda")
+        v_out = torch.zeros(batch, NKV, HD, dtype=torch.float16, device="cuda")
+
+        def step():
+            for l in range(layers):
+                torch.matmul(x[l], ws[l][0].t(), out=q_out.view(batch, 2048))
+                torch.matmul(x[l], ws[l][1].t(), out=k_out.view(batch, 512))
+                torch.matmul(x[l], ws[l][2].t(), out=v_out.view(batch, 512))
+                torch.matmul(x[l], ws[l][3].t(), out=gate_out)
+                ref.append(q_out, k_out, v_out, w.qw[l], w.kw[l], w.cos, w.sin, w.pos, w.k_ptrs[l], w.v_ptrs[l], batch)
+                ref.decode_attention(w.ctx[l], q_out, gate_out, w.k_ptrs[l], w.v_ptrs[l], w.lens, batch, 0, ctx_len, acc, stats)
+        launches = 13
+    for _ in range(3):
+        step()
+    graph = _graph_of(torch, step)
+    ms = _time_loop(torch, graph.replay, args.steps, 3)
+    out = {"workload": "projection_append_attention_8_layers_B128_ctx4096", "ms_per_step": round(ms, 4),
+           "us_per_layer": round(ms / layers * 1e3, 2), "launches_per_layer": launches, "launch": "cuda graph replay"}
     if impl == "ours":
         out["device_status"] = kv.device_status()
         kv.close()

@@ -42,7 +42,7 @@ struct oxi_handle {
     // copy streams and events of the host-buffer entry: the uploads of a group's later layers and the
     // downloads of its earlier layers overlap the kernels
     cudaStream_t h2d, d2h;
-    cudaEvent_t ev_start, ev_up_first, ev_up_rest, ev_comp[STG_MAX], ev_down_last;
+    cudaEvent_t ev_start, ev_up[6], ev_comp[STG_MAX], ev_down_last;  // ev_up: one per upload chunk of a group
     size_t bytes;
 };
 
@@ -159,8 +159,7 @@ int32_t oxi_create(oxi_handle** out, int32_t device, uint32_t max_batch, uint32_
         cudaError_t e = cudaStreamCreateWithFlags(&h->h2d, cudaStreamNonBlocking);
         if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&h->d2h, cudaStreamNonBlocking);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_start, cudaEventDisableTiming);
-        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_up_first, cudaEventDisableTiming);
-        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_up_rest, cudaEventDisableTiming);
+        for (int i = 0; i < 6 && e == cudaSuccess; i++) e = cudaEventCreateWithFlags(&h->ev_up[i], cudaEventDisableTiming);
         if (e == cudaSuccess) e = cudaEventCreateWithFlags(&h->ev_down_last, cudaEventDisableTiming);
         for (int i = 0; i < oxi_handle::STG_MAX && e == cudaSuccess; i++)
             e = cudaEventCreateWithFlags(&h->ev_comp[i], cudaEventDisableTiming);
@@ -214,8 +213,8 @@ int32_t oxi_destroy(oxi_handle* h) {
     if (h->h2d) cudaStreamDestroy(h->h2d);
     if (h->d2h) cudaStreamDestroy(h->d2h);
     if (h->ev_start) cudaEventDestroy(h->ev_start);
-    if (h->ev_up_first) cudaEventDestroy(h->ev_up_first);
-    if (h->ev_up_rest) cudaEventDestroy(h->ev_up_rest);
+    for (int i = 0; i < 6; i++)
+        if (h->ev_up[i]) cudaEventDestroy(h->ev_up[i]);
     if (h->ev_down_last) cudaEventDestroy(h->ev_down_last);
     for (int i = 0; i < oxi_handle::STG_MAX; i++)
         if (h->ev_comp[i]) cudaEventDestroy(h->ev_comp[i]);
@@ -696,42 +695,47 @@ int32_t oxi_decode_step_host(oxi_handle* h, void* stream, void* ctx_host, const 
     // re-reads pos_ids_host (pinned) at every replay.
     OXI_CUDA(cudaMemcpyAsync(h->stg_pos, pos_ids_host, (size_t)batch * 4, H2D, h->h2d), "pos upload");
     OXI_CUDA(launch_len_from_pos(h->h2d, h->stg_pos, h->stg_len, batch), "len_from_pos launch");
-    // Layers are processed in groups of up to stg_sets layers staged side by side.  A group's first layer is
-    // uploaded on its own (six small copies) so that its kernels start at once; the inputs of all the other layers
-    // of the group follow as ONE copy per kind (the caller's arrays are layer-major, the staging is compact for
-    // this batch) and arrive while the first layer computes.  The caller's stream therefore waits twice per group
-    // only; between the other layers nothing sits in the stream, so each layer's kernels keep their programmatic
-    // overlap with the previous layer's (a wait between two launches takes it away).  Contexts go back layer by
-    // layer on the download stream.
+    // Layers are processed in groups of up to stg_sets layers staged side by side.  Inside a group the inputs go
+    // up in chunks of 1, 1, 2, 4, 8 layers, each chunk with ONE copy per kind (the caller's arrays are layer-major,
+    // the staging is compact for this batch), and the caller's stream waits once per chunk, in front of the chunk's
+    // first layer.  A chunk has the compute time of all the layers before it to arrive (as long as a layer's
+    // kernels take, a chunk of as many layers needs no more than ~5 GB/s of host-to-device bandwidth at the
+    // benchmark shape), the first layer's kernels start after six small copies, and between the layers of a chunk
+    // nothing sits in the stream, so they keep their programmatic overlap with the layer before (a wait between two
+    // launches takes it away; with a wait in front of every layer the step measured 1.341 ms instead of 1.31).
+    // Contexts go back layer by layer on the download stream.
     const uint32_t G = h->stg_sets;
     for (uint32_t g0 = 0; g0 < layers; g0 += G) {
-        const uint32_t g1 = (g0 + G < layers) ? g0 + G : layers, rest = g1 - g0 - 1u;
+        const uint32_t g1 = (g0 + G < layers) ? g0 + G : layers, gn = g1 - g0;
         if (g0 > 0) {
             // the staging is reused: the previous group's kernels and downloads must be done
             OXI_CUDA(cudaStreamWaitEvent(h->h2d, h->ev_comp[G - 1u], 0), "stream wait");
             OXI_CUDA(cudaStreamWaitEvent(s, h->ev_down_last, 0), "stream wait");
         }
-        auto upload = [&](uint32_t l0, uint32_t n) -> cudaError_t {  // layers l0 .. l0 + n - 1 into slots l0 - g0 ...
-            const size_t slot = l0 - g0;
-            cudaError_t e = cudaMemcpyAsync(h->stg_q + slot * qb, (const char*)q_host + (size_t)l0 * qb, n * qb, H2D, h->h2d);
-            if (e == cudaSuccess) e = cudaMemcpyAsync(h->stg_k + slot * kb, (const char*)k_host + (size_t)l0 * kb, n * kb, H2D, h->h2d);
-            if (e == cudaSuccess) e = cudaMemcpyAsync(h->stg_v + slot * kb, (const char*)v_host + (size_t)l0 * kb, n * kb, H2D, h->h2d);
+        auto upload = [&](uint32_t slot, uint32_t n) -> cudaError_t {  // n layers from slot `slot` of the group
+            const size_t l0 = (size_t)g0 + slot;
+            cudaError_t e = cudaMemcpyAsync(h->stg_q + slot * qb, (const char*)q_host + l0 * qb, n * qb, H2D, h->h2d);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(h->stg_k + slot * kb, (const char*)k_host + l0 * kb, n * kb, H2D, h->h2d);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(h->stg_v + slot * kb, (const char*)v_host + l0 * kb, n * kb, H2D, h->h2d);
             if (e == cudaSuccess && gate_host)
-                e = cudaMemcpyAsync(h->stg_gate + slot * gb, (const char*)gate_host + (size_t)l0 * gb, n * gb, H2D, h->h2d);
-            if (e == cudaSuccess) e = cudaMemcpyAsync(h->stg_kp + slot * tb, k_ptrs_host + (size_t)l0 * batch, n * tb, H2D, h->h2d);
-            if (e == cudaSuccess) e = cudaMemcpyAsync(h->stg_vp + slot * tb, v_ptrs_host + (size_t)l0 * batch, n * tb, H2D, h->h2d);
+                e = cudaMemcpyAsync(h->stg_gate + slot * gb, (const char*)gate_host + l0 * gb, n * gb, H2D, h->h2d);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(h->stg_kp + slot * tb, k_ptrs_host + l0 * batch, n * tb, H2D, h->h2d);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(h->stg_vp + slot * tb, v_ptrs_host + l0 * batch, n * tb, H2D, h->h2d);
             return e;
         };
-        OXI_CUDA(upload(g0, 1u), "upload of a group's first layer");
-        OXI_CUDA(cudaEventRecord(h->ev_up_first, h->h2d), "event record");
-        if (rest) {
-            OXI_CUDA(upload(g0 + 1u, rest), "upload of a group's other layers");
-            OXI_CUDA(cudaEventRecord(h->ev_up_rest, h->h2d), "event record");
+        // chunk c covers slots [start(c), start(c + 1)) with start = 0, 1, 2, 4, 8, 16
+        for (uint32_t c0 = 0, c = 0; c0 < gn; c++) {
+            const uint32_t c1 = (c0 == 0u) ? 1u : (2u * c0 < gn ? 2u * c0 : gn);
+            OXI_CUDA(upload(c0, c1 - c0), "input upload");
+            OXI_CUDA(cudaEventRecord(h->ev_up[c], h->h2d), "event record");
+            c0 = c1;
         }
-        for (uint32_t l = g0; l < g1; l++) {
-            const size_t slot = l - g0;
-            if (l == g0) OXI_CUDA(cudaStreamWaitEvent(s, h->ev_up_first, 0), "stream wait");
-            else if (l == g0 + 1u) OXI_CUDA(cudaStreamWaitEvent(s, h->ev_up_rest, 0), "stream wait");
+        for (uint32_t slot = 0, c = 0; slot < gn; slot++) {
+            const uint32_t l = g0 + slot;
+            if (slot == 0u || (slot & (slot - 1u)) == 0u) {  // slots 0, 1, 2, 4, 8: a chunk starts here
+                OXI_CUDA(cudaStreamWaitEvent(s, h->ev_up[c], 0), "stream wait");
+                c++;
+            }
             OXI_CUDA(launch_append_decode(s, take_dws(h), h->stg_ctx + slot * qb, h->stg_q + slot * qb, h->stg_k + slot * kb,
                                           h->stg_v + slot * kb, gate_host ? h->stg_gate + slot * gb : nullptr,
                                           (const char*)q_norm_w_dev + (size_t)l * HD * 2,

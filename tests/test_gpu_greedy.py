@@ -41,9 +41,10 @@ def _initial_caches(lens, seed, layers):
     return [[(mk(int(n)), mk(int(n))) for n in lens] for _ in range(layers)]
 
 
-def _run(layer_fn, w, lens, caches, tok0, embed_fn, argmax_fn, layers):
+def _run(layer_fn, w, lens, caches, tok0, embed_fn, argmax_fn, layers, fused_fn=None):
     """layer_fn(l, q, k, v, gate, pos, seq_lens, k_ptrs, v_ptrs, cache) -> ctx [B,16,128] (may modify q in place);
-    embed_fn(table, tok int32 [B]) -> x [B,HID] f16; argmax_fn(logits f16 [B,VOCAB]) -> tok int32 [B]."""
+    embed_fn(table, tok int32 [B]) -> x [B,HID] f16; argmax_fn(logits f16 [B,VOCAB]) -> tok int32 [B].
+    fused_fn(l, x, pos, seq_lens, k_ptrs, v_ptrs) -> ctx replaces the four projection matmuls and layer_fn."""
     nseq = len(lens)
     caches = [[(k.clone(), v.clone()) for k, v in layer] for layer in caches]
     kp = [dev_ptr_table([k for k, _ in layer]) for layer in caches]
@@ -55,11 +56,14 @@ def _run(layer_fn, w, lens, caches, tok0, embed_fn, argmax_fn, layers):
         sl = pos + 1
         x = embed_fn(w["E"], tok)
         for l in range(layers):
-            q = (x @ w[f"q{l}"]).view(nseq, NQ, HD).contiguous()
-            k = (x @ w[f"k{l}"]).view(nseq, NKV, HD).contiguous()
-            v = (x @ w[f"v{l}"]).view(nseq, NKV, HD).contiguous()
-            gate = (x @ w[f"g{l}"]).contiguous()
-            ctx = layer_fn(l, q, k, v, gate, pos, sl, kp[l], vp[l], caches[l])
+            if fused_fn is not None:
+                ctx = fused_fn(l, x.contiguous(), pos, sl, kp[l], vp[l])
+            else:
+                q = (x @ w[f"q{l}"]).view(nseq, NQ, HD).contiguous()
+                k = (x @ w[f"k{l}"]).view(nseq, NKV, HD).contiguous()
+                v = (x @ w[f"v{l}"]).view(nseq, NKV, HD).contiguous()
+                gate = (x @ w[f"g{l}"]).contiguous()
+                ctx = layer_fn(l, q, k, v, gate, pos, sl, kp[l], vp[l], caches[l])
             x = x + ctx.view(nseq, NQ * HD) @ w[f"o{l}"]
         logits16 = (x @ w["out"]).contiguous()
         tok = argmax_fn(logits16)
@@ -164,6 +168,24 @@ def _greedy_case(lens, layers, seed, max_seq_len, oracle_rows, tok0=None, cache_
     assert np.array_equal(t_paged, t_ours)
     del pools, lays
     torch.cuda.empty_cache()
+
+    # the same loop with the four projections and the append fused into one kernel per layer (oxi_project_append,
+    # then oxi_decode_attn): the projections differ from the library matmuls of the glue by summation order only
+    from oxide_infer_b200 import Linear
+    lins = [Linear(*(w[f"{n}{l}"].t().contiguous() for n in "qkvg")) for l in range(layers)]
+
+    def fused(l, x, pos, sl, kp, vp):
+        q_out = torch.empty(nseq, NQ, HD, dtype=torch.float16, device="cuda")
+        gate_out = torch.empty(nseq, NQ, dtype=torch.float16, device="cuda")
+        ctx = torch.empty(nseq, NQ, HD, dtype=torch.float16, device="cuda")
+        kv.project_append(lins[l], x, q_out, gate_out, w[f"qn{l}"], w[f"kn{l}"], cos, sin, pos, kp, vp)
+        kv.decode_attn(ctx, q_out, gate_out, kp, vp, sl, 0)
+        return ctx
+
+    t_fused, m_fused = _run(None, w, lens, caches, tok0, our_embed, our_argmax, layers, fused_fn=fused)
+    assert kv.device_status() == 0
+    _same_tokens_up_to_near_ties(t_fused, t_ours, m_ours, "projections fused with the append, against library matmuls + append")
+    del lins
 
     ref = reference_or_policy()  # skips (or fails, or goes on without it) where the cubins are missing
     if ref is not None:
