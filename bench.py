@@ -237,7 +237,7 @@ def _timed_region(torch, fn, steps, barrier):
 
 def read_only_peak(torch, kv, bufs, reps=8):
     """GB/s of the library's read-only stream probe (the decode kernel's bulk-copy pipeline without
-    arithmetic): one launch per buffer of `bufs` (each one layer's K or V slab, far larger than L2),
+    arithmetic): one launch per buffer of `bufs` (each as large as the K + V bytes one decode launch reads, far larger than L2),
     replayed as a CUDA graph like the headline step, with the decode kernel's 4 KB copies and with
     32 KB copies."""
     out = {}
@@ -360,7 +360,11 @@ def run_ours(args, torch, rank, world, local_rank):
     status = kv.device_status()
     ctx_ok = bool(torch.isfinite(w.ctx.float()).all().item()) and bool(torch.isfinite(hctx.float()).all().item())
     same = bool((hctx.cuda() == w.ctx).all().item())
-    ro_peak = read_only_peak(torch, kv, [w.k_slab[0], w.v_slab[0], w.k_slab[1 % LAYERS], w.v_slab[1 % LAYERS]])
+    # two buffers of one decode launch's K + V bytes each (1.07 GB at the default shape), read alternately
+    probe_bytes = int(BATCH) * int(CTX) * 2 * ROW_BYTES
+    probe_bufs = [torch.empty(probe_bytes, dtype=torch.uint8, device="cuda").zero_() for _ in range(2)]
+    ro_peak = read_only_peak(torch, kv, probe_bufs)
+    del probe_bufs
     status |= kv.device_status()
     layer_bytes = alg_bytes_layer(w.seq_lens_host)
 
@@ -436,7 +440,7 @@ def run_ours(args, torch, rank, world, local_rank):
                      "read_only_peak": ro_peak["copy_32k"], "read_only_peak_4k_copies": ro_peak["copy_4k"],
                      "frac_of_read_only_peak": round(attn_gbs / ro_peak["copy_32k"], 4),
                      "read_only_peak_kind": "measured in this run: the decode kernel's bulk-copy ring without arithmetic "
-                                            "(oxi_debug_stream_read), one launch per 1.07 GB slab, graph replay, 32 KB copies; "
+                                            "(oxi_debug_stream_read), one launch per buffer of a decode launch's K + V bytes, graph replay, 32 KB copies; "
                                             "the decode kernel copies 4 KB",
                      # the ncu capture was taken at the default sizes only
                      "traffic": TRAFFIC_PER_LAUNCH if (not RAGGED and (LAYERS, BATCH, CTX) == (8, 128, 4096)) else None,

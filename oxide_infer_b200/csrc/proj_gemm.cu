@@ -123,6 +123,8 @@ __device__ __forceinline__ void proj_epilogue_cols(uint32_t t_row, uint32_t n_ti
                                                    const uint16_t* s_w) {
     constexpr int BN = 128;
     constexpr int N_QKVG = pg::N_QKVG;
+    // bounds build: a live thread's row exists and its feature group is one of the 25 (qkvg) / lies inside y (plain)
+    if (!OXI_IN_BOUNDS(!live || (row < p.rows && (kQkvg ? n_tile <= 24u : n_tile * 128u < p.out_features)), p.status)) live = false;
     // the row's table entries (not written by any kernel)
     uint32_t pos = 0;
     uint64_t kvp = 0;
