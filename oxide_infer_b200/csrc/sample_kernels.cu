@@ -26,6 +26,9 @@ namespace sm {
 constexpr int VT = 256;          // virtual threads = the reference's block size
 constexpr int THREADS = 256;
 constexpr int MAX_SPLITS = 8;    // CTAs per row at most
+constexpr int LOADS = 8;         // 16-byte loads in flight per thread
+constexpr int CTAS_PER_SM = 2;   // grid size aimed at
+constexpr int RESIDENT = 3;      // CTAs that fit an SM (80 registers; 85 are the limit for three)
 }  // namespace sm
 
 __global__ void __launch_bounds__(256)
@@ -33,6 +36,8 @@ embed_lookup_kernel(uint16_t* __restrict__ out, const uint16_t* __restrict__ tab
                     const uint32_t* __restrict__ token_ids, uint32_t hidden, uint32_t table_rows,
                     uint32_t batch, uint32_t* __restrict__ status) {
     const uint32_t b = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();  // the ids come from the preceding kernel (the argmax of the step before)
     if (b >= batch) return;
     const uint32_t tok = token_ids[b];
     const bool bad = tok >= table_rows;
@@ -73,6 +78,7 @@ argmax_kernel(uint32_t* __restrict__ tokens_out, const uint16_t* __restrict__ lo
     __shared__ uint32_t s_last;
     const uint32_t b = blockIdx.y, split = blockIdx.x;
     const int tid = threadIdx.x;
+    pdl_launch_dependents();  // a dependent only sets itself up until this grid has finished
     const uint32_t c = tid & 31, grp = tid >> 5;  // this thread serves virtual threads 8c .. 8c+7
     const uint16_t* row = logits + (size_t)b * vocab;
 
@@ -96,32 +102,38 @@ argmax_kernel(uint32_t* __restrict__ tokens_out, const uint16_t* __restrict__ lo
             bi[e] = idx;
         }
     };
-    uint32_t k = k0 + grp;
-    // four vectors in flight per thread
-    for (; k + 24 < k1 && vec_ok && (size_t)(k + 24) * VT + VT <= vocab; k += 32) {
-        uint4 v[4];
+    // LOADS vectors in flight per thread; a k-row that is ragged (the last one) or unaligned takes the scalar
+    // loads, in the same position of the visiting order
+    pdl_wait();  // the logits come from the preceding kernel
+    auto is_vec = [&](uint32_t kk) { return vec_ok && kk < k1 && (size_t)kk * VT + VT <= vocab; };
+    auto load = [&](uint4 (&v)[LOADS], uint32_t k) {
 #pragma unroll
-        for (int u = 0; u < 4; u++) v[u] = __ldg(reinterpret_cast<const uint4*>(row + (size_t)(k + 8 * u) * VT + 8 * c));
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-            const uint32_t base = (k + 8 * u) * VT + 8 * c;
-            const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-#pragma unroll
-            for (int e = 0; e < 8; e++) take(e, (uint16_t)(w[e >> 1] >> ((e & 1) * 16)), base + e);
+        for (int u = 0; u < LOADS; u++) {
+            const uint32_t kk = k + 8 * u;
+            if (is_vec(kk)) v[u] = __ldg(reinterpret_cast<const uint4*>(row + (size_t)kk * VT + 8 * c));
         }
-    }
-    for (; k < k1; k += 8) {  // remaining k-rows, the ragged last one and unaligned rows
-        const uint32_t base = k * VT + 8 * c;
-        if (vec_ok && (size_t)base + 8 <= vocab) {
-            const uint4 v = __ldg(reinterpret_cast<const uint4*>(row + base));
-            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    };
+    auto scan = [&](const uint4 (&v)[LOADS], uint32_t k) {
 #pragma unroll
-            for (int e = 0; e < 8; e++) take(e, (uint16_t)(w[e >> 1] >> ((e & 1) * 16)), base + e);
-        } else {
+        for (int u = 0; u < LOADS; u++) {
+            const uint32_t kk = k + 8 * u, base = kk * VT + 8 * c;
+            if (is_vec(kk)) {
+                const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
-            for (int e = 0; e < 8; e++)
-                if (base + e < vocab) take(e, row[base + e], base + e);
+                for (int e = 0; e < 8; e++) take(e, (uint16_t)(w[e >> 1] >> ((e & 1) * 16)), base + e);
+            } else if (kk < k1) {
+#pragma unroll
+                for (int e = 0; e < 8; e++)
+                    if (base + e < vocab) take(e, row[base + e], base + e);
+            }
         }
+    };
+    // one batch at a time: a second register buffer that holds the next batch's loads while this one is scanned
+    // measured the same, and at 128 registers no longer fits the grid into one wave
+    uint4 vbuf[LOADS];
+    for (uint32_t k = k0 + grp; k < k1; k += 8 * LOADS) {
+        load(vbuf, k);
+        scan(vbuf, k);
     }
 #pragma unroll
     for (int e = 0; e < 8; e++) {
@@ -154,13 +166,16 @@ argmax_kernel(uint32_t* __restrict__ tokens_out, const uint16_t* __restrict__ lo
         if (tid == 0) counters[b] = 0u;  // ready for the next launch
         v = -1.0e30f;
         ix = 0u;
-        for (uint32_t s = 0; s < splits; s++) {  // splits hold increasing index ranges: strict > keeps the first
-            const float2 cnd = __ldcg(cand_scratch + ((size_t)b * MAX_SPLITS + s) * VT + tid);
-            if (cnd.x > v) {
-                v = cnd.x;
-                ix = __float_as_uint(cnd.y);
+        float2 cnd[MAX_SPLITS];
+#pragma unroll
+        for (int s = 0; s < MAX_SPLITS; s++)  // all loads in flight at once
+            if ((uint32_t)s < splits) cnd[s] = __ldcg(cand_scratch + ((size_t)b * MAX_SPLITS + s) * VT + tid);
+#pragma unroll
+        for (int s = 0; s < MAX_SPLITS; s++)  // splits hold increasing index ranges: strict > keeps the first
+            if ((uint32_t)s < splits && cnd[s].x > v) {
+                v = cnd[s].x;
+                ix = __float_as_uint(cnd[s].y);
             }
-        }
     }
     // the reference's tree over the 256 candidates
 #pragma unroll
@@ -193,24 +208,23 @@ uint32_t argmax_max_splits() { return sm::MAX_SPLITS; }
 cudaError_t launch_embed_lookup(cudaStream_t stream, void* out, const void* table,
                                 const uint32_t* token_ids, uint32_t hidden, uint32_t table_rows,
                                 uint32_t batch, uint32_t* status) {
-    embed_lookup_kernel<<<batch, 256, 0, stream>>>((uint16_t*)out, (const uint16_t*)table, token_ids, hidden,
-                                                   table_rows, batch, status);
-    return cudaGetLastError();
+    return launch_pdl(embed_lookup_kernel, dim3(batch), dim3(256), 0, stream, (uint16_t*)out, (const uint16_t*)table, token_ids,
+                      hidden, table_rows, batch, status);
 }
 
 cudaError_t launch_argmax(cudaStream_t stream, uint32_t* tokens_out, const void* logits, uint32_t vocab,
                           uint32_t batch, int num_sms, void* cand_scratch, uint32_t* counters) {
-    // enough CTAs for two per SM (six per SM measured slower: the merge of the splits grows), but no
-    // split shorter than 32 k-rows (8192 logits)
-    uint32_t splits = (uint32_t)(2 * num_sms + (int)batch - 1) / batch;
+    // enough CTAs for two per SM, all resident at once (a grid that needs a second wave measured 40 % slower),
+    // but no split shorter than 32 k-rows (8192 logits)
+    uint32_t splits = (uint32_t)(sm::CTAS_PER_SM * num_sms + (int)batch - 1) / batch;
     const uint32_t nk = (vocab + sm::VT - 1) / sm::VT;
     const uint32_t by_len = nk / 32u;
     if (splits > by_len) splits = by_len;
     if (splits > (uint32_t)sm::MAX_SPLITS) splits = sm::MAX_SPLITS;
+    while (splits > 1u && splits * batch > (uint32_t)(sm::RESIDENT * num_sms)) splits--;
     if (splits < 1u) splits = 1u;
-    argmax_kernel<<<dim3(splits, batch), sm::THREADS, 0, stream>>>(tokens_out, (const uint16_t*)logits, vocab, batch,
-                                                                   splits, (float2*)cand_scratch, counters);
-    return cudaGetLastError();
+    return launch_pdl(argmax_kernel, dim3(splits, batch), dim3(sm::THREADS), 0, stream, tokens_out, (const uint16_t*)logits, vocab,
+                      batch, splits, (float2*)cand_scratch, counters);
 }
 
 }  // namespace oxi

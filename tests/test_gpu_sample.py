@@ -69,7 +69,7 @@ def test_argmax_twice_and_full_batch(kv):
     rng = np.random.default_rng(32)
     logits = (np.round(rng.standard_normal((256, 20000), dtype=np.float32) * 3) / 3).astype(np.float16)
     want = O.argmax(logits)
-    for b in (256, 1, 3, 37, 148, 256):
+    for b in (256, 1, 3, 37, 148, 160, 230, 256):  # 160: two CTAs per row; 230: two would not be resident at once, so one
         assert np.array_equal(_ours(kv, logits[:b]), want[:b]), b
 
 
