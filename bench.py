@@ -881,6 +881,22 @@ def leg_project_append(args, torch, impl):
         out[f"rows{rows}"] = {"us": round(ms * 1e3, 2), "tflops": round(flops / (ms * 1e-3) / 1e12, 1),
                               "frac_of_tensor_peak": round(flops / (ms * 1e-3) / 1e12 / peak_tf, 4),
                               "gbs": round(byts / (ms * 1e-3) / 1e9, 1), "launches": 1 if impl == "ours" else 10}
+        if impl == "ours":
+            # context only: ONE library GEMM of the same shape (weights concatenated, no epilogue, no append), i.e. what
+            # the vendor's kernel reaches on [rows][2048] x [2048][3088] when the peak was measured on a large square GEMM
+            wcat = torch.cat(ws, 0).contiguous()
+            y = torch.empty(rows, nout, dtype=torch.float16, device="cuda")
+
+            def lib():
+                for x in xs:
+                    torch.matmul(x, wcat.t(), out=y)
+            for _ in range(3):
+                lib()
+            lg = _graph_of(torch, lib)
+            lms = _time_loop(torch, lg.replay, max(args.steps, 20), 3) / len(xs)
+            out[f"rows{rows}"]["library_gemm_same_shape"] = {
+                "us": round(lms * 1e3, 2), "frac_of_tensor_peak": round(flops / (lms * 1e-3) / 1e12 / peak_tf, 4),
+                "what": "one torch.matmul, no epilogue: context for the fraction above, not a path of this library"}
     out.update({"tensor_peak": peak_tf, "tensor_peak_kind": kind + " (sustained bf16 GEMM)", "launch": "cuda graph replay",
                 "bound": "rows128: weight read (12.6 MB) and latency; rows4096: tensor"})
     if impl == "ours":

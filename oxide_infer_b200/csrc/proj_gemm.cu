@@ -15,12 +15,14 @@
 // in 128 columns of tensor memory, operands A = x tile and B = W tile (both K-major, 64 k-elements =
 // one 128-byte swizzle span per row) brought in by TMA tile copies (no multicast) through a ring of
 // shared-memory stages that complete on mbarriers.  Warp 0 issues the copies, warp 1 the MMAs (one
-// elected lane), warps 2-5 run the epilogue: thread = one row of the tile (its TMEM lane), so a
-// thread holds a whole head of its token and the per-head arithmetic needs no shuffles.
-// At the decode shape (128 rows: 25 CTAs) a launch takes ~15 us, of which the tile's 128 MMAs are ~5,
-// the epilogue ~4 and launch, set-up and the first copies' latency the rest; cutting K into four parts
-// that meet in an L2 workspace (100 CTAs) measured 16-18 us (the exchange costs what the shorter main
-// loop saves) and a ring twice as deep changed nothing, so neither is here.
+// elected lane), the other warps run the epilogue.  Two kernels:
+//   * proj_gemm_splitk_kernel (rows <= 256, the decode shape): a cluster of four CTAs per tile, each
+//     a quarter of k, partial accumulators exchanged through distributed shared memory; four threads
+//     finish a row's head.  8.9 us at 128 rows, where one CTA per tile needed 15.1 us (it has to pull
+//     1 MB through one SM's port while 123 SMs idle) and a split of k that met in an L2 workspace
+//     16-18 us.
+//   * proj_gemm_wave_kernel (larger waves): persistent, 128 x 256 tiles, two accumulators; thread = one
+//     row of the tile (its TMEM lane), so a thread holds a whole head of its token.
 //
 // Bit parity.  The projections are rounded to f16 exactly as the reference's GEMM output is, and
 // the epilogue applies the append kernel's arithmetic to those f16 values: the RMSNorm sum is formed
@@ -263,117 +265,6 @@ __device__ __forceinline__ void proj_epilogue_cols(uint32_t t_row, uint32_t n_ti
     }
 }
 
-template <bool kQkvg>
-__global__ void __launch_bounds__(pg::THREADS, 2)
-proj_gemm_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p) {
-    using namespace pg;
-    extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bar_full[NS], bar_empty[NS], bar_acc;
-    __shared__ uint32_t s_tmem, s_abort;
-    __shared__ uint16_t s_w[2 * HD];  // q and k norm weights
-
-    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;  // 1024-byte aligned tiles (128-byte swizzle)
-    const int tid = threadIdx.x, lane = tid & 31;
-    const int warp_u = __shfl_sync(0xffffffffu, tid >> 5, 0);
-    const uint32_t n_tile = blockIdx.x, m_tile = blockIdx.y;
-
-    pdl_launch_dependents();
-    if (warp_u == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    if (tid == 0) {
-        for (int s = 0; s < NS; s++) {
-            mbar_init(&bar_full[s], 1);
-            mbar_init(&bar_empty[s], 1);
-        }
-        mbar_init(&bar_acc, 1);
-        s_abort = 0u;
-        mbar_fence_init();
-    }
-    if (kQkvg && tid >= 64) {
-        const int i = tid - 64;  // 128 threads: both weight vectors (not written by any kernel)
-        s_w[i] = p.q_norm_w[i];
-        s_w[HD + i] = p.k_norm_w[i];
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = s_tmem;
-
-    // which weight matrix and which of its rows this tile covers
-    uint32_t wsel = 0, wrow = n_tile * BN;
-    if (kQkvg) {
-        if (n_tile >= 24) { wsel = 3; wrow = 0; }
-        else if (n_tile >= 20) { wsel = 2; wrow = (n_tile - 20) * BN; }
-        else if (n_tile >= 16) { wsel = 1; wrow = (n_tile - 16) * BN; }
-    }
-
-    if (warp_u == 0) {
-        // ===================== TMA producer =====================
-        pdl_wait();  // x is written by the kernel before this one
-        bool ok = true;
-        uint32_t issued = 0;
-        for (uint32_t kb = 0; kb < (uint32_t)NKB && ok; kb++, issued++) {
-            const uint32_t s = kb % NS;
-            if (kb >= (uint32_t)NS && !mbar_wait_bounded(&bar_empty[s], ((kb / NS) & 1u) ^ 1u, &s_abort)) {
-                ok = false;
-                break;
-            }
-            if (lane == 0) {
-                mbar_arrive_expect_tx(&bar_full[s], (uint32_t)STAGE_BYTES);
-                tma_load_box(sbase + s * STAGE_BYTES, &maps.x, kb * BK, m_tile * BM, &bar_full[s]);
-                tma_load_box(sbase + s * STAGE_BYTES + TILE_BYTES, &maps.w[wsel], kb * BK, wrow, &bar_full[s]);
-            }
-            __syncwarp();
-        }
-        if (!ok) {
-            if (lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
-            // copies already issued land before the shared memory is released
-            for (uint32_t k = issued > (uint32_t)NS ? issued - NS : 0; k < issued; ++k)
-                mbar_wait_drain(&bar_full[k % NS], (k / NS) & 1u, WAIT_LIMIT_US);
-        }
-    } else if (warp_u == 1) {
-        // ===================== MMA issuer =====================
-        bool ok = true;
-        for (uint32_t kb = 0; kb < (uint32_t)NKB; kb++) {
-            const uint32_t s = kb % NS;
-            ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(&bar_full[s], (kb / NS) & 1u, &s_abort));
-            tc_fence_after();
-            if (elect_one()) {
-                const uint64_t ad = umma_desc(sbase + s * STAGE_BYTES, 16, 1024);
-                const uint64_t bd = umma_desc(sbase + s * STAGE_BYTES + TILE_BYTES, 16, 1024);
-#pragma unroll
-                for (int kk = 0; kk < BK / 16; kk++)
-                    umma_ss(tmem, ad + (uint64_t)(kk * 2), bd + (uint64_t)(kk * 2), IDESC, (kb | (uint32_t)kk) != 0u ? 1u : 0u);
-                umma_commit(&bar_empty[s]);                       // the stage is free once these MMAs have read it
-                if (kb + 1 == (uint32_t)NKB && ok) umma_commit(&bar_acc);  // accumulator complete
-            }
-            __syncwarp();
-        }
-        if (!ok && lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
-    } else {
-        // ===================== epilogue: thread = one row (token) of the tile =====================
-        const uint32_t quarter = (uint32_t)warp_u & 3u;            // TMEM lanes this warp may read
-        const uint32_t row = m_tile * BM + quarter * 32 + (uint32_t)lane;
-        // warp-uniform: the tensor-memory loads below are warp-wide instructions
-        const bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar_acc, 0u, &s_abort));
-        tc_fence_after();
-        if (!ok) {
-            if (lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
-        } else {
-            proj_epilogue_cols<kQkvg>(tmem + ((quarter * 32) << 16), n_tile, row, row < p.rows, p, s_w);
-        }
-    }
-
-    tc_fence_before();
-    __syncthreads();
-    if (warp_u == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
-    }
-}
-
 // ---------------------------------------------------------------------------------------------------
 // The same GEMM for waves of rows (prefill): persistent, one CTA per SM, tiles of 128 rows x 256 features
 // (two heads), a ring of four 48 KB stages, and TWO accumulators in tensor memory (2 x 256 of the 512
@@ -542,10 +433,400 @@ proj_gemm_wave_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p,
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// The decode shape (rows <= 256: one or two row tiles).  One CTA per (row tile, head) has to pull 1 MB of
+// operands through one SM's port (~7 us for 25 CTAs while 123 SMs idle), so the k dimension is cut into
+// four parts computed by the four CTAs of a thread-block cluster, which meet in shared memory:
+//   1. CTA c runs the main loop over k-blocks [8c, 8c + 8) into its own accumulator; meanwhile its epilogue
+//      threads fetch the table entries and rotary values of the rows they will finish;
+//   2. cluster barrier: every main loop of the cluster is over, so every ring is free to receive;
+//   3. the four epilogue warps push the f32 accumulator: the 32 rows of TMEM lane quarter q go to CTA q, slot c
+//      of its receive area (the ring's bytes), with 16-byte remote stores laid out so that a warp's stores and
+//      the later loads are conflict-free (remote stores need no round trip; fetching from the peers instead
+//      measured 0.5 us slower, a cluster of eight 3 us slower);
+//   4. cluster barrier; CTA c finishes rows [32c, 32c + 32) of the tile from its own shared memory: thread
+//      (warp j, lane t) adds the four parts of 32 of row t's 128 columns in k order - the dims l, l + 32, l + 64,
+//      l + 96 for l in [8j, 8j + 8), i.e. what lanes 8j .. 8j + 7 of the reference's warp own, so the row's
+//      four threads form the RMSNorm partial sums with the reference's fma chains, exchange the 32 partials
+//      through shared memory, and each runs the reference's shfl.down tree on them; both members of every RoPE
+//      pair (d, d + 64) sit in the same thread.  After the second barrier a CTA touches only its own shared
+//      memory, so it may leave without waiting for its peers.
+// The barriers are hardware cluster barriers reached by every thread on every path (all other waits in the
+// kernel are bounded and fall through), so they cannot be left waiting; a CTA that gave up a wait says so
+// in a flag pushed to its peers, and nobody writes results.
+// Where the time goes at 128 rows (globaltimer stamps in one CTA, ns): set-up 350, main loop 2500, barrier 300,
+// push + barrier 1650, adding the parts 350, RMSNorm + RoPE + stores 1050 (q head; gate 250).
+namespace pgs {
+using pg::BM; using pg::BN; using pg::BK; using pg::NKB; using pg::NS; using pg::TILE_BYTES; using pg::STAGE_BYTES;
+using pg::THREADS; using pg::SMEM_BYTES; using pg::TMEM_COLS; using pg::IDESC;
+constexpr int KS = 4;                       // CTAs per cluster = parts of k = TMEM lane quarters of the tile
+constexpr int KB_PER = NKB / KS;            // 8 k-blocks per CTA
+static_assert(KS == 4 && BM == 128, "CTA c of the cluster finishes the 32 rows of lane quarter c");
+static_assert((size_t)BM * BN * 4 <= (size_t)NS * STAGE_BYTES, "the exported accumulator reuses the ring");
+}  // namespace pgs
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {  // every thread of every CTA of the cluster
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t dsmem_addr(uint32_t local_smem_addr, uint32_t cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(cta));
+    return r;
+}
+// 8 f16 bit patterns -> one 16-byte store
+__device__ __forceinline__ void store8(uint16_t* dst, const uint16_t* h) {
+    *reinterpret_cast<uint4*>(dst) = make_uint4(h[0] | ((uint32_t)h[1] << 16), h[2] | ((uint32_t)h[3] << 16),
+                                                 h[4] | ((uint32_t)h[5] << 16), h[6] | ((uint32_t)h[7] << 16));
+}
+
+// Finishes 32 columns of one row of a head: v[g][i] = accumulator of dim 32g + 8j + i, i.e. the dims owned by lanes
+// 8j .. 8j + 7 of the reference's warp.  Called by all 128 epilogue threads of the CTA (the q/k branch meets in a named
+// barrier); t = lane = row inside the CTA's 32 rows; s_part = [32 reference lanes][32 rows] f32 in shared memory.
+// What the finishing thread of a row needs from global memory besides the accumulators: fetched while the cluster
+// exchanges the partial sums (the table entry, then the rotary values it leads to, are two dependent round trips).
+struct RowTables {
+    uint32_t pos;
+    uint64_t kvp;
+    uint4 cs[4], sn[4];  // [2 * pair + 0 / 1]: cos / sin of dims [dl, dl + 8) and 64 + [dl, dl + 8), dl = 32 * pair + 8j
+    bool live;
+};
+template <bool kQkvg>
+__device__ __forceinline__ RowTables proj_fetch_row_tables(uint32_t j, uint32_t n_tile, uint32_t row, bool live, const ProjParams& p) {
+    RowTables rt;
+    rt.pos = 0;
+    rt.kvp = 0;
+    if (!OXI_IN_BOUNDS(!live || (row < p.rows && (kQkvg ? n_tile <= 24u : n_tile * 128u < p.out_features)), p.status)) live = false;
+    rt.live = live;
+    if (kQkvg && live && n_tile < 24u) {
+        rt.pos = p.pos_ids[row];
+        if (n_tile >= 16u && n_tile < 20u) rt.kvp = p.k_ptrs[row];
+        if (n_tile >= 20u) rt.kvp = p.v_ptrs[row];
+        if (n_tile < 20u) {
+            const uint16_t* cs = p.cos_t + (size_t)rt.pos * HD;
+            const uint16_t* sn = p.sin_t + (size_t)rt.pos * HD;
+#pragma unroll
+            for (int pr = 0; pr < 2; pr++) {
+                const uint32_t dl = 32u * pr + 8u * j, dh = dl + 64u;
+                rt.cs[2 * pr] = __ldg(reinterpret_cast<const uint4*>(cs + dl));
+                rt.cs[2 * pr + 1] = __ldg(reinterpret_cast<const uint4*>(cs + dh));
+                rt.sn[2 * pr] = __ldg(reinterpret_cast<const uint4*>(sn + dl));
+                rt.sn[2 * pr + 1] = __ldg(reinterpret_cast<const uint4*>(sn + dh));
+            }
+        }
+    }
+    return rt;
+}
+
+template <bool kQkvg>
+__device__ __forceinline__ void proj_finish_row(const float (&v)[4][8], uint32_t j, uint32_t t, uint32_t n_tile, uint32_t row,
+                                                const RowTables& rt, const ProjParams& p, const uint16_t* s_w, float* s_part) {
+    constexpr uint32_t N_QKVG = pg::N_QKVG;
+    const bool live = rt.live;
+    uint16_t h[4][8];
+    float f[4][8];
+#pragma unroll
+    for (int g = 0; g < 4; g++)
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            h[g][i] = f2h(v[g][i]);
+            f[g][i] = h2f(h[g][i]);
+        }
+    if (!kQkvg) {
+        // ---- plain linear layer
+        if (!live) return;
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            const uint32_t n0 = n_tile * 128u + 32u * g + 8u * j;
+            if (n0 >= p.out_features) continue;
+            uint16_t* dst = p.y + (size_t)row * p.out_features + n0;
+            if (n0 + 8u <= p.out_features && (p.out_features & 7u) == 0u) {
+                store8(dst, h[g]);
+            } else {
+                for (uint32_t i = 0; i < 8u && n0 + i < p.out_features; i++) dst[i] = h[g][i];
+            }
+        }
+        return;
+    }
+    if (n_tile == 24u) {
+        // ---- gate: 16 features, dims 8j .. 8j + 7 of threads j = 0, 1
+        if (live && j < 2u) {
+            store8(p.gate_out + (size_t)row * NQ + 8u * j, h[0]);
+            if (p.raw_out) store8(p.raw_out + (size_t)row * N_QKVG + 3072u + 8u * j, h[0]);
+        }
+        return;
+    }
+    const uint32_t pos = rt.pos;
+    const uint64_t kvp = rt.kvp;
+    if (n_tile >= 20u) {
+        // ---- v head: the f16 projection is the cache row
+        const uint32_t kvh = n_tile - 20u;
+        const bool aligned = (kvp & 15ull) == 0ull;
+        if (live && !aligned && kvh == 0u && j == 0u) atomicOr(p.status, DEV_MISALIGNED_PTR);
+        if (!live) return;
+        uint16_t* dst = reinterpret_cast<uint16_t*>(kvp + (size_t)pos * KV_ROW_BYTES) + kvh * HD;
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            const uint32_t d0 = 32u * g + 8u * j;
+            if (aligned) store8(dst + d0, h[g]);
+            if (p.raw_out) store8(p.raw_out + (size_t)row * N_QKVG + 2560u + kvh * HD + d0, h[g]);
+        }
+        return;
+    }
+    // ---- q or k head: RMSNorm + RoPE on the f16 projections, the append kernel's arithmetic
+    const bool is_k = n_tile >= 16u;
+    const uint32_t head = is_k ? n_tile - 16u : n_tile;
+    const uint16_t* wn = s_w + (is_k ? HD : 0);
+    const bool aligned = !is_k || (kvp & 15ull) == 0ull;
+    if (live && !aligned && head == 0u && j == 0u) atomicOr(p.status, DEV_MISALIGNED_PTR);
+    if (live && p.raw_out) {
+#pragma unroll
+        for (int g = 0; g < 4; g++)
+            store8(p.raw_out + (size_t)row * N_QKVG + (is_k ? 2048u : 0u) + head * HD + 32u * g + 8u * j, h[g]);
+    }
+    // the partial sums of reference lanes l = 8j + i: dims l, l + 32, l + 64, l + 96 in that order, fma
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        float pp = __fmaf_rn(f[0][i], f[0][i], 0.0f);
+        pp = __fmaf_rn(f[1][i], f[1][i], pp);
+        pp = __fmaf_rn(f[2][i], f[2][i], pp);
+        pp = __fmaf_rn(f[3][i], f[3][i], pp);
+        s_part[(8u * j + i) * 32u + t] = pp;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+    float partial[32];
+#pragma unroll
+    for (int l = 0; l < 32; l++) partial[l] = s_part[l * 32 + t];
+    // the shfl.down tree of the reference on one thread's registers: lane 0's value
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1)
+#pragma unroll
+        for (int l = 0; l < off; l++) partial[l] = __fadd_rn(partial[l], partial[l + off]);
+    float mean = div_approx_ftz(partial[0], 128.0f);
+    mean = __fadd_rn(mean, p.eps);
+    const float r = rsqrt_approx_ftz(mean);
+    if (!live) return;
+    uint16_t* dst = is_k ? reinterpret_cast<uint16_t*>(kvp + (size_t)pos * KV_ROW_BYTES) + head * HD
+                         : p.q_out + ((size_t)row * NQ + head) * HD;
+#pragma unroll
+    for (int pr = 0; pr < 2; pr++) {  // dims [dl, dl + 8) pair with dims 64 + [dl, dl + 8)
+        const uint32_t dl = 32u * pr + 8u * j, dh = dl + 64u;
+        const uint4 clo = rt.cs[2 * pr], chi = rt.cs[2 * pr + 1];
+        const uint4 slo = rt.sn[2 * pr], shi = rt.sn[2 * pr + 1];
+        const uint32_t cl[4] = {clo.x, clo.y, clo.z, clo.w}, ch[4] = {chi.x, chi.y, chi.z, chi.w};
+        const uint32_t sl[4] = {slo.x, slo.y, slo.z, slo.w}, sh4[4] = {shi.x, shi.y, shi.z, shi.w};
+        uint16_t olo[8], ohi[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float xlo = f[pr][i], xhi = f[pr + 2][i];
+            // y = f16((x * r) * w): two separate multiplies, then the f16 round trip
+            const float ylo = h2f(f2h(__fmul_rn(__fmul_rn(xlo, r), h2f(wn[dl + i]))));
+            const float yhi = h2f(f2h(__fmul_rn(__fmul_rn(xhi, r), h2f(wn[dh + i]))));
+            const int wd = i >> 1, sh = (i & 1) * 16;
+            const float c_lo = h2f((uint16_t)(cl[wd] >> sh)), c_hi = h2f((uint16_t)(ch[wd] >> sh));
+            const float s_lo = h2f((uint16_t)(sl[wd] >> sh)), s_hi = h2f((uint16_t)(sh4[wd] >> sh));
+            // rotate-half: out[d] = fma(-y[d+64], sin[d], y[d]*cos[d]);  out[d+64] = fma(y[d], sin[d+64], y[d+64]*cos[d+64])
+            olo[i] = f2h(__fmaf_rn(-yhi, s_lo, __fmul_rn(ylo, c_lo)));
+            ohi[i] = f2h(__fmaf_rn(ylo, s_hi, __fmul_rn(yhi, c_hi)));
+        }
+        if (aligned) {
+            store8(dst + dl, olo);
+            store8(dst + dh, ohi);
+        }
+    }
+}
+
+template <bool kQkvg>
+__global__ void __cluster_dims__(pgs::KS, 1, 1) __launch_bounds__(pgs::THREADS, 2)
+proj_gemm_splitk_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p) {
+    using namespace pgs;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[NS], bar_empty[NS], bar_acc;
+    __shared__ uint32_t s_tmem, s_abort;
+    __shared__ uint16_t s_w[2 * HD];        // q and k norm weights
+    __shared__ float s_part[32 * 32];       // RMSNorm partials: [reference lane][row of this CTA]
+    __shared__ uint32_t s_peer_abort[pgs::KS];  // written by the peers: did CTA cc give up a wait
+
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;  // 1024-byte aligned tiles (128-byte swizzle)
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp_u = __shfl_sync(0xffffffffu, tid >> 5, 0);
+    const uint32_t crank = cluster_ctarank();                      // which part of k, and which 32 rows to finish
+    const uint32_t n_tile = blockIdx.x / KS, m_tile = blockIdx.y;
+
+    pdl_launch_dependents();
+    if (warp_u == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (tid == 0) {
+        for (int s = 0; s < NS; s++) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_empty[s], 1);
+        }
+        mbar_init(&bar_acc, 1);
+        s_abort = 0u;
+        mbar_fence_init();
+    }
+    if (kQkvg && tid >= 64) {
+        const int i = tid - 64;  // 128 threads: both weight vectors (not written by any kernel)
+        s_w[i] = p.q_norm_w[i];
+        s_w[HD + i] = p.k_norm_w[i];
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+
+    uint32_t wsel = 0, wrow = n_tile * BN;
+    if (kQkvg) {
+        if (n_tile >= 24) { wsel = 3; wrow = 0; }
+        else if (n_tile >= 20) { wsel = 2; wrow = (n_tile - 20) * BN; }
+        else if (n_tile >= 16) { wsel = 1; wrow = (n_tile - 16) * BN; }
+    }
+    const uint32_t kb0 = crank * KB_PER;
+    bool acc_ok = true;  // epilogue warps: this CTA's accumulator completed
+    RowTables rt;
+    rt.live = false;
+
+    if (warp_u == 0) {
+        // ===================== TMA producer: this CTA's k-blocks =====================
+        pdl_wait();  // x is written by the kernel before this one
+        bool ok = true;
+        uint32_t issued = 0;
+        for (uint32_t kb = 0; kb < (uint32_t)KB_PER && ok; kb++, issued++) {
+            const uint32_t s = kb % NS;
+            if (kb >= (uint32_t)NS && !mbar_wait_bounded(&bar_empty[s], ((kb / NS) & 1u) ^ 1u, &s_abort)) {
+                ok = false;
+                break;
+            }
+            if (lane == 0) {
+                mbar_arrive_expect_tx(&bar_full[s], (uint32_t)STAGE_BYTES);
+                tma_load_box(sbase + s * STAGE_BYTES, &maps.x, (kb0 + kb) * BK, m_tile * BM, &bar_full[s]);
+                tma_load_box(sbase + s * STAGE_BYTES + TILE_BYTES, &maps.w[wsel], (kb0 + kb) * BK, wrow, &bar_full[s]);
+            }
+            __syncwarp();
+        }
+        if (!ok) {
+            if (lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
+            for (uint32_t k = issued > (uint32_t)NS ? issued - NS : 0; k < issued; ++k)
+                mbar_wait_drain(&bar_full[k % NS], (k / NS) & 1u, WAIT_LIMIT_US);
+        }
+    } else if (warp_u == 1) {
+        // ===================== MMA issuer =====================
+        bool ok = true;
+        for (uint32_t kb = 0; kb < (uint32_t)KB_PER; kb++) {
+            const uint32_t s = kb % NS;
+            ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(&bar_full[s], (kb / NS) & 1u, &s_abort));
+            tc_fence_after();
+            if (elect_one()) {
+                const uint64_t ad = umma_desc(sbase + s * STAGE_BYTES, 16, 1024);
+                const uint64_t bd = umma_desc(sbase + s * STAGE_BYTES + TILE_BYTES, 16, 1024);
+#pragma unroll
+                for (int kk = 0; kk < BK / 16; kk++)
+                    umma_ss(tmem, ad + (uint64_t)(kk * 2), bd + (uint64_t)(kk * 2), IDESC, (kb | (uint32_t)kk) != 0u ? 1u : 0u);
+                umma_commit(&bar_empty[s]);
+                if (kb + 1 == (uint32_t)KB_PER && ok) umma_commit(&bar_acc);  // this CTA's partial accumulator is complete
+            }
+            __syncwarp();
+        }
+        if (!ok && lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
+    } else {
+        // ===================== while the main loop runs: the tables of the row this thread will finish
+        // (thread (warp j, lane t): row 32 crank + t of the tile), final once the kernel before has finished
+        pdl_wait();
+        const uint32_t frow = m_tile * BM + crank * 32u + (uint32_t)lane;
+        rt = proj_fetch_row_tables<kQkvg>((uint32_t)warp_u - 2u, n_tile, frow, frow < p.rows, p);
+        // ===================== this CTA's partial accumulator is complete =====================
+        acc_ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar_acc, 0u, &s_abort));
+        tc_fence_after();
+        if (!acc_ok && lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
+    }
+
+    // every thread of every CTA: all main loops of the cluster are over, so every CTA's ring is free to receive
+    tc_fence_before();
+    __syncwarp();
+    cluster_sync_all();
+
+    if (warp_u >= 2) {
+        // ===================== push: thread = one row of the tile; its 128 columns go to the CTA that finishes
+        // the row's quarter, into slot `crank` of that CTA's receive area: [slot][column group of 4][row of the
+        // quarter] x 16 bytes (a warp's 32 stores are 512 consecutive bytes).  Remote stores need no round trip.
+        const uint32_t quarter = (uint32_t)warp_u & 3u;  // TMEM lanes this warp may read = destination CTA
+        tc_fence_after();
+        if (acc_ok) {
+            const uint32_t t_row = tmem + ((quarter * 32u) << 16);
+            const uint32_t dst = dsmem_addr(sbase + (crank * 32u * 32u + (uint32_t)lane) * 16u, quarter);
+#pragma unroll 2
+            for (int c = 0; c < BN / 16; c++) {
+                uint32_t acc[16];
+                tmem_ld16(t_row + c * 16, acc);
+                tmem_wait_ld();
+#pragma unroll
+                for (int q4 = 0; q4 < 4; q4++)
+                    asm volatile("st.shared::cluster.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(dst + (uint32_t)(c * 4 + q4) * 512u),
+                                 "r"(acc[4 * q4]), "r"(acc[4 * q4 + 1]), "r"(acc[4 * q4 + 2]), "r"(acc[4 * q4 + 3])
+                                 : "memory");
+            }
+        }
+        if (warp_u == 2 && lane < KS)  // tell every CTA of the cluster whether this one gave up
+            asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(dsmem_addr(smem_u32(&s_peer_abort[crank]), (uint32_t)lane)),
+                         "r"(acc_ok ? 0u : 1u)
+                         : "memory");
+    }
+
+    // every thread of every CTA: the partial accumulators and the flags have arrived.  After this barrier a CTA
+    // touches only its own shared memory, so it may leave without waiting for its peers.
+    tc_fence_before();
+    __syncwarp();
+    cluster_sync_all();
+
+    if (warp_u >= 2) {
+        // ===================== add the four parts + epilogue of rows [32 crank, 32 crank + 32) =====================
+        const uint32_t j = (uint32_t)warp_u - 2u, t = (uint32_t)lane;
+        bool any_abort = false;
+#pragma unroll
+        for (int cc = 0; cc < KS; cc++) any_abort |= s_peer_abort[cc] != 0u;
+        if (!any_abort) {
+            const uint32_t row = m_tile * BM + crank * 32u + t;
+            // dims 32g + 8j + i  ->  column groups 8g + 2j and 8g + 2j + 1, row t, of every slot
+            const float4* recv = reinterpret_cast<const float4*>(smem_raw + (sbase - smem_u32(smem_raw)));
+            float v[4][8];
+#pragma unroll
+            for (int cc = 0; cc < KS; cc++) {  // k order: part 0 + part 1 + ...
+#pragma unroll
+                for (int g = 0; g < 4; g++)
+#pragma unroll
+                    for (int hh = 0; hh < 2; hh++) {
+                        const float4 a = recv[((uint32_t)cc * 32u + (uint32_t)(8 * g + 2 * j + hh)) * 32u + t];
+                        if (cc == 0) {
+                            v[g][4 * hh] = a.x; v[g][4 * hh + 1] = a.y; v[g][4 * hh + 2] = a.z; v[g][4 * hh + 3] = a.w;
+                        } else {
+                            v[g][4 * hh] = __fadd_rn(v[g][4 * hh], a.x);
+                            v[g][4 * hh + 1] = __fadd_rn(v[g][4 * hh + 1], a.y);
+                            v[g][4 * hh + 2] = __fadd_rn(v[g][4 * hh + 2], a.z);
+                            v[g][4 * hh + 3] = __fadd_rn(v[g][4 * hh + 3], a.w);
+                        }
+                    }
+            }
+            proj_finish_row<kQkvg>(v, j, t, n_tile, row, rt, p, s_w, s_part);
+        }
+    }
+
+    // the tensor-memory loads of the epilogue warps finished before the second cluster barrier
+    if (warp_u == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 cudaError_t proj_gemm_init() {
-    cudaError_t e = cudaFuncSetAttribute(proj_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pg::SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(proj_gemm_splitk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pgs::SMEM_BYTES);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(proj_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pg::SMEM_BYTES);
+        e = cudaFuncSetAttribute(proj_gemm_splitk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pgs::SMEM_BYTES);
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(proj_gemm_wave_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pgw::SMEM_BYTES);
     if (e == cudaSuccess)
@@ -579,7 +860,7 @@ int proj_encode_map(TmaDesc* out, const void* base, uint64_t rows, uint32_t box_
     return r == CUDA_SUCCESS ? 0 : -2;
 }
 
-// rows up to this many run the one-tile-per-CTA kernel (more CTAs for a single row tile), larger waves the persistent one
+// rows up to this many run the cluster kernel (four CTAs per 128 x 128 tile), larger waves the persistent one
 constexpr uint32_t PROJ_SMALL_ROWS = 256;
 
 cudaError_t launch_project_append(cudaStream_t stream, const TmaDesc* w_maps /* q, k, v, gate; box 128 then box 256 */, int num_sms, const void* x, uint32_t rows,
@@ -610,7 +891,8 @@ cudaError_t launch_project_append(cudaStream_t stream, const TmaDesc* w_maps /* 
         return launch_pdl(proj_gemm_wave_kernel<true>, dim3(total < (uint32_t)num_sms ? total : (uint32_t)num_sms),
                           dim3(pgw::THREADS), pgw::SMEM_BYTES, stream, maps, p, (uint32_t)pgw::TILES_QKVG, tiles_m);
     }
-    return launch_pdl(proj_gemm_kernel<true>, dim3(pg::TILES_QKVG, tiles_m), dim3(pg::THREADS), pg::SMEM_BYTES, stream, maps, p);
+    return launch_pdl(proj_gemm_splitk_kernel<true>, dim3(pg::TILES_QKVG * pgs::KS, tiles_m), dim3(pgs::THREADS), pgs::SMEM_BYTES, stream,
+                      maps, p);
 }
 
 cudaError_t launch_linear(cudaStream_t stream, const TmaDesc* w_maps /* box 128, box 256 */, int num_sms, uint32_t out_features,
@@ -630,8 +912,8 @@ cudaError_t launch_linear(cudaStream_t stream, const TmaDesc* w_maps /* box 128,
         return launch_pdl(proj_gemm_wave_kernel<false>, dim3(total < (uint32_t)num_sms ? total : (uint32_t)num_sms),
                           dim3(pgw::THREADS), pgw::SMEM_BYTES, stream, maps, p, tiles_n, tiles_m);
     }
-    return launch_pdl(proj_gemm_kernel<false>, dim3((out_features + pg::BN - 1) / pg::BN, tiles_m), dim3(pg::THREADS),
-                      pg::SMEM_BYTES, stream, maps, p);
+    return launch_pdl(proj_gemm_splitk_kernel<false>, dim3((out_features + pg::BN - 1) / pg::BN * pgs::KS, tiles_m), dim3(pgs::THREADS),
+                      pgs::SMEM_BYTES, stream, maps, p);
 }
 
 }  // namespace oxi
