@@ -34,7 +34,7 @@ def _assert_same_projections(got, want):
 def kv():
     from oxide_infer_b200 import KvPath, build
     build.build()
-    p = KvPath(0, max_batch=512, max_seq_len=8192, max_prefill_rows=4096)
+    p = KvPath(0, max_batch=1024, max_seq_len=8192, max_prefill_rows=4096)
     yield p
     assert p.device_status() == 0
     p.close()
@@ -60,9 +60,10 @@ def _project(kv, case, x, ws, raw=True):
     return d, q_out, gate_out, raw_out
 
 
-# up to 256 rows run the one-tile-per-CTA kernel, more rows the persistent 128 x 256 kernel
+# up to 512 rows run the four-CTA cluster kernel (one to four row tiles), more rows the persistent 128 x 256 kernel
 @pytest.mark.parametrize("lens", [[5], [300, 1, 64, 777, 31, 2047, 512], list(range(100, 228)), list(range(10, 266)),
-                                  list(range(10, 267)), list(range(10, 310))])
+                                  list(range(10, 267)), list(range(10, 310)), list(range(10, 522)), list(range(10, 523)),
+                                  list(range(10, 650))])
 def test_project_append_equals_matmul_then_append(kv, ref, lens):
     b = len(lens)
     case = DecodeCase(lens, seed=80 + b)
