@@ -110,13 +110,13 @@ cudaError_t launch_append_decode_paged(cudaStream_t stream, const DecodeWorkspac
 // Projection GEMM (tcgen05) with the append operator as its epilogue, and the same GEMM as a plain linear layer.
 cudaError_t proj_gemm_init();
 int proj_encode_map(TmaDesc* out, const void* base, uint64_t rows, uint32_t box_rows);  // tiled map over [rows][2048] f16; 0 = ok
-// w_maps: the four weight matrices (q, k, v, gate) with 128-row boxes, then the same four with 256-row boxes
+// w_maps: tensor maps of the four weight matrices (q, k, v, gate), boxes of 128 rows
 cudaError_t launch_project_append(cudaStream_t stream, const TmaDesc* w_maps, int num_sms, const void* x, uint32_t rows,
                                   void* q_out, void* gate_out, void* raw_out, const void* q_norm_w, const void* k_norm_w,
                                   const void* cos_t, const void* sin_t, const uint32_t* pos_ids, const uint64_t* k_ptrs,
                                   const uint64_t* v_ptrs, float eps, uint32_t* status);
-// w_maps: the weight matrix with 128-row boxes, then with 256-row boxes
-cudaError_t launch_linear(cudaStream_t stream, const TmaDesc* w_maps, int num_sms, uint32_t out_features, const void* x,
+// w_map: tensor map of the weight matrix, boxes of 128 rows
+cudaError_t launch_linear(cudaStream_t stream, const TmaDesc* w_map, int num_sms, uint32_t out_features, const void* x,
                           uint32_t rows, void* y, uint32_t* status);
 
 // Read-only streaming probe (bench and tests): the decode kernel's copy pipeline without arithmetic.

@@ -576,7 +576,7 @@ int32_t oxi_sigmoid_gate(oxi_handle* h, void* stream, void* ctx_io, const void* 
 
 // ---- linear layers on either side of the path (tensor maps over the caller's weights; host objects only)
 struct oxi_linear_s {
-    TmaDesc maps[8];        // qkvg: q, k, v, gate with 128-row boxes, then with 256-row boxes; plain: maps[0], maps[1]
+    TmaDesc maps[4];        // boxes of 128 weight rows x 64 k; qkvg: q, k, v, gate; plain: maps[0]
     uint32_t out_features;  // plain: rows of the weight matrix; qkvg: 3088
     bool qkvg;
 };
@@ -596,15 +596,10 @@ int32_t oxi_qkvg_create(oxi_linear** out, const void* wq, const void* wk, const 
     oxi_linear_s* l = new (std::nothrow) oxi_linear_s();
     if (!l) return fail(OXI_ERR_WORKSPACE, "oxi_qkvg_create: host allocation failed");
     int32_t rc = OXI_OK;
-    for (int b = 0; b < 2 && rc == OXI_OK; b++) {
-        const uint32_t box = b ? 256u : 128u;
-        if ((rc = linear_map(&l->maps[4 * b + 0], wq, NQ * HD, box, "oxi_qkvg_create: q_proj is null")) ||
-            (rc = linear_map(&l->maps[4 * b + 1], wk, NKV * HD, box, "oxi_qkvg_create: k_proj is null")) ||
-            (rc = linear_map(&l->maps[4 * b + 2], wv, NKV * HD, box, "oxi_qkvg_create: v_proj is null")) ||
-            (rc = linear_map(&l->maps[4 * b + 3], wg, NQ, box, "oxi_qkvg_create: gate_proj is null")))
-            break;
-    }
-    if (rc != OXI_OK) {
+    if ((rc = linear_map(&l->maps[0], wq, NQ * HD, 128u, "oxi_qkvg_create: q_proj is null")) ||
+        (rc = linear_map(&l->maps[1], wk, NKV * HD, 128u, "oxi_qkvg_create: k_proj is null")) ||
+        (rc = linear_map(&l->maps[2], wv, NKV * HD, 128u, "oxi_qkvg_create: v_proj is null")) ||
+        (rc = linear_map(&l->maps[3], wg, NQ, 128u, "oxi_qkvg_create: gate_proj is null"))) {
         delete l;
         return rc;
     }
@@ -620,8 +615,7 @@ int32_t oxi_linear_create(oxi_linear** out, const void* w, uint32_t out_features
     if (out_features == 0 || out_features > (1u << 20)) return fail(OXI_ERR_ARG, "oxi_linear_create: out_features out of range");
     oxi_linear_s* l = new (std::nothrow) oxi_linear_s();
     if (!l) return fail(OXI_ERR_WORKSPACE, "oxi_linear_create: host allocation failed");
-    int32_t rc = linear_map(&l->maps[0], w, out_features, 128u, "oxi_linear_create: weights are null");
-    if (rc == OXI_OK) rc = linear_map(&l->maps[1], w, out_features, 256u, "oxi_linear_create: weights are null");
+    const int32_t rc = linear_map(&l->maps[0], w, out_features, 128u, "oxi_linear_create: weights are null");
     if (rc != OXI_OK) {
         delete l;
         return rc;

@@ -96,340 +96,33 @@ __device__ __forceinline__ void round16(const uint32_t (&acc)[16], uint16_t (&h)
         f[i] = h2f(h[i]);
     }
 }
+// 32 bytes per thread in one 256-bit access where the address allows it (half the instructions and half the L1
+// wavefronts of two 16-byte accesses: a thread of the epilogue works on its own row, so every lane touches another line)
+__device__ __forceinline__ void st_pairs(uint16_t* dst, const uint32_t (&w)[8]) {  // 16 f16 = 32 bytes, 16-byte aligned
+    if ((reinterpret_cast<uintptr_t>(dst) & 31u) == 0u) {
+        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]),
+                     "r"(w[5]), "r"(w[6]), "r"(w[7])
+                     : "memory");
+    } else {
+        reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+}
 __device__ __forceinline__ void store16(uint16_t* dst, const uint16_t (&h)[16]) {  // 32 bytes, 16-byte aligned
-    uint4 a, b;
-    a.x = h[0] | ((uint32_t)h[1] << 16);   a.y = h[2] | ((uint32_t)h[3] << 16);
-    a.z = h[4] | ((uint32_t)h[5] << 16);   a.w = h[6] | ((uint32_t)h[7] << 16);
-    b.x = h[8] | ((uint32_t)h[9] << 16);   b.y = h[10] | ((uint32_t)h[11] << 16);
-    b.z = h[12] | ((uint32_t)h[13] << 16); b.w = h[14] | ((uint32_t)h[15] << 16);
-    reinterpret_cast<uint4*>(dst)[0] = a;
-    reinterpret_cast<uint4*>(dst)[1] = b;
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) w[i] = h[2 * i] | ((uint32_t)h[2 * i + 1] << 16);
+    st_pairs(dst, w);
 }
-__device__ __forceinline__ void ld_pairs(const uint16_t* src, uint32_t (&w)[8]) {  // 16 f16 = 32 bytes, 16-byte aligned
-    const uint4 a = __ldg(reinterpret_cast<const uint4*>(src)), b = __ldg(reinterpret_cast<const uint4*>(src) + 1);
-    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
-    w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
-}
-__device__ __forceinline__ void st_pairs(uint16_t* dst, const uint32_t (&w)[8]) {
-    reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
-}
-
-// Epilogue of one 128-column group of an accumulator tile for one row (thread = row = TMEM lane):
-// t_row = the thread's TMEM lane base + the group's first column; ct = index of the group among the
-// output features in units of 128 (qkvg: 0-15 q heads, 16-19 k heads, 20-23 v heads, 24 gate).
-// Every lane of the warp must call it (the tensor-memory loads are warp-wide); `live` says whether the
-// row exists.
-template <bool kQkvg>
-__device__ __forceinline__ void proj_epilogue_cols(uint32_t t_row, uint32_t n_tile, uint32_t row, bool live, const ProjParams& p,
-                                                   const uint16_t* s_w) {
-    constexpr int BN = 128;
-    constexpr int N_QKVG = pg::N_QKVG;
-    // bounds build: a live thread's row exists and its feature group is one of the 25 (qkvg) / lies inside y (plain)
-    if (!OXI_IN_BOUNDS(!live || (row < p.rows && (kQkvg ? n_tile <= 24u : n_tile * 128u < p.out_features)), p.status)) live = false;
-    // the row's table entries (not written by any kernel)
-    uint32_t pos = 0;
-    uint64_t kvp = 0;
-    if (kQkvg && live) {
-        pos = p.pos_ids[row];
-        if (n_tile >= 16 && n_tile < 20) kvp = p.k_ptrs[row];
-        if (n_tile >= 20 && n_tile < 24) kvp = p.v_ptrs[row];
-    }
-    if (!kQkvg) {
-        // ---- plain linear layer: y[row][n] = f16(acc)
-#pragma unroll 1
-        for (int c = 0; c < BN / 16; c++) {
-            uint32_t acc[16];
-            tmem_ld16(t_row + c * 16, acc);
-            tmem_wait_ld();
-            const uint32_t n0 = n_tile * BN + c * 16;
-            if (live && n0 < p.out_features) {
-                uint16_t h[16];
-                float f[16];
-                round16(acc, h, f);
-                uint16_t* dst = p.y + (size_t)row * p.out_features + n0;
-                if (n0 + 16 <= p.out_features && (p.out_features & 7u) == 0u) {
-                    store16(dst, h);
-                } else {
-                    for (uint32_t i = 0; i < 16 && n0 + i < p.out_features; i++) dst[i] = h[i];
-                }
-            }
-        }
-    } else if (n_tile == 24) {
-        // ---- gate: 16 features
-        uint32_t acc[16];
-        tmem_ld16(t_row, acc);
-        tmem_wait_ld();
-        if (live) {
-            uint16_t h[16];
-            float f[16];
-            round16(acc, h, f);
-            store16(p.gate_out + (size_t)row * NQ, h);
-            if (p.raw_out) store16(p.raw_out + (size_t)row * N_QKVG + 3072, h);
-        }
-    } else if (n_tile >= 20) {
-        // ---- v head: the f16 projection is the cache row (batched_kv_copy_fp16 is a pure copy)
-        const uint32_t kvh = n_tile - 20;
-        const bool aligned = (kvp & 15ull) == 0ull;
-        if (live && !aligned && kvh == 0) atomicOr(p.status, DEV_MISALIGNED_PTR);
-        uint16_t* dst = reinterpret_cast<uint16_t*>(kvp + (size_t)pos * KV_ROW_BYTES) + kvh * HD;
-#pragma unroll 1
-        for (int c = 0; c < BN / 16; c++) {
-            uint32_t acc[16];
-            tmem_ld16(t_row + c * 16, acc);
-            tmem_wait_ld();
-            if (live) {
-                uint16_t h[16];
-                float f[16];
-                round16(acc, h, f);
-                if (aligned) store16(dst + c * 16, h);
-                if (p.raw_out) store16(p.raw_out + (size_t)row * N_QKVG + 2560 + kvh * HD + c * 16, h);
-            }
-        }
+__device__ __forceinline__ void ld_pairs(const uint16_t* src, uint32_t (&w)[8]) {  // read-only data; 16 f16 = 32 bytes, 16-byte aligned
+    if ((reinterpret_cast<uintptr_t>(src) & 31u) == 0u) {
+        asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+                     : "l"(src));
     } else {
-        // ---- q or k head: RMSNorm + RoPE on the f16 projections, the append kernel's arithmetic
-        const bool is_k = n_tile >= 16;
-        const uint32_t head = is_k ? n_tile - 16 : n_tile;
-        const uint16_t* wn = s_w + (is_k ? HD : 0);
-        const bool aligned = !is_k || (kvp & 15ull) == 0ull;
-        if (live && !aligned && head == 0) atomicOr(p.status, DEV_MISALIGNED_PTR);
-        // pass 1: partial[l] = sum over dims l, l+32, l+64, l+96 (in that order, fma), as lane l of the
-        // reference's warp forms it
-        float partial[32];
-#pragma unroll
-        for (int l = 0; l < 32; l++) partial[l] = 0.0f;
-#pragma unroll
-        for (int c = 0; c < BN / 16; c++) {
-            uint32_t acc[16];
-            tmem_ld16(t_row + c * 16, acc);
-            tmem_wait_ld();
-            uint16_t h[16];
-            float f[16];
-            round16(acc, h, f);
-#pragma unroll
-            for (int i = 0; i < 16; i++) partial[16 * (c & 1) + i] = __fmaf_rn(f[i], f[i], partial[16 * (c & 1) + i]);
-            if (live && p.raw_out)
-                store16(p.raw_out + (size_t)row * N_QKVG + (is_k ? 2048 : 0) + head * HD + c * 16, h);
-        }
-        // the shfl.down tree of the reference on one thread's registers: lane 0's value
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1)
-#pragma unroll
-            for (int l = 0; l < off; l++) partial[l] = __fadd_rn(partial[l], partial[l + off]);
-        float mean = div_approx_ftz(partial[0], 128.0f);
-        mean = __fadd_rn(mean, p.eps);
-        const float r = rsqrt_approx_ftz(mean);
-        // pass 2: dims [16j, 16j+16) pair with dims 64 + [16j, 16j+16)
-        const uint16_t* cs = p.cos_t + (size_t)pos * HD;
-        const uint16_t* sn = p.sin_t + (size_t)pos * HD;
-        uint16_t* dst = is_k ? reinterpret_cast<uint16_t*>(kvp + (size_t)pos * KV_ROW_BYTES) + head * HD
-                             : p.q_out + ((size_t)row * NQ + head) * HD;
-#pragma unroll 1
-        for (int j = 0; j < 4; j++) {
-            uint32_t alo[16], ahi[16];
-            tmem_ld16(t_row + j * 16, alo);
-            tmem_ld16(t_row + 64 + j * 16, ahi);
-            tmem_wait_ld();
-            if (!live) continue;
-            // cos / sin of the 16 + 16 dims as packed f16 pairs (two 16-byte loads each)
-            uint32_t clo[8], chi[8], slo[8], shi[8], olo[8], ohi[8];
-            ld_pairs(cs + j * 16, clo);
-            ld_pairs(cs + 64 + j * 16, chi);
-            ld_pairs(sn + j * 16, slo);
-            ld_pairs(sn + 64 + j * 16, shi);
-#pragma unroll
-            for (int i = 0; i < 16; i++) {
-                const float xlo = h2f(f2h(__uint_as_float(alo[i]))), xhi = h2f(f2h(__uint_as_float(ahi[i])));
-                // y = f16((x * r) * w): two separate multiplies, then the f16 round trip
-                const float ylo = h2f(f2h(__fmul_rn(__fmul_rn(xlo, r), h2f(wn[j * 16 + i]))));
-                const float yhi = h2f(f2h(__fmul_rn(__fmul_rn(xhi, r), h2f(wn[64 + j * 16 + i]))));
-                const int wd = i >> 1, sh = (i & 1) * 16;
-                const float c_lo = h2f((uint16_t)(clo[wd] >> sh)), c_hi = h2f((uint16_t)(chi[wd] >> sh));
-                const float s_lo = h2f((uint16_t)(slo[wd] >> sh)), s_hi = h2f((uint16_t)(shi[wd] >> sh));
-                // rotate-half: out[d] = fma(-y[d+64], sin[d], y[d]*cos[d]);  out[d+64] = fma(y[d], sin[d+64], y[d+64]*cos[d+64])
-                const uint32_t o_lo = f2h(__fmaf_rn(-yhi, s_lo, __fmul_rn(ylo, c_lo)));
-                const uint32_t o_hi = f2h(__fmaf_rn(ylo, s_hi, __fmul_rn(yhi, c_hi)));
-                if (i & 1) {
-                    olo[wd] |= o_lo << 16;
-                    ohi[wd] |= o_hi << 16;
-                } else {
-                    olo[wd] = o_lo;
-                    ohi[wd] = o_hi;
-                }
-            }
-            if (aligned) {
-                st_pairs(dst + j * 16, olo);
-                st_pairs(dst + 64 + j * 16, ohi);
-            }
-        }
-    }
-}
-
-// ---------------------------------------------------------------------------------------------------
-// The same GEMM for waves of rows (prefill): persistent, one CTA per SM, tiles of 128 rows x 256 features
-// (two heads), a ring of four 48 KB stages, and TWO accumulators in tensor memory (2 x 256 of the 512
-// columns) so that the epilogue of a tile runs while the tensor core works on the next one.
-// Why the larger tile: with 128 x 128 tiles every k-block of 4 MMAs needs 32 KB from L2 (64 flop per
-// byte); on the 4,096-row wave that kernel moved 11.7 TB/s from L2 into shared memory with the tensor
-// pipe 39 % busy.  128 x 256 tiles need a third less per flop and a stage feeds twice the MMA time, so the
-// same bytes in flight cover the L2 latency.
-namespace pgw {
-constexpr int BM = 128, BN = 256, BK = 64, NS = 4;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;  // 16 + 32 KB
-constexpr int THREADS = 320;  // TMA warp, MMA warp, 8 epilogue warps: two per TMEM lane quarter, one per head of the tile
-constexpr size_t SMEM_BYTES = 1024 + (size_t)NS * STAGE_BYTES;
-constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t IDESC_N256 = (1u << 4) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-constexpr uint32_t IDESC_N16 = (1u << 4) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);  // the gate tile
-constexpr int TILES_QKVG = 8 + 2 + 2 + 1;
-}  // namespace pgw
-
-template <bool kQkvg>
-__global__ void __launch_bounds__(pgw::THREADS, 1)
-proj_gemm_wave_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p, const uint32_t tiles_n, const uint32_t tiles_m) {
-    using namespace pgw;
-    constexpr int NKB = pg::NKB;
-    extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bar_full[NS], bar_empty[NS], bar_acc_full[2], bar_acc_empty[2];
-    __shared__ uint32_t s_tmem, s_abort;
-    __shared__ uint16_t s_w[2 * HD];
-
-    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const int tid = threadIdx.x, lane = tid & 31;
-    const int warp_u = __shfl_sync(0xffffffffu, tid >> 5, 0);
-
-    pdl_launch_dependents();
-    if (warp_u == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    if (tid == 0) {
-        for (int s = 0; s < NS; s++) {
-            mbar_init(&bar_full[s], 1);
-            mbar_init(&bar_empty[s], 1);
-        }
-        for (int b = 0; b < 2; b++) {
-            mbar_init(&bar_acc_full[b], 1);
-            mbar_init(&bar_acc_empty[b], 8);  // one arrival per epilogue warp
-        }
-        s_abort = 0u;
-        mbar_fence_init();
-    }
-    if (kQkvg && tid >= 64 && tid < 64 + HD) {
-        const int i = tid - 64;
-        s_w[i] = p.q_norm_w[i];
-        s_w[HD + i] = p.k_norm_w[i];
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem = s_tmem;
-    const uint32_t total = tiles_n * tiles_m;
-
-    // tile t: feature tile nt = t % tiles_n (fastest, so CTAs that run together share the rows' x tiles), row tile t / tiles_n
-    auto tile_weights = [&](uint32_t nt, uint32_t& wsel, uint32_t& wrow) {
-        wsel = 0;
-        wrow = nt * BN;
-        if (kQkvg) {
-            if (nt >= 12) { wsel = 3; wrow = 0; }
-            else if (nt >= 10) { wsel = 2; wrow = (nt - 10) * BN; }
-            else if (nt >= 8) { wsel = 1; wrow = (nt - 8) * BN; }
-        }
-    };
-
-    if (warp_u == 0) {
-        // ===================== TMA producer =====================
-        pdl_wait();  // x is written by the kernel before this one
-        bool ok = true;
-        uint32_t g = 0;  // k-blocks issued by this CTA so far (ring position)
-        for (uint32_t t = blockIdx.x; t < total && ok; t += gridDim.x) {
-            uint32_t wsel, wrow;
-            tile_weights(t % tiles_n, wsel, wrow);
-            const uint32_t mrow = (t / tiles_n) * BM;
-            for (uint32_t kb = 0; kb < (uint32_t)NKB; kb++, g++) {
-                const uint32_t s = g % NS;
-                if (g >= (uint32_t)NS && !mbar_wait_bounded(&bar_empty[s], ((g / NS) & 1u) ^ 1u, &s_abort)) {
-                    ok = false;
-                    break;
-                }
-                if (lane == 0) {
-                    mbar_arrive_expect_tx(&bar_full[s], (uint32_t)STAGE_BYTES);
-                    tma_load_box(sbase + s * STAGE_BYTES, &maps.x, kb * BK, mrow, &bar_full[s]);
-                    tma_load_box(sbase + s * STAGE_BYTES + A_BYTES, &maps.w[wsel], kb * BK, wrow, &bar_full[s]);
-                }
-                __syncwarp();
-            }
-        }
-        if (!ok) {
-            if (lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
-            for (uint32_t k = g > (uint32_t)NS ? g - NS : 0; k < g; ++k)
-                mbar_wait_drain(&bar_full[k % NS], (k / NS) & 1u, WAIT_LIMIT_US);
-        }
-    } else if (warp_u == 1) {
-        // ===================== MMA issuer =====================
-        bool ok = true;
-        uint32_t g = 0, i = 0;
-        for (uint32_t t = blockIdx.x; t < total; t += gridDim.x, i++) {
-            const uint32_t buf = i & 1u;
-            const uint32_t idesc = (kQkvg && t % tiles_n == 12u) ? IDESC_N16 : IDESC_N256;
-            // the epilogue has drained this accumulator's previous tile
-            if (i >= 2u) ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(&bar_acc_empty[buf], ((i >> 1) & 1u) ^ 1u, &s_abort));
-            for (uint32_t kb = 0; kb < (uint32_t)NKB; kb++, g++) {
-                const uint32_t s = g % NS;
-                ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(&bar_full[s], (g / NS) & 1u, &s_abort));
-                tc_fence_after();
-                if (elect_one()) {
-                    const uint64_t ad = umma_desc(sbase + s * STAGE_BYTES, 16, 1024);
-                    const uint64_t bd = umma_desc(sbase + s * STAGE_BYTES + A_BYTES, 16, 1024);
-#pragma unroll
-                    for (int kk = 0; kk < BK / 16; kk++)
-                        umma_ss(tmem + buf * 256u, ad + (uint64_t)(kk * 2), bd + (uint64_t)(kk * 2), idesc,
-                                (kb | (uint32_t)kk) != 0u ? 1u : 0u);
-                    umma_commit(&bar_empty[s]);
-                    if (kb + 1 == (uint32_t)NKB && ok) umma_commit(&bar_acc_full[buf]);
-                }
-                __syncwarp();
-            }
-        }
-        if (!ok && lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
-    } else {
-        // ===================== epilogue warps: thread = one row of the tile, warp pair = the tile's two heads =====================
-        const uint32_t quarter = (uint32_t)warp_u & 3u;          // TMEM lanes this warp may read
-        const uint32_t group = ((uint32_t)warp_u - 2u) >> 2;     // which 128 features of the tile
-        bool ok = true;
-        uint32_t i = 0;
-        for (uint32_t t = blockIdx.x; t < total && ok; t += gridDim.x, i++) {
-            const uint32_t buf = i & 1u, nt = t % tiles_n;
-            const uint32_t row = (t / tiles_n) * BM + quarter * 32 + (uint32_t)lane;
-            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar_acc_full[buf], (i >> 1) & 1u, &s_abort));
-            tc_fence_after();
-            if (!ok) {
-                if (lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
-                break;
-            }
-            const uint32_t t_row = tmem + ((quarter * 32) << 16) + buf * 256u;
-            // the tile's two groups of 128 features (qkvg: two heads; the gate tile has one group)
-            uint32_t ct0 = 2u * nt;
-            bool two = true;
-            if (kQkvg) {
-                if (nt >= 12u) { ct0 = 24u; two = false; }
-                else if (nt >= 10u) ct0 = 20u + 2u * (nt - 10u);
-                else if (nt >= 8u) ct0 = 16u + 2u * (nt - 8u);
-            } else {
-                two = (ct0 + 1u) * 128u < p.out_features;
-            }
-            if (group == 0u || two) proj_epilogue_cols<kQkvg>(t_row + group * 128u, ct0 + group, row, row < p.rows, p, s_w);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bar_acc_empty[buf]);
-        }
-    }
-
-    tc_fence_before();
-    __syncthreads();
-    if (warp_u == 1) {
-        tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(src)), b = __ldg(reinterpret_cast<const uint4*>(src) + 1);
+        w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+        w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
     }
 }
 
@@ -647,7 +340,7 @@ proj_gemm_splitk_kernel(const __grid_constant__ ProjMaps maps, const ProjParams 
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[NS], bar_empty[NS], bar_acc;
     __shared__ uint32_t s_tmem, s_abort;
-    __shared__ uint16_t s_w[2 * HD];        // q and k norm weights
+    __shared__ __align__(16) uint16_t s_w[2 * HD];  // q and k norm weights
     __shared__ float s_part[32 * 32];       // RMSNorm partials: [reference lane][row of this CTA]
     __shared__ uint32_t s_peer_abort[pgs::KS];  // written by the peers: did CTA cc give up a wait
 
@@ -823,18 +516,410 @@ proj_gemm_splitk_kernel(const __grid_constant__ ProjMaps maps, const ProjParams 
     }
 }
 
+// Epilogue of one head (128 accumulator columns) of one row by TWO threads in two warps of the same TMEM lane quarter
+// (the wave kernels: one thread per row and head was a dependent chain of ~35 k clocks per tile, longer than the tile's
+// main loop).  Thread j (0 / 1) owns what lanes 16j .. 16j + 15 of the reference's warp own: dims l, l + 32, l + 64, l + 96
+// = accumulator columns [32g + 16j, 32g + 16j + 16) for g = 0 .. 3, so the RMSNorm partial sums are the reference's fma
+// chains, both members of every RoPE pair (d, d + 64) sit in one thread, and the two threads exchange their 16 partial sums
+// through shared memory (named barrier `bar_id` of their two warps) and each run the reference's shfl.down tree on all 32.
+// t_row = the thread's TMEM lane base + the head's first column; s_part = [32 reference lanes][32 rows] f32 of this pair of
+// warps.  Every lane of both warps must call it.
+template <bool kQkvg>
+__device__ __forceinline__ void proj_epilogue_half(uint32_t t_row, uint32_t j, uint32_t n_tile, uint32_t row, bool live, const ProjParams& p,
+                                                   const uint16_t* s_w, float* s_part, uint32_t bar_id) {
+    constexpr uint32_t N_QKVG = pg::N_QKVG;
+    const uint32_t lane = threadIdx.x & 31u;
+    if (!OXI_IN_BOUNDS(!live || (row < p.rows && (kQkvg ? n_tile <= 24u : n_tile * 128u < p.out_features)), p.status)) live = false;
+    if (!kQkvg) {
+        // ---- plain linear layer: y[row][n] = f16(acc)
+#pragma unroll 1
+        for (int g = 0; g < 4; g++) {
+            uint32_t acc[16];
+            tmem_ld16(t_row + 32u * g + 16u * j, acc);
+            tmem_wait_ld();
+            const uint32_t n0 = n_tile * 128u + 32u * g + 16u * j;
+            if (live && n0 < p.out_features) {
+                uint16_t h[16];
+                float f[16];
+                round16(acc, h, f);
+                uint16_t* dst = p.y + (size_t)row * p.out_features + n0;
+                if (n0 + 16 <= p.out_features && (p.out_features & 7u) == 0u) {
+                    store16(dst, h);
+                } else {
+                    for (uint32_t i = 0; i < 16 && n0 + i < p.out_features; i++) dst[i] = h[i];
+                }
+            }
+        }
+        return;
+    }
+    if (n_tile == 24u) {
+        // ---- gate: 16 features, all in thread 0's first group
+        if (j == 0u) {
+            uint32_t acc[16];
+            tmem_ld16(t_row, acc);
+            tmem_wait_ld();
+            if (live) {
+                uint16_t h[16];
+                float f[16];
+                round16(acc, h, f);
+                store16(p.gate_out + (size_t)row * NQ, h);
+                if (p.raw_out) store16(p.raw_out + (size_t)row * N_QKVG + 3072, h);
+            }
+        }
+        return;
+    }
+    uint32_t pos = 0;
+    uint64_t kvp = 0;
+    if (live) {
+        pos = p.pos_ids[row];
+        if (n_tile >= 16u && n_tile < 20u) kvp = p.k_ptrs[row];
+        if (n_tile >= 20u) kvp = p.v_ptrs[row];
+    }
+    if (n_tile >= 20u) {
+        // ---- v head: the f16 projection is the cache row
+        const uint32_t kvh = n_tile - 20u;
+        const bool aligned = (kvp & 15ull) == 0ull;
+        if (live && !aligned && kvh == 0u && j == 0u) atomicOr(p.status, DEV_MISALIGNED_PTR);
+        uint16_t* dst = reinterpret_cast<uint16_t*>(kvp + (size_t)pos * KV_ROW_BYTES) + kvh * HD;
+#pragma unroll 1
+        for (int g = 0; g < 4; g++) {
+            uint32_t acc[16];
+            tmem_ld16(t_row + 32u * g + 16u * j, acc);
+            tmem_wait_ld();
+            if (live) {
+                uint16_t h[16];
+                float f[16];
+                round16(acc, h, f);
+                const uint32_t d0 = 32u * g + 16u * j;
+                if (aligned) store16(dst + d0, h);
+                if (p.raw_out) store16(p.raw_out + (size_t)row * N_QKVG + 2560 + kvh * HD + d0, h);
+            }
+        }
+        return;
+    }
+    // ---- q or k head: RMSNorm + RoPE on the f16 projections, the append kernel's arithmetic
+    const bool is_k = n_tile >= 16u;
+    const uint32_t head = is_k ? n_tile - 16u : n_tile;
+    const uint16_t* wn = s_w + (is_k ? HD : 0);
+    const bool aligned = !is_k || (kvp & 15ull) == 0ull;
+    if (live && !aligned && head == 0u && j == 0u) atomicOr(p.status, DEV_MISALIGNED_PTR);
+    // the rotary values of the thread's first pair of groups are on their way while pass 1 runs
+    const uint16_t* cs = p.cos_t + (size_t)pos * HD;
+    const uint16_t* sn = p.sin_t + (size_t)pos * HD;
+    uint32_t clo[8], chi[8], slo[8], shi[8];
+    ld_pairs(cs + 16u * j, clo);
+    ld_pairs(cs + 64u + 16u * j, chi);
+    ld_pairs(sn + 16u * j, slo);
+    ld_pairs(sn + 64u + 16u * j, shi);
+    // pass 1: partial[i] = sum over dims l, l+32, l+64, l+96 (in that order, fma) for l = 16j + i
+    float partial[32];
+#pragma unroll
+    for (int i = 0; i < 16; i++) partial[i] = 0.0f;
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+        uint32_t acc[16];
+        tmem_ld16(t_row + 32u * g + 16u * j, acc);
+        tmem_wait_ld();
+        uint16_t h[16];
+        float f[16];
+        round16(acc, h, f);
+#pragma unroll
+        for (int i = 0; i < 16; i++) partial[i] = __fmaf_rn(f[i], f[i], partial[i]);
+        if (live && p.raw_out)
+            store16(p.raw_out + (size_t)row * N_QKVG + (is_k ? 2048 : 0) + head * HD + 32u * g + 16u * j, h);
+    }
+#pragma unroll
+    for (int i = 0; i < 16; i++) s_part[(16u * j + i) * 32u + lane] = partial[i];
+    asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");  // the two warps of this row quarter and head
+#pragma unroll
+    for (int l = 0; l < 32; l++) partial[l] = s_part[l * 32 + lane];
+    asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");  // both have read: the next tile may overwrite the partials
+    // the shfl.down tree of the reference on one thread's registers: lane 0's value
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1)
+#pragma unroll
+        for (int l = 0; l < off; l++) partial[l] = __fadd_rn(partial[l], partial[l + off]);
+    float mean = div_approx_ftz(partial[0], 128.0f);
+    mean = __fadd_rn(mean, p.eps);
+    const float r = rsqrt_approx_ftz(mean);
+    uint16_t* dst = is_k ? reinterpret_cast<uint16_t*>(kvp + (size_t)pos * KV_ROW_BYTES) + head * HD
+                         : p.q_out + ((size_t)row * NQ + head) * HD;
+    // pass 2: dims [dl, dl + 16) pair with dims 64 + [dl, dl + 16), dl = 32 pr + 16 j
+#pragma unroll
+    for (int pr = 0; pr < 2; pr++) {
+        const uint32_t dl = 32u * pr + 16u * j, dh = dl + 64u;
+        uint32_t alo[16], ahi[16];
+        tmem_ld16(t_row + dl, alo);
+        tmem_ld16(t_row + dh, ahi);
+        tmem_wait_ld();
+        uint32_t olo[8], ohi[8];
+        // the norm weights of the 16 + 16 dims as packed pairs: four 16-byte reads instead of 32 two-byte ones
+        const uint4 wl0 = *reinterpret_cast<const uint4*>(wn + dl), wl1 = *reinterpret_cast<const uint4*>(wn + dl + 8);
+        const uint4 wh0 = *reinterpret_cast<const uint4*>(wn + dh), wh1 = *reinterpret_cast<const uint4*>(wn + dh + 8);
+        const uint32_t wlo[8] = {wl0.x, wl0.y, wl0.z, wl0.w, wl1.x, wl1.y, wl1.z, wl1.w};
+        const uint32_t whi[8] = {wh0.x, wh0.y, wh0.z, wh0.w, wh1.x, wh1.y, wh1.z, wh1.w};
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const int wd = i >> 1, sh = (i & 1) * 16;
+            const float xlo = h2f(f2h(__uint_as_float(alo[i]))), xhi = h2f(f2h(__uint_as_float(ahi[i])));
+            // y = f16((x * r) * w): two separate multiplies, then the f16 round trip
+            const float ylo = h2f(f2h(__fmul_rn(__fmul_rn(xlo, r), h2f((uint16_t)(wlo[wd] >> sh)))));
+            const float yhi = h2f(f2h(__fmul_rn(__fmul_rn(xhi, r), h2f((uint16_t)(whi[wd] >> sh)))));
+            const float c_lo = h2f((uint16_t)(clo[wd] >> sh)), c_hi = h2f((uint16_t)(chi[wd] >> sh));
+            const float s_lo = h2f((uint16_t)(slo[wd] >> sh)), s_hi = h2f((uint16_t)(shi[wd] >> sh));
+            // rotate-half: out[d] = fma(-y[d+64], sin[d], y[d]*cos[d]);  out[d+64] = fma(y[d], sin[d+64], y[d+64]*cos[d+64])
+            const uint32_t o_lo = f2h(__fmaf_rn(-yhi, s_lo, __fmul_rn(ylo, c_lo)));
+            const uint32_t o_hi = f2h(__fmaf_rn(ylo, s_hi, __fmul_rn(yhi, c_hi)));
+            if (i & 1) {
+                olo[wd] |= o_lo << 16;
+                ohi[wd] |= o_hi << 16;
+            } else {
+                olo[wd] = o_lo;
+                ohi[wd] = o_hi;
+            }
+        }
+        if (pr == 0) {  // the second pair's rotary values
+            ld_pairs(cs + 32u + 16u * j, clo);
+            ld_pairs(cs + 96u + 16u * j, chi);
+            ld_pairs(sn + 32u + 16u * j, slo);
+            ld_pairs(sn + 96u + 16u * j, shi);
+        }
+        if (live && aligned) {
+            st_pairs(dst + dl, olo);
+            st_pairs(dst + dh, ohi);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Waves of rows on CTA PAIRS: two CTAs of a cluster (two SMs) work on one 256-row x 256-feature tile with
+// tcgen05.mma.cta_group::2.  Each CTA keeps ITS 128 rows of x and ITS 128 of the tile's 256 weight rows in
+// shared memory (32 KB per 64-wide k-block instead of 48 KB for the same tensor-core time: the one-CTA
+// kernel above moves 682 MB from L2 into the SMs on the 4,096-row wave, which is what bounds it) and the
+// accumulator rows of its own 128 tokens in its own tensor memory, so the epilogue is unchanged.
+//   * CTA 0 of the pair (the leader) issues every MMA; the instruction reads both CTAs' shared memory at the
+//     same offsets.
+//   * Both CTAs' copies complete on the LEADER's "full" barrier of the stage (armed by the leader with the
+//     bytes of both); the leader's commit after a stage's MMAs arrives on the "empty" barrier of BOTH CTAs
+//     (two commits, the second with the peer's mapped address - no multicast anywhere), likewise "accumulator
+//     full"; the epilogue warps of both CTAs arrive on the leader's "accumulator empty" barrier.
+//   * Tensor memory is allocated and freed by the MMA warp of BOTH CTAs (cta_group::2 forms), the free after a
+//     cluster barrier that every thread reaches on every path (all other waits are bounded).
+namespace pgp {
+constexpr int BM = 128, BN_CTA = 128, BK = 64, NS = 5;   // per CTA: 128 rows of x, 128 weight rows; the pair: 256 x 256
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN_CTA * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;  // 16 + 16 KB
+constexpr int EPI_WARPS = 16;  // four per TMEM lane quarter: two heads of the tile x two threads per row and head
+constexpr int THREADS = 64 + 32 * EPI_WARPS;  // TMA warp, MMA warp, epilogue warps
+constexpr int PART_BYTES = 8 * 32 * 32 * 4;   // RMSNorm partial sums: [quarter][head of the tile][32 reference lanes][32 rows] f32
+constexpr size_t SMEM_BYTES = 1024 + (size_t)NS * STAGE_BYTES + PART_BYTES;
+constexpr uint32_t TMEM_COLS = 512;   // two accumulators of 256 columns
+constexpr uint32_t IDESC_N256 = (1u << 4) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);  // M = 256 over the pair
+constexpr uint32_t IDESC_N16 = (1u << 4) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);    // the gate tile
+constexpr int TILES_QKVG = 8 + 2 + 2 + 1;
+}  // namespace pgp
+
+__device__ __forceinline__ void umma_ss_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at shared::cluster address `bar` (own or the peer's) once all MMAs issued so far have completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// one box into this CTA's shared memory; completion counted on the barrier at shared::cluster address `bar`.  No multicast.
+__device__ __forceinline__ void tma_load_box_pair(uint32_t dst, const TmaDesc* map, uint32_t x, uint32_t y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <bool kQkvg>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pgp::THREADS, 1)
+proj_gemm_pair_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p, const uint32_t tiles_n, const uint32_t tiles_m2) {
+    using namespace pgp;
+    constexpr int NKB = pg::NKB;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[NS], bar_empty[NS], bar_acc_full[2], bar_acc_empty[2];
+    __shared__ uint32_t s_tmem, s_abort;
+    __shared__ __align__(16) uint16_t s_w[2 * HD];
+
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp_u = __shfl_sync(0xffffffffu, tid >> 5, 0);
+    const uint32_t crank = cluster_ctarank();     // 0: leader (issues the MMAs), 1: its peer
+    const uint32_t pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+    pdl_launch_dependents();
+    if (tid == 0) {
+        for (int s = 0; s < NS; s++) {
+            mbar_init(&bar_full[s], 1);    // used in the leader: its own arrive.expect_tx; both CTAs' copies complete on it
+            mbar_init(&bar_empty[s], 1);   // in both CTAs: one commit of the leader
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&bar_acc_full[b], 1);     // in both CTAs: one commit of the leader
+            mbar_init(&bar_acc_empty[b], 2 * EPI_WARPS);   // used in the leader: one arrival per epilogue warp of both CTAs
+        }
+        s_abort = 0u;
+        mbar_fence_init();
+    }
+    if (kQkvg && tid >= 64 && tid < 64 + HD) {
+        const int i = tid - 64;
+        s_w[i] = p.q_norm_w[i];
+        s_w[HD + i] = p.k_norm_w[i];
+    }
+    // the peer's barriers are initialised before anything of this CTA arrives on them
+    __syncwarp();
+    cluster_sync_all();
+    if (warp_u == 1) {  // the MMA warp of BOTH CTAs: the pair's tensor memory is allocated together
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = s_tmem;
+    const uint32_t total = tiles_n * tiles_m2;
+
+    // pair tile t: feature tile nt = t % tiles_n (256 features; fastest), row tile t / tiles_n (256 rows)
+    auto tile_weights = [&](uint32_t nt, uint32_t& wsel, uint32_t& wrow) {   // this CTA's 128 weight rows (8 of the gate's 16)
+        wsel = 0;
+        wrow = nt * 256u + crank * 128u;
+        if (kQkvg) {
+            if (nt >= 12) { wsel = 3; wrow = crank * 8u; }
+            else if (nt >= 10) { wsel = 2; wrow = (nt - 10) * 256u + crank * 128u; }
+            else if (nt >= 8) { wsel = 1; wrow = (nt - 8) * 256u + crank * 128u; }
+        }
+    };
+
+    if (warp_u == 0) {
+        // ===================== TMA producer (both CTAs) =====================
+        pdl_wait();  // x is written by the kernel before this one
+        bool ok = true;
+        uint32_t g = 0;
+        for (uint32_t t = pair; t < total && ok; t += npairs) {
+            uint32_t wsel, wrow;
+            tile_weights(t % tiles_n, wsel, wrow);
+            const uint32_t mrow = (t / tiles_n) * 256u + crank * 128u;
+            for (uint32_t kb = 0; kb < (uint32_t)NKB; kb++, g++) {
+                const uint32_t s = g % NS;
+                if (g >= (uint32_t)NS && !mbar_wait_bounded(&bar_empty[s], ((g / NS) & 1u) ^ 1u, &s_abort)) {
+                    ok = false;
+                    break;
+                }
+                if (lane == 0) {
+                    const uint32_t full = dsmem_addr(smem_u32(&bar_full[s]), 0u);   // the leader's barrier
+                    if (crank == 0u) mbar_arrive_expect_tx(&bar_full[s], 2u * (uint32_t)STAGE_BYTES);
+                    tma_load_box_pair(sbase + s * STAGE_BYTES, &maps.x, kb * BK, mrow, full);
+                    tma_load_box_pair(sbase + s * STAGE_BYTES + A_BYTES, &maps.w[wsel], kb * BK, wrow, full);
+                }
+                __syncwarp();
+            }
+        }
+        if (!ok) {
+            if (lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
+            // copies already issued complete on the leader's barriers, which the peer cannot poll: give them time to
+            // land before the shared memory is released (they take microseconds)
+            const uint64_t t0 = global_timer_ns();
+            while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
+    } else if (warp_u == 1) {
+        // ===================== MMA issuer (the leader only) =====================
+        if (crank == 0u) {
+            bool ok = true;
+            uint32_t g = 0, i = 0;
+            for (uint32_t t = pair; t < total; t += npairs, i++) {
+                const uint32_t buf = i & 1u;
+                const uint32_t idesc = (kQkvg && t % tiles_n == 12u) ? IDESC_N16 : IDESC_N256;
+                if (i >= 2u) ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(&bar_acc_empty[buf], ((i >> 1) & 1u) ^ 1u, &s_abort));
+                for (uint32_t kb = 0; kb < (uint32_t)NKB; kb++, g++) {
+                    const uint32_t s = g % NS;
+                    ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(&bar_full[s], (g / NS) & 1u, &s_abort));
+                    tc_fence_after();
+                    if (elect_one()) {
+                        const uint64_t ad = umma_desc(sbase + s * STAGE_BYTES, 16, 1024);
+                        const uint64_t bd = umma_desc(sbase + s * STAGE_BYTES + A_BYTES, 16, 1024);
+#pragma unroll
+                        for (int kk = 0; kk < BK / 16; kk++)
+                            umma_ss_pair(tmem + buf * 256u, ad + (uint64_t)(kk * 2), bd + (uint64_t)(kk * 2), idesc,
+                                         (kb | (uint32_t)kk) != 0u ? 1u : 0u);
+                        umma_commit_pair(smem_u32(&bar_empty[s]));
+                        umma_commit_pair(dsmem_addr(smem_u32(&bar_empty[s]), 1u));
+                        if (kb + 1 == (uint32_t)NKB && ok) {
+                            umma_commit_pair(smem_u32(&bar_acc_full[buf]));
+                            umma_commit_pair(dsmem_addr(smem_u32(&bar_acc_full[buf]), 1u));
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+            if (!ok && lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
+        }
+    } else {
+        // ===================== epilogue warps (both CTAs): four warps per TMEM lane quarter = (head of the tile, half of the
+        // head's reference lanes); thread = one row of this CTA's 128
+        const uint32_t quarter = (uint32_t)warp_u & 3u;
+        const uint32_t group = (((uint32_t)warp_u - 2u) >> 2) & 1u, half = ((uint32_t)warp_u - 2u) >> 3;
+        float* s_part = reinterpret_cast<float*>(smem_raw + (sbase - smem_u32(smem_raw)) + (size_t)NS * STAGE_BYTES) +
+                        (quarter * 2u + group) * 1024u;
+        const uint32_t bar_id = 1u + quarter * 2u + group;
+        const uint32_t acc_empty0 = dsmem_addr(smem_u32(&bar_acc_empty[0]), 0u), acc_empty1 = dsmem_addr(smem_u32(&bar_acc_empty[1]), 0u);
+        bool ok = true;
+        uint32_t i = 0;
+        for (uint32_t t = pair; t < total && ok; t += npairs, i++) {
+            const uint32_t buf = i & 1u, nt = t % tiles_n;
+            const uint32_t row = (t / tiles_n) * 256u + crank * 128u + quarter * 32 + (uint32_t)lane;
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar_acc_full[buf], (i >> 1) & 1u, &s_abort));
+            tc_fence_after();
+            if (!ok) {
+                if (lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
+                break;
+            }
+            const uint32_t t_row = tmem + ((quarter * 32) << 16) + buf * 256u;
+            uint32_t ct0 = 2u * nt;
+            bool two = true;
+            if (kQkvg) {
+                if (nt >= 12u) { ct0 = 24u; two = false; }
+                else if (nt >= 10u) ct0 = 20u + 2u * (nt - 10u);
+                else if (nt >= 8u) ct0 = 16u + 2u * (nt - 8u);
+            } else {
+                two = (ct0 + 1u) * 128u < p.out_features;
+            }
+            if (group == 0u || two)
+                proj_epilogue_half<kQkvg>(t_row + group * 128u, half, ct0 + group, row, row < p.rows, p, s_w, s_part, bar_id);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(buf ? acc_empty1 : acc_empty0);
+        }
+    }
+
+    // every thread of both CTAs: nothing of the pair is in flight any more (or a wait ran out and was recorded)
+    tc_fence_before();
+    __syncwarp();
+    cluster_sync_all();
+    if (warp_u == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 cudaError_t proj_gemm_init() {
     cudaError_t e = cudaFuncSetAttribute(proj_gemm_splitk_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pgs::SMEM_BYTES);
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(proj_gemm_splitk_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pgs::SMEM_BYTES);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(proj_gemm_wave_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pgw::SMEM_BYTES);
+        e = cudaFuncSetAttribute(proj_gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pgp::SMEM_BYTES);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(proj_gemm_wave_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pgw::SMEM_BYTES);
+        e = cudaFuncSetAttribute(proj_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pgp::SMEM_BYTES);
     return e;
 }
 
-// Encodes a tiled map over a row-major [rows][2048] f16 matrix: box = 64 elements x box_rows (128 or 256) rows, 128-byte swizzle,
+// Encodes a tiled map over a row-major [rows][2048] f16 matrix: box = 64 elements x box_rows rows, 128-byte swizzle,
 // rows beyond the matrix read as zeros.  Pure host work, no allocation.
 int proj_encode_map(TmaDesc* out, const void* base, uint64_t rows, uint32_t box_rows) {
     typedef CUresult (*encode_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -865,14 +950,13 @@ int proj_encode_map(TmaDesc* out, const void* base, uint64_t rows, uint32_t box_
 // 768 rows 27.6 / 18.1 against 23.5 / 15.4.
 constexpr uint32_t PROJ_SMALL_ROWS = 512;
 
-cudaError_t launch_project_append(cudaStream_t stream, const TmaDesc* w_maps /* q, k, v, gate; box 128 then box 256 */, int num_sms, const void* x, uint32_t rows,
+cudaError_t launch_project_append(cudaStream_t stream, const TmaDesc* w_maps /* q, k, v, gate */, int num_sms, const void* x, uint32_t rows,
                                   void* q_out, void* gate_out, void* raw_out, const void* q_norm_w, const void* k_norm_w,
                                   const void* cos_t, const void* sin_t, const uint32_t* pos_ids, const uint64_t* k_ptrs,
                                   const uint64_t* v_ptrs, float eps, uint32_t* status) {
     ProjMaps maps;
     if (proj_encode_map(&maps.x, x, rows, pg::BM) != 0) return cudaErrorInvalidValue;
-    const bool wave = rows > PROJ_SMALL_ROWS;
-    for (int i = 0; i < 4; i++) maps.w[i] = w_maps[wave ? 4 + i : i];
+    for (int i = 0; i < 4; i++) maps.w[i] = w_maps[i];
     ProjParams p = {};
     p.rows = rows;
     p.q_out = (uint16_t*)q_out;
@@ -887,33 +971,34 @@ cudaError_t launch_project_append(cudaStream_t stream, const TmaDesc* w_maps /* 
     p.v_ptrs = v_ptrs;
     p.status = status;
     p.eps = eps;
-    const uint32_t tiles_m = (rows + pg::BM - 1) / pg::BM;
-    if (wave) {
-        const uint32_t total = (uint32_t)pgw::TILES_QKVG * tiles_m;
-        return launch_pdl(proj_gemm_wave_kernel<true>, dim3(total < (uint32_t)num_sms ? total : (uint32_t)num_sms),
-                          dim3(pgw::THREADS), pgw::SMEM_BYTES, stream, maps, p, (uint32_t)pgw::TILES_QKVG, tiles_m);
+    if (rows > PROJ_SMALL_ROWS) {
+        const uint32_t tiles_m2 = (rows + 255u) / 256u, total = (uint32_t)pgp::TILES_QKVG * tiles_m2;
+        const uint32_t pairs = total < (uint32_t)num_sms / 2u ? total : (uint32_t)num_sms / 2u;
+        return launch_pdl(proj_gemm_pair_kernel<true>, dim3(2u * pairs), dim3(pgp::THREADS), pgp::SMEM_BYTES, stream, maps, p,
+                          (uint32_t)pgp::TILES_QKVG, tiles_m2);
     }
+    const uint32_t tiles_m = (rows + pg::BM - 1) / pg::BM;
     return launch_pdl(proj_gemm_splitk_kernel<true>, dim3(pg::TILES_QKVG * pgs::KS, tiles_m), dim3(pgs::THREADS), pgs::SMEM_BYTES, stream,
                       maps, p);
 }
 
-cudaError_t launch_linear(cudaStream_t stream, const TmaDesc* w_maps /* box 128, box 256 */, int num_sms, uint32_t out_features,
-                          const void* x, uint32_t rows, void* y, uint32_t* status) {
+cudaError_t launch_linear(cudaStream_t stream, const TmaDesc* w_map, int num_sms, uint32_t out_features, const void* x, uint32_t rows,
+                          void* y, uint32_t* status) {
     ProjMaps maps;
     if (proj_encode_map(&maps.x, x, rows, pg::BM) != 0) return cudaErrorInvalidValue;
-    const bool wave = rows > PROJ_SMALL_ROWS;
-    maps.w[0] = maps.w[1] = maps.w[2] = maps.w[3] = w_maps[wave ? 1 : 0];
+    maps.w[0] = maps.w[1] = maps.w[2] = maps.w[3] = *w_map;
     ProjParams p = {};
     p.rows = rows;
     p.out_features = out_features;
     p.y = (uint16_t*)y;
     p.status = status;
-    const uint32_t tiles_m = (rows + pg::BM - 1) / pg::BM;
-    if (wave) {
-        const uint32_t tiles_n = (out_features + pgw::BN - 1) / pgw::BN, total = tiles_n * tiles_m;
-        return launch_pdl(proj_gemm_wave_kernel<false>, dim3(total < (uint32_t)num_sms ? total : (uint32_t)num_sms),
-                          dim3(pgw::THREADS), pgw::SMEM_BYTES, stream, maps, p, tiles_n, tiles_m);
+    if (rows > PROJ_SMALL_ROWS) {
+        const uint32_t tiles_n = (out_features + 255u) / 256u, tiles_m2 = (rows + 255u) / 256u, total = tiles_n * tiles_m2;
+        const uint32_t pairs = total < (uint32_t)num_sms / 2u ? total : (uint32_t)num_sms / 2u;
+        return launch_pdl(proj_gemm_pair_kernel<false>, dim3(2u * pairs), dim3(pgp::THREADS), pgp::SMEM_BYTES, stream, maps, p, tiles_n,
+                          tiles_m2);
     }
+    const uint32_t tiles_m = (rows + pg::BM - 1) / pg::BM;
     return launch_pdl(proj_gemm_splitk_kernel<false>, dim3((out_features + pg::BN - 1) / pg::BN * pgs::KS, tiles_m), dim3(pgs::THREADS),
                       pgs::SMEM_BYTES, stream, maps, p);
 }
