@@ -706,7 +706,10 @@ __device__ __forceinline__ void proj_epilogue_half(uint32_t t_row, uint32_t j, u
 //   * Tensor memory is allocated and freed by the MMA warp of BOTH CTAs (cta_group::2 forms), the free after a
 //     cluster barrier that every thread reaches on every path (all other waits are bounded).
 namespace pgp {
-constexpr int BM = 128, BN_CTA = 128, BK = 64, NS = 5;   // per CTA: 128 rows of x, 128 weight rows; the pair: 256 x 256
+constexpr int BM = 128, BN_CTA = 128, BK = 64;            // per CTA: 128 rows of x, 128 weight rows; the pair: 256 x 256
+// ring stages: measured on the 4,096-row wave 2: 63.3 us, 3: 46.7, 4: 45.2, 5: 46.0, 6: 47.9 - beyond four stages the shared memory
+// taken from the L1 cache costs more (the epilogue's rotary-table reads miss) than the deeper ring gains
+constexpr int NS = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN_CTA * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;  // 16 + 16 KB
 constexpr int EPI_WARPS = 16;  // four per TMEM lane quarter: two heads of the tile x two threads per row and head
 constexpr int THREADS = 64 + 32 * EPI_WARPS;  // TMA warp, MMA warp, epilogue warps
