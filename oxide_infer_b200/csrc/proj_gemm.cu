@@ -21,13 +21,13 @@
 //     finish a row's head.  8.9 us at 128 rows, where one CTA per tile needed 15.1 us (it has to pull
 //     1 MB through one SM's port while 123 SMs idle) and a split of k that met in an L2 workspace
 //     16-18 us.
-//   * proj_gemm_wave_kernel (larger waves): persistent, 128 x 256 tiles, two accumulators; thread = one
-//     row of the tile (its TMEM lane), so a thread holds a whole head of its token.
+//   * proj_gemm_pair_kernel (larger waves): persistent CTA pairs on 256 x 256 tiles (tcgen05.mma.cta_group::2),
+//     two accumulators per CTA, sixteen epilogue warps (two threads per row and head).
 //
 // Bit parity.  The projections are rounded to f16 exactly as the reference's GEMM output is, and
 // the epilogue applies the append kernel's arithmetic to those f16 values: the RMSNorm sum is formed
 // in the reference's order (32 partial sums over dims l, l+32, l+64, l+96 with fma, then the
-// shfl.down tree 16, 8, 4, 2, 1 - here as the same additions on 32 registers of one thread),
+// shfl.down tree 16, 8, 4, 2, 1 - here as the same additions on 32 registers of a thread),
 // div.approx / rsqrt.approx, two separate multiplies, f16 round trip, then mul + fma for RoPE.  Given
 // the same f16 projections, q and the cache rows are the bytes oxi_append writes.
 #include <cuda.h>  // CUtensorMap and its enums only
@@ -516,9 +516,11 @@ proj_gemm_splitk_kernel(const __grid_constant__ ProjMaps maps, const ProjParams 
     }
 }
 
-// Epilogue of one head (128 accumulator columns) of one row by TWO threads in two warps of the same TMEM lane quarter
-// (the wave kernels: one thread per row and head was a dependent chain of ~35 k clocks per tile, longer than the tile's
-// main loop).  Thread j (0 / 1) owns what lanes 16j .. 16j + 15 of the reference's warp own: dims l, l + 32, l + 64, l + 96
+// Epilogue of one head (128 accumulator columns) of one row by TWO threads in two warps of the same TMEM lane quarter.
+// What the epilogue costs is the number of its memory accesses rather than its arithmetic: a thread works on its own row,
+// so each lane of a load or store touches another line and every access is one wavefront of the L1 data pipe that the TMA
+// fills and the tensor core's operand reads keep busy; hence 32 bytes per global access and packed reads of the weights.
+// Thread j (0 / 1) owns what lanes 16j .. 16j + 15 of the reference's warp own: dims l, l + 32, l + 64, l + 96
 // = accumulator columns [32g + 16j, 32g + 16j + 16) for g = 0 .. 3, so the RMSNorm partial sums are the reference's fma
 // chains, both members of every RoPE pair (d, d + 64) sit in one thread, and the two threads exchange their 16 partial sums
 // through shared memory (named barrier `bar_id` of their two warps) and each run the reference's shfl.down tree on all 32.
@@ -694,9 +696,9 @@ __device__ __forceinline__ void proj_epilogue_half(uint32_t t_row, uint32_t j, u
 // ---------------------------------------------------------------------------------------------------
 // Waves of rows on CTA PAIRS: two CTAs of a cluster (two SMs) work on one 256-row x 256-feature tile with
 // tcgen05.mma.cta_group::2.  Each CTA keeps ITS 128 rows of x and ITS 128 of the tile's 256 weight rows in
-// shared memory (32 KB per 64-wide k-block instead of 48 KB for the same tensor-core time: the one-CTA
-// kernel above moves 682 MB from L2 into the SMs on the 4,096-row wave, which is what bounds it) and the
-// accumulator rows of its own 128 tokens in its own tensor memory, so the epilogue is unchanged.
+// shared memory (32 KB per 64-wide k-block, where one CTA on a 128 x 256 tile needs 48 KB for the same
+// tensor-core time: 477 instead of 682 MB from L2 into the SMs on the 4,096-row wave) and the accumulator rows
+// of its own 128 tokens in its own tensor memory.
 //   * CTA 0 of the pair (the leader) issues every MMA; the instruction reads both CTAs' shared memory at the
 //     same offsets.
 //   * Both CTAs' copies complete on the LEADER's "full" barrier of the stage (armed by the leader with the
