@@ -22,7 +22,7 @@
 //     1 MB through one SM's port while 123 SMs idle) and a split of k that met in an L2 workspace
 //     16-18 us.
 //   * proj_gemm_pair_kernel (larger waves): persistent CTA pairs on 256 x 256 tiles (tcgen05.mma.cta_group::2),
-//     two accumulators per CTA, sixteen epilogue warps (two threads per row and head).
+//     two accumulators per CTA, eight epilogue warps (two threads per row; a thread serves both heads of the tile).
 //
 // Bit parity.  The projections are rounded to f16 exactly as the reference's GEMM output is, and
 // the epilogue applies the append kernel's arithmetic to those f16 values: the RMSNorm sum is formed
@@ -516,7 +516,8 @@ proj_gemm_splitk_kernel(const __grid_constant__ ProjMaps maps, const ProjParams 
     }
 }
 
-// Epilogue of one head (128 accumulator columns) of one row by TWO threads in two warps of the same TMEM lane quarter.
+// Epilogue of one head (128 accumulator columns) of one row by TWO threads in two warps of the same TMEM lane quarter
+// (a thread serves both heads of a tile, one after the other, with one set of rotary values).
 // What the epilogue costs is the number of its memory accesses rather than its arithmetic: a thread works on its own row,
 // so each lane of a load or store touches another line and every access is one wavefront of the L1 data pipe that the TMA
 // fills and the tensor core's operand reads keep busy; hence 32 bytes per global access and packed reads of the weights.
@@ -526,9 +527,14 @@ proj_gemm_splitk_kernel(const __grid_constant__ ProjMaps maps, const ProjParams 
 // through shared memory (named barrier `bar_id` of their two warps) and each run the reference's shfl.down tree on all 32.
 // t_row = the thread's TMEM lane base + the head's first column; s_part = [32 reference lanes][32 rows] f32 of this pair of
 // warps.  Every lane of both warps must call it.
+// The rotary values of a thread's 64 dims: [pair of column groups][cos low, cos high, sin low, sin high][8 packed pairs].
+// They depend on the row only, so the caller fetches them once per tile for both heads.
+struct RotRegs {
+    uint32_t v[2][4][8];
+};
 template <bool kQkvg>
 __device__ __forceinline__ void proj_epilogue_half(uint32_t t_row, uint32_t j, uint32_t n_tile, uint32_t row, bool live, const ProjParams& p,
-                                                   const uint16_t* s_w, float* s_part, uint32_t bar_id) {
+                                                   const uint16_t* s_w, float* s_part, uint32_t bar_id, uint32_t pos, const RotRegs& rot) {
     constexpr uint32_t N_QKVG = pg::N_QKVG;
     const uint32_t lane = threadIdx.x & 31u;
     if (!OXI_IN_BOUNDS(!live || (row < p.rows && (kQkvg ? n_tile <= 24u : n_tile * 128u < p.out_features)), p.status)) live = false;
@@ -570,10 +576,8 @@ __device__ __forceinline__ void proj_epilogue_half(uint32_t t_row, uint32_t j, u
         }
         return;
     }
-    uint32_t pos = 0;
     uint64_t kvp = 0;
     if (live) {
-        pos = p.pos_ids[row];
         if (n_tile >= 16u && n_tile < 20u) kvp = p.k_ptrs[row];
         if (n_tile >= 20u) kvp = p.v_ptrs[row];
     }
@@ -605,14 +609,6 @@ __device__ __forceinline__ void proj_epilogue_half(uint32_t t_row, uint32_t j, u
     const uint16_t* wn = s_w + (is_k ? HD : 0);
     const bool aligned = !is_k || (kvp & 15ull) == 0ull;
     if (live && !aligned && head == 0u && j == 0u) atomicOr(p.status, DEV_MISALIGNED_PTR);
-    // the rotary values of the thread's first pair of groups are on their way while pass 1 runs
-    const uint16_t* cs = p.cos_t + (size_t)pos * HD;
-    const uint16_t* sn = p.sin_t + (size_t)pos * HD;
-    uint32_t clo[8], chi[8], slo[8], shi[8];
-    ld_pairs(cs + 16u * j, clo);
-    ld_pairs(cs + 64u + 16u * j, chi);
-    ld_pairs(sn + 16u * j, slo);
-    ld_pairs(sn + 64u + 16u * j, shi);
     // pass 1: partial[i] = sum over dims l, l+32, l+64, l+96 (in that order, fma) for l = 16j + i
     float partial[32];
 #pragma unroll
@@ -667,8 +663,8 @@ __device__ __forceinline__ void proj_epilogue_half(uint32_t t_row, uint32_t j, u
             // y = f16((x * r) * w): two separate multiplies, then the f16 round trip
             const float ylo = h2f(f2h(__fmul_rn(__fmul_rn(xlo, r), h2f((uint16_t)(wlo[wd] >> sh)))));
             const float yhi = h2f(f2h(__fmul_rn(__fmul_rn(xhi, r), h2f((uint16_t)(whi[wd] >> sh)))));
-            const float c_lo = h2f((uint16_t)(clo[wd] >> sh)), c_hi = h2f((uint16_t)(chi[wd] >> sh));
-            const float s_lo = h2f((uint16_t)(slo[wd] >> sh)), s_hi = h2f((uint16_t)(shi[wd] >> sh));
+            const float c_lo = h2f((uint16_t)(rot.v[pr][0][wd] >> sh)), c_hi = h2f((uint16_t)(rot.v[pr][1][wd] >> sh));
+            const float s_lo = h2f((uint16_t)(rot.v[pr][2][wd] >> sh)), s_hi = h2f((uint16_t)(rot.v[pr][3][wd] >> sh));
             // rotate-half: out[d] = fma(-y[d+64], sin[d], y[d]*cos[d]);  out[d+64] = fma(y[d], sin[d+64], y[d+64]*cos[d+64])
             const uint32_t o_lo = f2h(__fmaf_rn(-yhi, s_lo, __fmul_rn(ylo, c_lo)));
             const uint32_t o_hi = f2h(__fmaf_rn(ylo, s_hi, __fmul_rn(yhi, c_hi)));
@@ -679,12 +675,6 @@ __device__ __forceinline__ void proj_epilogue_half(uint32_t t_row, uint32_t j, u
                 olo[wd] = o_lo;
                 ohi[wd] = o_hi;
             }
-        }
-        if (pr == 0) {  // the second pair's rotary values
-            ld_pairs(cs + 32u + 16u * j, clo);
-            ld_pairs(cs + 96u + 16u * j, chi);
-            ld_pairs(sn + 32u + 16u * j, slo);
-            ld_pairs(sn + 96u + 16u * j, shi);
         }
         if (live && aligned) {
             st_pairs(dst + dl, olo);
@@ -709,13 +699,13 @@ __device__ __forceinline__ void proj_epilogue_half(uint32_t t_row, uint32_t j, u
 //     cluster barrier that every thread reaches on every path (all other waits are bounded).
 namespace pgp {
 constexpr int BM = 128, BN_CTA = 128, BK = 64;            // per CTA: 128 rows of x, 128 weight rows; the pair: 256 x 256
-// ring stages: measured on the 4,096-row wave 2: 63.3 us, 3: 46.7, 4: 45.2, 5: 46.0, 6: 47.9 - beyond four stages the shared memory
-// taken from the L1 cache costs more (the epilogue's rotary-table reads miss) than the deeper ring gains
+// ring stages: measured on the 4,096-row wave 2: 63.3 us, 3: 46.7, 4: 45.2, 5: 46.0, 6: 47.9 (with the rotary values fetched once per
+// tile for both heads: 4: 44.3, 5: 44.5, 6: 45.3) - four stages cover the latency, more shared memory only shrinks the L1 cache
 constexpr int NS = 4;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN_CTA * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;  // 16 + 16 KB
-constexpr int EPI_WARPS = 16;  // four per TMEM lane quarter: two heads of the tile x two threads per row and head
+constexpr int EPI_WARPS = 8;   // two per TMEM lane quarter: two threads per row, each serving both heads of the tile
 constexpr int THREADS = 64 + 32 * EPI_WARPS;  // TMA warp, MMA warp, epilogue warps
-constexpr int PART_BYTES = 8 * 32 * 32 * 4;   // RMSNorm partial sums: [quarter][head of the tile][32 reference lanes][32 rows] f32
+constexpr int PART_BYTES = 4 * 32 * 32 * 4;   // RMSNorm partial sums: [quarter][32 reference lanes][32 rows] f32
 constexpr size_t SMEM_BYTES = 1024 + (size_t)NS * STAGE_BYTES + PART_BYTES;
 constexpr uint32_t TMEM_COLS = 512;   // two accumulators of 256 columns
 constexpr uint32_t IDESC_N256 = (1u << 4) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);  // M = 256 over the pair
@@ -866,13 +856,11 @@ proj_gemm_pair_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p,
             if (!ok && lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
         }
     } else {
-        // ===================== epilogue warps (both CTAs): four warps per TMEM lane quarter = (head of the tile, half of the
-        // head's reference lanes); thread = one row of this CTA's 128
-        const uint32_t quarter = (uint32_t)warp_u & 3u;
-        const uint32_t group = (((uint32_t)warp_u - 2u) >> 2) & 1u, half = ((uint32_t)warp_u - 2u) >> 3;
-        float* s_part = reinterpret_cast<float*>(smem_raw + (sbase - smem_u32(smem_raw)) + (size_t)NS * STAGE_BYTES) +
-                        (quarter * 2u + group) * 1024u;
-        const uint32_t bar_id = 1u + quarter * 2u + group;
+        // ===================== epilogue warps (both CTAs): two warps per TMEM lane quarter = the two halves of a head's reference
+        // lanes; thread = one row of this CTA's 128, serving both heads of the tile with one set of rotary values
+        const uint32_t quarter = (uint32_t)warp_u & 3u, half = ((uint32_t)warp_u - 2u) >> 2;
+        float* s_part = reinterpret_cast<float*>(smem_raw + (sbase - smem_u32(smem_raw)) + (size_t)NS * STAGE_BYTES) + quarter * 1024u;
+        const uint32_t bar_id = 1u + quarter;
         const uint32_t acc_empty0 = dsmem_addr(smem_u32(&bar_acc_empty[0]), 0u), acc_empty1 = dsmem_addr(smem_u32(&bar_acc_empty[1]), 0u);
         bool ok = true;
         uint32_t i = 0;
@@ -895,8 +883,25 @@ proj_gemm_pair_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p,
             } else {
                 two = (ct0 + 1u) * 128u < p.out_features;
             }
-            if (group == 0u || two)
-                proj_epilogue_half<kQkvg>(t_row + group * 128u, half, ct0 + group, row, row < p.rows, p, s_w, s_part, bar_id);
+            const bool live = row < p.rows;
+            uint32_t pos = 0;
+            RotRegs rot;
+            if (kQkvg && ct0 < 24u) {
+                if (live) pos = p.pos_ids[row];
+                if (ct0 < 20u) {  // q and k heads rotate: dims [32 pr + 16 half, +16) pair with the dims 64 further on
+                    const uint16_t* cs = p.cos_t + (size_t)pos * HD + 16u * half;
+                    const uint16_t* sn = p.sin_t + (size_t)pos * HD + 16u * half;
+#pragma unroll
+                    for (int pr = 0; pr < 2; pr++) {
+                        ld_pairs(cs + 32 * pr, rot.v[pr][0]);
+                        ld_pairs(cs + 32 * pr + 64, rot.v[pr][1]);
+                        ld_pairs(sn + 32 * pr, rot.v[pr][2]);
+                        ld_pairs(sn + 32 * pr + 64, rot.v[pr][3]);
+                    }
+                }
+            }
+            proj_epilogue_half<kQkvg>(t_row, half, ct0, row, live, p, s_w, s_part, bar_id, pos, rot);
+            if (two) proj_epilogue_half<kQkvg>(t_row + 128u, half, ct0 + 1u, row, live, p, s_w, s_part, bar_id, pos, rot);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(buf ? acc_empty1 : acc_empty0);
