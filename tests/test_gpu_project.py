@@ -220,3 +220,34 @@ def test_argument_errors(kv):
     torch.cuda.synchronize()
     assert kv.device_status() == 1
     assert torch.equal(d.k_cache[1].cpu(), torch.from_numpy(case.k_cache[1]))
+
+
+def test_wave_kernel_skips_rows_with_misaligned_cache_pointers(kv):
+    """More than 512 rows run the CTA-pair kernel: a K pointer and a V pointer that are not 16-byte aligned are reported, those
+    two cache rows stay untouched, every other row is written as by the aligned call."""
+    from oxide_infer_b200 import Linear
+    lens = list(range(20, 620))
+    case = DecodeCase(lens, seed=91)
+    b = len(lens)
+    g = torch.Generator(device="cuda").manual_seed(91)
+    x = torch.randn(b, HIDDEN, device="cuda", generator=g).half()
+    lin = Linear(*_weights(91))
+    good, d = case.device(), case.device()
+    outs = [torch.zeros(b, NQ, HD, dtype=torch.float16, device="cuda") for _ in range(2)]
+    gates = [torch.zeros(b, NQ, dtype=torch.float16, device="cuda") for _ in range(2)]
+    kv.project_append(lin, x, outs[0], gates[0], good.q_norm_w, good.k_norm_w, good.cos, good.sin, good.pos_ids, good.k_ptrs, good.v_ptrs)
+    torch.cuda.synchronize()
+    assert kv.device_status() == 0
+    bad_k, bad_v = d.k_ptrs.clone(), d.v_ptrs.clone()
+    bad_k[300] += 2
+    bad_v[599] += 6
+    kv.project_append(lin, x, outs[1], gates[1], d.q_norm_w, d.k_norm_w, d.cos, d.sin, d.pos_ids, bad_k, bad_v)
+    torch.cuda.synchronize()
+    assert kv.device_status() == 1
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    assert torch.equal(gates[0].view(torch.int16), gates[1].view(torch.int16))
+    for i in range(b):
+        want_k = torch.from_numpy(case.k_cache[i]).cuda() if i == 300 else good.k_cache[i]
+        want_v = torch.from_numpy(case.v_cache[i]).cuda() if i == 599 else good.v_cache[i]
+        assert torch.equal(d.k_cache[i].view(torch.int16), want_k.view(torch.int16)), i
+        assert torch.equal(d.v_cache[i].view(torch.int16), want_v.view(torch.int16)), i
