@@ -742,6 +742,7 @@ proj_gemm_pair_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p,
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[NS], bar_empty[NS], bar_acc_full[2], bar_acc_empty[2];
     __shared__ uint32_t s_tmem, s_abort;
+    __shared__ volatile uint32_t s_fail[4];   // per TMEM lane quarter: one of its two epilogue warps gave up a wait
     __shared__ __align__(16) uint16_t s_w[2 * HD];
 
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -761,6 +762,7 @@ proj_gemm_pair_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p,
             mbar_init(&bar_acc_empty[b], 2 * EPI_WARPS);   // used in the leader: one arrival per epilogue warp of both CTAs
         }
         s_abort = 0u;
+        s_fail[0] = s_fail[1] = s_fail[2] = s_fail[3] = 0u;
         mbar_fence_init();
     }
     if (kQkvg && tid >= 64 && tid < 64 + HD) {
@@ -869,6 +871,11 @@ proj_gemm_pair_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p,
             const uint32_t row = (t / tiles_n) * 256u + crank * 128u + quarter * 32 + (uint32_t)lane;
             ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar_acc_full[buf], (i >> 1) & 1u, &s_abort));
             tc_fence_after();
+            // The two warps of a lane quarter meet in named barriers inside the epilogue, so they must take the same decision
+            // here: a warp that gave up says so before they meet, and both look afterwards (nobody else writes the word).
+            if (!ok && lane == 0) s_fail[quarter] = 1u;
+            asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+            ok = s_fail[quarter] == 0u;
             if (!ok) {
                 if (lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
                 break;
