@@ -406,14 +406,16 @@ const uint32_t* oxi_tables_seq_lens(const oxi_step_tables* tables);
  * gives up, the CTA finishes without writing output and OXI_DEV_WAIT_TIMEOUT is
  * raised.  Nothing in normal operation makes a wait run out, so this call exists
  * to exercise that path without faulting or hanging the GPU: it arms the NEXT
- * launch of this handle's decode-attention kernel (which = 0) or prefill-attention
+ * launch of this handle's decode-attention kernel (which = 0), prefill-attention
  * kernel (which = 1; oxi_prefill_attn only, the armed wave runs unsplit and without
- * a registered slab) so that CTA 0 withholds its stage-th pipeline stage (decode:
- * no copy is issued for it; prefill: the K tile is copied but never published) and
- * all waits of that launch last limit_us microseconds instead of a second.  The
- * armed launch returns normally with OXI_DEV_WAIT_TIMEOUT set and with the rows of
- * CTA 0's work items unwritten; later launches are unaffected.  No counterpart in
- * the reference. */
+ * a registered slab) or projection GEMM (which = 2: oxi_project_append or
+ * oxi_linear_forward, whichever kernel the row count selects) so that CTA 0
+ * withholds its stage-th pipeline stage (decode and projection: no copy is issued
+ * for it; prefill: the K tile is copied but never published) and all waits of that
+ * launch last limit_us microseconds instead of a second.  The armed launch returns
+ * normally with OXI_DEV_WAIT_TIMEOUT set and with the outputs of CTA 0's work
+ * (projection: of its cluster's tile) unwritten; later launches are unaffected.
+ * No counterpart in the reference. */
 int32_t oxi_debug_arm_wait_fault(oxi_handle* h, uint32_t which, uint32_t stage, uint32_t limit_us);
 
 /* Measurement support: streams `bytes` (rounded down to whole 64 KB stages) from

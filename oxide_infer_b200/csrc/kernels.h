@@ -114,10 +114,10 @@ int proj_encode_map(TmaDesc* out, const void* base, uint64_t rows, uint32_t box_
 cudaError_t launch_project_append(cudaStream_t stream, const TmaDesc* w_maps, int num_sms, const void* x, uint32_t rows,
                                   void* q_out, void* gate_out, void* raw_out, const void* q_norm_w, const void* k_norm_w,
                                   const void* cos_t, const void* sin_t, const uint32_t* pos_ids, const uint64_t* k_ptrs,
-                                  const uint64_t* v_ptrs, float eps, uint32_t* status);
+                                  const uint64_t* v_ptrs, float eps, uint32_t* status, const WaitFault* fault);
 // w_map: tensor map of the weight matrix, boxes of 128 rows
 cudaError_t launch_linear(cudaStream_t stream, const TmaDesc* w_map, int num_sms, uint32_t out_features, const void* x,
-                          uint32_t rows, void* y, uint32_t* status);
+                          uint32_t rows, void* y, uint32_t* status, const WaitFault* fault);
 
 // Read-only streaming probe (bench and tests): the decode kernel's copy pipeline without arithmetic.
 cudaError_t stream_probe_init();

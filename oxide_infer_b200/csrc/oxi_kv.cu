@@ -25,7 +25,7 @@ struct oxi_handle {
     PrefillSplitWs pf_split;  // reserved by oxi_prefill_split_configure
     uint32_t pf_part_keys;    // keys per part of a split block; 0: off
     PrefillSlab pf_slab;      // registered by oxi_register_kv_slab; rows == 0: none
-    WaitFault dbg_decode, dbg_prefill;  // armed by oxi_debug_arm_wait_fault for the next launch only
+    WaitFault dbg_decode, dbg_prefill, dbg_proj;  // armed by oxi_debug_arm_wait_fault for the next launch only
     // staging for the host-buffer entry: one contiguous buffer per kind holding a group of up to STG_MAX layers
     // (layer-major, compact for the call's batch), so that a group's inputs arrive with one copy per kind
     static constexpr int STG_MAX = 16;
@@ -248,15 +248,20 @@ static WaitFault take_prefill_fault(oxi_handle* h) {
     h->dbg_prefill = WaitFault{};
     return f;
 }
+static WaitFault take_proj_fault(oxi_handle* h) {
+    const WaitFault f = h->dbg_proj;
+    h->dbg_proj = WaitFault{};
+    return f;
+}
 
 int32_t oxi_debug_arm_wait_fault(oxi_handle* h, uint32_t which, uint32_t stage, uint32_t limit_us) {
     if (!h) return fail(OXI_ERR_NULL, "oxi_debug_arm_wait_fault: handle is null");
-    if (which > 1u || limit_us == 0u || limit_us > 1000000u || stage >= 0x7fffffffu)
-        return fail(OXI_ERR_ARG, "oxi_debug_arm_wait_fault: which is 0 or 1, limit_us 1..1000000");
+    if (which > 2u || limit_us == 0u || limit_us > 1000000u || stage >= 0x7fffffffu)
+        return fail(OXI_ERR_ARG, "oxi_debug_arm_wait_fault: which is 0, 1 or 2, limit_us 1..1000000");
     WaitFault f;
     f.skip_plus1 = stage + 1u;
     f.limit_us = limit_us;
-    (which == 0u ? h->dbg_decode : h->dbg_prefill) = f;
+    (which == 0u ? h->dbg_decode : which == 1u ? h->dbg_prefill : h->dbg_proj) = f;
     return OXI_OK;
 }
 
@@ -645,8 +650,9 @@ int32_t oxi_project_append(oxi_handle* h, void* stream, const oxi_linear* qkvg, 
     if ((((uintptr_t)x | (uintptr_t)q_out | (uintptr_t)gate_out | (uintptr_t)raw_out | (uintptr_t)cos_table |
           (uintptr_t)sin_table) & 15u) != 0u)
         return fail(OXI_ERR_ARG, "oxi_project_append: x, q_out, gate_out, raw_out and the rope tables must be 16-byte aligned");
+    const WaitFault flt = take_proj_fault(h);
     OXI_CUDA(launch_project_append((cudaStream_t)stream, l->maps, h->num_sms, x, rows, q_out, gate_out, raw_out, q_norm_w, k_norm_w,
-                                   cos_table, sin_table, pos_ids, k_ptrs, v_ptrs, eps, h->dws.status),
+                                   cos_table, sin_table, pos_ids, k_ptrs, v_ptrs, eps, h->dws.status, &flt),
              "project_append launch");
     return OXI_OK;
 }
@@ -658,7 +664,8 @@ int32_t oxi_linear_forward(oxi_handle* h, void* stream, const oxi_linear* w, con
     if (l->qkvg) return fail(OXI_ERR_ARG, "oxi_linear_forward: the weights object was made by oxi_qkvg_create");
     if (rows == 0 || rows > (1u << 20)) return fail(OXI_ERR_BATCH, "oxi_linear_forward: rows out of range");
     if ((((uintptr_t)x | (uintptr_t)y) & 15u) != 0u) return fail(OXI_ERR_ARG, "oxi_linear_forward: x and y must be 16-byte aligned");
-    OXI_CUDA(launch_linear((cudaStream_t)stream, l->maps, h->num_sms, l->out_features, x, rows, y, h->dws.status), "linear launch");
+    const WaitFault flt = take_proj_fault(h);
+    OXI_CUDA(launch_linear((cudaStream_t)stream, l->maps, h->num_sms, l->out_features, x, rows, y, h->dws.status, &flt), "linear launch");
     return OXI_OK;
 }
 

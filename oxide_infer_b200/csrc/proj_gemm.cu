@@ -75,6 +75,8 @@ struct ProjParams {
     const uint64_t* v_ptrs;
     uint32_t* status;
     float eps;
+    uint32_t wait_us;          // limit of every pipeline wait of this launch (a second unless a test armed a fault)
+    uint32_t skip_plus1;       // test support: CTA 0 issues no copies for its (skip_plus1 - 1)-th k-block; 0 = off
 };
 
 // this thread's TMEM lane, 16 consecutive 32-bit columns
@@ -392,11 +394,12 @@ proj_gemm_splitk_kernel(const __grid_constant__ ProjMaps maps, const ProjParams 
         uint32_t issued = 0;
         for (uint32_t kb = 0; kb < (uint32_t)KB_PER && ok; kb++, issued++) {
             const uint32_t s = kb % NS;
-            if (kb >= (uint32_t)NS && !mbar_wait_bounded(&bar_empty[s], ((kb / NS) & 1u) ^ 1u, &s_abort)) {
+            if (kb >= (uint32_t)NS && !mbar_wait_bounded(&bar_empty[s], ((kb / NS) & 1u) ^ 1u, &s_abort, p.wait_us)) {
                 ok = false;
                 break;
             }
-            if (lane == 0) {
+            const bool withheld = p.skip_plus1 == kb + 1u && blockIdx.x == 0u && blockIdx.y == 0u;  // test support
+            if (lane == 0 && !withheld) {
                 mbar_arrive_expect_tx(&bar_full[s], (uint32_t)STAGE_BYTES);
                 tma_load_box(sbase + s * STAGE_BYTES, &maps.x, (kb0 + kb) * BK, m_tile * BM, &bar_full[s]);
                 tma_load_box(sbase + s * STAGE_BYTES + TILE_BYTES, &maps.w[wsel], (kb0 + kb) * BK, wrow, &bar_full[s]);
@@ -406,14 +409,15 @@ proj_gemm_splitk_kernel(const __grid_constant__ ProjMaps maps, const ProjParams 
         if (!ok) {
             if (lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
             for (uint32_t k = issued > (uint32_t)NS ? issued - NS : 0; k < issued; ++k)
-                mbar_wait_drain(&bar_full[k % NS], (k / NS) & 1u, WAIT_LIMIT_US);
+                mbar_wait_drain(&bar_full[k % NS], (k / NS) & 1u, p.wait_us);
         }
     } else if (warp_u == 1) {
         // ===================== MMA issuer =====================
         bool ok = true;
         for (uint32_t kb = 0; kb < (uint32_t)KB_PER; kb++) {
             const uint32_t s = kb % NS;
-            ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(&bar_full[s], (kb / NS) & 1u, &s_abort));
+            ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(&bar_full[s], (kb / NS) & 1u, &s_abort, p.wait_us));
+            if (!ok) break;  // gave up: nothing more is issued or committed, so the producer stops at its next "empty" wait
             tc_fence_after();
             if (elect_one()) {
                 const uint64_t ad = umma_desc(sbase + s * STAGE_BYTES, 16, 1024);
@@ -434,7 +438,7 @@ proj_gemm_splitk_kernel(const __grid_constant__ ProjMaps maps, const ProjParams 
         const uint32_t frow = m_tile * BM + crank * 32u + (uint32_t)lane;
         rt = proj_fetch_row_tables<kQkvg>((uint32_t)warp_u - 2u, n_tile, frow, frow < p.rows, p);
         // ===================== this CTA's partial accumulator is complete =====================
-        acc_ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar_acc, 0u, &s_abort));
+        acc_ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar_acc, 0u, &s_abort, p.wait_us));
         tc_fence_after();
         if (!acc_ok && lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
     }
@@ -805,11 +809,12 @@ proj_gemm_pair_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p,
             const uint32_t mrow = (t / tiles_n) * 256u + crank * 128u;
             for (uint32_t kb = 0; kb < (uint32_t)NKB; kb++, g++) {
                 const uint32_t s = g % NS;
-                if (g >= (uint32_t)NS && !mbar_wait_bounded(&bar_empty[s], ((g / NS) & 1u) ^ 1u, &s_abort)) {
+                if (g >= (uint32_t)NS && !mbar_wait_bounded(&bar_empty[s], ((g / NS) & 1u) ^ 1u, &s_abort, p.wait_us)) {
                     ok = false;
                     break;
                 }
-                if (lane == 0) {
+                const bool withheld = p.skip_plus1 == g + 1u && blockIdx.x == 0u;  // test support: the first pair's leader
+                if (lane == 0 && !withheld) {
                     const uint32_t full = dsmem_addr(smem_u32(&bar_full[s]), 0u);   // the leader's barrier
                     if (crank == 0u) mbar_arrive_expect_tx(&bar_full[s], 2u * (uint32_t)STAGE_BYTES);
                     tma_load_box_pair(sbase + s * STAGE_BYTES, &maps.x, kb * BK, mrow, full);
@@ -833,10 +838,11 @@ proj_gemm_pair_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p,
             for (uint32_t t = pair; t < total; t += npairs, i++) {
                 const uint32_t buf = i & 1u;
                 const uint32_t idesc = (kQkvg && t % tiles_n == 12u) ? IDESC_N16 : IDESC_N256;
-                if (i >= 2u) ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(&bar_acc_empty[buf], ((i >> 1) & 1u) ^ 1u, &s_abort));
+                if (i >= 2u) ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(&bar_acc_empty[buf], ((i >> 1) & 1u) ^ 1u, &s_abort, p.wait_us));
                 for (uint32_t kb = 0; kb < (uint32_t)NKB; kb++, g++) {
                     const uint32_t s = g % NS;
-                    ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(&bar_full[s], (g / NS) & 1u, &s_abort));
+                    ok = __all_sync(0xffffffffu, ok && mbar_wait_bounded(&bar_full[s], (g / NS) & 1u, &s_abort, p.wait_us));
+                    if (!ok) break;  // gave up: nothing more is issued or committed, so both producers stop at their next "empty" wait
                     tc_fence_after();
                     if (elect_one()) {
                         const uint64_t ad = umma_desc(sbase + s * STAGE_BYTES, 16, 1024);
@@ -854,6 +860,7 @@ proj_gemm_pair_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p,
                     }
                     __syncwarp();
                 }
+                if (!ok) break;
             }
             if (!ok && lane == 0) atomicOr(p.status, DEV_WAIT_TIMEOUT);
         }
@@ -869,7 +876,7 @@ proj_gemm_pair_kernel(const __grid_constant__ ProjMaps maps, const ProjParams p,
         for (uint32_t t = pair; t < total && ok; t += npairs, i++) {
             const uint32_t buf = i & 1u, nt = t % tiles_n;
             const uint32_t row = (t / tiles_n) * 256u + crank * 128u + quarter * 32 + (uint32_t)lane;
-            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar_acc_full[buf], (i >> 1) & 1u, &s_abort));
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bar_acc_full[buf], (i >> 1) & 1u, &s_abort, p.wait_us));
             tc_fence_after();
             // The two warps of a lane quarter meet in named barriers inside the epilogue, so they must take the same decision
             // here: a warp that gave up says so before they meet, and both look afterwards (nobody else writes the word).
@@ -970,7 +977,7 @@ constexpr uint32_t PROJ_SMALL_ROWS = 512;
 cudaError_t launch_project_append(cudaStream_t stream, const TmaDesc* w_maps /* q, k, v, gate */, int num_sms, const void* x, uint32_t rows,
                                   void* q_out, void* gate_out, void* raw_out, const void* q_norm_w, const void* k_norm_w,
                                   const void* cos_t, const void* sin_t, const uint32_t* pos_ids, const uint64_t* k_ptrs,
-                                  const uint64_t* v_ptrs, float eps, uint32_t* status) {
+                                  const uint64_t* v_ptrs, float eps, uint32_t* status, const WaitFault* fault) {
     ProjMaps maps;
     if (proj_encode_map(&maps.x, x, rows, pg::BM) != 0) return cudaErrorInvalidValue;
     for (int i = 0; i < 4; i++) maps.w[i] = w_maps[i];
@@ -988,6 +995,8 @@ cudaError_t launch_project_append(cudaStream_t stream, const TmaDesc* w_maps /* 
     p.v_ptrs = v_ptrs;
     p.status = status;
     p.eps = eps;
+    p.wait_us = fault && fault->skip_plus1 ? fault->limit_us : WAIT_LIMIT_US;
+    p.skip_plus1 = fault ? fault->skip_plus1 : 0u;
     if (rows > PROJ_SMALL_ROWS) {
         const uint32_t tiles_m2 = (rows + 255u) / 256u, total = (uint32_t)pgp::TILES_QKVG * tiles_m2;
         const uint32_t pairs = total < (uint32_t)num_sms / 2u ? total : (uint32_t)num_sms / 2u;
@@ -1000,7 +1009,7 @@ cudaError_t launch_project_append(cudaStream_t stream, const TmaDesc* w_maps /* 
 }
 
 cudaError_t launch_linear(cudaStream_t stream, const TmaDesc* w_map, int num_sms, uint32_t out_features, const void* x, uint32_t rows,
-                          void* y, uint32_t* status) {
+                          void* y, uint32_t* status, const WaitFault* fault) {
     ProjMaps maps;
     if (proj_encode_map(&maps.x, x, rows, pg::BM) != 0) return cudaErrorInvalidValue;
     maps.w[0] = maps.w[1] = maps.w[2] = maps.w[3] = *w_map;
@@ -1009,6 +1018,8 @@ cudaError_t launch_linear(cudaStream_t stream, const TmaDesc* w_map, int num_sms
     p.out_features = out_features;
     p.y = (uint16_t*)y;
     p.status = status;
+    p.wait_us = fault && fault->skip_plus1 ? fault->limit_us : WAIT_LIMIT_US;
+    p.skip_plus1 = fault ? fault->skip_plus1 : 0u;
     if (rows > PROJ_SMALL_ROWS) {
         const uint32_t tiles_n = (out_features + 255u) / 256u, tiles_m2 = (rows + 255u) / 256u, total = tiles_n * tiles_m2;
         const uint32_t pairs = total < (uint32_t)num_sms / 2u ? total : (uint32_t)num_sms / 2u;

@@ -125,7 +125,8 @@ class KvPath:
 
     def arm_wait_fault(self, which: int, stage: int, limit_us: int = 1000):
         """Test support (oxi_debug_arm_wait_fault): the next decode (which=0) or prefill (which=1)
-        attention launch loses one pipeline stage of CTA 0 and its waits last limit_us."""
+        attention launch, or the next projection GEMM launch (which=2), loses one pipeline stage of
+        CTA 0 and its waits last limit_us."""
         _check(self.lib.oxi_debug_arm_wait_fault(self.h, which, stage, limit_us), "oxi_debug_arm_wait_fault")
 
     def stream_read(self, src, copy_bytes: int = 4096):

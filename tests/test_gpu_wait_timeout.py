@@ -108,3 +108,59 @@ def test_prefill_wait_runs_out_and_the_handle_recovers(kv, tile):
     again = run()
     assert kv.device_status() == 0
     assert torch.equal(again.view(torch.int16), good.view(torch.int16))
+
+
+@pytest.mark.parametrize("rows,stage", [(128, 0), (128, 6), (600, 0), (600, 9)])
+def test_projection_wait_runs_out_and_the_handle_recovers(rows, stage):
+    """The projection GEMMs: 128 rows run the four-CTA cluster kernel (CTA 0 = the first quarter of k of head 0's tile),
+    600 rows the CTA-pair kernel (CTA 0 = the leader of the pair that owns rows 0-255 of q heads 0 and 1).  The armed launch
+    returns within milliseconds with the status bit set, every tile of another cluster is right, nothing of the
+    cluster's own tile is written, and the next launch is bit-identical to an undisturbed one."""
+    from oxide_infer_b200 import KvPath, Linear, build
+    build.build()
+    kv = KvPath(0, max_batch=64, max_seq_len=2048, max_prefill_rows=1024)
+    lens = [40 + (i % 300) for i in range(rows)]
+    case = DecodeCase(lens, seed=93)
+    g = torch.Generator(device="cuda").manual_seed(93)
+    x = torch.randn(rows, 2048, device="cuda", generator=g).half()
+    ws = [(torch.randn(o, 2048, device="cuda", generator=g) * 2048 ** -0.5).half() for o in (NQ * HD, NKV * HD, NKV * HD, NQ)]
+    lin = Linear(*ws)
+
+    def run(d, q_out, gate_out):
+        kv.project_append(lin, x, q_out, gate_out, d.q_norm_w, d.k_norm_w, d.cos, d.sin, d.pos_ids, d.k_ptrs, d.v_ptrs)
+
+    new_out = lambda: (torch.full((rows, NQ, HD), 7.0, dtype=torch.float16, device="cuda"),
+                       torch.zeros(rows, NQ, dtype=torch.float16, device="cuda"))
+    good, (gq, gg) = case.device(), new_out()
+    run(good, gq, gg)
+    torch.cuda.synchronize()
+    assert kv.device_status() == 0
+
+    hit, (hq, hg) = case.device(), new_out()
+    kv.arm_wait_fault(2, stage, 1000)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    run(hit, hq, hg)
+    t1.record()
+    torch.cuda.synchronize()                       # the launch returns: no hang
+    assert t0.elapsed_time(t1) < 500.0
+    assert kv.device_status() == WAIT_TIMEOUT
+    assert kv.device_status() == 0
+    own_heads = 1 if rows <= 512 else 2            # the tile of CTA 0's cluster: head 0 (and 1) of the first 128 (256) rows
+    own_rows = min(rows, 128 if rows <= 512 else 256)
+    assert torch.equal(hq[:, own_heads:].contiguous().view(torch.int16), gq[:, own_heads:].contiguous().view(torch.int16))
+    assert torch.equal(hq[own_rows:].view(torch.int16), gq[own_rows:].view(torch.int16))
+    assert bool((hq[:own_rows, :own_heads] == 7.0).all())          # nothing written where the cluster gave up
+    assert torch.equal(hg.view(torch.int16), gg.view(torch.int16))
+    for i in range(rows):
+        assert torch.equal(hit.k_cache[i].view(torch.int16), good.k_cache[i].view(torch.int16)), i
+        assert torch.equal(hit.v_cache[i].view(torch.int16), good.v_cache[i].view(torch.int16)), i
+
+    again, (aq, ag) = case.device(), new_out()     # armed for one launch only
+    run(again, aq, ag)
+    torch.cuda.synchronize()
+    assert kv.device_status() == 0
+    assert torch.equal(aq.view(torch.int16), gq.view(torch.int16))
+    for i in (0, rows // 2, rows - 1):
+        assert torch.equal(again.k_cache[i].view(torch.int16), good.k_cache[i].view(torch.int16))
+    kv.close()
